@@ -1,0 +1,435 @@
+#!/usr/bin/env python
+"""Benchmark of the fast-weight hot path: delta-rule forward+backward tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One *step* is one pass of the hot path over one batch: forward and backward of
+four consecutive carried segments at the language-model shape (B=64, H=8, L=256,
+d=16, fp32; the state is handed from segment i to i+1 as a clone, exactly as the
+reference's layers do).  Tokens per step = 4*B*L per GPU.  With N > 1 every rank
+runs the same per-GPU workload on its own (batch x head) shard -- there is no
+collective on the data path -- so scaling is weak and `value` is the sum over
+ranks divided by the slowest rank's device time.
+
+The line printed by rank 0 carries, besides the contract keys:
+  roofline      the dominant kernel (the fused backward) against the measured HBM peak
+  roofline_fwd_bwd  forward+backward kernels together (the figure the 60% target is stated on)
+  cpu_baseline  the reference's per-timestep PyTorch formulation timed on this host's cores
+  e2e           the same metric through the public autograd API with pinned host buffers,
+                host->device copies of the inputs and device->host copies of the results timed
+
+`--impl reference` times the reference's CPU formulation (the oracle's per-timestep
+loops, forward+backward through autograd) on all host threads; a step there is a
+bounded sample of the workload (one segment).
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, L, d, segments, dtype)
+    'lm': (64, 8, 256, 16, 4, 'fp32'),            # BASELINE configs[1]
+    'small': (2, 8, 256, 16, 1, 'fp32'),          # BASELINE configs[0]
+    'long': (256, 16, 4096, 64, 1, 'bf16'),       # BASELINE configs[4], kernel part
+    'long_slice': (32, 16, 4096, 64, 1, 'bf16'),  # an eighth of it (one GPU's shard at N=8)
+}
+
+
+def peaks():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        with open(p) as fh:
+            return float(json.load(fh)['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+         'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', '-i', str(index), '--query-gpu=' + self.Q, '--format=csv,noheader,nounits', '-lms', '100'],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(',')])
+
+    def stop(self):
+        if not self.proc:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for nme, val in zip(names, r[3:7]):
+                if val.lower().startswith('active'):
+                    reasons.add(nme)
+        return {'sm_mhz': statistics.median(sm) if sm else None,
+                'sm_max_mhz': max(mx) if mx else None, 'samples': len(sm), 'reasons': sorted(reasons)}
+
+
+def make_inputs(seed, B, H, L, d, dtype, device=None, pin=False):
+    """q,k ~ sum_norm(elu(N(0,1))+1), v ~ N(0,1), beta = sigmoid(N(0,1)), gy ~ N(0,1); seeded on the CPU generator."""
+    import torch.nn.functional as F
+    big = B * H * L * d > 2 ** 27 and device is not None and not pin
+    gdev = device if big else 'cpu'     # very large shapes are drawn on the device to spare host RAM and time
+    g = torch.Generator(device=gdev)
+    g.manual_seed(seed)
+
+    def phi(x):
+        x = F.elu(x) + 1.
+        return x / x.sum(-1, keepdim=True)
+    q = phi(torch.randn(B, H, L, d, generator=g, device=gdev)).to(dtype)
+    k = phi(torch.randn(B, H, L, d, generator=g, device=gdev)).to(dtype)
+    v = torch.randn(B, H, L, d, generator=g, device=gdev).to(dtype)
+    beta = torch.sigmoid(torch.randn(B, H, L, 1, generator=g, device=gdev)).to(dtype)
+    gy = torch.randn(B, H, L, d, generator=g, device=gdev).to(dtype)
+    out = [q, k, v, beta, gy]
+    if pin:
+        out = [t.pin_memory() for t in out]
+    if device is not None:
+        out = [t.to(device) for t in out]
+    return out
+
+
+# ----------------------------------------------------------------------- CPU arm
+def cpu_loop_tokens_per_s(B, H, L, d, reps, warm=1):
+    """The reference's CPU path: per-timestep PyTorch loop, fp32, forward+backward by autograd."""
+    from oracle import loops
+    torch.set_num_threads(os.cpu_count() or 1)
+    times = []
+    for i in range(warm + reps):
+        q, k, v, beta, gy = make_inputs(1000 + i, B, H, L, d, torch.float32)
+        leaves = [t.requires_grad_() for t in (q, k, v, beta)]
+        t0 = time.perf_counter()
+        y, _ = loops.delta_rule(*leaves, torch.zeros(B, H, d, d))
+        (y * gy).sum().backward()
+        dt = time.perf_counter() - t0
+        if i >= warm:
+            times.append(dt)
+    return B * L / statistics.mean(times), statistics.mean(times)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    B, H, L, d, segs, dt = WORKLOADS[args.workload]
+    # bounded sample: one segment of the workload per step, batch capped so a step stays ~1 s
+    Bs = min(B, 64)
+    Ls = min(L, 256)
+    tps, sec = cpu_loop_tokens_per_s(Bs, H, Ls, d, reps=args.steps, warm=max(1, min(args.warmup, 2)))
+    sample = 'per-timestep PyTorch loop (oracle port of the reference formulation), fwd+bwd by autograd, fp32, ' \
+             'one segment B=%d,H=%d,L=%d,d=%d per step' % (Bs, H, Ls, d)
+    line = {
+        'impl': 'reference', 'metric': 'fast-weight fwd+bwd tokens/s', 'value': tps, 'unit': 'tokens/s',
+        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': sec * 1e3,
+        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp32', 'data': 'synthetic',
+        'config': {'workload': 'delta-rule fwd+bwd, %s shape B=%d,H=%d,L=%d,d=%d' % (args.workload, B, H, L, d),
+                   'sample': sample},
+        'cpu_baseline': {'value': tps, 'unit': 'tokens/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+                         'sample': sample},
+        'e2e': {'value': tps, 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------- GPU arm
+class DeltaStep:
+    """Device-resident fwd+bwd over `segs` carried segments through the C ABI, pre-allocated buffers."""
+
+    def __init__(self, B, H, L, d, segs, dtype, device, seed):
+        from recurrent_fwp_b200 import _lib
+        self.L_ = _lib
+        self.shape = (B, H, L, d)
+        self.segs = segs
+        self.dtype = dtype
+        self.device = device
+        self.inp = [make_inputs(seed + s, B, H, L, d, dtype, device) for s in range(segs)]
+        f32 = dict(device=device, dtype=torch.float32)
+        io = dict(device=device, dtype=dtype)
+        self.W = torch.zeros(B, H, d, d, **f32)
+        self.W_keep = [torch.empty(B, H, d, d, **f32) for _ in range(segs)]
+        self.y = [torch.empty(B, H, L, d, **io) for _ in range(segs)]
+        self.vo = [torch.empty(B, H, L, d, **f32) for _ in range(segs)]
+        self.vi = [torch.empty(B, H, L, d, **f32) for _ in range(segs)]
+        self.g = [[torch.empty(B, H, L, d, **io) for _ in range(3)] + [torch.empty(B, H, L, 1, **io)]
+                  for _ in range(segs)]
+        self.code = _lib.io_dtype(self.inp[0][0])
+        D = _lib.desc
+        self.d_in = [[D(t) for t in seg] for seg in self.inp]
+        self.d_W = D(self.W)
+        self.d_y = [D(t) for t in self.y]
+        self.d_vo = [D(t) for t in self.vo]
+        self.d_vi = [D(t) for t in self.vi]
+        self.d_g = [[D(t) for t in seg] for seg in self.g]
+        self.dev_index = device.index
+
+    def fwd(self, s, stream):
+        B, H, L, d = self.shape
+        q, k, v, b, _ = self.d_in[s]
+        self.L_.check(self.L_.lib.fwp_fast_weight_forward(
+            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], self.d_W, self.d_y[s],
+            self.code, stream, self.dev_index), 'fwd')
+
+    def bwd(self, s, stream):
+        B, H, L, d = self.shape
+        q, k, v, b, gy = self.d_in[s]
+        gq, gk, gv, gb = self.d_g[s]
+        self.L_.check(self.L_.lib.fwp_fast_weight_backward(
+            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], gy, self.d_W, gq, gk, gv, gb,
+            self.code, stream, self.dev_index), 'bwd')
+
+    def step(self):
+        """fwd, keep a clone of the end state (the carried memory), bwd (rewinds W), restore the carried state."""
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        self.W.zero_()
+        for s in range(self.segs):
+            self.fwd(s, stream)
+            self.W_keep[s].copy_(self.W)
+            self.bwd(s, stream)
+            self.W.copy_(self.W_keep[s])
+
+
+def time_kernels(ds, flush, reps):
+    """Average device time of one forward and one backward launch (CUDA events on the launching stream,
+    L2 flushed before each launch)."""
+    stream_obj = torch.cuda.current_stream(ds.device)
+    stream = ctypes.c_void_p(stream_obj.cuda_stream)
+    tf, tb = [], []
+    for i in range(reps):
+        s = i % ds.segs
+        ds.W.zero_()
+        flush()
+        e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        e0.record(stream_obj)
+        ds.fwd(s, stream)
+        e1.record(stream_obj)
+        flush()
+        e2.record(stream_obj)
+        ds.bwd(s, stream)
+        e3.record(stream_obj)
+        torch.cuda.synchronize(ds.device)
+        tf.append(e0.elapsed_time(e1))
+        tb.append(e2.elapsed_time(e3))
+    return statistics.mean(tf) * 1e-3, statistics.mean(tb) * 1e-3, min(tf) * 1e-3, min(tb) * 1e-3
+
+
+def run_gpu_arm(args):
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)')
+    device = torch.device('cuda', local)
+    torch.cuda.set_device(device)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    import recurrent_fwp_b200 as fwp
+    from recurrent_fwp_b200 import _lib
+
+    B, H, L, d, segs, dts = WORKLOADS[args.workload]
+    dtype = torch.float32 if dts == 'fp32' else torch.bfloat16
+    esz = 4 if dts == 'fp32' else 2
+    ds = DeltaStep(B, H, L, d, segs, dtype, device, seed=1234 + 100 * rank)
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+
+    def flush():
+        flush_buf.zero_()
+
+    # ---- the step, captured in a CUDA graph (launch gaps would otherwise dominate microsecond kernels)
+    use_graph = not args.no_graph
+    graph = None
+    for _ in range(2):
+        ds.step()
+    torch.cuda.synchronize(device)
+    if use_graph:
+        try:
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                ds.step()
+            torch.cuda.current_stream(device).wait_stream(side)
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                ds.step()
+        except Exception as exc:  # report, and time eager launches instead
+            sys.stderr.write('bench.py: CUDA graph capture failed (%r); timing eager launches\n' % (exc,))
+            graph = None
+            torch.cuda.synchronize(device)
+    run_step = graph.replay if graph is not None else ds.step
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        flush()
+        run_step()
+    torch.cuda.synchronize(device)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = _lib.launch_count()
+    evs = []
+    t_wall0 = time.perf_counter()
+    for _ in range(args.steps):
+        flush()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        run_step()
+        b_.record()
+        evs.append((a, b_))
+    torch.cuda.synchronize(device)
+    barrier()
+    t_wall = time.perf_counter() - t_wall0
+    launches = _lib.launch_count() - launches0
+    if graph is not None:
+        launches = 2 * segs * args.steps      # replays re-issue the captured launches: fwd+bwd per segment
+    dev_s = sum(a.elapsed_time(b_) for a, b_ in evs) * 1e-3
+    tmax = torch.tensor([dev_s], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    dev_s = float(tmax.item())
+    tokens_per_step = segs * B * L
+    value = world * tokens_per_step * args.steps / dev_s
+
+    # ---- e2e: public autograd API, pinned host buffers, copies inside the timed region
+    Be = B if B * H * L * d <= 2 ** 27 else 8     # very large shapes: the end-to-end leg runs a batch slice
+    host_in = [make_inputs(4321 + s + 100 * rank, Be, H, L, d, dtype, pin=True) for s in range(segs)]
+    host_out = [[torch.empty(Be, H, L, d, dtype=dtype).pin_memory() for _ in range(4)] +
+                [torch.empty(Be, H, L, 1, dtype=dtype).pin_memory()] for _ in range(segs)]
+    h2d = sum(t.numel() * t.element_size() for seg in host_in for t in seg)
+    d2h = sum(t.numel() * t.element_size() for seg in host_out for t in seg)
+
+    def e2e_step():
+        W = torch.zeros(Be, H, d, d, device=device)
+        for s in range(segs):
+            q, k, v, b, gy = (t.to(device, non_blocking=True) for t in host_in[s])
+            q.requires_grad_(); k.requires_grad_(); v.requires_grad_(); b.requires_grad_()
+            y = fwp.fast_weight_delta(q, k, v, b, W)
+            W_next = W.clone()
+            y.backward(gy)
+            for dst, src in zip(host_out[s], (y.detach(), q.grad, k.grad, v.grad, b.grad)):
+                dst.copy_(src, non_blocking=True)
+            W = W_next
+        torch.cuda.synchronize(device)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ea.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    eb.record()
+    torch.cuda.synchronize(device)
+    e2e_s = max(ea.elapsed_time(eb) * 1e-3, 1e-9)
+    barrier()
+    te = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = world * segs * Be * L * e2e_steps / float(te.item())
+    clocks = sampler.stop() if sampler else None
+
+    # ---- per-kernel timing for the roofline (rank 0 only; separate from the step timing)
+    line = None
+    if rank == 0:
+        tf, tb, tf_min, tb_min = time_kernels(ds, flush, reps=max(10, min(4 * args.steps, 40)))
+        peak, peak_kind = peaks()
+        units = B * H * L
+        bytes_fwd = units * (2 * d + d + 1 + d) * esz + B * H * 2 * d * d * 4
+        bytes_bwd = units * ((2 * d + 2 * d + 1) + (2 * d + d + 1)) * esz + B * H * 2 * d * d * 4
+        ach_b = bytes_bwd / tb / 1e9
+        ach_fb = (bytes_fwd + bytes_bwd) / (tf + tb) / 1e9
+        cpu = None
+        if world == 1 and not args.skip_cpu:
+            Bs, Ls = min(B, 64), min(L, 256)
+            tps, sec = cpu_loop_tokens_per_s(Bs, H, Ls, d, reps=8, warm=1)
+            cpu = {'value': tps, 'unit': 'tokens/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+                   'sample': 'per-timestep PyTorch loop (oracle port of the reference formulation), fwd+bwd by '
+                             'autograd, fp32, 8 repetitions of one segment B=%d,H=%d,L=%d,d=%d (%.2f s each)'
+                             % (Bs, H, Ls, d, sec)}
+        line = {
+            'metric': 'fast-weight fwd+bwd tokens/s', 'value': value, 'unit': 'tokens/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': dev_s / args.steps * 1e3,
+            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': dts, 'data': 'synthetic',
+            'config': {'workload': 'delta-rule fast weight memory fwd+bwd, B=%d,H=%d,L=%d,d_k=d_v=%d, %d carried '
+                                   'segment(s) per step, %s streams, fp32 state' % (B, H, L, d, segs, dts),
+                       'name': args.workload, 'tokens_per_step_per_gpu': tokens_per_step,
+                       'sharding': 'batch x head units split over ranks, no collective on the data path',
+                       'l2': 'flushed between timed steps (256 MiB write)', 'cuda_graph': graph is not None,
+                       'timing': 'CUDA events per step, summed; max over ranks'},
+            'roofline': {'bound': 'hbm', 'kernel': 'delta_bwd_kernel', 'achieved': ach_b, 'peak': peak, 'unit': 'GB/s',
+                         'frac': ach_b / peak, 'peak_kind': peak_kind, 'traffic': None,
+                         'algorithmic_bytes_per_launch': bytes_bwd, 'launch_s': tb, 'launch_s_min': tb_min},
+            'roofline_fwd_bwd': {'achieved': ach_fb, 'peak': peak, 'unit': 'GB/s', 'frac': ach_fb / peak,
+                                 'algorithmic_bytes': bytes_fwd + bytes_bwd, 'fwd_s': tf, 'bwd_s': tb,
+                                 'fwd_s_min': tf_min, 'bwd_s_min': tb_min},
+            'cpu_baseline': cpu,
+            'e2e': {'value': e2e_value, 'unit': 'tokens/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+                    'steps': e2e_steps, 'batch': Be, 'api': 'recurrent_fwp_b200.fast_weight_delta (autograd) + .backward()'},
+            'gpu_launches': int(launches), 'clocks': clocks, 'wall_s_timed_region': t_wall,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='fwp', choices=['fwp', 'reference'])
+    ap.add_argument('--workload', default='lm', choices=sorted(WORKLOADS))
+    ap.add_argument('--no-graph', action='store_true')
+    ap.add_argument('--skip-cpu', action='store_true')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,231 @@
+/*
+ * fwp.h -- C ABI of the B200 (sm_100a) fast-weight update kernels.
+ *
+ * One entry point per native function of the reference project's JIT-compiled
+ * CUDA extensions (the pybind functions its torch.autograd.Function wrappers
+ * call).  Each declaration cites the reference function it replaces, by the
+ * file's path inside the reference project.  Argument order follows the
+ * reference function; the differences are the ones a C ABI needs:
+ *
+ *   - tensors are passed as `fwp_tensor` (device pointer + 4 element strides
+ *     of the logical (N, H, L, D) view) instead of torch::Tensor;
+ *   - sizes are explicit; the CUDA stream and the device ordinal are explicit
+ *     (the reference launches on the legacy default stream of device 0);
+ *   - every function returns a status code (0 = ok) instead of void, validates
+ *     on the host before any launch, and never throws;
+ *   - `io_dtype` selects the element type of the *streamed* tensors
+ *     (q, k, v, beta, z, outputs, gradients).  Fast-weight states (kv, states,
+ *     cells), the tensors saved for the backward pass (v_old, v_insert, gates,
+ *     post-activation copies) and parameter gradients are always fp32.
+ *
+ * Layout contract (same as the reference's PackedTensorAccessor32 view):
+ * 4-D logical shape, arbitrary strides for the three outer dimensions,
+ * innermost stride must be 1.  Strides are in elements and 64-bit.
+ * Output buffers are overwritten (the reference accumulates into zeros).
+ * State tensors are in/out: the forward leaves the end-of-segment state in
+ * them, the backward rewinds them in place to the start-of-segment state.
+ *
+ * Ownership: the caller allocates everything, including scratch; the library
+ * allocates nothing, keeps no pointer after a call returns, and is re-entrant.
+ */
+#ifndef FWP_H_
+#define FWP_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct fwp_tensor {
+    void*   data;       /* device pointer to element (0,0,0,0) */
+    int64_t stride[4];  /* element strides of (N, H, L, D); stride[3] must be 1 */
+} fwp_tensor;
+
+enum fwp_dtype { FWP_F32 = 0, FWP_BF16 = 1 };
+
+enum fwp_status {
+    FWP_OK = 0,
+    FWP_ERR_NULL = 1,         /* a required pointer is NULL */
+    FWP_ERR_SHAPE = 2,        /* a size is <= 0 or inconsistent */
+    FWP_ERR_STRIDE = 3,       /* innermost stride != 1, or a negative stride */
+    FWP_ERR_ALIGN = 4,        /* pointer not aligned to its element size */
+    FWP_ERR_DTYPE = 5,        /* unknown io_dtype */
+    FWP_ERR_UNSUPPORTED = 6,  /* head dimension beyond what the kernels cover */
+    FWP_ERR_CUDA = 7,         /* a CUDA runtime call failed; see fwp_last_cuda_error */
+    FWP_ERR_VARIANT = 8,      /* unknown LSTM variant */
+    FWP_ERR_SCRATCH = 9       /* scratch buffer missing or too small */
+};
+
+/* Human-readable text for a status code.  Never NULL. */
+const char* fwp_status_string(int status);
+/* cudaError_t of the last failing CUDA call made by this thread (0 if none). */
+int fwp_last_cuda_error(void);
+/* Library version, major*10000 + minor*100 + patch. */
+int fwp_version(void);
+/* Largest head dimension the register-resident kernels cover (E, M <= this). */
+int fwp_max_head_dim(void);
+/* Number of kernels this library has launched in this process (all threads). */
+unsigned long long fwp_launch_count(void);
+/* Tuning knob for experiments: key is "<op>.<D>.split" or "<op>.<D>.chunk";
+ * returns 0 if the key/value pair is accepted. */
+int fwp_tune(const char* key, int value);
+
+/* ---- delta rule --------------------------------------------------------
+ * replaces fast_weight_forward(Q,K,V,beta,v_old,v_insert,kv,out),
+ *   algorithmic/fast_weight/fast_weight_cuda.cu:182-240
+ * Q,K [N,H,L,E]; V,v_old,v_insert,out [N,H,L,M]; beta [N,H,L,1]; kv [N,H,E,M].
+ * v_insert may have data == NULL (the backward recomputes it). */
+int fwp_fast_weight_forward(int N, int H, int L, int E, int M,
+                            const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                            const fwp_tensor* beta, const fwp_tensor* v_old,
+                            const fwp_tensor* v_insert, const fwp_tensor* kv,
+                            const fwp_tensor* out, int io_dtype, void* stream, int device);
+
+/* replaces fast_weight_backward(Q,K,V,beta,v_old,v_insert,grad_out,fw_mem,gQ,gK,gV,gbeta),
+ *   algorithmic/fast_weight/fast_weight_cuda.cu:564-664
+ * One fused pass (the reference runs two).  v_insert is accepted for
+ * signature parity and ignored (data may be NULL). */
+int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
+                             const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                             const fwp_tensor* beta, const fwp_tensor* v_old,
+                             const fwp_tensor* v_insert, const fwp_tensor* grad_out,
+                             const fwp_tensor* fw_mem,
+                             const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
+                             const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
+                             int io_dtype, void* stream, int device);
+
+/* ---- sum rule (linear-transformer causal product with carried state) ----
+ * replaces causal_dot_product(Q,K,V,kv,out),
+ *   algorithmic/fast_transformers/causal_product_cuda.cu:98-140 */
+int fwp_causal_dot_product(int N, int H, int L, int E, int M,
+                           const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                           const fwp_tensor* kv, const fwp_tensor* out,
+                           int io_dtype, void* stream, int device);
+
+/* replaces causal_dot_backward(Q,K,V,grad_out,gQ,gK,gV),
+ *   algorithmic/fast_transformers/causal_product_cuda.cu:369-445
+ * Like the reference it takes no state: the prefix sums restart from zero. */
+int fwp_causal_dot_backward(int N, int H, int L, int E, int M,
+                            const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                            const fwp_tensor* grad_out,
+                            const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
+                            const fwp_tensor* grad_V,
+                            int io_dtype, void* stream, int device);
+
+/* ---- recurrent delta net -------------------------------------------------
+ * replaces rec_update_fwm_tanh_forward(qx,kx,vx,bx,Rq,Rk,Rv,rb,q,k,v,beta,v_old,states,kv,out),
+ *   algorithmic/rec_update_fwm_tanh/rec_update_fwm_tanh.cu:349-444
+ * qx,kx,vx,q,k,v,v_old,out [N,H,L,D]; bx,beta_out [N,H,L,1]; Rq,Rk,Rv [1,H,D,D];
+ * rb [1,H,1,D]; states [N,H,1,D] in/out; kv [N,H,D,D] in/out. */
+int fwp_rec_update_fwm_tanh_forward(int N, int H, int L, int D,
+                                    const fwp_tensor* qx, const fwp_tensor* kx,
+                                    const fwp_tensor* vx, const fwp_tensor* bx,
+                                    const fwp_tensor* Rq, const fwp_tensor* Rk,
+                                    const fwp_tensor* Rv, const fwp_tensor* rb,
+                                    const fwp_tensor* q_out, const fwp_tensor* k_out,
+                                    const fwp_tensor* v_out, const fwp_tensor* beta_out,
+                                    const fwp_tensor* v_old, const fwp_tensor* states,
+                                    const fwp_tensor* kv, const fwp_tensor* out,
+                                    int io_dtype, void* stream, int device);
+
+/* replaces rec_update_fwm_tanh_backward(q,k,v,beta,v_old,o_delayed,grad_out,Rq,Rk,Rv,rb,fw_mem,
+ *                                       gq,gk,gv,gbeta,gRq,gRk,gRv,grb),
+ *   algorithmic/rec_update_fwm_tanh/rec_update_fwm_tanh.cu:880-986
+ * The reference adds every sequence's parameter gradient into gR* with global
+ * atomics; here each (n,h) writes its partial sums into `scratch` and a second
+ * kernel adds them over n in a fixed order.  scratch: fp32, at least
+ * fwp_rec_update_fwm_tanh_scratch_floats(N,H,D) elements, 16-byte aligned. */
+int fwp_rec_update_fwm_tanh_backward(int N, int H, int L, int D,
+                                     const fwp_tensor* q, const fwp_tensor* k,
+                                     const fwp_tensor* v, const fwp_tensor* beta,
+                                     const fwp_tensor* v_old, const fwp_tensor* o_delayed,
+                                     const fwp_tensor* grad_out,
+                                     const fwp_tensor* Rq, const fwp_tensor* Rk,
+                                     const fwp_tensor* Rv, const fwp_tensor* rb,
+                                     const fwp_tensor* fw_mem,
+                                     const fwp_tensor* grad_q, const fwp_tensor* grad_k,
+                                     const fwp_tensor* grad_v, const fwp_tensor* grad_beta,
+                                     const fwp_tensor* grad_Rq, const fwp_tensor* grad_Rk,
+                                     const fwp_tensor* grad_Rv, const fwp_tensor* grad_rb,
+                                     float* scratch, int64_t scratch_floats,
+                                     int io_dtype, void* stream, int device);
+int64_t fwp_rec_update_fwm_tanh_scratch_floats(int N, int H, int D);
+
+/* ---- delta RNN v2 and v1 ---------------------------------------------------
+ * replaces fast_rnn_v2_forward(Z,K,V,beta,v_old,states,kv,out,out_nmz),
+ *   algorithmic/fast_weight_rnn_v2/fast_rnn_cuda.cu:233-293 */
+int fwp_fast_rnn_v2_forward(int N, int H, int L, int D,
+                            const fwp_tensor* Z, const fwp_tensor* K, const fwp_tensor* V,
+                            const fwp_tensor* beta, const fwp_tensor* v_old,
+                            const fwp_tensor* states, const fwp_tensor* kv,
+                            const fwp_tensor* out, const fwp_tensor* out_nmz,
+                            int io_dtype, void* stream, int device);
+/* replaces fast_rnn_v2_backward(K,V,beta,v_old,grad_out,out,out_delayed,fw_mem,gZ,gK,gV,gbeta),
+ *   algorithmic/fast_weight_rnn_v2/fast_rnn_cuda.cu:592-659.  `out` is unused (may have data NULL). */
+int fwp_fast_rnn_v2_backward(int N, int H, int L, int D,
+                             const fwp_tensor* K, const fwp_tensor* V, const fwp_tensor* beta,
+                             const fwp_tensor* v_old, const fwp_tensor* grad_out,
+                             const fwp_tensor* out, const fwp_tensor* out_delayed,
+                             const fwp_tensor* fw_mem,
+                             const fwp_tensor* grad_Z, const fwp_tensor* grad_K,
+                             const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
+                             int io_dtype, void* stream, int device);
+/* replaces fast_rnn_forward(Z,K,V,beta,v_old,states,kv,out),
+ *   language_modeling/src/utils/fast_weight_rnn/fast_rnn_cuda.cu (forward host function) */
+int fwp_fast_rnn_forward(int N, int H, int L, int D,
+                         const fwp_tensor* Z, const fwp_tensor* K, const fwp_tensor* V,
+                         const fwp_tensor* beta, const fwp_tensor* v_old,
+                         const fwp_tensor* states, const fwp_tensor* kv,
+                         const fwp_tensor* out,
+                         int io_dtype, void* stream, int device);
+/* replaces fast_rnn_backward(K,V,beta,v_old,grad_out,out,out_delayed,fw_mem,gZ,gK,gV,gbeta),
+ *   language_modeling/src/utils/fast_weight_rnn/fast_rnn_cuda.cu (backward host function) */
+int fwp_fast_rnn_backward(int N, int H, int L, int D,
+                          const fwp_tensor* K, const fwp_tensor* V, const fwp_tensor* beta,
+                          const fwp_tensor* v_old, const fwp_tensor* grad_out,
+                          const fwp_tensor* out, const fwp_tensor* out_delayed,
+                          const fwp_tensor* fw_mem,
+                          const fwp_tensor* grad_Z, const fwp_tensor* grad_K,
+                          const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
+                          int io_dtype, void* stream, int device);
+
+/* ---- delta LSTM v1..v4 -----------------------------------------------------
+ * One entry point for the four variants (variant = 1..4).  The twelve streamed
+ * inputs are passed as arrays ordered by gate: index 0 = input gate (i),
+ * 1 = update (u), 2 = output gate (o).
+ * replaces fast_lstm_forward / fast_lstm_v2_forward / _v3_ / _v4_
+ *   (Zi,Ki,Vi,bi, Zu,Ku,Vu,bu, Zo,Ko,Vo,bo, states, cells, kv_i,kv_u,kv_o,
+ *    out, [out_del_nmz,] cell_out, gate_i, update_u, gate_o, v_old_i, v_old_u, v_old_o),
+ *   language_modeling/src/utils/fast_lstm/fast_lstm_cuda.cu:364-480 and
+ *   language_modeling/src/utils/fast_lstm_v{2,3,4}/fast_lstm_v{2,3,4}_cuda.cu (forward host functions).
+ * out_del_nmz is required for variants 2-4 and ignored for variant 1. */
+int fwp_fast_lstm_forward(int variant, int N, int H, int L, int D,
+                          const fwp_tensor Z[3], const fwp_tensor K[3],
+                          const fwp_tensor V[3], const fwp_tensor beta[3],
+                          const fwp_tensor* states, const fwp_tensor* cells,
+                          const fwp_tensor kv[3],
+                          const fwp_tensor* out, const fwp_tensor* out_del_nmz,
+                          const fwp_tensor* cell_out,
+                          const fwp_tensor gates[3], /* gate_i, update_u, gate_o */
+                          const fwp_tensor v_old[3],
+                          int io_dtype, void* stream, int device);
+/* replaces fast_lstm*_backward(grad_out, Ki,Vi,bi, Ku,Vu,bu, Ko,Vo,bo, v_old_i,v_old_u,v_old_o,
+ *    out, out_delayed, cell_out, u_minus_c, gate_i, update_u, gate_o, kv_i,kv_u,kv_o,
+ *    gZi,gKi,gVi,gbi, gZu,gKu,gVu,gbu, gZo,gKo,gVo,gbo),
+ *   language_modeling/src/utils/fast_lstm/fast_lstm_cuda.cu:1061-1205 and the v2-v4 files. */
+int fwp_fast_lstm_backward(int variant, int N, int H, int L, int D,
+                           const fwp_tensor* grad_out,
+                           const fwp_tensor K[3], const fwp_tensor V[3], const fwp_tensor beta[3],
+                           const fwp_tensor v_old[3],
+                           const fwp_tensor* out, const fwp_tensor* out_delayed,
+                           const fwp_tensor* cell_out, const fwp_tensor* u_minus_c,
+                           const fwp_tensor gates[3], const fwp_tensor kv[3],
+                           const fwp_tensor grad_Z[3], const fwp_tensor grad_K[3],
+                           const fwp_tensor grad_V[3], const fwp_tensor grad_beta[3],
+                           int io_dtype, void* stream, int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FWP_H_ */

@@ -1,0 +1,308 @@
+// Shared device/host building blocks of the fast-weight kernels (sm_100a only).
+//
+// Execution model used by every kernel in this library:
+//   * one CTA per (batch, head) sequence; the d x d fast-weight matrices live in
+//     registers for the whole sequence;
+//   * a thread is identified by (s, idx): `idx` in [0, D) is the column it owns
+//     in the "column role" (reductions over the key index e are thread-local)
+//     and, at the same time, the row it owns in the "row role" (reductions over
+//     the value index m are thread-local); `s` in [0, SPLIT) selects which
+//     D/SPLIT-long slice of that column / row the thread holds.  The SPLIT
+//     threads of one idx sit in one warp, so a slice reduction is 0-2 shuffles;
+//   * inputs stream through a two-stage shared-memory ring filled with
+//     cp.async (16-byte copies when rows are aligned, 4-byte otherwise), so any
+//     outer strides are accepted and padding columns read as zero;
+//   * fp32 arithmetic uses the packed two-wide FMA of sm_100 (fma.rn.f32x2).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include "../../include/fwp.h"
+
+// every entry point declared in include/fwp.h is defined with this
+#define FWP_API extern "C" __attribute__((visibility("default")))
+
+namespace fwp {
+
+// ------------------------------------------------------------------ host side
+struct Row4 {            // one (N,H,L,width) tensor with unit inner stride
+    void* p;
+    long long sN, sH, sL;
+};
+
+static inline Row4 row4(const fwp_tensor* t) {
+    Row4 r;
+    r.p = t ? t->data : nullptr;
+    r.sN = t ? t->stride[0] : 0;
+    r.sH = t ? t->stride[1] : 0;
+    r.sL = t ? t->stride[2] : 0;
+    return r;
+}
+
+int check_tensor(const fwp_tensor* t, int elem_bytes, bool required);
+int set_cuda_error(cudaError_t e);
+void count_launch(int n = 1);
+int tune_get(const char* key, int fallback);
+
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    int status = FWP_OK;
+    explicit DeviceGuard(int device) {
+        if (device < 0) return;
+        cudaError_t e = cudaGetDevice(&prev);
+        if (e != cudaSuccess) { status = set_cuda_error(e); return; }
+        if (prev != device) {
+            e = cudaSetDevice(device);
+            if (e != cudaSuccess) { status = set_cuda_error(e); return; }
+            switched = true;
+        }
+    }
+    ~DeviceGuard() { if (switched) cudaSetDevice(prev); }
+};
+
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+constexpr int r4(int x) { return (x + 3) & ~3; }   // round a float count up to 16 bytes
+
+static inline int pad_dim(int d) { return d <= 16 ? 16 : (d <= 32 ? 32 : (d <= 64 ? 64 : 0)); }
+
+// ---------------------------------------------------------------- device side
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+
+template <int D_, int SPLIT_>
+struct Geo {
+    static constexpr int D = D_;
+    static constexpr int SPLIT = SPLIT_;
+    static constexpr int NT = D * SPLIT;     // threads per CTA
+    static constexpr int NR = D / SPLIT;     // slice length held by one thread
+    static constexpr int NP = NR / 2;        // ... in packed pairs
+    static constexpr int MC = 32 / SPLIT;    // idx values per warp
+    static constexpr int WPS = NT / 32;      // warps per sequence
+    static_assert(NT % 32 == 0 && NR % 4 == 0 && SPLIT <= 4, "unsupported geometry");
+    int tid, lane, warp, s, idx, off;        // off = first element of the slice
+    __device__ __forceinline__ Geo() {
+        tid = threadIdx.x;
+        lane = tid & 31;
+        warp = tid >> 5;
+        s = lane / MC;
+        idx = warp * MC + (lane % MC);
+        off = s * NR;
+    }
+};
+
+// sum over the SPLIT threads that share one idx (all of them get the result)
+template <int SPLIT>
+__device__ __forceinline__ float reduce_split(float x) {
+#pragma unroll
+    for (int o = 16; o >= 32 / SPLIT; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+
+// sum / max over the idx values of one warp (threads with equal s)
+template <int SPLIT>
+__device__ __forceinline__ float warp_sum_idx(float x) {
+#pragma unroll
+    for (int o = (32 / SPLIT) / 2; o >= 1; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+template <int SPLIT>
+__device__ __forceinline__ float warp_max_idx(float x) {
+#pragma unroll
+    for (int o = (32 / SPLIT) / 2; o >= 1; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+    return x;
+}
+
+template <int WPS>
+__device__ __forceinline__ void cta_sync() {
+    if constexpr (WPS == 1) __syncwarp(); else __syncthreads();
+}
+
+// All-reduce over idx across the whole CTA.  `slot` points at WPS floats of
+// shared memory that no other reduction uses until the *next* cta_sync after
+// this call (callers rotate slots).  Contains one cta_sync when WPS > 1.
+template <class G, bool IS_MAX>
+__device__ __forceinline__ float cta_allreduce_idx(const G& g, float x, float* slot) {
+    x = IS_MAX ? warp_max_idx<G::SPLIT>(x) : warp_sum_idx<G::SPLIT>(x);
+    if constexpr (G::WPS > 1) {
+        if (g.lane == 0) slot[g.warp] = x;
+        __syncthreads();
+        float r = slot[0];
+#pragma unroll
+        for (int w = 1; w < G::WPS; w++) r = IS_MAX ? fmaxf(r, slot[w]) : r + slot[w];
+        x = r;
+    }
+    return x;
+}
+
+// slice of a shared-memory row -> packed registers (row must be 16-byte aligned)
+template <int NR>
+__device__ __forceinline__ void lds_slice(float2 (&d)[NR / 2], const float* p) {
+#pragma unroll
+    for (int i = 0; i < NR / 4; i++) {
+        float4 t = *reinterpret_cast<const float4*>(p + 4 * i);
+        d[2 * i] = make_float2(t.x, t.y);
+        d[2 * i + 1] = make_float2(t.z, t.w);
+    }
+}
+
+template <int NP>
+__device__ __forceinline__ float dot2(const float2 (&a)[NP], const float2 (&b)[NP]) {
+    float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < NP; i += 2) {
+        acc0 = ffma2(a[i], b[i], acc0);
+        if (i + 1 < NP) acc1 = ffma2(a[i + 1], b[i + 1], acc1);
+    }
+    return (acc0.x + acc1.x) + (acc0.y + acc1.y);
+}
+
+// A += x * a  (a scalar)
+template <int NP>
+__device__ __forceinline__ void axpy2(float2 (&A)[NP], const float2 (&x)[NP], float a) {
+    const float2 aa = make_float2(a, a);
+#pragma unroll
+    for (int i = 0; i < NP; i++) A[i] = ffma2(x[i], aa, A[i]);
+}
+
+// ---- fast-weight matrix <-> registers.  Column role: thread holds
+// S[off..off+NR, idx]; row role: thread holds S[idx, off..off+NR].
+template <class G>
+__device__ __forceinline__ void load_cols(const G& g, float2 (&S)[G::NP], const float* W, long long sE, int E, int M) {
+#pragma unroll
+    for (int i = 0; i < G::NR; i++) {
+        int e = g.off + i;
+        float x = (e < E && g.idx < M) ? W[(long long)e * sE + g.idx] : 0.f;
+        if (i & 1) S[i >> 1].y = x; else S[i >> 1].x = x;
+    }
+}
+template <class G>
+__device__ __forceinline__ void store_cols(const G& g, const float2 (&S)[G::NP], float* W, long long sE, int E, int M) {
+#pragma unroll
+    for (int i = 0; i < G::NR; i++) {
+        int e = g.off + i;
+        if (e < E && g.idx < M) W[(long long)e * sE + g.idx] = (i & 1) ? S[i >> 1].y : S[i >> 1].x;
+    }
+}
+template <class G>
+__device__ __forceinline__ void load_rows(const G& g, float2 (&S)[G::NP], const float* W, long long sE, int E, int M) {
+#pragma unroll
+    for (int i = 0; i < G::NR; i++) {
+        int m = g.off + i;
+        float x = (g.idx < E && m < M) ? W[(long long)g.idx * sE + m] : 0.f;
+        if (i & 1) S[i >> 1].y = x; else S[i >> 1].x = x;
+    }
+}
+template <class G>
+__device__ __forceinline__ void store_rows(const G& g, const float2 (&S)[G::NP], float* W, long long sE, int E, int M) {
+#pragma unroll
+    for (int i = 0; i < G::NR; i++) {
+        int m = g.off + i;
+        if (g.idx < E && m < M) W[(long long)g.idx * sE + m] = (i & 1) ? S[i >> 1].y : S[i >> 1].x;
+    }
+}
+
+// ---- cp.async staging -------------------------------------------------------
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// One streamed tensor of one sequence: rows of `width` elements, row stride sL.
+template <typename T>
+struct Src {
+    const T* base;      // element (n, h, 0, 0)
+    long long sL;
+    int width;          // valid elements per row (<= D)
+    bool vec;           // rows can be copied in 16-byte pieces
+    __device__ __forceinline__ void init(const Row4& r, int n, int h, int w) {
+        base = reinterpret_cast<const T*>(r.p) + n * r.sN + h * r.sH;
+        sL = r.sL;
+        width = w;
+        constexpr int per16 = 16 / (int)sizeof(T);
+        vec = (w % per16 == 0) && ((reinterpret_cast<uintptr_t>(base) & 15) == 0) && (sL % per16 == 0);
+    }
+};
+
+// Copy rows [t0, t0+nt) into a tile whose rows are D elements of T (row r of the
+// tile = time step t0+r).  Elements beyond `width` are never written (the tile
+// is zeroed once at kernel start).
+template <int D, typename T>
+__device__ __forceinline__ void stage_rows(T* tile, const Src<T>& src, int t0, int nt, int tid, int nthreads) {
+    constexpr int per16 = 16 / (int)sizeof(T);
+    if (src.vec) {
+        const int ppr = src.width / per16;             // 16-byte pieces per row
+        const int total = nt * ppr;
+        for (int i = tid; i < total; i += nthreads) {
+            int r = i / ppr, c = (i - r * ppr) * per16;
+            cp_async16(tile + r * D + c, src.base + (long long)(t0 + r) * src.sL + c);
+        }
+    } else if (sizeof(T) == 4) {
+        const int total = nt * src.width;
+        for (int i = tid; i < total; i += nthreads) {
+            int r = i / src.width, c = i - r * src.width;
+            cp_async4(tile + r * D + c, src.base + (long long)(t0 + r) * src.sL + c);
+        }
+    } else {
+        // 2-byte elements without 16-byte alignment: plain loads (rare path)
+        const int total = nt * src.width;
+        for (int i = tid; i < total; i += nthreads) {
+            int r = i / src.width, c = i - r * src.width;
+            tile[r * D + c] = src.base[(long long)(t0 + r) * src.sL + c];
+        }
+    }
+}
+
+// shared-memory tile of one streamed tensor: fp32 rows the compute loop reads,
+// plus (for 16-bit inputs) the raw rows cp.async lands in.
+template <int D, int TC, typename T>
+struct Tile {
+    static constexpr bool kRaw = sizeof(T) != 4;
+    static constexpr int kFloats = TC * D + (kRaw ? TC * D / 2 : 0);
+    float* f;     // [TC][D] fp32
+    T* raw;       // [TC][D] T   (aliases f when T is float)
+    __device__ __forceinline__ void bind(float* mem) {
+        f = mem;
+        raw = kRaw ? reinterpret_cast<T*>(mem + TC * D) : reinterpret_cast<T*>(mem);
+    }
+    __device__ __forceinline__ void load(const Src<T>& src, int t0, int nt, int tid, int nthreads) {
+        stage_rows<D, T>(raw, src, t0, nt, tid, nthreads);
+    }
+    // after the copies have landed and a barrier: widen 16-bit rows to fp32
+    __device__ __forceinline__ void widen(int nt, int width, int tid, int nthreads) {
+        if constexpr (kRaw) {
+            for (int i = tid; i < nt * D; i += nthreads) {
+                int c = i % D;
+                f[i] = (c < width) ? to_f32(raw[i]) : 0.f;
+            }
+        }
+    }
+};
+
+// write one element of a streamed output
+template <typename T>
+__device__ __forceinline__ void put(const Row4& r, int n, int h, int t, int c, float x) {
+    reinterpret_cast<T*>(r.p)[n * r.sN + h * r.sH + (long long)t * r.sL + c] = from_f32<T>(x);
+}
+
+#endif  // __CUDACC__
+}  // namespace fwp

@@ -1,0 +1,564 @@
+// Delta-rule fast weight memory, forward and fused backward (sm_100a).
+//
+//   v_old_t = S_{t-1}^T k_t ; u_t = beta_t (v_t - v_old_t) ; S_t = S_{t-1} + k_t (x) u_t ; y_t = S_t^T q_t
+//
+// Restates the math of the reference's algorithmic/fast_weight/fast_weight_cuda.cu
+// (forward kernel :17-178, backward kernels :244-560) with a different execution
+// plan: the matrix never leaves registers, every reduction is thread-local plus
+// at most two shuffles, outputs are plain stores, and the backward is one pass.
+// The same file holds the sum rule (causal_product_cuda.cu), which is the delta
+// rule without beta and v_old.
+#include "fwp_core.cuh"
+
+namespace fwp {
+
+struct DeltaFwdParams {
+    Row4 q, k, v, beta, v_old, v_ins, out;
+    float* W; long long wN, wH, wE;
+    int H, L, E, M;
+};
+
+template <int D, int TC, typename T>
+struct FwdStage {
+    Tile<D, TC, T> q, k, v;
+    Tile<1, TC, T> b;
+    static constexpr int kFloats = 3 * r4(Tile<D, TC, T>::kFloats) + r4(Tile<1, TC, T>::kFloats);
+    __device__ __forceinline__ void bind(float* mem) {
+        q.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        k.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        v.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        b.bind(mem);
+    }
+};
+
+// SUM = true drops beta / v_old (sum rule): S_t = S_{t-1} + k_t (x) v_t.
+template <int D, int SPLIT, int TC, typename T, bool SUM>
+__global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdParams p) {
+    using G = Geo<D, SPLIT>;
+    const G g;
+    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
+    extern __shared__ __align__(16) float smem[];
+    using Stage = FwdStage<D, TC, T>;
+    for (int i = g.tid; i < 2 * Stage::kFloats; i += G::NT) smem[i] = 0.f;
+
+    Src<T> sq, sk, sv, sb;
+    sq.init(p.q, n, h, p.E);
+    sk.init(p.k, n, h, p.E);
+    sv.init(p.v, n, h, p.M);
+    if (!SUM) sb.init(p.beta, n, h, 1);
+
+    float* W = p.W + n * p.wN + h * p.wH;
+    float2 S[G::NP];
+    load_cols(g, S, W, p.wE, p.E, p.M);
+    __syncthreads();   // zero-fill done before any copy lands
+
+    const int nchunks = (p.L + TC - 1) / TC;
+    auto issue = [&](int c) {
+        Stage s; s.bind(smem + (c & 1) * Stage::kFloats);
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        s.q.load(sq, t0, nt, g.tid, G::NT);
+        s.k.load(sk, t0, nt, g.tid, G::NT);
+        s.v.load(sv, t0, nt, g.tid, G::NT);
+        if (!SUM) s.b.load(sb, t0, nt, g.tid, G::NT);
+        cp_async_commit();
+    };
+    issue(0);
+    const bool col_ok = g.idx < p.M;
+    for (int c = 0; c < nchunks; c++) {
+        if (c + 1 < nchunks) { issue(c + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncthreads();
+        Stage s; s.bind(smem + (c & 1) * Stage::kFloats);
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        if constexpr (sizeof(T) != 4) {
+            s.q.widen(nt, p.E, g.tid, G::NT);
+            s.k.widen(nt, p.E, g.tid, G::NT);
+            s.v.widen(nt, p.M, g.tid, G::NT);
+            if (!SUM) s.b.widen(nt, 1, g.tid, G::NT);
+            __syncthreads();
+        }
+#pragma unroll 2
+        for (int t = 0; t < nt; t++) {
+            float2 kk[G::NP], qq[G::NP];
+            lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
+            lds_slice<G::NR>(qq, s.q.f + t * D + g.off);
+            const float vv = s.v.f[t * D + g.idx];
+            float u, vo = 0.f;
+            if constexpr (SUM) {
+                u = vv;
+            } else {
+                vo = reduce_split<SPLIT>(dot2<G::NP>(S, kk));
+                u = s.b.f[t] * (vv - vo);
+            }
+            axpy2<G::NP>(S, kk, u);
+            const float y = reduce_split<SPLIT>(dot2<G::NP>(S, qq));
+            if (col_ok && g.s == 0) {
+                put<T>(p.out, n, h, t0 + t, g.idx, y);
+                if constexpr (!SUM) {
+                    put<float>(p.v_old, n, h, t0 + t, g.idx, vo);
+                    if (p.v_ins.p) put<float>(p.v_ins, n, h, t0 + t, g.idx, u);
+                }
+            }
+        }
+        __syncthreads();   // stage may be refilled by the next iteration's issue
+    }
+    store_cols(g, S, W, p.wE, p.E, p.M);
+}
+
+// ------------------------------------------------------------------ backward
+struct DeltaBwdParams {
+    Row4 q, k, v, beta, v_old, gy, gq, gk, gv, gb;
+    float* W; long long wN, wH, wE;
+    int H, L, E, M;
+};
+
+template <int D, int TC, typename T>
+struct BwdStage {
+    Tile<D, TC, T> q, k, v, gy;
+    Tile<D, TC, float> vo;
+    Tile<1, TC, T> b;
+    static constexpr int kFloats = 4 * r4(Tile<D, TC, T>::kFloats) + r4(Tile<D, TC, float>::kFloats) +
+                                   r4(Tile<1, TC, T>::kFloats);
+    __device__ __forceinline__ void bind(float* mem) {
+        q.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        k.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        v.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        gy.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        vo.bind(mem); mem += r4(Tile<D, TC, float>::kFloats);
+        b.bind(mem);
+    }
+};
+
+// Per step, walking time backwards with S = S_t (row role) and G = dL/dS_t kept
+// twice (column role Gc for the reduction over e that sits on the dependency
+// chain, row role Gr for the reductions over m that feed dk):
+//   Gc += q (x) gy ; r = Gc^T k ; dv = beta r ; dbeta = r . (v - v_old) ; Gc -= k (x) beta r
+//   dq = S gy ; Gr += q (x) gy ; dk = Gr u ; S -= k (x) u ; dk -= S (beta r) ; Gr -= k (x) beta r
+template <int D, int SPLIT, int TC, typename T>
+__global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdParams p) {
+    using G = Geo<D, SPLIT>;
+    const G g;
+    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
+    extern __shared__ __align__(16) float smem[];
+    using Stage = BwdStage<D, TC, T>;
+    constexpr int kXch = 2 * (2 * D + 8);   // per parity: u[D], br[D], dbeta partials[WPS<=8]
+    for (int i = g.tid; i < 2 * Stage::kFloats + kXch; i += G::NT) smem[i] = 0.f;
+    float* xch = smem + 2 * Stage::kFloats;
+
+    Src<T> sq, sk, sv, sg, sb;
+    Src<float> so;
+    sq.init(p.q, n, h, p.E);
+    sk.init(p.k, n, h, p.E);
+    sv.init(p.v, n, h, p.M);
+    sg.init(p.gy, n, h, p.M);
+    so.init(p.v_old, n, h, p.M);
+    sb.init(p.beta, n, h, 1);
+
+    float* W = p.W + n * p.wN + h * p.wH;
+    float2 Sr[G::NP], Gr[G::NP], Gc[G::NP];
+    load_rows(g, Sr, W, p.wE, p.E, p.M);
+#pragma unroll
+    for (int i = 0; i < G::NP; i++) { Gr[i] = make_float2(0.f, 0.f); Gc[i] = make_float2(0.f, 0.f); }
+    __syncthreads();
+
+    const int nchunks = (p.L + TC - 1) / TC;
+    auto issue = [&](int j) {   // j-th chunk counted from the end of the sequence
+        Stage s; s.bind(smem + (j & 1) * Stage::kFloats);
+        const int c = nchunks - 1 - j;
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        s.q.load(sq, t0, nt, g.tid, G::NT);
+        s.k.load(sk, t0, nt, g.tid, G::NT);
+        s.v.load(sv, t0, nt, g.tid, G::NT);
+        s.gy.load(sg, t0, nt, g.tid, G::NT);
+        s.vo.load(so, t0, nt, g.tid, G::NT);
+        s.b.load(sb, t0, nt, g.tid, G::NT);
+        cp_async_commit();
+    };
+    issue(0);
+    const bool col_ok = g.idx < p.M, row_ok = g.idx < p.E;
+    int par = 0;
+    for (int j = 0; j < nchunks; j++) {
+        if (j + 1 < nchunks) { issue(j + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncthreads();
+        Stage s; s.bind(smem + (j & 1) * Stage::kFloats);
+        const int c = nchunks - 1 - j;
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        if constexpr (sizeof(T) != 4) {
+            s.q.widen(nt, p.E, g.tid, G::NT);
+            s.k.widen(nt, p.E, g.tid, G::NT);
+            s.v.widen(nt, p.M, g.tid, G::NT);
+            s.gy.widen(nt, p.M, g.tid, G::NT);
+            s.b.widen(nt, 1, g.tid, G::NT);
+            __syncthreads();
+        }
+        for (int t = nt - 1; t >= 0; t--) {
+            float* xu = xch + par * (2 * D + 8);
+            float* xbr = xu + D;
+            float* xdb = xbr + D;
+            par ^= 1;
+            const float beta = s.b.f[t];
+            // ---- column role
+            {
+                float2 kk[G::NP], qq[G::NP];
+                lds_slice<G::NR>(qq, s.q.f + t * D + g.off);
+                lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
+                const float gym = s.gy.f[t * D + g.idx];
+                const float w = s.v.f[t * D + g.idx] - s.vo.f[t * D + g.idx];
+                axpy2<G::NP>(Gc, qq, gym);
+                const float r = reduce_split<SPLIT>(dot2<G::NP>(Gc, kk));
+                const float br = beta * r;
+                axpy2<G::NP>(Gc, kk, -br);
+                float pw = warp_sum_idx<SPLIT>(r * w);
+                if (g.s == 0) {
+                    xu[g.idx] = beta * w;
+                    xbr[g.idx] = br;
+                    if (col_ok) put<T>(p.gv, n, h, t0 + t, g.idx, br);
+                }
+                if (G::WPS > 1 && g.lane == 0) xdb[g.warp] = pw;
+                if (G::WPS == 1 && g.tid == 0) put<T>(p.gb, n, h, t0 + t, 0, pw);
+            }
+            cta_sync<G::WPS>();
+            // ---- row role
+            {
+                float2 gr[G::NP], ur[G::NP], brr[G::NP];
+                lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
+                lds_slice<G::NR>(ur, xu + g.off);
+                lds_slice<G::NR>(brr, xbr + g.off);
+                const float qe = s.q.f[t * D + g.idx], ke = s.k.f[t * D + g.idx];
+                float dq = dot2<G::NP>(Sr, gr);
+                axpy2<G::NP>(Gr, gr, qe);
+                float dk = dot2<G::NP>(Gr, ur);
+                axpy2<G::NP>(Sr, ur, -ke);
+                dk -= dot2<G::NP>(Sr, brr);
+                axpy2<G::NP>(Gr, brr, -ke);
+                dq = reduce_split<SPLIT>(dq);
+                dk = reduce_split<SPLIT>(dk);
+                if (row_ok && g.s == 0) {
+                    put<T>(p.gq, n, h, t0 + t, g.idx, dq);
+                    put<T>(p.gk, n, h, t0 + t, g.idx, dk);
+                }
+                if (G::WPS > 1 && g.tid == 0) {
+                    float db = xdb[0];
+#pragma unroll
+                    for (int w2 = 1; w2 < G::WPS; w2++) db += xdb[w2];
+                    put<T>(p.gb, n, h, t0 + t, 0, db);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    store_rows(g, Sr, W, p.wE, p.E, p.M);
+}
+
+// sum-rule backward: dq_t = S_t gy_t with S accumulated forwards from zero,
+// dk_t = G_t v_t, dv_t = G_t^T k_t with G accumulated backwards (causal_product_cuda.cu:369-445).
+struct SumBwdParams {
+    Row4 q, k, v, gy, gq, gk, gv;
+    int H, L, E, M;
+};
+
+template <int D, int TC, typename T>
+struct SumStage {
+    Tile<D, TC, T> q, k, v, gy;
+    static constexpr int kFloats = 4 * r4(Tile<D, TC, T>::kFloats);
+    __device__ __forceinline__ void bind(float* mem) {
+        q.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        k.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        v.bind(mem); mem += r4(Tile<D, TC, T>::kFloats);
+        gy.bind(mem);
+    }
+};
+
+template <int D, int SPLIT, int TC, typename T>
+__global__ void __launch_bounds__(D * SPLIT) sum_bwd_kernel(const SumBwdParams p) {
+    using G = Geo<D, SPLIT>;
+    const G g;
+    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
+    extern __shared__ __align__(16) float smem[];
+    using Stage = SumStage<D, TC, T>;
+    for (int i = g.tid; i < 2 * Stage::kFloats; i += G::NT) smem[i] = 0.f;
+    Src<T> sq, sk, sv, sg;
+    sq.init(p.q, n, h, p.E);
+    sk.init(p.k, n, h, p.E);
+    sv.init(p.v, n, h, p.M);
+    sg.init(p.gy, n, h, p.M);
+    __syncthreads();
+    const int nchunks = (p.L + TC - 1) / TC;
+    const bool col_ok = g.idx < p.M, row_ok = g.idx < p.E;
+    // phase 0: forwards, S row role, dq.  phase 1: backwards, G in both roles, dk and dv.
+    for (int phase = 0; phase < 2; phase++) {
+        float2 A[G::NP], B[G::NP];
+#pragma unroll
+        for (int i = 0; i < G::NP; i++) { A[i] = make_float2(0.f, 0.f); B[i] = make_float2(0.f, 0.f); }
+        auto issue = [&](int j) {
+            Stage s; s.bind(smem + (j & 1) * Stage::kFloats);
+            const int c = phase ? nchunks - 1 - j : j;
+            const int t0 = c * TC, nt = min(TC, p.L - t0);
+            s.q.load(sq, t0, nt, g.tid, G::NT);
+            s.k.load(sk, t0, nt, g.tid, G::NT);
+            s.v.load(sv, t0, nt, g.tid, G::NT);
+            s.gy.load(sg, t0, nt, g.tid, G::NT);
+            cp_async_commit();
+        };
+        issue(0);
+        for (int j = 0; j < nchunks; j++) {
+            if (j + 1 < nchunks) { issue(j + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+            __syncthreads();
+            Stage s; s.bind(smem + (j & 1) * Stage::kFloats);
+            const int c = phase ? nchunks - 1 - j : j;
+            const int t0 = c * TC, nt = min(TC, p.L - t0);
+            if constexpr (sizeof(T) != 4) {
+                s.q.widen(nt, p.E, g.tid, G::NT);
+                s.k.widen(nt, p.E, g.tid, G::NT);
+                s.v.widen(nt, p.M, g.tid, G::NT);
+                s.gy.widen(nt, p.M, g.tid, G::NT);
+                __syncthreads();
+            }
+            for (int i = 0; i < nt; i++) {
+                const int t = phase ? nt - 1 - i : i;
+                if (phase == 0) {
+                    float2 vr[G::NP], gr[G::NP];
+                    lds_slice<G::NR>(vr, s.v.f + t * D + g.off);
+                    lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
+                    axpy2<G::NP>(A, vr, s.k.f[t * D + g.idx]);
+                    const float dq = reduce_split<SPLIT>(dot2<G::NP>(A, gr));
+                    if (row_ok && g.s == 0) put<T>(p.gq, n, h, t0 + t, g.idx, dq);
+                } else {
+                    float2 vr[G::NP], gr[G::NP], kk[G::NP], qq[G::NP];
+                    lds_slice<G::NR>(vr, s.v.f + t * D + g.off);
+                    lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
+                    lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
+                    lds_slice<G::NR>(qq, s.q.f + t * D + g.off);
+                    axpy2<G::NP>(A, gr, s.q.f[t * D + g.idx]);        // row role G
+                    axpy2<G::NP>(B, qq, s.gy.f[t * D + g.idx]);       // column role G
+                    const float dk = reduce_split<SPLIT>(dot2<G::NP>(A, vr));
+                    const float dv = reduce_split<SPLIT>(dot2<G::NP>(B, kk));
+                    if (g.s == 0) {
+                        if (row_ok) put<T>(p.gk, n, h, t0 + t, g.idx, dk);
+                        if (col_ok) put<T>(p.gv, n, h, t0 + t, g.idx, dv);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// ------------------------------------------------------------------ launchers
+template <typename K>
+static int set_smem(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return set_cuda_error(e);
+    }
+    return FWP_OK;
+}
+
+template <int D, int SPLIT, int TC, typename T, bool SUM>
+static int launch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
+    auto kern = delta_fwd_kernel<D, SPLIT, TC, T, SUM>;
+    const size_t bytes = 2 * FwdStage<D, TC, T>::kFloats * sizeof(float);
+    if (int rc = set_smem(kern, bytes)) return rc;
+    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+template <int D, int SPLIT, int TC, typename T>
+static int launch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
+    auto kern = delta_bwd_kernel<D, SPLIT, TC, T>;
+    const size_t bytes = (2 * BwdStage<D, TC, T>::kFloats + 2 * (2 * D + 8)) * sizeof(float);
+    if (int rc = set_smem(kern, bytes)) return rc;
+    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+template <int D, int SPLIT, int TC, typename T>
+static int launch_sum_bwd(const SumBwdParams& p, int nseq, cudaStream_t st) {
+    auto kern = sum_bwd_kernel<D, SPLIT, TC, T>;
+    const size_t bytes = 2 * SumStage<D, TC, T>::kFloats * sizeof(float);
+    if (int rc = set_smem(kern, bytes)) return rc;
+    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+template <typename T, bool SUM>
+static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, const char* op) {
+    const int D = pad_dim(p.E > p.M ? p.E : p.M);
+    char key[48];
+    snprintf(key, sizeof key, "%s.%d.split", op, D);
+    switch (D) {
+        case 16: {
+            int sp = tune_get(key, 2);
+            if (sp == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
+            return launch_fwd<16, 2, 32, T, SUM>(p, nseq, st);
+        }
+        case 32: {
+            int sp = tune_get(key, 1);
+            if (sp == 2) return launch_fwd<32, 2, 16, T, SUM>(p, nseq, st);
+            if (sp == 4) return launch_fwd<32, 4, 16, T, SUM>(p, nseq, st);
+            return launch_fwd<32, 1, 16, T, SUM>(p, nseq, st);
+        }
+        case 64: {
+            int sp = tune_get(key, 2);
+            if (sp == 1) return launch_fwd<64, 1, 8, T, SUM>(p, nseq, st);
+            if (sp == 4) return launch_fwd<64, 4, 8, T, SUM>(p, nseq, st);
+            return launch_fwd<64, 2, 8, T, SUM>(p, nseq, st);
+        }
+    }
+    return FWP_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+static int dispatch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
+    const int D = pad_dim(p.E > p.M ? p.E : p.M);
+    char key[48];
+    snprintf(key, sizeof key, "delta_bwd.%d.split", D);
+    switch (D) {
+        case 16: {
+            int sp = tune_get(key, 2);
+            if (sp == 4) return launch_bwd<16, 4, 16, T>(p, nseq, st);
+            return launch_bwd<16, 2, 16, T>(p, nseq, st);
+        }
+        case 32: {
+            int sp = tune_get(key, 2);
+            if (sp == 1) return launch_bwd<32, 1, 8, T>(p, nseq, st);
+            if (sp == 4) return launch_bwd<32, 4, 8, T>(p, nseq, st);
+            return launch_bwd<32, 2, 8, T>(p, nseq, st);
+        }
+        case 64: {
+            int sp = tune_get(key, 4);
+            if (sp == 2) return launch_bwd<64, 2, 4, T>(p, nseq, st);
+            return launch_bwd<64, 4, 4, T>(p, nseq, st);
+        }
+    }
+    return FWP_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+static int dispatch_sum_bwd(const SumBwdParams& p, int nseq, cudaStream_t st) {
+    const int D = pad_dim(p.E > p.M ? p.E : p.M);
+    switch (D) {
+        case 16: return launch_sum_bwd<16, 2, 16, T>(p, nseq, st);
+        case 32: return launch_sum_bwd<32, 2, 8, T>(p, nseq, st);
+        case 64: return launch_sum_bwd<64, 4, 4, T>(p, nseq, st);
+    }
+    return FWP_ERR_UNSUPPORTED;
+}
+
+static int check_common(int N, int H, int L, int E, int M, int io_dtype) {
+    if (N <= 0 || H <= 0 || L <= 0 || E <= 0 || M <= 0) return FWP_ERR_SHAPE;
+    if ((long long)N * H > 0x7fffffffLL) return FWP_ERR_SHAPE;
+    if (io_dtype != FWP_F32 && io_dtype != FWP_BF16) return FWP_ERR_DTYPE;
+    if (pad_dim(E > M ? E : M) == 0) return FWP_ERR_UNSUPPORTED;
+    return FWP_OK;
+}
+
+}  // namespace fwp
+
+using namespace fwp;
+
+FWP_API int fwp_fast_weight_forward(int N, int H, int L, int E, int M,
+                                       const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                       const fwp_tensor* beta, const fwp_tensor* v_old,
+                                       const fwp_tensor* v_insert, const fwp_tensor* kv,
+                                       const fwp_tensor* out, int io_dtype, void* stream, int device) {
+    if (int rc = check_common(N, H, L, E, M, io_dtype)) return rc;
+    const int eb = io_dtype == FWP_F32 ? 4 : 2;
+    int rc;
+    if ((rc = check_tensor(Q, eb, true)) || (rc = check_tensor(K, eb, true)) || (rc = check_tensor(V, eb, true)) ||
+        (rc = check_tensor(beta, eb, true)) || (rc = check_tensor(v_old, 4, true)) ||
+        (rc = check_tensor(v_insert, 4, false)) || (rc = check_tensor(kv, 4, true)) ||
+        (rc = check_tensor(out, eb, true)))
+        return rc;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    DeltaFwdParams p;
+    p.q = row4(Q); p.k = row4(K); p.v = row4(V); p.beta = row4(beta);
+    p.v_old = row4(v_old); p.v_ins = row4(v_insert); p.out = row4(out);
+    p.W = (float*)kv->data; p.wN = kv->stride[0]; p.wH = kv->stride[1]; p.wE = kv->stride[2];
+    p.H = H; p.L = L; p.E = E; p.M = M;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (io_dtype == FWP_F32) return dispatch_fwd<float, false>(p, N * H, st, "delta_fwd");
+    return dispatch_fwd<__nv_bfloat16, false>(p, N * H, st, "delta_fwd");
+}
+
+FWP_API int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
+                                        const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                        const fwp_tensor* beta, const fwp_tensor* v_old,
+                                        const fwp_tensor* v_insert, const fwp_tensor* grad_out,
+                                        const fwp_tensor* fw_mem,
+                                        const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
+                                        const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
+                                        int io_dtype, void* stream, int device) {
+    (void)v_insert;
+    if (int rc = check_common(N, H, L, E, M, io_dtype)) return rc;
+    const int eb = io_dtype == FWP_F32 ? 4 : 2;
+    int rc;
+    if ((rc = check_tensor(Q, eb, true)) || (rc = check_tensor(K, eb, true)) || (rc = check_tensor(V, eb, true)) ||
+        (rc = check_tensor(beta, eb, true)) || (rc = check_tensor(v_old, 4, true)) ||
+        (rc = check_tensor(grad_out, eb, true)) || (rc = check_tensor(fw_mem, 4, true)) ||
+        (rc = check_tensor(grad_Q, eb, true)) || (rc = check_tensor(grad_K, eb, true)) ||
+        (rc = check_tensor(grad_V, eb, true)) || (rc = check_tensor(grad_beta, eb, true)))
+        return rc;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    DeltaBwdParams p;
+    p.q = row4(Q); p.k = row4(K); p.v = row4(V); p.beta = row4(beta); p.v_old = row4(v_old);
+    p.gy = row4(grad_out); p.gq = row4(grad_Q); p.gk = row4(grad_K); p.gv = row4(grad_V); p.gb = row4(grad_beta);
+    p.W = (float*)fw_mem->data; p.wN = fw_mem->stride[0]; p.wH = fw_mem->stride[1]; p.wE = fw_mem->stride[2];
+    p.H = H; p.L = L; p.E = E; p.M = M;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (io_dtype == FWP_F32) return dispatch_bwd<float>(p, N * H, st);
+    return dispatch_bwd<__nv_bfloat16>(p, N * H, st);
+}
+
+FWP_API int fwp_causal_dot_product(int N, int H, int L, int E, int M,
+                                      const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                      const fwp_tensor* kv, const fwp_tensor* out,
+                                      int io_dtype, void* stream, int device) {
+    if (int rc = check_common(N, H, L, E, M, io_dtype)) return rc;
+    const int eb = io_dtype == FWP_F32 ? 4 : 2;
+    int rc;
+    if ((rc = check_tensor(Q, eb, true)) || (rc = check_tensor(K, eb, true)) || (rc = check_tensor(V, eb, true)) ||
+        (rc = check_tensor(kv, 4, true)) || (rc = check_tensor(out, eb, true)))
+        return rc;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    DeltaFwdParams p;
+    p.q = row4(Q); p.k = row4(K); p.v = row4(V); p.beta = row4(nullptr);
+    p.v_old = row4(nullptr); p.v_ins = row4(nullptr); p.out = row4(out);
+    p.W = (float*)kv->data; p.wN = kv->stride[0]; p.wH = kv->stride[1]; p.wE = kv->stride[2];
+    p.H = H; p.L = L; p.E = E; p.M = M;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (io_dtype == FWP_F32) return dispatch_fwd<float, true>(p, N * H, st, "sum_fwd");
+    return dispatch_fwd<__nv_bfloat16, true>(p, N * H, st, "sum_fwd");
+}
+
+FWP_API int fwp_causal_dot_backward(int N, int H, int L, int E, int M,
+                                       const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                       const fwp_tensor* grad_out,
+                                       const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
+                                       const fwp_tensor* grad_V,
+                                       int io_dtype, void* stream, int device) {
+    if (int rc = check_common(N, H, L, E, M, io_dtype)) return rc;
+    const int eb = io_dtype == FWP_F32 ? 4 : 2;
+    int rc;
+    if ((rc = check_tensor(Q, eb, true)) || (rc = check_tensor(K, eb, true)) || (rc = check_tensor(V, eb, true)) ||
+        (rc = check_tensor(grad_out, eb, true)) || (rc = check_tensor(grad_Q, eb, true)) ||
+        (rc = check_tensor(grad_K, eb, true)) || (rc = check_tensor(grad_V, eb, true)))
+        return rc;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    SumBwdParams p;
+    p.q = row4(Q); p.k = row4(K); p.v = row4(V); p.gy = row4(grad_out);
+    p.gq = row4(grad_Q); p.gk = row4(grad_K); p.gv = row4(grad_V);
+    p.H = H; p.L = L; p.E = E; p.M = M;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (io_dtype == FWP_F32) return dispatch_sum_bwd<float>(p, N * H, st);
+    return dispatch_sum_bwd<__nv_bfloat16>(p, N * H, st);
+}

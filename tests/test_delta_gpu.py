@@ -1,0 +1,172 @@
+"""GPU parity of the delta-rule (and sum-rule) kernels, through the C ABI, against
+the CPU oracle on identical seeded inputs and against the golden fixtures.
+
+Tolerances (fp32): max |dy| <= 1e-4; gradients: the reference self-test's measure
+max |d| / (|ref| + 1e-6) <= 1e-3 on the reference-shaped golden case, and
+max |d| / (|ref| + mean|ref|) <= 1e-3 on the N(0,1)-driven configurations.
+"""
+import pytest
+import torch
+
+from oracle import kernels as K, loops
+from tests import util
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda:0'
+
+
+def run_cuda(fwp, q, k, v, b, W, gy):
+    leaves = [t.to(DEV).requires_grad_() for t in (q, k, v, b)]
+    y = fwp.fast_weight_delta(*leaves, W)
+    W_end = W.clone()
+    y.backward(gy.to(DEV))
+    return y.detach(), [l.grad for l in leaves], W_end
+
+
+def run_loop(q, k, v, b, W0, gy, dtype):
+    leaves = [t.to(dtype).requires_grad_() for t in (q, k, v, b)]
+    y, S = loops.delta_rule(*leaves, W0.to(dtype))
+    (y * gy.to(dtype)).sum().backward()
+    return y.detach(), [l.grad for l in leaves], S.detach()
+
+
+def test_golden_reference_selftest_case(fwp):
+    gd = util.golden('delta')
+    q, k, v, b = (gd['in_' + n] for n in ('q0', 'k0', 'v0', 'beta0'))
+    N, H, L, E = q.shape
+    W = torch.zeros(N, H, E, v.shape[3], device=DEV)
+    y, grads, _ = run_cuda(fwp, q, k, v, b, W, torch.ones(N, H, L, v.shape[3]))
+    assert util.max_rel(y, gd['out_LBHd'].permute(1, 2, 0, 3)) < 1e-3
+    for g, n in zip(grads, ('q2', 'k2', 'v2', 'beta2')):
+        assert util.max_rel(g, gd['grad_' + n]) < 1e-3
+    assert W.abs().max().item() < 1e-4     # rewound to the zero start state
+
+
+@pytest.mark.parametrize('B,H,L,E,M', [
+    (2, 8, 256, 16, 16),     # configs[0]
+    (3, 2, 37, 32, 32),
+    (2, 2, 41, 64, 64),
+    (2, 3, 1, 16, 16),       # single step (the RL callers)
+    (2, 2, 19, 18, 18),      # not a power of two
+    (2, 2, 23, 20, 5),       # E != M
+    (1, 2, 17, 16, 49),      # M = 3d+1
+    (1, 1, 9, 64, 3),
+])
+def test_parity_vs_oracle(fwp, B, H, L, E, M):
+    q, k, v, b, gy = util.delta_inputs(11, B, H, L, E, M)
+    W0 = torch.randn(B, H, E, M, generator=util.gen(12)) * 0.1
+    W = W0.to(DEV)
+    y, grads, W_end = run_cuda(fwp, q, k, v, b, W, gy)
+    y32, g32, S32 = run_loop(q, k, v, b, W0, gy, torch.float32)
+    y64, g64, S64 = run_loop(q, k, v, b, W0, gy, torch.float64)
+    assert util.max_abs(y, y32) <= 1e-4 and util.max_abs(y, y64) <= 1e-4
+    assert util.max_abs(W_end, S64) <= 1e-4
+    for g, r32, r64 in zip(grads, g32, g64):
+        assert util.scaled_rel(g, r64) <= 1e-3
+        assert util.scaled_rel(g, r32) <= 1e-3
+    assert util.max_abs(W, W0) <= 1e-5     # backward rewound the state in place
+
+
+def test_four_carried_segments_lm_shape(fwp):
+    """configs[1]: B=64,H=8,L=256,d=16, state handed over 4 segments, fwd+bwd per segment."""
+    B, H, L, d = 64, 8, 256, 16
+    W = torch.zeros(B, H, d, d, device=DEV)
+    S = torch.zeros(B, H, d, d, dtype=torch.float64)
+    for seg in range(4):
+        q, k, v, b, gy = util.delta_inputs(100 + seg, B, H, L, d)
+        W_in = W.clone()
+        y, grads, W_end = run_cuda(fwp, q, k, v, b, W, gy)
+        assert util.max_abs(W, W_in) <= 1e-5
+        y64, g64, S_next = run_loop(q, k, v, b, S, gy, torch.float64)
+        assert util.max_abs(y, y64) <= 1e-4
+        for g, r in zip(grads, g64):
+            assert util.scaled_rel(g, r) <= 1e-3
+        W = W_end            # the caller's clone of the end state, as the reference layers do
+        S = S_next
+        assert util.max_abs(W, S) <= 1e-4
+
+
+def test_strided_views_of_a_fused_projection(fwp):
+    """Callers pass permuted views of one (L, B, H, 3d+1) projection; no copy is required."""
+    L, B, H, d = 33, 2, 4, 16
+    g = util.gen(5)
+    fused = torch.randn(L, B, H, 3 * d + 1, generator=g)
+    hq, hk, hv, hb = torch.split(fused, (d, d, d, 1), -1)
+    q = loops.sum_norm(loops.elu_p1(hq)).permute(1, 2, 0, 3)
+    k = loops.sum_norm(loops.elu_p1(hk)).permute(1, 2, 0, 3)
+    v = hv.permute(1, 2, 0, 3)
+    b = torch.sigmoid(hb).permute(1, 2, 0, 3)
+    gy = torch.randn(L, B, H, d, generator=g).permute(1, 2, 0, 3)
+    assert not v.is_contiguous()
+    fused_dev = fused.to(DEV)
+    vq = fused_dev[..., 2 * d:3 * d].permute(1, 2, 0, 3).requires_grad_()   # a true strided view on the device
+    qd, kd, bd = (t.to(DEV).requires_grad_() for t in (q, k, b))
+    W = torch.zeros(B, H, d, d, device=DEV)
+    y = fwp.fast_weight_delta(qd, kd, vq, bd, W)
+    y.backward(gy.to(DEV))
+    y64, g64, _ = run_loop(q, k, v, b, torch.zeros(B, H, d, d), gy, torch.float64)
+    assert util.max_abs(y, y64) <= 1e-4
+    for got, ref in zip((qd.grad, kd.grad, vq.grad, bd.grad), g64):
+        assert util.scaled_rel(got, ref) <= 1e-3
+
+
+def test_batch_prefix_slice_of_a_larger_state(fwp):
+    """`mems[:bsz]`: the state may be a prefix slice of a bigger buffer; only that slice is touched."""
+    B, H, L, d = 2, 3, 12, 16
+    big = torch.full((4, H, d, d), 7.0, device=DEV)
+    big[:B] = 0
+    q, k, v, b, gy = util.delta_inputs(21, B, H, L, d)
+    y = fwp.fast_weight_delta(q.to(DEV), k.to(DEV), v.to(DEV), b.to(DEV), big[:B])
+    y64, _, S64 = run_loop(q, k, v, b, torch.zeros(B, H, d, d), gy, torch.float64)
+    assert util.max_abs(y, y64) <= 1e-4 and util.max_abs(big[:B], S64) <= 1e-4
+    assert (big[B:] == 7.0).all()
+
+
+def test_bitwise_reproducible(fwp):
+    q, k, v, b, gy = util.delta_inputs(31, 4, 4, 64, 32)
+    outs = []
+    for _ in range(2):
+        W = torch.zeros(4, 4, 32, 32, device=DEV)
+        y, grads, _ = run_cuda(fwp, q, k, v, b, W, gy)
+        outs.append([y] + grads)
+    for a, c in zip(*outs):
+        assert torch.equal(a, c)
+
+
+def test_bf16_streams_fp32_state(fwp):
+    """bf16 q/k/v/beta/gy with an fp32 state: oracle = fp64 loop on the bf16-rounded inputs.
+    Bounds: |dy| <= 2e-2 * max|y| (outputs are rounded to bf16), gradients scaled-rel <= 3e-2."""
+    B, H, L, d = 2, 4, 128, 64
+    q, k, v, b, gy = [t.to(torch.bfloat16) for t in util.delta_inputs(41, B, H, L, d)]
+    W = torch.zeros(B, H, d, d, device=DEV)
+    y, grads, W_end = run_cuda(fwp, q, k, v, b, W, gy)
+    assert y.dtype == torch.bfloat16
+    y64, g64, S64 = run_loop(q.float(), k.float(), v.float(), b.float(), torch.zeros(B, H, d, d), gy.float(),
+                             torch.float64)
+    assert util.max_abs(y.float(), y64) <= 2e-2 * y64.abs().max().item()
+    assert util.max_abs(W_end, S64) <= 1e-4
+    for g, r in zip(grads, g64):
+        assert util.scaled_rel(g.float(), r) <= 3e-2
+
+
+def test_sum_rule_golden_and_oracle(fwp):
+    gd = util.golden('sum')
+    q, k, v = gd['in_q0'], gd['in_k0'], gd['in_v0']
+    N, H, L, E = q.shape
+    M = v.shape[3]
+    leaves = [t.to(DEV).requires_grad_() for t in (q, k, v)]
+    W = torch.zeros(N, H, E, M, device=DEV)
+    y = fwp.fast_weight_sum(*leaves, W)
+    y.sum().backward()
+    ref = [t.clone().requires_grad_() for t in (q, k, v)]
+    y2, S2 = loops.sum_rule(*ref, torch.zeros(N, H, E, M))
+    y2.sum().backward()
+    assert util.max_rel(y, y2) < 1e-3 and util.max_abs(W, S2) < 1e-4
+    for leaf, n in zip(leaves, ('q2', 'k2', 'v2')):
+        assert util.max_rel(leaf.grad, gd['grad_' + n]) < 1e-3
+
+
+def test_unsupported_head_dim_is_an_error_not_a_fallback(fwp):
+    q = torch.rand(1, 1, 4, 128, device=DEV)
+    with pytest.raises(RuntimeError, match='head dimension'):
+        fwp.fast_weight_delta(q, q, q, torch.rand(1, 1, 4, 1, device=DEV), torch.zeros(1, 1, 128, 128, device=DEV))
