@@ -1,0 +1,496 @@
+// Recurrent delta net (rec_update_fwm_tanh): delta-rule fast weight memory whose
+// query, key, value and beta receive additive feedback R . tanh(y_{t-1}).  sm_100a.
+//
+//   ht = tanh(y_{t-1}) ; q = softmax(qx_t + Rq^T ht) ; k = softmax(kx_t + Rk^T ht)
+//   v = vx_t + Rv^T ht ; beta = sigmoid(bx_t + rb . ht) ; delta-rule step ; y_t = S_t^T q
+//
+// Restates algorithmic/rec_update_fwm_tanh/rec_update_fwm_tanh.cu (forward kernel :25-345,
+// backward kernel :448-876) with the register-resident plan of fwp_core.cuh.  The
+// parameter gradients dRq, dRk, dRv, drb are accumulated per (n, h) in registers,
+// written once to a scratch buffer and summed over n by a second kernel in a fixed
+// order (the reference adds them with global atomics every step).
+#include "fwp_core.cuh"
+
+namespace fwp {
+
+struct RecFwdParams {
+    Row4 qx, kx, vx, bx, q_out, k_out, v_out, b_out, v_old, out;
+    const float *Rq, *Rk, *Rv, *rb;
+    long long rH, rE;       // strides of R over head and first matrix index
+    long long rbH;          // stride of rb over head
+    float* W; long long wN, wH, wE;
+    float* h; long long hN, hH;
+    int H, L, D;
+};
+
+template <int D, int TC>
+struct RecFwdStage {
+    Tile<D, TC, float> q, k, v;
+    Tile<1, TC, float> b;
+    static constexpr int kFloats = 3 * r4(TC * D) + r4(TC);
+    __device__ __forceinline__ void bind(float* mem) {
+        q.bind(mem); mem += r4(TC * D);
+        k.bind(mem); mem += r4(TC * D);
+        v.bind(mem); mem += r4(TC * D);
+        b.bind(mem);
+    }
+};
+
+template <int D, int SPLIT, int TC>
+__global__ void __launch_bounds__(D * SPLIT) rec_fwd_kernel(const RecFwdParams p) {
+    using G = Geo<D, SPLIT>;
+    const G g;
+    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
+    extern __shared__ __align__(16) float smem[];
+    using Stage = RecFwdStage<D, TC>;
+    constexpr int kX = 3 * D + 32;        // per parity: ht[D], eq[D], ek[D], slots[4][8]
+    for (int i = g.tid; i < 2 * Stage::kFloats + 2 * kX; i += G::NT) smem[i] = 0.f;
+    float* xch = smem + 2 * Stage::kFloats;
+
+    Src<float> sq, sk, sv, sb;
+    sq.init(p.qx, n, h, p.D);
+    sk.init(p.kx, n, h, p.D);
+    sv.init(p.vx, n, h, p.D);
+    sb.init(p.bx, n, h, 1);
+
+    float2 S[G::NP], Rq[G::NP], Rk[G::NP], Rv[G::NP], rb[G::NP];
+    load_cols(g, S, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
+    load_cols(g, Rq, p.Rq + h * p.rH, p.rE, p.D, p.D);
+    load_cols(g, Rk, p.Rk + h * p.rH, p.rE, p.D, p.D);
+    load_cols(g, Rv, p.Rv + h * p.rH, p.rE, p.D, p.D);
+#pragma unroll
+    for (int i = 0; i < G::NR; i++) {
+        const int e = g.off + i;
+        const float x = e < p.D ? p.rb[h * p.rbH + e] : 0.f;
+        if (i & 1) rb[i >> 1].y = x; else rb[i >> 1].x = x;
+    }
+    const bool ok = g.idx < p.D;
+    float* hp = p.h + n * p.hN + h * p.hH;
+    float hv = ok ? hp[g.idx] : 0.f;
+    __syncthreads();
+
+    const int nchunks = (p.L + TC - 1) / TC;
+    auto issue = [&](int c) {
+        Stage s; s.bind(smem + (c & 1) * Stage::kFloats);
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        s.q.load(sq, t0, nt, g.tid, G::NT);
+        s.k.load(sk, t0, nt, g.tid, G::NT);
+        s.v.load(sv, t0, nt, g.tid, G::NT);
+        s.b.load(sb, t0, nt, g.tid, G::NT);
+        cp_async_commit();
+    };
+    issue(0);
+    int par = 0;
+    for (int c = 0; c < nchunks; c++) {
+        if (c + 1 < nchunks) { issue(c + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncthreads();
+        Stage s; s.bind(smem + (c & 1) * Stage::kFloats);
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        for (int t = 0; t < nt; t++) {
+            float* xh = xch + par * kX;
+            float* xq = xh + D;
+            float* xk = xq + D;
+            float* slot = xk + D;
+            par ^= 1;
+            const int o = t * D + g.idx;
+            if (g.s == 0) xh[g.idx] = ok ? tanhf(hv) : 0.f;
+            cta_sync<G::WPS>();
+            float2 hs[G::NP];
+            lds_slice<G::NR>(hs, xh + g.off);
+            const float qh = s.q.f[o] + reduce_split<SPLIT>(dot2<G::NP>(Rq, hs));
+            const float kh = s.k.f[o] + reduce_split<SPLIT>(dot2<G::NP>(Rk, hs));
+            const float vv = s.v.f[o] + reduce_split<SPLIT>(dot2<G::NP>(Rv, hs));
+            const float beta = sigmoidf_(s.b.f[t] + reduce_split<SPLIT>(dot2<G::NP>(rb, hs)));
+            const float mq = cta_allreduce_idx<G, true>(g, ok ? qh : -INFINITY, slot);
+            const float mk = cta_allreduce_idx<G, true>(g, ok ? kh : -INFINITY, slot + 8);
+            const float eq = ok ? expf(qh - mq) : 0.f;
+            const float ek = ok ? expf(kh - mk) : 0.f;
+            if (g.s == 0) { xq[g.idx] = eq; xk[g.idx] = ek; }
+            const float invq = 1.f / cta_allreduce_idx<G, false>(g, eq, slot + 16);
+            const float invk = 1.f / cta_allreduce_idx<G, false>(g, ek, slot + 24);
+            cta_sync<G::WPS>();
+            float2 ks[G::NP], qs[G::NP];
+            lds_slice<G::NR>(ks, xk + g.off);
+            lds_slice<G::NR>(qs, xq + g.off);
+            const float vo = reduce_split<SPLIT>(dot2<G::NP>(S, ks)) * invk;
+            const float u = beta * (vv - vo);
+            axpy2<G::NP>(S, ks, u * invk);
+            const float y = reduce_split<SPLIT>(dot2<G::NP>(S, qs)) * invq;
+            hv = y;
+            if (ok && g.s == 0) {
+                const int tt = t0 + t;
+                put<float>(p.out, n, h, tt, g.idx, y);
+                put<float>(p.q_out, n, h, tt, g.idx, eq * invq);
+                put<float>(p.k_out, n, h, tt, g.idx, ek * invk);
+                put<float>(p.v_out, n, h, tt, g.idx, vv);
+                put<float>(p.v_old, n, h, tt, g.idx, vo);
+                if (g.idx == 0) put<float>(p.b_out, n, h, tt, 0, beta);
+            }
+        }
+        __syncthreads();
+    }
+    store_cols(g, S, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
+    if (ok && g.s == 0) hp[g.idx] = hv;
+}
+
+// ------------------------------------------------------------------ backward
+struct RecBwdParams {
+    Row4 q, k, v, beta, v_old, od, gy, gq, gk, gv, gb;
+    const float *Rq, *Rk, *Rv, *rb;
+    long long rH, rE, rbH;
+    float* W; long long wN, wH, wE;
+    float* scratch;          // [N*H][3*d*d + d] partial parameter gradients
+    int H, L, D;
+};
+
+template <int D, int TC>
+struct RecBwdStage {
+    Tile<D, TC, float> q, k, v, vo, od, gy;
+    Tile<1, TC, float> b;
+    static constexpr int kFloats = 6 * r4(TC * D) + r4(TC);
+    __device__ __forceinline__ void bind(float* mem) {
+        q.bind(mem); mem += r4(TC * D);
+        k.bind(mem); mem += r4(TC * D);
+        v.bind(mem); mem += r4(TC * D);
+        vo.bind(mem); mem += r4(TC * D);
+        od.bind(mem); mem += r4(TC * D);
+        gy.bind(mem); mem += r4(TC * D);
+        b.bind(mem);
+    }
+};
+
+template <int D>
+struct RecBwdSmem {
+    static constexpr int kRS = D + 4;                    // padded row stride of the R copies
+    static constexpr int kR = 3 * D * kRS + D;           // Rq, Rk, Rv rows + rb
+    static constexpr int kXs = 5 * D + 40;               // per parity: g, u, br, dq, dk [D] + slots[5][8]
+};
+
+template <int D, int SPLIT, int TC>
+__global__ void __launch_bounds__(D * SPLIT) rec_bwd_kernel(const RecBwdParams p) {
+    using G = Geo<D, SPLIT>;
+    using SM = RecBwdSmem<D>;
+    const G g;
+    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
+    extern __shared__ __align__(16) float smem[];
+    using Stage = RecBwdStage<D, TC>;
+    for (int i = g.tid; i < 2 * Stage::kFloats + 2 * SM::kXs + SM::kR; i += G::NT) smem[i] = 0.f;
+    float* xch = smem + 2 * Stage::kFloats;
+    float* rmem = xch + 2 * SM::kXs;       // R rows: [3][D][kRS], then rb[D]
+    __syncthreads();
+    for (int i = g.tid; i < p.D * p.D; i += G::NT) {
+        const int e = i / p.D, m = i - e * p.D;
+        const long long src = h * p.rH + (long long)e * p.rE + m;
+        rmem[0 * D * SM::kRS + e * SM::kRS + m] = p.Rq[src];
+        rmem[1 * D * SM::kRS + e * SM::kRS + m] = p.Rk[src];
+        rmem[2 * D * SM::kRS + e * SM::kRS + m] = p.Rv[src];
+    }
+    for (int i = g.tid; i < p.D; i += G::NT) rmem[3 * D * SM::kRS + i] = p.rb[h * p.rbH + i];
+
+    Src<float> sq, sk, sv, so, sd, sg, sb;
+    sq.init(p.q, n, h, p.D);
+    sk.init(p.k, n, h, p.D);
+    sv.init(p.v, n, h, p.D);
+    so.init(p.v_old, n, h, p.D);
+    sd.init(p.od, n, h, p.D);
+    sg.init(p.gy, n, h, p.D);
+    sb.init(p.beta, n, h, 1);
+
+    float2 Sr[G::NP], Gr[G::NP], Gc[G::NP], aq[G::NP], ak[G::NP], av[G::NP];
+    load_rows(g, Sr, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
+#pragma unroll
+    for (int i = 0; i < G::NP; i++) {
+        Gr[i] = Gc[i] = aq[i] = ak[i] = av[i] = make_float2(0.f, 0.f);
+    }
+    float gh = 0.f, arb = 0.f;
+    const bool ok = g.idx < p.D;
+    __syncthreads();
+
+    const int nchunks = (p.L + TC - 1) / TC;
+    auto issue = [&](int j) {
+        Stage s; s.bind(smem + (j & 1) * Stage::kFloats);
+        const int c = nchunks - 1 - j;
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        s.q.load(sq, t0, nt, g.tid, G::NT);
+        s.k.load(sk, t0, nt, g.tid, G::NT);
+        s.v.load(sv, t0, nt, g.tid, G::NT);
+        s.vo.load(so, t0, nt, g.tid, G::NT);
+        s.od.load(sd, t0, nt, g.tid, G::NT);
+        s.gy.load(sg, t0, nt, g.tid, G::NT);
+        s.b.load(sb, t0, nt, g.tid, G::NT);
+        cp_async_commit();
+    };
+    issue(0);
+    int par = 0;
+    for (int j = 0; j < nchunks; j++) {
+        if (j + 1 < nchunks) { issue(j + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncthreads();
+        Stage s; s.bind(smem + (j & 1) * Stage::kFloats);
+        const int c = nchunks - 1 - j;
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        for (int t = nt - 1; t >= 0; t--) {
+            float* xg = xch + par * SM::kXs;
+            float* xu = xg + D;
+            float* xbr = xu + D;
+            float* xdq = xbr + D;
+            float* xdk = xdq + D;
+            float* slot = xdk + D;
+            par ^= 1;
+            const int o = t * D + g.idx;
+            const float beta = s.b.f[t];
+            const float gcol = s.gy.f[o] + gh;
+            float dv, dbh;
+            // ---- column role
+            {
+                float2 qq[G::NP], kk[G::NP];
+                lds_slice<G::NR>(qq, s.q.f + t * D + g.off);
+                lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
+                const float w = s.v.f[o] - s.vo.f[o];
+                axpy2<G::NP>(Gc, qq, gcol);
+                const float r = reduce_split<SPLIT>(dot2<G::NP>(Gc, kk));
+                dv = beta * r;
+                axpy2<G::NP>(Gc, kk, -dv);
+                if (g.s == 0) { xg[g.idx] = gcol; xu[g.idx] = beta * w; xbr[g.idx] = dv; }
+                const float db = cta_allreduce_idx<G, false>(g, r * w, slot);
+                dbh = db * beta * (1.f - beta);
+            }
+            cta_sync<G::WPS>();
+            // ---- row role: the delta block, then the two softmax backward maps
+            float dqh, dkh;
+            const float qe = s.q.f[o], ke = s.k.f[o], hte = s.od.f[o];
+            {
+                float2 gr[G::NP], ur[G::NP], brr[G::NP];
+                lds_slice<G::NR>(gr, xg + g.off);
+                lds_slice<G::NR>(ur, xu + g.off);
+                lds_slice<G::NR>(brr, xbr + g.off);
+                float dq = dot2<G::NP>(Sr, gr);
+                axpy2<G::NP>(Gr, gr, qe);
+                float dk = dot2<G::NP>(Gr, ur);
+                axpy2<G::NP>(Sr, ur, -ke);
+                dk -= dot2<G::NP>(Sr, brr);
+                axpy2<G::NP>(Gr, brr, -ke);
+                dq = reduce_split<SPLIT>(dq);
+                dk = reduce_split<SPLIT>(dk);
+                const float cq = cta_allreduce_idx<G, false>(g, qe * dq, slot + 8);
+                const float ck = cta_allreduce_idx<G, false>(g, ke * dk, slot + 16);
+                dqh = qe * (dq - cq);
+                dkh = ke * (dk - ck);
+            }
+            if (g.s == 0) {
+                xdq[g.idx] = dqh;
+                xdk[g.idx] = dkh;
+                if (ok) {
+                    const int tt = t0 + t;
+                    put<float>(p.gq, n, h, tt, g.idx, dqh);
+                    put<float>(p.gk, n, h, tt, g.idx, dkh);
+                    put<float>(p.gv, n, h, tt, g.idx, dv);
+                    if (g.idx == 0) put<float>(p.gb, n, h, tt, 0, dbh);
+                }
+            }
+            cta_sync<G::WPS>();
+            // ---- feedback gradient (row role over R) and parameter gradients (column role)
+            {
+                float2 dqs[G::NP], dks[G::NP], dvs[G::NP], rr[G::NP];
+                lds_slice<G::NR>(dqs, xdq + g.off);
+                lds_slice<G::NR>(dks, xdk + g.off);
+                lds_slice<G::NR>(dvs, xbr + g.off);
+                const float* rrow = rmem + g.idx * SM::kRS + g.off;
+                lds_slice<G::NR>(rr, rrow);
+                float back = dot2<G::NP>(rr, dqs);
+                lds_slice<G::NR>(rr, rrow + D * SM::kRS);
+                back += dot2<G::NP>(rr, dks);
+                lds_slice<G::NR>(rr, rrow + 2 * D * SM::kRS);
+                back += dot2<G::NP>(rr, dvs);
+                back = reduce_split<SPLIT>(back) + rmem[3 * D * SM::kRS + g.idx] * dbh;
+                gh = (1.f - hte * hte) * back;
+                float2 hs[G::NP];
+                lds_slice<G::NR>(hs, s.od.f + t * D + g.off);
+                axpy2<G::NP>(aq, hs, dqh);
+                axpy2<G::NP>(ak, hs, dkh);
+                axpy2<G::NP>(av, hs, dv);
+                arb += hte * dbh;
+            }
+        }
+        __syncthreads();
+    }
+    store_rows(g, Sr, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
+    // partial parameter gradients of this (n, h): [3][d][d] then [d]
+    float* out = p.scratch + (long long)blockIdx.x * (3 * p.D * p.D + p.D);
+    store_cols(g, aq, out, p.D, p.D, p.D);
+    store_cols(g, ak, out + p.D * p.D, p.D, p.D, p.D);
+    store_cols(g, av, out + 2 * p.D * p.D, p.D, p.D, p.D);
+    if (ok && g.s == 0) out[3 * p.D * p.D + g.idx] = arb;
+}
+
+// sum the per-(n,h) partials over n in index order: one thread per (h, element)
+__global__ void rec_param_reduce_kernel(const float* __restrict__ scratch, int N, int H, int D,
+                                        float* gRq, float* gRk, float* gRv, float* grb,
+                                        long long rH, long long rE, long long rbH) {
+    const int per = 3 * D * D + D;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H * per) return;
+    const int h = i / per, j = i - h * per;
+    float acc = 0.f;
+    for (int n = 0; n < N; n++) acc += scratch[((long long)n * H + h) * per + j];
+    if (j < 3 * D * D) {
+        const int which = j / (D * D), r = j - which * D * D, e = r / D, m = r - e * D;
+        float* dst = which == 0 ? gRq : (which == 1 ? gRk : gRv);
+        dst[h * rH + (long long)e * rE + m] = acc;
+    } else {
+        grb[h * rbH + (j - 3 * D * D)] = acc;
+    }
+}
+
+// ------------------------------------------------------------------ launchers
+template <typename K>
+static int smem_optin(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return set_cuda_error(e);
+    }
+    return FWP_OK;
+}
+
+template <int D, int SPLIT, int TC>
+static int launch_rec_fwd(const RecFwdParams& p, int nseq, cudaStream_t st) {
+    auto kern = rec_fwd_kernel<D, SPLIT, TC>;
+    const size_t bytes = (2 * RecFwdStage<D, TC>::kFloats + 2 * (3 * D + 32)) * sizeof(float);
+    if (int rc = smem_optin(kern, bytes)) return rc;
+    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+template <int D, int SPLIT, int TC>
+static int launch_rec_bwd(const RecBwdParams& p, int nseq, cudaStream_t st) {
+    auto kern = rec_bwd_kernel<D, SPLIT, TC>;
+    const size_t bytes = (2 * RecBwdStage<D, TC>::kFloats + 2 * RecBwdSmem<D>::kXs + RecBwdSmem<D>::kR) * sizeof(float);
+    if (int rc = smem_optin(kern, bytes)) return rc;
+    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+static int check_params(const fwp_tensor* Rq, const fwp_tensor* Rk, const fwp_tensor* Rv, const fwp_tensor* rb) {
+    int rc;
+    if ((rc = check_tensor(Rq, 4, true)) || (rc = check_tensor(Rk, 4, true)) || (rc = check_tensor(Rv, 4, true)) ||
+        (rc = check_tensor(rb, 4, true)))
+        return rc;
+    // one kernel-side stride set serves the three matrices
+    for (int i = 1; i < 3; i++)
+        if (Rk->stride[i] != Rq->stride[i] || Rv->stride[i] != Rq->stride[i]) return FWP_ERR_STRIDE;
+    return FWP_OK;
+}
+
+}  // namespace fwp
+
+using namespace fwp;
+
+FWP_API int64_t fwp_rec_update_fwm_tanh_scratch_floats(int N, int H, int D) {
+    if (N <= 0 || H <= 0 || D <= 0) return 0;
+    return (int64_t)N * H * (3LL * D * D + D);
+}
+
+FWP_API int fwp_rec_update_fwm_tanh_forward(int N, int H, int L, int D,
+                                            const fwp_tensor* qx, const fwp_tensor* kx,
+                                            const fwp_tensor* vx, const fwp_tensor* bx,
+                                            const fwp_tensor* Rq, const fwp_tensor* Rk,
+                                            const fwp_tensor* Rv, const fwp_tensor* rb,
+                                            const fwp_tensor* q_out, const fwp_tensor* k_out,
+                                            const fwp_tensor* v_out, const fwp_tensor* beta_out,
+                                            const fwp_tensor* v_old, const fwp_tensor* states,
+                                            const fwp_tensor* kv, const fwp_tensor* out,
+                                            int io_dtype, void* stream, int device) {
+    if (N <= 0 || H <= 0 || L <= 0 || D <= 0) return FWP_ERR_SHAPE;
+    if (io_dtype != FWP_F32) return FWP_ERR_DTYPE;
+    const int DP = pad_dim(D);
+    if (!DP) return FWP_ERR_UNSUPPORTED;
+    int rc;
+    if ((rc = check_tensor(qx, 4, true)) || (rc = check_tensor(kx, 4, true)) || (rc = check_tensor(vx, 4, true)) ||
+        (rc = check_tensor(bx, 4, true)) || (rc = check_params(Rq, Rk, Rv, rb)) ||
+        (rc = check_tensor(q_out, 4, true)) || (rc = check_tensor(k_out, 4, true)) ||
+        (rc = check_tensor(v_out, 4, true)) || (rc = check_tensor(beta_out, 4, true)) ||
+        (rc = check_tensor(v_old, 4, true)) || (rc = check_tensor(states, 4, true)) ||
+        (rc = check_tensor(kv, 4, true)) || (rc = check_tensor(out, 4, true)))
+        return rc;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    RecFwdParams p;
+    p.qx = row4(qx); p.kx = row4(kx); p.vx = row4(vx); p.bx = row4(bx);
+    p.q_out = row4(q_out); p.k_out = row4(k_out); p.v_out = row4(v_out); p.b_out = row4(beta_out);
+    p.v_old = row4(v_old); p.out = row4(out);
+    p.Rq = (const float*)Rq->data; p.Rk = (const float*)Rk->data; p.Rv = (const float*)Rv->data;
+    p.rb = (const float*)rb->data;
+    p.rH = Rq->stride[1]; p.rE = Rq->stride[2]; p.rbH = rb->stride[1];
+    p.W = (float*)kv->data; p.wN = kv->stride[0]; p.wH = kv->stride[1]; p.wE = kv->stride[2];
+    p.h = (float*)states->data; p.hN = states->stride[0]; p.hH = states->stride[1];
+    p.H = H; p.L = L; p.D = D;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (DP) {
+        case 16: return launch_rec_fwd<16, 2, 32>(p, N * H, st);
+        case 32: return launch_rec_fwd<32, 2, 16>(p, N * H, st);
+        case 64: return launch_rec_fwd<64, 4, 8>(p, N * H, st);
+    }
+    return FWP_ERR_UNSUPPORTED;
+}
+
+FWP_API int fwp_rec_update_fwm_tanh_backward(int N, int H, int L, int D,
+                                             const fwp_tensor* q, const fwp_tensor* k,
+                                             const fwp_tensor* v, const fwp_tensor* beta,
+                                             const fwp_tensor* v_old, const fwp_tensor* o_delayed,
+                                             const fwp_tensor* grad_out,
+                                             const fwp_tensor* Rq, const fwp_tensor* Rk,
+                                             const fwp_tensor* Rv, const fwp_tensor* rb,
+                                             const fwp_tensor* fw_mem,
+                                             const fwp_tensor* grad_q, const fwp_tensor* grad_k,
+                                             const fwp_tensor* grad_v, const fwp_tensor* grad_beta,
+                                             const fwp_tensor* grad_Rq, const fwp_tensor* grad_Rk,
+                                             const fwp_tensor* grad_Rv, const fwp_tensor* grad_rb,
+                                             float* scratch, int64_t scratch_floats,
+                                             int io_dtype, void* stream, int device) {
+    if (N <= 0 || H <= 0 || L <= 0 || D <= 0) return FWP_ERR_SHAPE;
+    if (io_dtype != FWP_F32) return FWP_ERR_DTYPE;
+    const int DP = pad_dim(D);
+    if (!DP) return FWP_ERR_UNSUPPORTED;
+    int rc;
+    if ((rc = check_tensor(q, 4, true)) || (rc = check_tensor(k, 4, true)) || (rc = check_tensor(v, 4, true)) ||
+        (rc = check_tensor(beta, 4, true)) || (rc = check_tensor(v_old, 4, true)) ||
+        (rc = check_tensor(o_delayed, 4, true)) || (rc = check_tensor(grad_out, 4, true)) ||
+        (rc = check_params(Rq, Rk, Rv, rb)) || (rc = check_tensor(fw_mem, 4, true)) ||
+        (rc = check_tensor(grad_q, 4, true)) || (rc = check_tensor(grad_k, 4, true)) ||
+        (rc = check_tensor(grad_v, 4, true)) || (rc = check_tensor(grad_beta, 4, true)) ||
+        (rc = check_params(grad_Rq, grad_Rk, grad_Rv, grad_rb)))
+        return rc;
+    if (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15) ||
+        scratch_floats < fwp_rec_update_fwm_tanh_scratch_floats(N, H, D))
+        return FWP_ERR_SCRATCH;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    RecBwdParams p;
+    p.q = row4(q); p.k = row4(k); p.v = row4(v); p.beta = row4(beta); p.v_old = row4(v_old);
+    p.od = row4(o_delayed); p.gy = row4(grad_out);
+    p.gq = row4(grad_q); p.gk = row4(grad_k); p.gv = row4(grad_v); p.gb = row4(grad_beta);
+    p.Rq = (const float*)Rq->data; p.Rk = (const float*)Rk->data; p.Rv = (const float*)Rv->data;
+    p.rb = (const float*)rb->data;
+    p.rH = Rq->stride[1]; p.rE = Rq->stride[2]; p.rbH = rb->stride[1];
+    p.W = (float*)fw_mem->data; p.wN = fw_mem->stride[0]; p.wH = fw_mem->stride[1]; p.wE = fw_mem->stride[2];
+    p.scratch = scratch;
+    p.H = H; p.L = L; p.D = D;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (DP) {
+        case 16: rc = launch_rec_bwd<16, 2, 16>(p, N * H, st); break;
+        case 32: rc = launch_rec_bwd<32, 4, 8>(p, N * H, st); break;
+        case 64: rc = launch_rec_bwd<64, 4, 4>(p, N * H, st); break;
+        default: rc = FWP_ERR_UNSUPPORTED;
+    }
+    if (rc) return rc;
+    const int total = H * (3 * D * D + D);
+    rec_param_reduce_kernel<<<(total + 255) / 256, 256, 0, st>>>(
+        scratch, N, H, D, (float*)grad_Rq->data, (float*)grad_Rk->data, (float*)grad_Rv->data,
+        (float*)grad_rb->data, grad_Rq->stride[1], grad_Rq->stride[2], grad_rb->stride[1]);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}

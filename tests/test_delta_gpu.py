@@ -16,7 +16,7 @@ DEV = 'cuda:0'
 
 
 def run_cuda(fwp, q, k, v, b, W, gy):
-    leaves = [t.to(DEV).requires_grad_() for t in (q, k, v, b)]
+    leaves = [t.detach().to(DEV).requires_grad_() for t in (q, k, v, b)]
     y = fwp.fast_weight_delta(*leaves, W)
     W_end = W.clone()
     y.backward(gy.to(DEV))
@@ -24,7 +24,7 @@ def run_cuda(fwp, q, k, v, b, W, gy):
 
 
 def run_loop(q, k, v, b, W0, gy, dtype):
-    leaves = [t.to(dtype).requires_grad_() for t in (q, k, v, b)]
+    leaves = [t.detach().to(dtype).clone().requires_grad_() for t in (q, k, v, b)]
     y, S = loops.delta_rule(*leaves, W0.to(dtype))
     (y * gy.to(dtype)).sum().backward()
     return y.detach(), [l.grad for l in leaves], S.detach()
