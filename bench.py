@@ -273,6 +273,12 @@ def run_gpu_arm(args):
     def flush():
         flush_buf.zero_()
 
+    if args.kernels_only:
+        tf, tb, tf_min, tb_min = time_kernels(ds, flush, reps=max(3, args.steps))
+        print(json.dumps({'workload': args.workload, 'fwd_us': tf * 1e6, 'bwd_us': tb * 1e6,
+                          'fwd_min_us': tf_min * 1e6, 'bwd_min_us': tb_min * 1e6}), flush=True)
+        return
+
     # ---- the step, captured in a CUDA graph (launch gaps would otherwise dominate microsecond kernels)
     use_graph = not args.no_graph
     graph = None
@@ -424,6 +430,9 @@ def main():
     ap.add_argument('--workload', default='lm', choices=sorted(WORKLOADS))
     ap.add_argument('--no-graph', action='store_true')
     ap.add_argument('--skip-cpu', action='store_true')
+    ap.add_argument('--kernels-only', action='store_true',
+                    help='run the forward and backward kernels a few times and print their device times '
+                         '(the command the ncu captures under profiles/ use)')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference_arm(args)

@@ -304,5 +304,104 @@ __device__ __forceinline__ void put(const Row4& r, int n, int h, int t, int c, f
     reinterpret_cast<T*>(r.p)[n * r.sN + h * r.sH + (long long)t * r.sL + c] = from_f32<T>(x);
 }
 
+
+// Flush rows [0, nt) of an fp32 shared-memory tile (row length D, first `width`
+// columns valid) to rows [t0, t0+nt) of a streamed output of element type T.
+// 16-byte stores when the destination rows allow it, element stores otherwise.
+template <int D, typename T>
+__device__ __forceinline__ void flush_rows(const float* tile, const Row4& r, int n, int h, int t0, int nt,
+                                           int width, int tid, int nthreads) {
+    T* base = reinterpret_cast<T*>(r.p) + n * r.sN + h * r.sH + (long long)t0 * r.sL;
+    constexpr int per16 = 16 / (int)sizeof(T);
+    const bool vec = (width % per16 == 0) && ((reinterpret_cast<uintptr_t>(base) & 15) == 0) && (r.sL % per16 == 0);
+    if (vec) {
+        const int ppr = width / per16;
+        for (int i = tid; i < nt * ppr; i += nthreads) {
+            const int row = i / ppr, c = (i - row * ppr) * per16;
+            const float* src = tile + row * D + c;
+            T* dst = base + (long long)row * r.sL + c;
+            if constexpr (sizeof(T) == 4) {
+                *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+            } else {
+                const float4 a = *reinterpret_cast<const float4*>(src);
+                const float4 b = *reinterpret_cast<const float4*>(src + 4);
+                __nv_bfloat162 o[4];
+                o[0] = __floats2bfloat162_rn(a.x, a.y);
+                o[1] = __floats2bfloat162_rn(a.z, a.w);
+                o[2] = __floats2bfloat162_rn(b.x, b.y);
+                o[3] = __floats2bfloat162_rn(b.z, b.w);
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+            }
+        }
+    } else {
+        for (int i = tid; i < nt * width; i += nthreads) {
+            const int row = i / width, c = i - row * width;
+            base[(long long)row * r.sL + c] = from_f32<T>(tile[row * D + c]);
+        }
+    }
+}
+
+// Gram scalars of one group of four consecutive steps, in time order within the group:
+//   slot b(b-1)/2 + a      : k_a . k_b   for a <  b   (6 values)
+//   slot 6 + b(b+1)/2 + a  : k_a . q_b   for a <= b   (10 values)
+__host__ __device__ constexpr int gram_kk(int a, int b) { return b * (b - 1) / 2 + a; }
+__host__ __device__ constexpr int gram_kq(int a, int b) { return 6 + b * (b + 1) / 2 + a; }
+
+// Fill gram[g][16] for groups g < ng from the fp32 k and q tiles (rows 4g..4g+3).
+template <int D>
+__device__ __forceinline__ void gram_phase(const float* ktile, const float* qtile, float* gram, int ng,
+                                           int tid, int nthreads) {
+    constexpr unsigned IA = 0u | (0u << 2) | (1u << 4) | (0u << 6) | (1u << 8) | (2u << 10) |
+                            (0u << 12) | (0u << 14) | (1u << 16) | (0u << 18) | (1u << 20) | (2u << 22) |
+                            (0u << 24) | (1u << 26) | (2u << 28) | (3u << 30);
+    constexpr unsigned IB = 1u | (2u << 2) | (2u << 4) | (3u << 6) | (3u << 8) | (3u << 10) |
+                            (0u << 12) | (1u << 14) | (1u << 16) | (2u << 18) | (2u << 20) | (2u << 22) |
+                            (3u << 24) | (3u << 26) | (3u << 28) | (3u << 30);
+    for (int w = tid; w < ng * 16; w += nthreads) {
+        const int gi = w >> 4, pidx = w & 15;
+        const int a = (IA >> (2 * pidx)) & 3, b = (IB >> (2 * pidx)) & 3;
+        const float* x = ktile + (4 * gi + a) * D;
+        const float* y = (pidx < 6 ? ktile : qtile) + (4 * gi + b) * D;
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < D / 4; i++) {
+            const float4 xa = *reinterpret_cast<const float4*>(x + 4 * i);
+            const float4 ya = *reinterpret_cast<const float4*>(y + 4 * i);
+            acc0 = ffma2(make_float2(xa.x, xa.y), make_float2(ya.x, ya.y), acc0);
+            acc1 = ffma2(make_float2(xa.z, xa.w), make_float2(ya.z, ya.w), acc1);
+        }
+        gram[w] = (acc0.x + acc1.x) + (acc0.y + acc1.y);
+    }
+}
+
+// Sum four per-thread values over the idx lanes of a warp with a halving butterfly
+// (5-6 shuffles instead of 16-20).  Afterwards, within each group of MC lanes, the
+// lane whose (lane % MC) == j * sum4_stride<SPLIT>() holds the total of value j.
+template <int SPLIT>
+__host__ __device__ constexpr int sum4_stride() { return ((32 / SPLIT) >= 16 ? 16 : (32 / SPLIT)) / 4; }
+template <int SPLIT>
+__device__ __forceinline__ float warp_sum4_idx(float p0, float p1, float p2, float p3, int lane) {
+    constexpr int MC = 32 / SPLIT;
+    if constexpr (MC == 32) {   // fold the top level first so that 16 lanes remain
+        p0 += __shfl_xor_sync(0xffffffffu, p0, 16);
+        p1 += __shfl_xor_sync(0xffffffffu, p1, 16);
+        p2 += __shfl_xor_sync(0xffffffffu, p2, 16);
+        p3 += __shfl_xor_sync(0xffffffffu, p3, 16);
+    }
+    constexpr int H1 = (MC >= 16 ? 16 : MC) / 2;   // 8 (or 4 when MC == 8)
+    constexpr int H2 = H1 / 2;
+    const bool hi1 = lane & H1;
+    float k0 = hi1 ? p2 : p0, s0 = hi1 ? p0 : p2;
+    float k1 = hi1 ? p3 : p1, s1 = hi1 ? p1 : p3;
+    k0 += __shfl_xor_sync(0xffffffffu, s0, H1);
+    k1 += __shfl_xor_sync(0xffffffffu, s1, H1);
+    const bool hi2 = lane & H2;
+    float k = hi2 ? k1 : k0, sx = hi2 ? k0 : k1;
+    k += __shfl_xor_sync(0xffffffffu, sx, H2);
+#pragma unroll
+    for (int o = H2 / 2; o >= 1; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
+    return k;
+}
+
 #endif  // __CUDACC__
 }  // namespace fwp

@@ -33,7 +33,7 @@ struct FwdStage {
 
 // SUM = true drops beta / v_old (sum rule): S_t = S_{t-1} + k_t (x) v_t.
 template <int D, int SPLIT, int TC, typename T, bool SUM>
-__global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT) delta_fwd_step_kernel(const DeltaFwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
     const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
@@ -134,7 +134,7 @@ struct BwdStage {
 //   Gc += q (x) gy ; r = Gc^T k ; dv = beta r ; dbeta = r . (v - v_old) ; Gc -= k (x) beta r
 //   dq = S gy ; Gr += q (x) gy ; dk = Gr u ; S -= k (x) u ; dk -= S (beta r) ; Gr -= k (x) beta r
 template <int D, int SPLIT, int TC, typename T>
-__global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT) delta_bwd_step_kernel(const DeltaBwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
     const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
@@ -343,6 +343,12 @@ __global__ void __launch_bounds__(D * SPLIT) sum_bwd_kernel(const SumBwdParams p
     }
 }
 
+}  // namespace fwp
+
+#include "fwp_delta_blocked.cuh"
+
+namespace fwp {
+
 // ------------------------------------------------------------------ launchers
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
@@ -353,59 +359,64 @@ static int set_smem(K kernel, size_t bytes) {
     return FWP_OK;
 }
 
+template <typename K, typename P>
+static int launch(K kern, const P& p, int nseq, int threads, size_t bytes, cudaStream_t st) {
+    if (int rc = set_smem(kern, bytes)) return rc;
+    kern<<<nseq, threads, bytes, st>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
 template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
-    auto kern = delta_fwd_kernel<D, SPLIT, TC, T, SUM>;
-    const size_t bytes = 2 * FwdStage<D, TC, T>::kFloats * sizeof(float);
-    if (int rc = set_smem(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
-    count_launch();
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+    return launch(delta_fwd_kernel<D, SPLIT, TC, T, SUM>, p, nseq, D * SPLIT,
+                  BlkFwdSmem<D, TC, T>::kFloats * sizeof(float), st);
 }
-
 template <int D, int SPLIT, int TC, typename T>
 static int launch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
-    auto kern = delta_bwd_kernel<D, SPLIT, TC, T>;
-    const size_t bytes = (2 * BwdStage<D, TC, T>::kFloats + 2 * (2 * D + 8)) * sizeof(float);
-    if (int rc = set_smem(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
-    count_launch();
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+    return launch(delta_bwd_kernel<D, SPLIT, TC, T>, p, nseq, D * SPLIT,
+                  BlkBwdSmem<D, TC, T>::kFloats * sizeof(float), st);
 }
-
+template <int D, int SPLIT, int TC, typename T, bool SUM>
+static int launch_fwd_step(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
+    return launch(delta_fwd_step_kernel<D, SPLIT, TC, T, SUM>, p, nseq, D * SPLIT,
+                  2 * FwdStage<D, TC, T>::kFloats * sizeof(float), st);
+}
+template <int D, int SPLIT, int TC, typename T>
+static int launch_bwd_step(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
+    return launch(delta_bwd_step_kernel<D, SPLIT, TC, T>, p, nseq, D * SPLIT,
+                  (2 * BwdStage<D, TC, T>::kFloats + 2 * (2 * D + 8)) * sizeof(float), st);
+}
 template <int D, int SPLIT, int TC, typename T>
 static int launch_sum_bwd(const SumBwdParams& p, int nseq, cudaStream_t st) {
-    auto kern = sum_bwd_kernel<D, SPLIT, TC, T>;
-    const size_t bytes = 2 * SumStage<D, TC, T>::kFloats * sizeof(float);
-    if (int rc = set_smem(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
-    count_launch();
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+    return launch(sum_bwd_kernel<D, SPLIT, TC, T>, p, nseq, D * SPLIT,
+                  2 * SumStage<D, TC, T>::kFloats * sizeof(float), st);
 }
 
+// "delta.blocked" = 0 selects the per-step kernels (kept as a cross-check of the blocked form).
 template <typename T, bool SUM>
 static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, const char* op) {
     const int D = pad_dim(p.E > p.M ? p.E : p.M);
     char key[48];
     snprintf(key, sizeof key, "%s.%d.split", op, D);
+    const bool blocked = tune_get("delta.blocked", 1) != 0;
     switch (D) {
         case 16: {
-            int sp = tune_get(key, 2);
-            if (sp == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
+            if (!blocked) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
+            if (tune_get(key, 2) == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
             return launch_fwd<16, 2, 32, T, SUM>(p, nseq, st);
         }
         case 32: {
-            int sp = tune_get(key, 1);
-            if (sp == 2) return launch_fwd<32, 2, 16, T, SUM>(p, nseq, st);
+            if (!blocked) return launch_fwd_step<32, 1, 16, T, SUM>(p, nseq, st);
+            const int sp = tune_get(key, 2);
+            if (sp == 1) return launch_fwd<32, 1, 16, T, SUM>(p, nseq, st);
             if (sp == 4) return launch_fwd<32, 4, 16, T, SUM>(p, nseq, st);
-            return launch_fwd<32, 1, 16, T, SUM>(p, nseq, st);
+            return launch_fwd<32, 2, 16, T, SUM>(p, nseq, st);
         }
         case 64: {
-            int sp = tune_get(key, 2);
-            if (sp == 1) return launch_fwd<64, 1, 8, T, SUM>(p, nseq, st);
+            if (!blocked) return launch_fwd_step<64, 2, 8, T, SUM>(p, nseq, st);
+            const int sp = tune_get(key, 2);
             if (sp == 4) return launch_fwd<64, 4, 8, T, SUM>(p, nseq, st);
             return launch_fwd<64, 2, 8, T, SUM>(p, nseq, st);
         }
@@ -418,21 +429,21 @@ static int dispatch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     const int D = pad_dim(p.E > p.M ? p.E : p.M);
     char key[48];
     snprintf(key, sizeof key, "delta_bwd.%d.split", D);
+    const bool blocked = tune_get("delta.blocked", 1) != 0;
     switch (D) {
         case 16: {
-            int sp = tune_get(key, 2);
-            if (sp == 4) return launch_bwd<16, 4, 16, T>(p, nseq, st);
+            if (!blocked) return launch_bwd_step<16, 2, 16, T>(p, nseq, st);
+            if (tune_get(key, 2) == 4) return launch_bwd<16, 4, 16, T>(p, nseq, st);
             return launch_bwd<16, 2, 16, T>(p, nseq, st);
         }
         case 32: {
-            int sp = tune_get(key, 2);
-            if (sp == 1) return launch_bwd<32, 1, 8, T>(p, nseq, st);
-            if (sp == 4) return launch_bwd<32, 4, 8, T>(p, nseq, st);
+            if (!blocked) return launch_bwd_step<32, 2, 8, T>(p, nseq, st);
+            if (tune_get(key, 2) == 4) return launch_bwd<32, 4, 8, T>(p, nseq, st);
             return launch_bwd<32, 2, 8, T>(p, nseq, st);
         }
         case 64: {
-            int sp = tune_get(key, 4);
-            if (sp == 2) return launch_bwd<64, 2, 4, T>(p, nseq, st);
+            if (!blocked) return launch_bwd_step<64, 4, 4, T>(p, nseq, st);
+            if (tune_get(key, 4) == 2) return launch_bwd<64, 2, 4, T>(p, nseq, st);
             return launch_bwd<64, 4, 4, T>(p, nseq, st);
         }
     }

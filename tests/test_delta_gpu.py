@@ -170,3 +170,27 @@ def test_unsupported_head_dim_is_an_error_not_a_fallback(fwp):
     q = torch.rand(1, 1, 4, 128, device=DEV)
     with pytest.raises(RuntimeError, match='head dimension'):
         fwp.fast_weight_delta(q, q, q, torch.rand(1, 1, 4, 1, device=DEV), torch.zeros(1, 1, 128, 128, device=DEV))
+
+
+@pytest.mark.parametrize('B,H,L,d', [(2, 2, 37, 16), (1, 2, 21, 32), (1, 1, 13, 64)])
+def test_per_step_kernels_agree_with_blocked_form(fwp, B, H, L, d):
+    """The four-step blocked kernels (default) and the per-step kernels are two execution plans
+    of the same recurrence; both must meet the oracle tolerance and agree with each other."""
+    from recurrent_fwp_b200 import _lib
+    q, k, v, b, gy = util.delta_inputs(51, B, H, L, d)
+    W0 = torch.randn(B, H, d, d, generator=util.gen(52)) * 0.1
+    res = {}
+    try:
+        for blocked in (1, 0):
+            _lib.tune('delta.blocked', blocked)
+            W = W0.to(DEV)
+            res[blocked] = run_cuda(fwp, q, k, v, b, W, gy)
+    finally:
+        _lib.tune('delta.blocked', 1)
+    y64, g64, _ = run_loop(q, k, v, b, W0, gy, torch.float64)
+    for blocked in (1, 0):
+        y, grads, _ = res[blocked]
+        assert util.max_abs(y, y64) <= 1e-4
+        for g, r in zip(grads, g64):
+            assert util.scaled_rel(g, r) <= 1e-3
+    assert util.max_abs(res[1][0], res[0][0]) <= 1e-5
