@@ -72,7 +72,34 @@ static inline int pad_dim(int d) { return d <= 16 ? 16 : (d <= 32 ? 32 : (d <= 6
 // ---------------------------------------------------------------- device side
 #ifdef __CUDACC__
 
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+// Two fp32 values packed in one 64-bit register.  Everything that lives across
+// time steps (the matrices, operand slices, dot-product accumulators) stays in
+// this form, so the packed FMA needs no pack/unpack moves around it.
+typedef unsigned long long f2;
+
+__device__ __forceinline__ f2 f2_pack(float lo, float hi) {
+    f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(f2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ float f2_hsum(f2 v) {
+    float lo, hi;
+    f2_unpack(v, lo, hi);
+    return lo + hi;
+}
+__device__ __forceinline__ f2 ffma2(f2 a, f2 b, f2 c) {
+    f2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f2 fadd2(f2 a, f2 b) {
+    f2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
@@ -149,30 +176,38 @@ __device__ __forceinline__ float cta_allreduce_idx(const G& g, float x, float* s
 
 // slice of a shared-memory row -> packed registers (row must be 16-byte aligned)
 template <int NR>
-__device__ __forceinline__ void lds_slice(float2 (&d)[NR / 2], const float* p) {
+__device__ __forceinline__ void lds_slice(f2 (&d)[NR / 2], const float* p) {
 #pragma unroll
     for (int i = 0; i < NR / 4; i++) {
-        float4 t = *reinterpret_cast<const float4*>(p + 4 * i);
-        d[2 * i] = make_float2(t.x, t.y);
-        d[2 * i + 1] = make_float2(t.z, t.w);
+        const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(p + 4 * i);
+        d[2 * i] = t.x;
+        d[2 * i + 1] = t.y;
     }
 }
 
 template <int NP>
-__device__ __forceinline__ float dot2(const float2 (&a)[NP], const float2 (&b)[NP]) {
-    float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+__device__ __forceinline__ float dot2(const f2 (&a)[NP], const f2 (&b)[NP]) {
+    f2 acc0 = 0ull, acc1 = 0ull;
 #pragma unroll
     for (int i = 0; i < NP; i += 2) {
         acc0 = ffma2(a[i], b[i], acc0);
         if (i + 1 < NP) acc1 = ffma2(a[i + 1], b[i + 1], acc1);
     }
-    return (acc0.x + acc1.x) + (acc0.y + acc1.y);
+    return f2_hsum(NP > 1 ? fadd2(acc0, acc1) : acc0);
+}
+// same with one accumulator chain: fewer instructions, for places with many independent dots
+template <int NP>
+__device__ __forceinline__ float dot2_chain(const f2 (&a)[NP], const f2 (&b)[NP]) {
+    f2 acc = 0ull;
+#pragma unroll
+    for (int i = 0; i < NP; i++) acc = ffma2(a[i], b[i], acc);
+    return f2_hsum(acc);
 }
 
 // A += x * a  (a scalar)
 template <int NP>
-__device__ __forceinline__ void axpy2(float2 (&A)[NP], const float2 (&x)[NP], float a) {
-    const float2 aa = make_float2(a, a);
+__device__ __forceinline__ void axpy2(f2 (&A)[NP], const f2 (&x)[NP], float a) {
+    const f2 aa = f2_pack(a, a);
 #pragma unroll
     for (int i = 0; i < NP; i++) A[i] = ffma2(x[i], aa, A[i]);
 }
@@ -180,37 +215,45 @@ __device__ __forceinline__ void axpy2(float2 (&A)[NP], const float2 (&x)[NP], fl
 // ---- fast-weight matrix <-> registers.  Column role: thread holds
 // S[off..off+NR, idx]; row role: thread holds S[idx, off..off+NR].
 template <class G>
-__device__ __forceinline__ void load_cols(const G& g, float2 (&S)[G::NP], const float* W, long long sE, int E, int M) {
+__device__ __forceinline__ void load_cols(const G& g, f2 (&S)[G::NP], const float* W, long long sE, int E, int M) {
+    float v[2];
 #pragma unroll
     for (int i = 0; i < G::NR; i++) {
         int e = g.off + i;
         float x = (e < E && g.idx < M) ? W[(long long)e * sE + g.idx] : 0.f;
-        if (i & 1) S[i >> 1].y = x; else S[i >> 1].x = x;
+        v[i & 1] = x;
+        if (i & 1) S[i >> 1] = f2_pack(v[0], v[1]);
     }
 }
 template <class G>
-__device__ __forceinline__ void store_cols(const G& g, const float2 (&S)[G::NP], float* W, long long sE, int E, int M) {
+__device__ __forceinline__ void store_cols(const G& g, const f2 (&S)[G::NP], float* W, long long sE, int E, int M) {
 #pragma unroll
     for (int i = 0; i < G::NR; i++) {
         int e = g.off + i;
-        if (e < E && g.idx < M) W[(long long)e * sE + g.idx] = (i & 1) ? S[i >> 1].y : S[i >> 1].x;
+        float lo, hi;
+        f2_unpack(S[i >> 1], lo, hi);
+        if (e < E && g.idx < M) W[(long long)e * sE + g.idx] = (i & 1) ? hi : lo;
     }
 }
 template <class G>
-__device__ __forceinline__ void load_rows(const G& g, float2 (&S)[G::NP], const float* W, long long sE, int E, int M) {
+__device__ __forceinline__ void load_rows(const G& g, f2 (&S)[G::NP], const float* W, long long sE, int E, int M) {
+    float v[2];
 #pragma unroll
     for (int i = 0; i < G::NR; i++) {
         int m = g.off + i;
         float x = (g.idx < E && m < M) ? W[(long long)g.idx * sE + m] : 0.f;
-        if (i & 1) S[i >> 1].y = x; else S[i >> 1].x = x;
+        v[i & 1] = x;
+        if (i & 1) S[i >> 1] = f2_pack(v[0], v[1]);
     }
 }
 template <class G>
-__device__ __forceinline__ void store_rows(const G& g, const float2 (&S)[G::NP], float* W, long long sE, int E, int M) {
+__device__ __forceinline__ void store_rows(const G& g, const f2 (&S)[G::NP], float* W, long long sE, int E, int M) {
 #pragma unroll
     for (int i = 0; i < G::NR; i++) {
         int m = g.off + i;
-        if (g.idx < E && m < M) W[(long long)g.idx * sE + m] = (i & 1) ? S[i >> 1].y : S[i >> 1].x;
+        float lo, hi;
+        f2_unpack(S[i >> 1], lo, hi);
+        if (g.idx < E && m < M) W[(long long)g.idx * sE + m] = (i & 1) ? hi : lo;
     }
 }
 
@@ -362,15 +405,15 @@ __device__ __forceinline__ void gram_phase(const float* ktile, const float* qtil
         const int a = (IA >> (2 * pidx)) & 3, b = (IB >> (2 * pidx)) & 3;
         const float* x = ktile + (4 * gi + a) * D;
         const float* y = (pidx < 6 ? ktile : qtile) + (4 * gi + b) * D;
-        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+        f2 acc0 = 0ull, acc1 = 0ull;
 #pragma unroll
         for (int i = 0; i < D / 4; i++) {
-            const float4 xa = *reinterpret_cast<const float4*>(x + 4 * i);
-            const float4 ya = *reinterpret_cast<const float4*>(y + 4 * i);
-            acc0 = ffma2(make_float2(xa.x, xa.y), make_float2(ya.x, ya.y), acc0);
-            acc1 = ffma2(make_float2(xa.z, xa.w), make_float2(ya.z, ya.w), acc1);
+            const ulonglong2 xa = *reinterpret_cast<const ulonglong2*>(x + 4 * i);
+            const ulonglong2 ya = *reinterpret_cast<const ulonglong2*>(y + 4 * i);
+            acc0 = ffma2(xa.x, ya.x, acc0);
+            acc1 = ffma2(xa.y, ya.y, acc1);
         }
-        gram[w] = (acc0.x + acc1.x) + (acc0.y + acc1.y);
+        gram[w] = f2_hsum(fadd2(acc0, acc1));
     }
 }
 

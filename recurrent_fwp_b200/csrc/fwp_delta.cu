@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_step_kernel(const DeltaFw
     if (!SUM) sb.init(p.beta, n, h, 1);
 
     float* W = p.W + n * p.wN + h * p.wH;
-    float2 S[G::NP];
+    f2 S[G::NP];
     load_cols(g, S, W, p.wE, p.E, p.M);
     __syncthreads();   // zero-fill done before any copy lands
 
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_step_kernel(const DeltaFw
         }
 #pragma unroll 2
         for (int t = 0; t < nt; t++) {
-            float2 kk[G::NP], qq[G::NP];
+            f2 kk[G::NP], qq[G::NP];
             lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
             lds_slice<G::NR>(qq, s.q.f + t * D + g.off);
             const float vv = s.v.f[t * D + g.idx];
@@ -154,10 +154,10 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_step_kernel(const DeltaBw
     sb.init(p.beta, n, h, 1);
 
     float* W = p.W + n * p.wN + h * p.wH;
-    float2 Sr[G::NP], Gr[G::NP], Gc[G::NP];
+    f2 Sr[G::NP], Gr[G::NP], Gc[G::NP];
     load_rows(g, Sr, W, p.wE, p.E, p.M);
 #pragma unroll
-    for (int i = 0; i < G::NP; i++) { Gr[i] = make_float2(0.f, 0.f); Gc[i] = make_float2(0.f, 0.f); }
+    for (int i = 0; i < G::NP; i++) { Gr[i] = 0ull; Gc[i] = 0ull; }
     __syncthreads();
 
     const int nchunks = (p.L + TC - 1) / TC;
@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_step_kernel(const DeltaBw
             const float beta = s.b.f[t];
             // ---- column role
             {
-                float2 kk[G::NP], qq[G::NP];
+                f2 kk[G::NP], qq[G::NP];
                 lds_slice<G::NR>(qq, s.q.f + t * D + g.off);
                 lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
                 const float gym = s.gy.f[t * D + g.idx];
@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_step_kernel(const DeltaBw
             cta_sync<G::WPS>();
             // ---- row role
             {
-                float2 gr[G::NP], ur[G::NP], brr[G::NP];
+                f2 gr[G::NP], ur[G::NP], brr[G::NP];
                 lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
                 lds_slice<G::NR>(ur, xu + g.off);
                 lds_slice<G::NR>(brr, xbr + g.off);
@@ -286,9 +286,9 @@ __global__ void __launch_bounds__(D * SPLIT) sum_bwd_kernel(const SumBwdParams p
     const bool col_ok = g.idx < p.M, row_ok = g.idx < p.E;
     // phase 0: forwards, S row role, dq.  phase 1: backwards, G in both roles, dk and dv.
     for (int phase = 0; phase < 2; phase++) {
-        float2 A[G::NP], B[G::NP];
+        f2 A[G::NP], B[G::NP];
 #pragma unroll
-        for (int i = 0; i < G::NP; i++) { A[i] = make_float2(0.f, 0.f); B[i] = make_float2(0.f, 0.f); }
+        for (int i = 0; i < G::NP; i++) { A[i] = 0ull; B[i] = 0ull; }
         auto issue = [&](int j) {
             Stage s; s.bind(smem + (j & 1) * Stage::kFloats);
             const int c = phase ? nchunks - 1 - j : j;
@@ -316,14 +316,14 @@ __global__ void __launch_bounds__(D * SPLIT) sum_bwd_kernel(const SumBwdParams p
             for (int i = 0; i < nt; i++) {
                 const int t = phase ? nt - 1 - i : i;
                 if (phase == 0) {
-                    float2 vr[G::NP], gr[G::NP];
+                    f2 vr[G::NP], gr[G::NP];
                     lds_slice<G::NR>(vr, s.v.f + t * D + g.off);
                     lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
                     axpy2<G::NP>(A, vr, s.k.f[t * D + g.idx]);
                     const float dq = reduce_split<SPLIT>(dot2<G::NP>(A, gr));
                     if (row_ok && g.s == 0) put<T>(p.gq, n, h, t0 + t, g.idx, dq);
                 } else {
-                    float2 vr[G::NP], gr[G::NP], kk[G::NP], qq[G::NP];
+                    f2 vr[G::NP], gr[G::NP], kk[G::NP], qq[G::NP];
                     lds_slice<G::NR>(vr, s.v.f + t * D + g.off);
                     lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
                     lds_slice<G::NR>(kk, s.k.f + t * D + g.off);

@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
     if (!SUM) sb.init(p.beta, n, h, 1);
 
     float* W = p.W + n * p.wN + h * p.wH;
-    float2 S[G::NP];
+    f2 S[G::NP];
     load_cols(g, S, W, p.wE, p.E, p.M);
     __syncthreads();
 
@@ -113,15 +113,37 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
         for (int gi = 0; gi < ng; gi++) {
             const int tb = 4 * gi;
             float a[4], b[4];
-            float2 kk[KEEP ? 4 : 1][G::NP];
+            f2 kk[KEEP ? 4 : 1][G::NP];
+            if constexpr (G::NR <= 8) {
+                // small slices: fetch all eight operand slices first, then run the eight
+                // dot-product chains interleaved so that no FMA waits on its predecessor
+                f2 qq[4][G::NP];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float2 (&kj)[G::NP] = kk[KEEP ? j : 0];
-                lds_slice<G::NR>(kj, s.k.f + (tb + j) * D + g.off);
-                if constexpr (!SUM) a[j] = dot2<G::NP>(S, kj); else a[j] = 0.f;
-                float2 qq[G::NP];
-                lds_slice<G::NR>(qq, s.q.f + (tb + j) * D + g.off);
-                b[j] = dot2<G::NP>(S, qq);
+                for (int j = 0; j < 4; j++) {
+                    lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                    lds_slice<G::NR>(qq[j], s.q.f + (tb + j) * D + g.off);
+                }
+                f2 aa[4] = {0ull, 0ull, 0ull, 0ull}, bb[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+                for (int i = 0; i < G::NP; i++) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        if constexpr (!SUM) aa[j] = ffma2(S[i], kk[j][i], aa[j]);
+                        bb[j] = ffma2(S[i], qq[j][i], bb[j]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) { a[j] = SUM ? 0.f : f2_hsum(aa[j]); b[j] = f2_hsum(bb[j]); }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    f2 (&kj)[G::NP] = kk[KEEP ? j : 0];
+                    lds_slice<G::NR>(kj, s.k.f + (tb + j) * D + g.off);
+                    if constexpr (!SUM) a[j] = dot2_chain<G::NP>(S, kj); else a[j] = 0.f;
+                    f2 qq[G::NP];
+                    lds_slice<G::NR>(qq, s.q.f + (tb + j) * D + g.off);
+                    b[j] = dot2_chain<G::NP>(S, qq);
+                }
             }
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -243,10 +265,10 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdPara
     sb.init(p.beta, n, h, 1);
 
     float* W = p.W + n * p.wN + h * p.wH;
-    float2 Sr[G::NP], Gr[G::NP], Gc[G::NP];
+    f2 Sr[G::NP], Gr[G::NP], Gc[G::NP];
     load_rows(g, Sr, W, p.wE, p.E, p.M);
 #pragma unroll
-    for (int i = 0; i < G::NP; i++) { Gr[i] = make_float2(0.f, 0.f); Gc[i] = make_float2(0.f, 0.f); }
+    for (int i = 0; i < G::NP; i++) { Gr[i] = 0ull; Gc[i] = 0ull; }
     __syncthreads();
 
     const int nchunks = (p.L + TC - 1) / TC;
@@ -300,12 +322,24 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdPara
             // ---------------- column role: one reduction round for the four steps
             {
                 float a[4];
-                float2 kk[KEEP ? 4 : 1][G::NP];
+                f2 kk[KEEP ? 4 : 1][G::NP];
+                if constexpr (KEEP) {
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    float2 (&kj)[G::NP] = kk[KEEP ? j : 0];
-                    lds_slice<G::NR>(kj, s.k.f + (tb + j) * D + g.off);
-                    a[j] = dot2<G::NP>(Gc, kj);
+                    for (int j = 0; j < 4; j++) lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                    f2 aa[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+                    for (int i = 0; i < G::NP; i++) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) aa[j] = ffma2(Gc[i], kk[j][i], aa[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) a[j] = f2_hsum(aa[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        lds_slice<G::NR>(kk[0], s.k.f + (tb + j) * D + g.off);
+                        a[j] = dot2_chain<G::NP>(Gc, kk[0]);
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 4; j++) a[j] = reduce_split<SPLIT>(a[j]);
@@ -336,7 +370,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdPara
                 }
 #pragma unroll
                 for (int j = 3; j >= 0; j--) {
-                    float2 qq[G::NP];
+                    f2 qq[G::NP];
                     lds_slice<G::NR>(qq, s.q.f + (tb + j) * D + g.off);
                     axpy2<G::NP>(Gc, qq, gy[j]);
                     if constexpr (KEEP) {
@@ -364,7 +398,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdPara
             // ---------------- row role: per step, time reversed
             for (int j = nv - 1; j >= 0; j--) {
                 const int t = tb + j;
-                float2 gr[G::NP], ur[G::NP], brr[G::NP];
+                f2 gr[G::NP], ur[G::NP], brr[G::NP];
                 lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
                 lds_slice<G::NR>(ur, xu + j * D + g.off);
                 lds_slice<G::NR>(brr, xbr + j * D + g.off);

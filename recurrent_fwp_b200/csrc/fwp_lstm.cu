@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(D * SPLIT) lstm_fwd_kernel(const LstmFwdParams
         sv[a].init(p.v[a], n, h, p.D);
         sb[a].init(p.beta[a], n, h, 1);
     }
-    float2 S[3][G::NP];
+    f2 S[3][G::NP];
 #pragma unroll
     for (int a = 0; a < 3; a++) load_cols(g, S[a], p.W[a] + n * p.wN[a] + h * p.wH[a], p.wE[a], p.D, p.D);
     const bool ok = g.idx < p.D;
@@ -108,12 +108,12 @@ __global__ void __launch_bounds__(D * SPLIT) lstm_fwd_kernel(const LstmFwdParams
             }
             if (g.s == 0) xv[g.idx] = xe;
             cta_sync<G::WPS>();
-            float2 xs[G::NP];
+            f2 xs[G::NP];
             lds_slice<G::NR>(xs, xv + g.off);
             float pre[3], vo[3];
 #pragma unroll
             for (int a = 0; a < 3; a++) {
-                float2 kk[G::NP];
+                f2 kk[G::NP];
                 lds_slice<G::NR>(kk, s.k[a].f + t * D + g.off);
                 vo[a] = reduce_split<SPLIT>(dot2<G::NP>(S[a], kk));
                 const float u = s.b[a].f[t] * (s.v[a].f[t * D + g.idx] - vo[a]);
@@ -211,12 +211,12 @@ __global__ void __launch_bounds__(D * SPLIT) lstm_bwd_kernel(const LstmBwdParams
     sc.init(p.cell, n, h, p.D);
     sumc.init(p.umc, n, h, p.D);
 
-    float2 Sr[3][G::NP], Gr[3][G::NP], Gc[3][G::NP];
+    f2 Sr[3][G::NP], Gr[3][G::NP], Gc[3][G::NP];
 #pragma unroll
     for (int a = 0; a < 3; a++) {
         load_rows(g, Sr[a], p.W[a] + n * p.wN[a] + h * p.wH[a], p.wE[a], p.D, p.D);
 #pragma unroll
-        for (int i = 0; i < G::NP; i++) { Gr[a][i] = make_float2(0.f, 0.f); Gc[a][i] = make_float2(0.f, 0.f); }
+        for (int i = 0; i < G::NP; i++) { Gr[a][i] = 0ull; Gc[a][i] = 0ull; }
     }
     float gh = 0.f, gc = 0.f;
     const bool ok = g.idx < p.D;
@@ -274,11 +274,11 @@ __global__ void __launch_bounds__(D * SPLIT) lstm_bwd_kernel(const LstmBwdParams
             if constexpr (VAR != 4) dz[1] = dz[1] * (1.f - uu) * uu;
             gc *= (1.f - gi);
             // ---- column role, one delta block per gate
-            float2 xs[G::NP];
+            f2 xs[G::NP];
             lds_slice<G::NR>(xs, s.od.f + t * D + g.off);
 #pragma unroll
             for (int q = 0; q < 3; q++) {
-                float2 kk[G::NP];
+                f2 kk[G::NP];
                 lds_slice<G::NR>(kk, s.k[q].f + t * D + g.off);
                 const float beta = s.b[q].f[t];
                 const float w = s.v[q].f[o] - s.vo[q].f[o];
@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(D * SPLIT) lstm_bwd_kernel(const LstmBwdParams
                 float ghn = 0.f;
 #pragma unroll
                 for (int q = 0; q < 3; q++) {
-                    float2 dr[G::NP], ur[G::NP], brr[G::NP];
+                    f2 dr[G::NP], ur[G::NP], brr[G::NP];
                     lds_slice<G::NR>(dr, xdz + q * D + g.off);
                     lds_slice<G::NR>(ur, xu + q * D + g.off);
                     lds_slice<G::NR>(brr, xbr + q * D + g.off);

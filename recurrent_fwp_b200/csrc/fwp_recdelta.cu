@@ -53,16 +53,19 @@ __global__ void __launch_bounds__(D * SPLIT) rec_fwd_kernel(const RecFwdParams p
     sv.init(p.vx, n, h, p.D);
     sb.init(p.bx, n, h, 1);
 
-    float2 S[G::NP], Rq[G::NP], Rk[G::NP], Rv[G::NP], rb[G::NP];
+    f2 S[G::NP], Rq[G::NP], Rk[G::NP], Rv[G::NP], rb[G::NP];
     load_cols(g, S, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
     load_cols(g, Rq, p.Rq + h * p.rH, p.rE, p.D, p.D);
     load_cols(g, Rk, p.Rk + h * p.rH, p.rE, p.D, p.D);
     load_cols(g, Rv, p.Rv + h * p.rH, p.rE, p.D, p.D);
+    {
+        float pr[2];
 #pragma unroll
-    for (int i = 0; i < G::NR; i++) {
-        const int e = g.off + i;
-        const float x = e < p.D ? p.rb[h * p.rbH + e] : 0.f;
-        if (i & 1) rb[i >> 1].y = x; else rb[i >> 1].x = x;
+        for (int i = 0; i < G::NR; i++) {
+            const int e = g.off + i;
+            pr[i & 1] = e < p.D ? p.rb[h * p.rbH + e] : 0.f;
+            if (i & 1) rb[i >> 1] = f2_pack(pr[0], pr[1]);
+        }
     }
     const bool ok = g.idx < p.D;
     float* hp = p.h + n * p.hN + h * p.hH;
@@ -95,7 +98,7 @@ __global__ void __launch_bounds__(D * SPLIT) rec_fwd_kernel(const RecFwdParams p
             const int o = t * D + g.idx;
             if (g.s == 0) xh[g.idx] = ok ? tanhf(hv) : 0.f;
             cta_sync<G::WPS>();
-            float2 hs[G::NP];
+            f2 hs[G::NP];
             lds_slice<G::NR>(hs, xh + g.off);
             const float qh = s.q.f[o] + reduce_split<SPLIT>(dot2<G::NP>(Rq, hs));
             const float kh = s.k.f[o] + reduce_split<SPLIT>(dot2<G::NP>(Rk, hs));
@@ -109,7 +112,7 @@ __global__ void __launch_bounds__(D * SPLIT) rec_fwd_kernel(const RecFwdParams p
             const float invq = 1.f / cta_allreduce_idx<G, false>(g, eq, slot + 16);
             const float invk = 1.f / cta_allreduce_idx<G, false>(g, ek, slot + 24);
             cta_sync<G::WPS>();
-            float2 ks[G::NP], qs[G::NP];
+            f2 ks[G::NP], qs[G::NP];
             lds_slice<G::NR>(ks, xk + g.off);
             lds_slice<G::NR>(qs, xq + g.off);
             const float vo = reduce_split<SPLIT>(dot2<G::NP>(S, ks)) * invk;
@@ -196,11 +199,11 @@ __global__ void __launch_bounds__(D * SPLIT) rec_bwd_kernel(const RecBwdParams p
     sg.init(p.gy, n, h, p.D);
     sb.init(p.beta, n, h, 1);
 
-    float2 Sr[G::NP], Gr[G::NP], Gc[G::NP], aq[G::NP], ak[G::NP], av[G::NP];
+    f2 Sr[G::NP], Gr[G::NP], Gc[G::NP], aq[G::NP], ak[G::NP], av[G::NP];
     load_rows(g, Sr, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
 #pragma unroll
     for (int i = 0; i < G::NP; i++) {
-        Gr[i] = Gc[i] = aq[i] = ak[i] = av[i] = make_float2(0.f, 0.f);
+        Gr[i] = Gc[i] = aq[i] = ak[i] = av[i] = 0ull;
     }
     float gh = 0.f, arb = 0.f;
     const bool ok = g.idx < p.D;
@@ -242,7 +245,7 @@ __global__ void __launch_bounds__(D * SPLIT) rec_bwd_kernel(const RecBwdParams p
             float dv, dbh;
             // ---- column role
             {
-                float2 qq[G::NP], kk[G::NP];
+                f2 qq[G::NP], kk[G::NP];
                 lds_slice<G::NR>(qq, s.q.f + t * D + g.off);
                 lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
                 const float w = s.v.f[o] - s.vo.f[o];
@@ -259,7 +262,7 @@ __global__ void __launch_bounds__(D * SPLIT) rec_bwd_kernel(const RecBwdParams p
             float dqh, dkh;
             const float qe = s.q.f[o], ke = s.k.f[o], hte = s.od.f[o];
             {
-                float2 gr[G::NP], ur[G::NP], brr[G::NP];
+                f2 gr[G::NP], ur[G::NP], brr[G::NP];
                 lds_slice<G::NR>(gr, xg + g.off);
                 lds_slice<G::NR>(ur, xu + g.off);
                 lds_slice<G::NR>(brr, xbr + g.off);
@@ -290,7 +293,7 @@ __global__ void __launch_bounds__(D * SPLIT) rec_bwd_kernel(const RecBwdParams p
             cta_sync<G::WPS>();
             // ---- feedback gradient (row role over R) and parameter gradients (column role)
             {
-                float2 dqs[G::NP], dks[G::NP], dvs[G::NP], rr[G::NP];
+                f2 dqs[G::NP], dks[G::NP], dvs[G::NP], rr[G::NP];
                 lds_slice<G::NR>(dqs, xdq + g.off);
                 lds_slice<G::NR>(dks, xdk + g.off);
                 lds_slice<G::NR>(dvs, xbr + g.off);
@@ -303,7 +306,7 @@ __global__ void __launch_bounds__(D * SPLIT) rec_bwd_kernel(const RecBwdParams p
                 back += dot2<G::NP>(rr, dvs);
                 back = reduce_split<SPLIT>(back) + rmem[3 * D * SM::kRS + g.idx] * dbh;
                 gh = (1.f - hte * hte) * back;
-                float2 hs[G::NP];
+                f2 hs[G::NP];
                 lds_slice<G::NR>(hs, s.od.f + t * D + g.off);
                 axpy2<G::NP>(aq, hs, dqh);
                 axpy2<G::NP>(ak, hs, dkh);

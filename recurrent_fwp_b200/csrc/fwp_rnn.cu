@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(D * SPLIT) rnn_fwd_kernel(const RnnFwdParams p
 
     float* W = p.W + n * p.wN + h * p.wH;
     float* hp = p.h + n * p.hN + h * p.hH;
-    float2 S[G::NP];
+    f2 S[G::NP];
     load_cols(g, S, W, p.wE, p.D, p.D);
     const bool ok = g.idx < p.D;
     float hv = ok ? hp[g.idx] : 0.f;
@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(D * SPLIT) rnn_fwd_kernel(const RnnFwdParams p
             float* slot = xv + D;
             par ^= 1;
             // delta update of the recurrent matrix (independent of the hidden state)
-            float2 kk[G::NP];
+            f2 kk[G::NP];
             lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
             const float vo = reduce_split<SPLIT>(dot2<G::NP>(S, kk));
             const float u = s.b.f[t] * (s.v.f[t * D + g.idx] - vo);
@@ -95,14 +95,14 @@ __global__ void __launch_bounds__(D * SPLIT) rnn_fwd_kernel(const RnnFwdParams p
                 const float den = cta_allreduce_idx<G, false>(g, ex, slot + 8);
                 cta_sync<G::WPS>();
                 const float inv = 1.f / (den + kSoftmaxEps);
-                float2 ss[G::NP];
+                f2 ss[G::NP];
                 lds_slice<G::NR>(ss, xv + g.off);
                 hn = reduce_split<SPLIT>(dot2<G::NP>(S, ss)) * inv + zz;
                 if (ok && g.s == 0) put<float>(p.out_nmz, n, h, t0 + t, g.idx, ex * inv);
             } else {
                 if (g.s == 0) xv[g.idx] = hv;
                 cta_sync<G::WPS>();
-                float2 ss[G::NP];
+                f2 ss[G::NP];
                 lds_slice<G::NR>(ss, xv + g.off);
                 const float pre = reduce_split<SPLIT>(dot2<G::NP>(S, ss)) + zz;
                 const float mx = cta_allreduce_idx<G, true>(g, ok ? pre : -INFINITY, slot);
@@ -168,10 +168,10 @@ __global__ void __launch_bounds__(D * SPLIT) rnn_bwd_kernel(const RnnBwdParams p
     if (V1) sout.init(p.out, n, h, p.D);
 
     float* W = p.W + n * p.wN + h * p.wH;
-    float2 Sr[G::NP], Gr[G::NP], Gc[G::NP];
+    f2 Sr[G::NP], Gr[G::NP], Gc[G::NP];
     load_rows(g, Sr, W, p.wE, p.D, p.D);
 #pragma unroll
-    for (int i = 0; i < G::NP; i++) { Gr[i] = make_float2(0.f, 0.f); Gc[i] = make_float2(0.f, 0.f); }
+    for (int i = 0; i < G::NP; i++) { Gr[i] = 0ull; Gc[i] = 0ull; }
     float gh = 0.f;
     const bool ok = g.idx < p.D;
     __syncthreads();
@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(D * SPLIT) rnn_bwd_kernel(const RnnBwdParams p
                 gcol = hm * (gcol - dotp);               // dz[m]
             }
             {
-                float2 xs[G::NP], kk[G::NP];
+                f2 xs[G::NP], kk[G::NP];
                 lds_slice<G::NR>(xs, s.od.f + t * D + g.off);
                 lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
                 const float w = s.v.f[t * D + g.idx] - s.vo.f[t * D + g.idx];
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(D * SPLIT) rnn_bwd_kernel(const RnnBwdParams p
             cta_sync<G::WPS>();
             // ---- row role
             {
-                float2 gr[G::NP], ur[G::NP], brr[G::NP];
+                f2 gr[G::NP], ur[G::NP], brr[G::NP];
                 lds_slice<G::NR>(gr, xg + g.off);
                 lds_slice<G::NR>(ur, xu + g.off);
                 lds_slice<G::NR>(brr, xbr + g.off);
