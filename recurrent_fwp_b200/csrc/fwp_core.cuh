@@ -72,6 +72,19 @@ static inline int pad_dim(int d) { return d <= 16 ? 16 : (d <= 32 ? 32 : (d <= 6
 // ---------------------------------------------------------------- device side
 #ifdef __CUDACC__
 
+// Optional phase timers (cycles of thread 0 of CTA 0), compiled in only for
+// development builds with -DFWP_PROFILE; they expand to nothing otherwise.
+#ifdef FWP_PROFILE
+static __device__ long long fwp_prof_out[16];
+#define FWP_PROF_BEGIN long long _pt[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long _pc = clock64();
+#define FWP_PROF(i) { const long long _n = clock64(); _pt[i] += _n - _pc; _pc = _n; }
+#define FWP_PROF_END if (blockIdx.x == 0 && threadIdx.x == 0) { for (int _i = 0; _i < 16; _i++) fwp_prof_out[_i] = _pt[_i]; }
+#else
+#define FWP_PROF_BEGIN
+#define FWP_PROF(i)
+#define FWP_PROF_END
+#endif
+
 // Two fp32 values packed in one 64-bit register.  Everything that lives across
 // time steps (the matrices, operand slices, dot-product accumulators) stays in
 // this form, so the packed FMA needs no pack/unpack moves around it.
@@ -288,29 +301,41 @@ struct Src {
 
 // Copy rows [t0, t0+nt) into a tile whose rows are D elements of T (row r of the
 // tile = time step t0+r).  Elements beyond `width` are never written (the tile
-// is zeroed once at kernel start).
-template <int D, typename T>
-__device__ __forceinline__ void stage_rows(T* tile, const Src<T>& src, int t0, int nt, int tid, int nthreads) {
+// is zeroed once at kernel start).  NT = threads of the CTA.  The common case
+// (full-width rows) walks rows with a fixed per-thread column, so each copy costs
+// one address add; only padded widths pay for an integer division.
+template <int D, int NT, typename T>
+__device__ __forceinline__ void stage_rows(T* tile, const Src<T>& src, int t0, int nt, int tid) {
     constexpr int per16 = 16 / (int)sizeof(T);
-    if (src.vec) {
-        const int ppr = src.width / per16;             // 16-byte pieces per row
+    if (src.vec && src.width == D && D >= per16) {
+        constexpr int PPR = (D >= per16) ? D / per16 : 1;    // 16-byte pieces per row
+        constexpr int RSTEP = (NT >= PPR) ? NT / PPR : 1;    // rows covered per sweep of the CTA
+        static_assert(D < per16 || NT % PPR == 0, "thread count must be a multiple of the pieces per row");
+        int r = tid / PPR;
+        const int c = (tid % PPR) * per16;
+        const T* gp = src.base + (long long)(t0 + r) * src.sL + c;
+        T* sp = tile + r * D + c;
+        const long long gstep = (long long)RSTEP * src.sL;
+        for (; r < nt; r += RSTEP, gp += gstep, sp += RSTEP * D) cp_async16(sp, gp);
+    } else if (src.vec) {
+        const int ppr = src.width / per16;
         const int total = nt * ppr;
-        for (int i = tid; i < total; i += nthreads) {
+        for (int i = tid; i < total; i += NT) {
             int r = i / ppr, c = (i - r * ppr) * per16;
             cp_async16(tile + r * D + c, src.base + (long long)(t0 + r) * src.sL + c);
         }
-    } else if (sizeof(T) == 4) {
-        const int total = nt * src.width;
-        for (int i = tid; i < total; i += nthreads) {
-            int r = i / src.width, c = i - r * src.width;
-            cp_async4(tile + r * D + c, src.base + (long long)(t0 + r) * src.sL + c);
+    } else if (src.width == D) {
+        for (int i = tid; i < nt * D; i += NT) {
+            const int r = i / D, c = i % D;
+            const T* gp = src.base + (long long)(t0 + r) * src.sL + c;
+            if constexpr (sizeof(T) == 4) cp_async4(tile + i, gp); else tile[i] = *gp;
         }
     } else {
-        // 2-byte elements without 16-byte alignment: plain loads (rare path)
         const int total = nt * src.width;
-        for (int i = tid; i < total; i += nthreads) {
+        for (int i = tid; i < total; i += NT) {
             int r = i / src.width, c = i - r * src.width;
-            tile[r * D + c] = src.base[(long long)(t0 + r) * src.sL + c];
+            const T* gp = src.base + (long long)(t0 + r) * src.sL + c;
+            if constexpr (sizeof(T) == 4) cp_async4(tile + r * D + c, gp); else tile[r * D + c] = *gp;
         }
     }
 }
@@ -327,8 +352,9 @@ struct Tile {
         f = mem;
         raw = kRaw ? reinterpret_cast<T*>(mem + TC * D) : reinterpret_cast<T*>(mem);
     }
-    __device__ __forceinline__ void load(const Src<T>& src, int t0, int nt, int tid, int nthreads) {
-        stage_rows<D, T>(raw, src, t0, nt, tid, nthreads);
+    template <int NT>
+    __device__ __forceinline__ void load(const Src<T>& src, int t0, int nt, int tid) {
+        stage_rows<D, NT, T>(raw, src, t0, nt, tid);
     }
     // after the copies have landed and a barrier: widen 16-bit rows to fp32
     __device__ __forceinline__ void widen(int nt, int width, int tid, int nthreads) {
@@ -350,19 +376,23 @@ __device__ __forceinline__ void put(const Row4& r, int n, int h, int t, int c, f
 
 // Flush rows [0, nt) of an fp32 shared-memory tile (row length D, first `width`
 // columns valid) to rows [t0, t0+nt) of a streamed output of element type T.
-// 16-byte stores when the destination rows allow it, element stores otherwise.
-template <int D, typename T>
+// 16-byte stores with a fixed per-thread column when the destination rows allow
+// it, element stores otherwise.
+template <int D, int NT, typename T>
 __device__ __forceinline__ void flush_rows(const float* tile, const Row4& r, int n, int h, int t0, int nt,
-                                           int width, int tid, int nthreads) {
+                                           int width, int tid) {
     T* base = reinterpret_cast<T*>(r.p) + n * r.sN + h * r.sH + (long long)t0 * r.sL;
     constexpr int per16 = 16 / (int)sizeof(T);
     const bool vec = (width % per16 == 0) && ((reinterpret_cast<uintptr_t>(base) & 15) == 0) && (r.sL % per16 == 0);
-    if (vec) {
-        const int ppr = width / per16;
-        for (int i = tid; i < nt * ppr; i += nthreads) {
-            const int row = i / ppr, c = (i - row * ppr) * per16;
-            const float* src = tile + row * D + c;
-            T* dst = base + (long long)row * r.sL + c;
+    if (vec && width == D && D >= per16) {
+        constexpr int PPR = (D >= per16) ? D / per16 : 1;
+        constexpr int RSTEP = (NT >= PPR) ? NT / PPR : 1;
+        int row = tid / PPR;
+        const int c = (tid % PPR) * per16;
+        const float* src = tile + row * D + c;
+        T* dst = base + (long long)row * r.sL + c;
+        const long long dstep = (long long)RSTEP * r.sL;
+        for (; row < nt; row += RSTEP, src += RSTEP * D, dst += dstep) {
             if constexpr (sizeof(T) == 4) {
                 *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
             } else {
@@ -376,8 +406,13 @@ __device__ __forceinline__ void flush_rows(const float* tile, const Row4& r, int
                 *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
             }
         }
+    } else if (width == D) {
+        for (int i = tid; i < nt * D; i += NT) {
+            const int row = i / D, c = i % D;
+            base[(long long)row * r.sL + c] = from_f32<T>(tile[i]);
+        }
     } else {
-        for (int i = tid; i < nt * width; i += nthreads) {
+        for (int i = tid; i < nt * width; i += NT) {
             const int row = i / width, c = i - row * width;
             base[(long long)row * r.sL + c] = from_f32<T>(tile[row * D + c]);
         }

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
     static_assert(TC % 4 == 0, "chunk must hold whole groups");
     constexpr bool KEEP = G::NR <= 16;     // keep the four key slices in registers between dot and update
     const G g;
+    FWP_PROF_BEGIN
     const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
     extern __shared__ __align__(16) float smem[];
     for (int i = g.tid; i < SM::kFloats; i += G::NT) smem[i] = 0.f;
@@ -81,16 +82,18 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
     auto issue = [&](int c) {
         Stage s; s.bind(smem + (c & 1) * SM::kStage);
         const int t0 = c * TC, nt = min(TC, p.L - t0);
-        s.q.load(sq, t0, nt, g.tid, G::NT);
-        s.k.load(sk, t0, nt, g.tid, G::NT);
-        s.v.load(sv, t0, nt, g.tid, G::NT);
-        if (!SUM) s.b.load(sb, t0, nt, g.tid, G::NT);
+        s.q.template load<G::NT>(sq, t0, nt, g.tid);
+        s.k.template load<G::NT>(sk, t0, nt, g.tid);
+        s.v.template load<G::NT>(sv, t0, nt, g.tid);
+        if (!SUM) s.b.template load<G::NT>(sb, t0, nt, g.tid);
         cp_async_commit();
     };
     issue(0);
+    FWP_PROF(0)
     for (int c = 0; c < nchunks; c++) {
-        if (c + 1 < nchunks) { issue(c + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        if (c + 1 < nchunks) { issue(c + 1); FWP_PROF(1) cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         __syncthreads();
+        FWP_PROF(2)
         Stage s; s.bind(smem + (c & 1) * SM::kStage);
         const int t0 = c * TC, nt = min(TC, p.L - t0);
         const int ng = (nt + 3) >> 2;
@@ -109,6 +112,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
         if ((sizeof(T) != 4) || (nt & 3)) __syncthreads();
         gram_phase<D>(s.k.f, s.q.f, gram, ng, g.tid, G::NT);
         __syncthreads();
+        FWP_PROF(3)
 
         for (int gi = 0; gi < ng; gi++) {
             const int tb = 4 * gi;
@@ -123,6 +127,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
                     lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
                     lds_slice<G::NR>(qq[j], s.q.f + (tb + j) * D + g.off);
                 }
+                FWP_PROF(8)
                 f2 aa[4] = {0ull, 0ull, 0ull, 0ull}, bb[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
                 for (int i = 0; i < G::NP; i++) {
@@ -134,6 +139,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
                 }
 #pragma unroll
                 for (int j = 0; j < 4; j++) { a[j] = SUM ? 0.f : f2_hsum(aa[j]); b[j] = f2_hsum(bb[j]); }
+                FWP_PROF(9)
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
@@ -150,6 +156,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
                 if constexpr (!SUM) a[j] = reduce_split<SPLIT>(a[j]);
                 b[j] = reduce_split<SPLIT>(b[j]);
             }
+            FWP_PROF(10)
             float gs[16];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -180,6 +187,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
                 for (int i = 0; i <= j; i++) yy = fmaf(u[i], gs[gram_kq(i, j)], yy);
                 y[j] = yy;
             }
+            FWP_PROF(11)
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 if constexpr (KEEP) {
@@ -189,6 +197,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
                     axpy2<G::NP>(S, kk[0], u[j]);
                 }
             }
+            FWP_PROF(12)
             if (g.s == 0) {
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
@@ -199,15 +208,20 @@ __global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdPara
                     }
                 }
             }
+            FWP_PROF(13)
         }
         __syncthreads();
-        flush_rows<D, T>(oy, p.out, n, h, t0, nt, p.M, g.tid, G::NT);
+        FWP_PROF(4)
+        flush_rows<D, G::NT, T>(oy, p.out, n, h, t0, nt, p.M, g.tid);
         if constexpr (!SUM) {
-            flush_rows<D, float>(ovo, p.v_old, n, h, t0, nt, p.M, g.tid, G::NT);
-            if (p.v_ins.p) flush_rows<D, float>(ou, p.v_ins, n, h, t0, nt, p.M, g.tid, G::NT);
+            flush_rows<D, G::NT, float>(ovo, p.v_old, n, h, t0, nt, p.M, g.tid);
+            if (p.v_ins.p) flush_rows<D, G::NT, float>(ou, p.v_ins, n, h, t0, nt, p.M, g.tid);
         }
+        FWP_PROF(5)
     }
     store_cols(g, S, W, p.wE, p.E, p.M);
+    FWP_PROF(6)
+    FWP_PROF_END
 }
 
 // ------------------------------------------------------------------ backward
@@ -276,12 +290,12 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdPara
         Stage s; s.bind(smem + (jc & 1) * SM::kStage);
         const int c = nchunks - 1 - jc;
         const int t0 = c * TC, nt = min(TC, p.L - t0);
-        s.q.load(sq, t0, nt, g.tid, G::NT);
-        s.k.load(sk, t0, nt, g.tid, G::NT);
-        s.v.load(sv, t0, nt, g.tid, G::NT);
-        s.gy.load(sg, t0, nt, g.tid, G::NT);
-        s.vo.load(so, t0, nt, g.tid, G::NT);
-        s.b.load(sb, t0, nt, g.tid, G::NT);
+        s.q.template load<G::NT>(sq, t0, nt, g.tid);
+        s.k.template load<G::NT>(sk, t0, nt, g.tid);
+        s.v.template load<G::NT>(sv, t0, nt, g.tid);
+        s.gy.template load<G::NT>(sg, t0, nt, g.tid);
+        s.vo.template load<G::NT>(so, t0, nt, g.tid);
+        s.b.template load<G::NT>(sb, t0, nt, g.tid);
         cp_async_commit();
     };
     issue(0);
@@ -424,10 +438,10 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdPara
             }
         }
         __syncthreads();
-        flush_rows<D, T>(odq, p.gq, n, h, t0, nt, p.E, g.tid, G::NT);
-        flush_rows<D, T>(odk, p.gk, n, h, t0, nt, p.E, g.tid, G::NT);
-        flush_rows<D, T>(odv, p.gv, n, h, t0, nt, p.M, g.tid, G::NT);
-        flush_rows<1, T>(odb, p.gb, n, h, t0, nt, 1, g.tid, G::NT);
+        flush_rows<D, G::NT, T>(odq, p.gq, n, h, t0, nt, p.E, g.tid);
+        flush_rows<D, G::NT, T>(odk, p.gk, n, h, t0, nt, p.E, g.tid);
+        flush_rows<D, G::NT, T>(odv, p.gv, n, h, t0, nt, p.M, g.tid);
+        flush_rows<1, G::NT, T>(odb, p.gb, n, h, t0, nt, 1, g.tid);
     }
     store_rows(g, Sr, W, p.wE, p.E, p.M);
 }

@@ -77,10 +77,10 @@ __global__ void __launch_bounds__(D * SPLIT) lstm_fwd_kernel(const LstmFwdParams
         const int t0 = c * TC, nt = min(TC, p.L - t0);
 #pragma unroll
         for (int a = 0; a < 3; a++) {
-            s.z[a].load(sz[a], t0, nt, g.tid, G::NT);
-            s.k[a].load(sk[a], t0, nt, g.tid, G::NT);
-            s.v[a].load(sv[a], t0, nt, g.tid, G::NT);
-            s.b[a].load(sb[a], t0, nt, g.tid, G::NT);
+            s.z[a].template load<G::NT>(sz[a], t0, nt, g.tid);
+            s.k[a].template load<G::NT>(sk[a], t0, nt, g.tid);
+            s.v[a].template load<G::NT>(sv[a], t0, nt, g.tid);
+            s.b[a].template load<G::NT>(sb[a], t0, nt, g.tid);
         }
         cp_async_commit();
     };
@@ -229,17 +229,17 @@ __global__ void __launch_bounds__(D * SPLIT) lstm_bwd_kernel(const LstmBwdParams
         const int t0 = c * TC, nt = min(TC, p.L - t0);
 #pragma unroll
         for (int a = 0; a < 3; a++) {
-            s.k[a].load(sk[a], t0, nt, g.tid, G::NT);
-            s.v[a].load(sv[a], t0, nt, g.tid, G::NT);
-            s.vo[a].load(so[a], t0, nt, g.tid, G::NT);
-            s.gate[a].load(sgt[a], t0, nt, g.tid, G::NT);
-            s.b[a].load(sb[a], t0, nt, g.tid, G::NT);
+            s.k[a].template load<G::NT>(sk[a], t0, nt, g.tid);
+            s.v[a].template load<G::NT>(sv[a], t0, nt, g.tid);
+            s.vo[a].template load<G::NT>(so[a], t0, nt, g.tid);
+            s.gate[a].template load<G::NT>(sgt[a], t0, nt, g.tid);
+            s.b[a].template load<G::NT>(sb[a], t0, nt, g.tid);
         }
-        s.gy.load(sgy, t0, nt, g.tid, G::NT);
-        if (VAR == 1) s.out.load(sout, t0, nt, g.tid, G::NT);
-        s.od.load(sod, t0, nt, g.tid, G::NT);
-        s.cell.load(sc, t0, nt, g.tid, G::NT);
-        s.umc.load(sumc, t0, nt, g.tid, G::NT);
+        s.gy.template load<G::NT>(sgy, t0, nt, g.tid);
+        if (VAR == 1) s.out.template load<G::NT>(sout, t0, nt, g.tid);
+        s.od.template load<G::NT>(sod, t0, nt, g.tid);
+        s.cell.template load<G::NT>(sc, t0, nt, g.tid);
+        s.umc.template load<G::NT>(sumc, t0, nt, g.tid);
         cp_async_commit();
     };
     issue(0);

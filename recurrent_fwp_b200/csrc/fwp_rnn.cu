@@ -63,10 +63,10 @@ __global__ void __launch_bounds__(D * SPLIT) rnn_fwd_kernel(const RnnFwdParams p
     auto issue = [&](int c) {
         Stage s; s.bind(smem + (c & 1) * Stage::kFloats);
         const int t0 = c * TC, nt = min(TC, p.L - t0);
-        s.z.load(sz, t0, nt, g.tid, G::NT);
-        s.k.load(sk, t0, nt, g.tid, G::NT);
-        s.v.load(sv, t0, nt, g.tid, G::NT);
-        s.b.load(sb, t0, nt, g.tid, G::NT);
+        s.z.template load<G::NT>(sz, t0, nt, g.tid);
+        s.k.template load<G::NT>(sk, t0, nt, g.tid);
+        s.v.template load<G::NT>(sv, t0, nt, g.tid);
+        s.b.template load<G::NT>(sb, t0, nt, g.tid);
         cp_async_commit();
     };
     issue(0);
@@ -181,13 +181,13 @@ __global__ void __launch_bounds__(D * SPLIT) rnn_bwd_kernel(const RnnBwdParams p
         Stage s; s.bind(smem + (j & 1) * Stage::kFloats);
         const int c = nchunks - 1 - j;
         const int t0 = c * TC, nt = min(TC, p.L - t0);
-        s.k.load(sk, t0, nt, g.tid, G::NT);
-        s.v.load(sv, t0, nt, g.tid, G::NT);
-        s.gy.load(sg, t0, nt, g.tid, G::NT);
-        s.vo.load(so, t0, nt, g.tid, G::NT);
-        s.od.load(sd, t0, nt, g.tid, G::NT);
-        if (V1) s.out.load(sout, t0, nt, g.tid, G::NT);
-        s.b.load(sb, t0, nt, g.tid, G::NT);
+        s.k.template load<G::NT>(sk, t0, nt, g.tid);
+        s.v.template load<G::NT>(sv, t0, nt, g.tid);
+        s.gy.template load<G::NT>(sg, t0, nt, g.tid);
+        s.vo.template load<G::NT>(so, t0, nt, g.tid);
+        s.od.template load<G::NT>(sd, t0, nt, g.tid);
+        if (V1) s.out.template load<G::NT>(sout, t0, nt, g.tid);
+        s.b.template load<G::NT>(sb, t0, nt, g.tid);
         cp_async_commit();
     };
     issue(0);
