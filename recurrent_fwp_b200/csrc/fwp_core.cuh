@@ -78,11 +78,11 @@ static inline int pad_dim(int d) { return d <= 16 ? 16 : (d <= 32 ? 32 : (d <= 6
 static __device__ long long fwp_prof_out[16];
 #define FWP_PROF_BEGIN long long _pt[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long _pc = clock64();
 #define FWP_PROF(i) { const long long _n = clock64(); _pt[i] += _n - _pc; _pc = _n; }
-#define FWP_PROF_END if (blockIdx.x == 0 && threadIdx.x == 0) { for (int _i = 0; _i < 16; _i++) fwp_prof_out[_i] = _pt[_i]; }
+#define FWP_PROF_END(base, cond) if (blockIdx.x == 0 && (cond)) { for (int _i = 0; _i < 8; _i++) fwp_prof_out[(base) + _i] = _pt[_i]; }
 #else
 #define FWP_PROF_BEGIN
 #define FWP_PROF(i)
-#define FWP_PROF_END
+#define FWP_PROF_END(base, cond)
 #endif
 
 // Two fp32 values packed in one 64-bit register.  Everything that lives across
@@ -133,8 +133,21 @@ struct Geo {
     static constexpr int WPS = NT / 32;      // warps per sequence
     static_assert(NT % 32 == 0 && NR % 4 == 0 && SPLIT <= 4, "unsupported geometry");
     int tid, lane, warp, s, idx, off;        // off = first element of the slice
+    int slot, seq;                           // several sequences may share a CTA: slot in the CTA, global sequence
+    // Warps are spread over the four SM sub-partitions by their index in the CTA, so a CTA
+    // should hold at least four warps: CTAs of fewer warps are packed with several sequences.
     __device__ __forceinline__ Geo() {
-        tid = threadIdx.x;
+        init(threadIdx.x);
+        seq = blockIdx.x * (blockDim.x / NT) + slot;
+    }
+    // t = index of the thread among the threads that play this role in the CTA
+    __device__ __forceinline__ explicit Geo(int t) {
+        init(t);
+        seq = -1;
+    }
+    __device__ __forceinline__ void init(int t) {
+        slot = t / NT;
+        tid = t - slot * NT;
         lane = tid & 31;
         warp = tid >> 5;
         s = lane / MC;
@@ -142,6 +155,17 @@ struct Geo {
         off = s * NR;
     }
 };
+
+// sequences per CTA that fill four warps
+__host__ __device__ constexpr int slots_for(int threads_per_seq) { return threads_per_seq >= 128 ? 1 : 128 / threads_per_seq; }
+
+// the slice of dynamic shared memory that belongs to one sequence slot
+template <class G>
+__device__ __forceinline__ float* slot_smem(float* smem_all, const G& g) {
+    unsigned dsz;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dsz));
+    return smem_all + (size_t)g.slot * (dsz / (blockDim.x / G::NT) / 4);
+}
 
 // sum over the SPLIT threads that share one idx (all of them get the result)
 template <int SPLIT>
@@ -196,6 +220,17 @@ __device__ __forceinline__ void lds_slice(f2 (&d)[NR / 2], const float* p) {
         d[2 * i] = t.x;
         d[2 * i + 1] = t.y;
     }
+}
+
+// Same load, but pinned in program order (volatile): used for operand prefetch, where the
+// point is that the loads issue *before* the arithmetic of the current group, not next to
+// their first use.
+template <int NR>
+__device__ __forceinline__ void lds_slice_early(f2 (&d)[NR / 2], const float* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+#pragma unroll
+    for (int i = 0; i < NR / 4; i++)
+        asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(d[2 * i]), "=l"(d[2 * i + 1]) : "r"(a + 16 * i));
 }
 
 template <int NP>
@@ -304,7 +339,7 @@ struct Src {
 // is zeroed once at kernel start).  NT = threads of the CTA.  The common case
 // (full-width rows) walks rows with a fixed per-thread column, so each copy costs
 // one address add; only padded widths pay for an integer division.
-template <int D, int NT, typename T>
+template <int D, int NT, int TC, typename T>
 __device__ __forceinline__ void stage_rows(T* tile, const Src<T>& src, int t0, int nt, int tid) {
     constexpr int per16 = 16 / (int)sizeof(T);
     if (src.vec && src.width == D && D >= per16) {
@@ -316,7 +351,12 @@ __device__ __forceinline__ void stage_rows(T* tile, const Src<T>& src, int t0, i
         const T* gp = src.base + (long long)(t0 + r) * src.sL + c;
         T* sp = tile + r * D + c;
         const long long gstep = (long long)RSTEP * src.sL;
-        for (; r < nt; r += RSTEP, gp += gstep, sp += RSTEP * D) cp_async16(sp, gp);
+        if (nt == TC && TC % RSTEP == 0) {      // full chunk: fixed trip count, copies issue back to back
+#pragma unroll
+            for (int it = 0; it < TC / RSTEP; it++) cp_async16(sp + it * RSTEP * D, gp + it * gstep);
+        } else {
+            for (; r < nt; r += RSTEP, gp += gstep, sp += RSTEP * D) cp_async16(sp, gp);
+        }
     } else if (src.vec) {
         const int ppr = src.width / per16;
         const int total = nt * ppr;
@@ -354,7 +394,7 @@ struct Tile {
     }
     template <int NT>
     __device__ __forceinline__ void load(const Src<T>& src, int t0, int nt, int tid) {
-        stage_rows<D, NT, T>(raw, src, t0, nt, tid);
+        stage_rows<D, NT, TC, T>(raw, src, t0, nt, tid);
     }
     // after the copies have landed and a barrier: widen 16-bit rows to fp32
     __device__ __forceinline__ void widen(int nt, int width, int tid, int nthreads) {
@@ -379,6 +419,22 @@ __device__ __forceinline__ void put(const Row4& r, int n, int h, int t, int c, f
 // 16-byte stores with a fixed per-thread column when the destination rows allow
 // it, element stores otherwise.
 template <int D, int NT, typename T>
+__device__ __forceinline__ void flush_piece(T* dst, const float* src) {
+    if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+    } else {
+        const float4 a = *reinterpret_cast<const float4*>(src);
+        const float4 b = *reinterpret_cast<const float4*>(src + 4);
+        __nv_bfloat162 o[4];
+        o[0] = __floats2bfloat162_rn(a.x, a.y);
+        o[1] = __floats2bfloat162_rn(a.z, a.w);
+        o[2] = __floats2bfloat162_rn(b.x, b.y);
+        o[3] = __floats2bfloat162_rn(b.z, b.w);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+    }
+}
+
+template <int D, int NT, typename T, int TC = 0>
 __device__ __forceinline__ void flush_rows(const float* tile, const Row4& r, int n, int h, int t0, int nt,
                                            int width, int tid) {
     T* base = reinterpret_cast<T*>(r.p) + n * r.sN + h * r.sH + (long long)t0 * r.sL;
@@ -392,19 +448,12 @@ __device__ __forceinline__ void flush_rows(const float* tile, const Row4& r, int
         const float* src = tile + row * D + c;
         T* dst = base + (long long)row * r.sL + c;
         const long long dstep = (long long)RSTEP * r.sL;
-        for (; row < nt; row += RSTEP, src += RSTEP * D, dst += dstep) {
-            if constexpr (sizeof(T) == 4) {
-                *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
-            } else {
-                const float4 a = *reinterpret_cast<const float4*>(src);
-                const float4 b = *reinterpret_cast<const float4*>(src + 4);
-                __nv_bfloat162 o[4];
-                o[0] = __floats2bfloat162_rn(a.x, a.y);
-                o[1] = __floats2bfloat162_rn(a.z, a.w);
-                o[2] = __floats2bfloat162_rn(b.x, b.y);
-                o[3] = __floats2bfloat162_rn(b.z, b.w);
-                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
-            }
+        if (TC > 0 && nt == TC && TC % RSTEP == 0) {
+#pragma unroll
+            for (int it = 0; it < (TC > 0 ? TC / RSTEP : 1); it++)
+                flush_piece<D, NT, T>(dst + it * dstep, src + it * RSTEP * D);
+        } else {
+            for (; row < nt; row += RSTEP, src += RSTEP * D, dst += dstep) flush_piece<D, NT, T>(dst, src);
         }
     } else if (width == D) {
         for (int i = tid; i < nt * D; i += NT) {
@@ -426,16 +475,19 @@ __host__ __device__ constexpr int gram_kk(int a, int b) { return b * (b - 1) / 2
 __host__ __device__ constexpr int gram_kq(int a, int b) { return 6 + b * (b + 1) / 2 + a; }
 
 // Fill gram[g][16] for groups g < ng from the fp32 k and q tiles (rows 4g..4g+3).
-template <int D>
-__device__ __forceinline__ void gram_phase(const float* ktile, const float* qtile, float* gram, int ng,
-                                           int tid, int nthreads) {
+template <int D, int NT, int TC>
+__device__ __forceinline__ void gram_phase(const float* ktile, const float* qtile, float* gram, int ng, int tid) {
     constexpr unsigned IA = 0u | (0u << 2) | (1u << 4) | (0u << 6) | (1u << 8) | (2u << 10) |
                             (0u << 12) | (0u << 14) | (1u << 16) | (0u << 18) | (1u << 20) | (2u << 22) |
                             (0u << 24) | (1u << 26) | (2u << 28) | (3u << 30);
     constexpr unsigned IB = 1u | (2u << 2) | (2u << 4) | (3u << 6) | (3u << 8) | (3u << 10) |
                             (0u << 12) | (1u << 14) | (1u << 16) | (2u << 18) | (2u << 20) | (2u << 22) |
                             (3u << 24) | (3u << 26) | (3u << 28) | (3u << 30);
-    for (int w = tid; w < ng * 16; w += nthreads) {
+    constexpr int ITER = ((TC / 4) * 16 + NT - 1) / NT;
+#pragma unroll
+    for (int it = 0; it < ITER; it++) {
+        const int w = tid + it * NT;
+        if (w >= ng * 16) break;
         const int gi = w >> 4, pidx = w & 15;
         const int a = (IA >> (2 * pidx)) & 3, b = (IB >> (2 * pidx)) & 3;
         const float* x = ktile + (4 * gi + a) * D;

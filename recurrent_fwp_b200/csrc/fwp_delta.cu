@@ -16,6 +16,7 @@ struct DeltaFwdParams {
     Row4 q, k, v, beta, v_old, v_ins, out;
     float* W; long long wN, wH, wE;
     int H, L, E, M;
+    int NH;     // number of sequences (N*H)
 };
 
 template <int D, int TC, typename T>
@@ -33,11 +34,12 @@ struct FwdStage {
 
 // SUM = true drops beta / v_old (sum rule): S_t = S_{t-1} + k_t (x) v_t.
 template <int D, int SPLIT, int TC, typename T, bool SUM>
-__global__ void __launch_bounds__(D * SPLIT) delta_fwd_step_kernel(const DeltaFwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) delta_fwd_step_kernel(const DeltaFwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = FwdStage<D, TC, T>;
     for (int i = g.tid; i < 2 * Stage::kFloats; i += G::NT) smem[i] = 0.f;
 
@@ -109,6 +111,7 @@ struct DeltaBwdParams {
     Row4 q, k, v, beta, v_old, gy, gq, gk, gv, gb;
     float* W; long long wN, wH, wE;
     int H, L, E, M;
+    int NH;     // number of sequences (N*H)
 };
 
 template <int D, int TC, typename T>
@@ -134,11 +137,12 @@ struct BwdStage {
 //   Gc += q (x) gy ; r = Gc^T k ; dv = beta r ; dbeta = r . (v - v_old) ; Gc -= k (x) beta r
 //   dq = S gy ; Gr += q (x) gy ; dk = Gr u ; S -= k (x) u ; dk -= S (beta r) ; Gr -= k (x) beta r
 template <int D, int SPLIT, int TC, typename T>
-__global__ void __launch_bounds__(D * SPLIT) delta_bwd_step_kernel(const DeltaBwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) delta_bwd_step_kernel(const DeltaBwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = BwdStage<D, TC, T>;
     constexpr int kXch = 2 * (2 * D + 8);   // per parity: u[D], br[D], dbeta partials[WPS<=8]
     for (int i = g.tid; i < 2 * Stage::kFloats + kXch; i += G::NT) smem[i] = 0.f;
@@ -254,6 +258,7 @@ __global__ void __launch_bounds__(D * SPLIT) delta_bwd_step_kernel(const DeltaBw
 struct SumBwdParams {
     Row4 q, k, v, gy, gq, gk, gv;
     int H, L, E, M;
+    int NH;     // number of sequences (N*H)
 };
 
 template <int D, int TC, typename T>
@@ -269,11 +274,12 @@ struct SumStage {
 };
 
 template <int D, int SPLIT, int TC, typename T>
-__global__ void __launch_bounds__(D * SPLIT) sum_bwd_kernel(const SumBwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) sum_bwd_kernel(const SumBwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = SumStage<D, TC, T>;
     for (int i = g.tid; i < 2 * Stage::kFloats; i += G::NT) smem[i] = 0.f;
     Src<T> sq, sk, sv, sg;
@@ -360,9 +366,9 @@ static int set_smem(K kernel, size_t bytes) {
 }
 
 template <typename K, typename P>
-static int launch(K kern, const P& p, int nseq, int threads, size_t bytes, cudaStream_t st) {
+static int launch(K kern, const P& p, int grid, int threads, size_t bytes, cudaStream_t st) {
     if (int rc = set_smem(kern, bytes)) return rc;
-    kern<<<nseq, threads, bytes, st>>>(p);
+    kern<<<grid, threads, bytes, st>>>(p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
@@ -370,28 +376,36 @@ static int launch(K kern, const P& p, int nseq, int threads, size_t bytes, cudaS
 
 template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
-    return launch(delta_fwd_kernel<D, SPLIT, TC, T, SUM>, p, nseq, D * SPLIT,
-                  BlkFwdSmem<D, TC, T>::kFloats * sizeof(float), st);
+    constexpr int NSL = slots_for(D * SPLIT);
+    return launch(delta_fwd_kernel<D, SPLIT, TC, T, SUM>, p, (nseq + NSL - 1) / NSL, NSL * (D * SPLIT + 32),
+                  NSL * WsFwdSmem<D, TC, T>::kFloats * sizeof(float), st);
 }
 template <int D, int SPLIT, int TC, typename T>
 static int launch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
-    return launch(delta_bwd_kernel<D, SPLIT, TC, T>, p, nseq, D * SPLIT,
-                  BlkBwdSmem<D, TC, T>::kFloats * sizeof(float), st);
+    constexpr int NSL = slots_for(D * SPLIT);
+    return launch(delta_bwd_kernel<D, SPLIT, TC, T>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
+                  NSL * WsBwdSmem<D, TC, T>::kFloats * sizeof(float), st);
 }
 template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd_step(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
-    return launch(delta_fwd_step_kernel<D, SPLIT, TC, T, SUM>, p, nseq, D * SPLIT,
-                  2 * FwdStage<D, TC, T>::kFloats * sizeof(float), st);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    return launch(delta_fwd_step_kernel<D, SPLIT, TC, T, SUM>, p, nseq / slots, D * SPLIT * slots,
+                  slots * 2 * FwdStage<D, TC, T>::kFloats * sizeof(float), st);
 }
 template <int D, int SPLIT, int TC, typename T>
 static int launch_bwd_step(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
-    return launch(delta_bwd_step_kernel<D, SPLIT, TC, T>, p, nseq, D * SPLIT,
-                  (2 * BwdStage<D, TC, T>::kFloats + 2 * (2 * D + 8)) * sizeof(float), st);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    return launch(delta_bwd_step_kernel<D, SPLIT, TC, T>, p, nseq / slots, D * SPLIT * slots,
+                  slots * (2 * BwdStage<D, TC, T>::kFloats + 2 * (2 * D + 8)) * sizeof(float), st);
 }
 template <int D, int SPLIT, int TC, typename T>
 static int launch_sum_bwd(const SumBwdParams& p, int nseq, cudaStream_t st) {
-    return launch(sum_bwd_kernel<D, SPLIT, TC, T>, p, nseq, D * SPLIT,
-                  2 * SumStage<D, TC, T>::kFloats * sizeof(float), st);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    return launch(sum_bwd_kernel<D, SPLIT, TC, T>, p, nseq / slots, D * SPLIT * slots,
+                  slots * 2 * SumStage<D, TC, T>::kFloats * sizeof(float), st);
 }
 
 // "delta.blocked" = 0 selects the per-step kernels (kept as a cross-check of the blocked form).
@@ -492,7 +506,7 @@ FWP_API int fwp_fast_weight_forward(int N, int H, int L, int E, int M,
     p.q = row4(Q); p.k = row4(K); p.v = row4(V); p.beta = row4(beta);
     p.v_old = row4(v_old); p.v_ins = row4(v_insert); p.out = row4(out);
     p.W = (float*)kv->data; p.wN = kv->stride[0]; p.wH = kv->stride[1]; p.wE = kv->stride[2];
-    p.H = H; p.L = L; p.E = E; p.M = M;
+    p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
     if (io_dtype == FWP_F32) return dispatch_fwd<float, false>(p, N * H, st, "delta_fwd");
     return dispatch_fwd<__nv_bfloat16, false>(p, N * H, st, "delta_fwd");
@@ -522,7 +536,7 @@ FWP_API int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
     p.q = row4(Q); p.k = row4(K); p.v = row4(V); p.beta = row4(beta); p.v_old = row4(v_old);
     p.gy = row4(grad_out); p.gq = row4(grad_Q); p.gk = row4(grad_K); p.gv = row4(grad_V); p.gb = row4(grad_beta);
     p.W = (float*)fw_mem->data; p.wN = fw_mem->stride[0]; p.wH = fw_mem->stride[1]; p.wE = fw_mem->stride[2];
-    p.H = H; p.L = L; p.E = E; p.M = M;
+    p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
     if (io_dtype == FWP_F32) return dispatch_bwd<float>(p, N * H, st);
     return dispatch_bwd<__nv_bfloat16>(p, N * H, st);
@@ -544,7 +558,7 @@ FWP_API int fwp_causal_dot_product(int N, int H, int L, int E, int M,
     p.q = row4(Q); p.k = row4(K); p.v = row4(V); p.beta = row4(nullptr);
     p.v_old = row4(nullptr); p.v_ins = row4(nullptr); p.out = row4(out);
     p.W = (float*)kv->data; p.wN = kv->stride[0]; p.wH = kv->stride[1]; p.wE = kv->stride[2];
-    p.H = H; p.L = L; p.E = E; p.M = M;
+    p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
     if (io_dtype == FWP_F32) return dispatch_fwd<float, true>(p, N * H, st, "sum_fwd");
     return dispatch_fwd<__nv_bfloat16, true>(p, N * H, st, "sum_fwd");
@@ -568,7 +582,7 @@ FWP_API int fwp_causal_dot_backward(int N, int H, int L, int E, int M,
     SumBwdParams p;
     p.q = row4(Q); p.k = row4(K); p.v = row4(V); p.gy = row4(grad_out);
     p.gq = row4(grad_Q); p.gk = row4(grad_K); p.gv = row4(grad_V);
-    p.H = H; p.L = L; p.E = E; p.M = M;
+    p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
     if (io_dtype == FWP_F32) return dispatch_sum_bwd<float>(p, N * H, st);
     return dispatch_sum_bwd<__nv_bfloat16>(p, N * H, st);

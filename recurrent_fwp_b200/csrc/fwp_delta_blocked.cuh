@@ -1,11 +1,10 @@
-// Delta rule, four-step blocked form (sm_100a).
+// Delta rule, four-step blocked and warp-specialised (sm_100a).
 //
-// The per-step kernels put one reduction round (dot, shuffle, scalar update) on
-// the dependency chain of every time step.  Here four consecutive steps share one
-// round: all eight matrix-vector products of a group are taken with the state at
-// the *start* of the group and corrected with Gram scalars of the group's keys
-// and queries, which do not depend on the state and are computed per chunk off
-// the chain:
+// Blocking.  The per-step kernels put one reduction round (dot, shuffle, scalar
+// update) on the dependency chain of every time step.  Here four consecutive
+// steps share one round: all matrix-vector products of a group are taken with the
+// state at the *start* of the group and corrected with Gram scalars of the
+// group's keys and queries, which do not depend on the state:
 //
 //   a_j = S^T k_j,  b_j = S^T q_j                      (S = state before the group)
 //   v_old_j = a_j + sum_{i<j}  u_i (k_i . k_j) ;  u_j = beta_j (v_j - v_old_j)
@@ -15,16 +14,39 @@
 //   a_j = G^T k_j
 //   r_j = a_j + gy_j (q_j . k_j) + sum_{i later than j} ( gy_i (q_i . k_j) - beta_i r_i (k_i . k_j) )
 //   G  += sum_j ( q_j (x) gy_j - k_j (x) beta_j r_j )
-// and the row-role part (dq, dk, rewind of S) runs per step from the published u_j, beta_j r_j.
 // The algebra is exact; only the fp32 summation order differs from the per-step form.
-// Outputs are staged in shared memory and written per chunk with 16-byte stores.
+//
+// Warp specialisation.  With a few hundred sequences there is about one warp per
+// SM sub-partition, so anything a warp does besides the dependency chain is
+// exposed latency.  Each CTA therefore runs separate warps in lock step, one
+// __syncthreads() per chunk:
+//   * a producer warp: cp.async staging two chunks ahead, Gram scalars one chunk
+//     ahead, and the 16-byte flush of the previous chunk's outputs;
+//   * forward: the consumer warps own the state columns and only run the group loop;
+//   * backward: "column" warps run the blocked chain on G and publish u_t, beta_t r_t
+//     for a whole chunk; "row" warps follow one chunk behind with the per-step part
+//     (dq, dk, in-place rewind of S).
 #pragma once
 #include "fwp_core.cuh"
 
 namespace fwp {
 
+template <int RL>
+__device__ __forceinline__ void zero_rows(float* tile, int r0, int r1, int tid, int nthreads) {
+    for (int i = r0 * RL + tid; i < r1 * RL; i += nthreads) tile[i] = 0.f;
+}
+
+__device__ __forceinline__ void load16(float (&gs)[16], const float* p) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float4 t4 = *reinterpret_cast<const float4*>(p + 4 * i);
+        gs[4 * i] = t4.x; gs[4 * i + 1] = t4.y; gs[4 * i + 2] = t4.z; gs[4 * i + 3] = t4.w;
+    }
+}
+
+// ------------------------------------------------------------------ forward
 template <int D, int TC, typename T>
-struct BlkFwdStage {
+struct WsFwdStage {
     Tile<D, TC, T> q, k, v;
     Tile<1, TC, T> b;
     static constexpr int kFloats = 3 * r4(Tile<D, TC, T>::kFloats) + r4(Tile<1, TC, T>::kFloats);
@@ -37,196 +59,272 @@ struct BlkFwdStage {
 };
 
 template <int D, int TC, typename T>
-struct BlkFwdSmem {
-    static constexpr int kStage = BlkFwdStage<D, TC, T>::kFloats;
+struct WsFwdSmem {
+    static constexpr int NS = 3;                       // stages: in flight, prepared, consumed
+    static constexpr int kStage = WsFwdStage<D, TC, T>::kFloats;
     static constexpr int kGram = (TC / 4) * 16;
-    static constexpr int kOut = TC * D;
-    static constexpr int kFloats = 2 * kStage + kGram + 3 * kOut;
+    static constexpr int kOut = 3 * TC * D;            // y, v_old, u
+    static constexpr int kFloats = NS * kStage + 2 * kGram + 2 * kOut;
 };
 
-// zero rows [r0, r1) of an fp32 tile with row length RL
-template <int RL>
-__device__ __forceinline__ void zero_rows(float* tile, int r0, int r1, int tid, int nthreads) {
-    for (int i = r0 * RL + tid; i < r1 * RL; i += nthreads) tile[i] = 0.f;
-}
-
 template <int D, int SPLIT, int TC, typename T, bool SUM>
-__global__ void __launch_bounds__(D * SPLIT) delta_fwd_kernel(const DeltaFwdParams p) {
+__global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta_fwd_kernel(const DeltaFwdParams p) {
     using G = Geo<D, SPLIT>;
-    using SM = BlkFwdSmem<D, TC, T>;
-    using Stage = BlkFwdStage<D, TC, T>;
+    using SM = WsFwdSmem<D, TC, T>;
+    using Stage = WsFwdStage<D, TC, T>;
     static_assert(TC % 4 == 0, "chunk must hold whole groups");
-    constexpr bool KEEP = G::NR <= 16;     // keep the four key slices in registers between dot and update
-    const G g;
-    FWP_PROF_BEGIN
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
-    for (int i = g.tid; i < SM::kFloats; i += G::NT) smem[i] = 0.f;
-    float* gram = smem + 2 * SM::kStage;
-    float* oy = gram + SM::kGram;
-    float* ovo = oy + SM::kOut;
-    float* ou = ovo + SM::kOut;
-
-    Src<T> sq, sk, sv, sb;
-    sq.init(p.q, n, h, p.E);
-    sk.init(p.k, n, h, p.E);
-    sv.init(p.v, n, h, p.M);
-    if (!SUM) sb.init(p.beta, n, h, 1);
-
-    float* W = p.W + n * p.wN + h * p.wH;
-    f2 S[G::NP];
-    load_cols(g, S, W, p.wE, p.E, p.M);
-    __syncthreads();
-
+    constexpr bool KEEP = G::NR <= 16;
+    constexpr int NSL = slots_for(G::NT);          // sequences per CTA
+    constexpr int NCONS = NSL * G::NT;             // consumer threads come first, then one producer warp per slot
+    const int tid = threadIdx.x;
+    const bool producer = tid >= NCONS;
+    const int slot = producer ? (tid - NCONS) >> 5 : tid / G::NT;
+    const int ptid = (tid - NCONS) & 31;
+    const int seq = blockIdx.x * NSL + slot;
+    const int n = seq / p.H, h = seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    for (int i = tid; i < NSL * SM::kFloats; i += NSL * (G::NT + 32)) smem_all[i] = 0.f;
+    float* smem = smem_all + slot * SM::kFloats;
+    float* gram0 = smem + SM::NS * SM::kStage;
+    float* out0 = gram0 + 2 * SM::kGram;
     const int nchunks = (p.L + TC - 1) / TC;
-    auto issue = [&](int c) {
-        Stage s; s.bind(smem + (c & 1) * SM::kStage);
-        const int t0 = c * TC, nt = min(TC, p.L - t0);
-        s.q.template load<G::NT>(sq, t0, nt, g.tid);
-        s.k.template load<G::NT>(sk, t0, nt, g.tid);
-        s.v.template load<G::NT>(sv, t0, nt, g.tid);
-        if (!SUM) s.b.template load<G::NT>(sb, t0, nt, g.tid);
-        cp_async_commit();
-    };
-    issue(0);
-    FWP_PROF(0)
-    for (int c = 0; c < nchunks; c++) {
-        if (c + 1 < nchunks) { issue(c + 1); FWP_PROF(1) cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-        __syncthreads();
-        FWP_PROF(2)
-        Stage s; s.bind(smem + (c & 1) * SM::kStage);
-        const int t0 = c * TC, nt = min(TC, p.L - t0);
-        const int ng = (nt + 3) >> 2;
-        if constexpr (sizeof(T) != 4) {
-            s.q.widen(nt, p.E, g.tid, G::NT);
-            s.k.widen(nt, p.E, g.tid, G::NT);
-            s.v.widen(nt, p.M, g.tid, G::NT);
-            if (!SUM) s.b.widen(nt, 1, g.tid, G::NT);
-        }
-        if (nt & 3) {   // pad the last group with inert steps (k = q = v = beta = 0)
-            zero_rows<D>(s.q.f, nt, 4 * ng, g.tid, G::NT);
-            zero_rows<D>(s.k.f, nt, 4 * ng, g.tid, G::NT);
-            zero_rows<D>(s.v.f, nt, 4 * ng, g.tid, G::NT);
-            if (!SUM) zero_rows<1>(s.b.f, nt, 4 * ng, g.tid, G::NT);
-        }
-        if ((sizeof(T) != 4) || (nt & 3)) __syncthreads();
-        gram_phase<D>(s.k.f, s.q.f, gram, ng, g.tid, G::NT);
-        __syncthreads();
-        FWP_PROF(3)
+    __syncthreads();
+    if (seq >= p.NH) {      // an empty slot of the last CTA only keeps the barrier count
+        for (int c = 0; c <= nchunks + 1; c++) __syncthreads();
+        return;
+    }
 
-        for (int gi = 0; gi < ng; gi++) {
-            const int tb = 4 * gi;
-            float a[4], b[4];
-            f2 kk[KEEP ? 4 : 1][G::NP];
-            if constexpr (G::NR <= 8) {
-                // small slices: fetch all eight operand slices first, then run the eight
-                // dot-product chains interleaved so that no FMA waits on its predecessor
-                f2 qq[4][G::NP];
+    if (producer) {
+        // ===================================================== producer warp
+        Src<T> sq, sk, sv, sb;
+        sq.init(p.q, n, h, p.E);
+        sk.init(p.k, n, h, p.E);
+        sv.init(p.v, n, h, p.M);
+        if (!SUM) sb.init(p.beta, n, h, 1);
+        auto issue = [&](int c) {
+            Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
+            const int t0 = c * TC, nt = min(TC, p.L - t0);
+            s.q.template load<32>(sq, t0, nt, ptid);
+            s.k.template load<32>(sk, t0, nt, ptid);
+            s.v.template load<32>(sv, t0, nt, ptid);
+            if (!SUM) s.b.template load<32>(sb, t0, nt, ptid);
+            cp_async_commit();
+        };
+        auto prepare = [&](int c) {     // chunk c has landed: widen, pad, Gram scalars
+            Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
+            const int nt = min(TC, p.L - c * TC), ng = (nt + 3) >> 2;
+            __syncwarp();
+            if constexpr (sizeof(T) != 4) {
+                s.q.widen(nt, p.E, ptid, 32);
+                s.k.widen(nt, p.E, ptid, 32);
+                s.v.widen(nt, p.M, ptid, 32);
+                if (!SUM) s.b.widen(nt, 1, ptid, 32);
+            }
+            if (nt & 3) {   // pad the last group with inert steps (k = q = v = beta = 0)
+                zero_rows<D>(s.q.f, nt, 4 * ng, ptid, 32);
+                zero_rows<D>(s.k.f, nt, 4 * ng, ptid, 32);
+                zero_rows<D>(s.v.f, nt, 4 * ng, ptid, 32);
+                if (!SUM) zero_rows<1>(s.b.f, nt, 4 * ng, ptid, 32);
+            }
+            if ((sizeof(T) != 4) || (nt & 3)) __syncwarp();
+            gram_phase<D, 32, TC>(s.k.f, s.q.f, gram0 + (c & 1) * SM::kGram, ng, ptid);
+        };
+        auto flush = [&](int c) {
+            const float* o = out0 + (c & 1) * SM::kOut;
+            const int t0 = c * TC, nt = min(TC, p.L - t0);
+            flush_rows<D, 32, T, TC>(o, p.out, n, h, t0, nt, p.M, ptid);
+            if constexpr (!SUM) {
+                flush_rows<D, 32, float, TC>(o + TC * D, p.v_old, n, h, t0, nt, p.M, ptid);
+                if (p.v_ins.p) flush_rows<D, 32, float, TC>(o + 2 * TC * D, p.v_ins, n, h, t0, nt, p.M, ptid);
+            }
+        };
+        FWP_PROF_BEGIN
+        issue(0);
+        if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        prepare(0);
+        __syncthreads();
+        FWP_PROF(0)
+        for (int c = 0; c <= nchunks; c++) {
+            if (c + 2 < nchunks) issue(c + 2);      // lands while this iteration's other work runs
+            FWP_PROF(4)
+            if (c >= 1) flush(c - 1);
+            FWP_PROF(3)
+            if (c + 1 < nchunks) {
+                if (c + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
+                FWP_PROF(1)
+                prepare(c + 1);
+            }
+            FWP_PROF(2)
+            __syncthreads();
+            FWP_PROF(5)
+        }
+        FWP_PROF_END(0, ptid == 0 && slot == 0)
+    } else {
+        // ===================================================== consumer warps: the group loop
+        const G g(tid);
+        float* W = p.W + n * p.wN + h * p.wH;
+        f2 S[G::NP];
+        FWP_PROF_BEGIN
+        load_cols(g, S, W, p.wE, p.E, p.M);
+        __syncthreads();
+        FWP_PROF(0)
+        for (int c = 0; c <= nchunks; c++) {
+            if (c < nchunks) {
+                Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
+                const float* gram = gram0 + (c & 1) * SM::kGram;
+                float* oy = out0 + (c & 1) * SM::kOut;
+                float* ovo = oy + TC * D;
+                float* ou = ovo + TC * D;
+                const int nt = min(TC, p.L - c * TC), ng = (nt + 3) >> 2;
+                // One group: dots with the pre-group state, scalar recurrences, rank-4 update, staged outputs.
+                // `cur` holds this group's operand slices (already in registers); `nxt` receives the next
+                // group's slices, whose loads are issued before this group's arithmetic.
+                auto tail = [&](int tb, float (&a)[4], float (&b)[4], auto&& update) {
+                    float gs[16], vv[4];
+#ifdef FWP_ABL_NOGRAM
+                    for (int i = 0; i < 16; i++) gs[i] = 0.01f * i;
+#else
+                    load16(gs, gram + (tb >> 2) * 16);
+#endif
+                    float be[4] = {1.f, 1.f, 1.f, 1.f};
+                    if constexpr (!SUM) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
+                        be[0] = b4.x; be[1] = b4.y; be[2] = b4.z; be[3] = b4.w;
+                    }
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
-                    lds_slice<G::NR>(qq[j], s.q.f + (tb + j) * D + g.off);
-                }
-                FWP_PROF(8)
-                f2 aa[4] = {0ull, 0ull, 0ull, 0ull}, bb[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-                for (int i = 0; i < G::NP; i++) {
+                    for (int j = 0; j < 4; j++) vv[j] = s.v.f[(tb + j) * D + g.idx];
+#ifndef FWP_ABL_NOSHFL
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        if constexpr (!SUM) aa[j] = ffma2(S[i], kk[j][i], aa[j]);
-                        bb[j] = ffma2(S[i], qq[j][i], bb[j]);
+                        if constexpr (!SUM) a[j] = reduce_split<SPLIT>(a[j]);
+                        b[j] = reduce_split<SPLIT>(b[j]);
+                    }
+#endif
+                    float u[4], vo[4], y[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        if constexpr (SUM) {
+                            vo[j] = 0.f;
+                            u[j] = vv[j];
+                        } else {
+                            float acc = a[j];
+#ifndef FWP_ABL_NOSCALAR
+#pragma unroll
+                            for (int i = 0; i < j; i++) acc = fmaf(u[i], gs[gram_kk(i, j)], acc);
+#endif
+                            vo[j] = acc;
+                            u[j] = be[j] * (vv[j] - acc);
+                        }
+                        float yy = b[j];
+#ifndef FWP_ABL_NOSCALAR
+#pragma unroll
+                        for (int i = 0; i <= j; i++) yy = fmaf(u[i], gs[gram_kq(i, j)], yy);
+#endif
+                        y[j] = yy;
+                    }
+#ifndef FWP_ABL_NOAXPY
+                    update(u);
+#endif
+#ifdef FWP_ABL_NOSTS
+                    if (y[0] + y[1] + y[2] + y[3] + u[3] + vo[3] == 123.456f)
+#else
+                    if (g.s == 0)
+#endif
+                    {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            oy[(tb + j) * D + g.idx] = y[j];
+                            if constexpr (!SUM) {
+                                ovo[(tb + j) * D + g.idx] = vo[j];
+                                ou[(tb + j) * D + g.idx] = u[j];
+                            }
+                        }
+                    }
+                };
+                if constexpr (G::NR <= 8) {
+                    auto fetch = [&](int tb, f2 (&kk)[4][G::NP], f2 (&qq)[4][G::NP]) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+#ifdef FWP_ABL_NOFETCH
+                            for (int i = 0; i < G::NP; i++) { kk[j][i] = 0x3c23d70a3c23d70aull + tb; qq[j][i] = 0x3c23d70a3c23d70aull + j; }
+#else
+                            lds_slice_early<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                            lds_slice_early<G::NR>(qq[j], s.q.f + (tb + j) * D + g.off);
+#endif
+                        }
+                    };
+                    auto group = [&](int gi, f2 (&kk)[4][G::NP], f2 (&qq)[4][G::NP],
+                                     f2 (&kn)[4][G::NP], f2 (&qn)[4][G::NP]) {
+                        if (gi + 1 < ng) fetch(4 * (gi + 1), kn, qn);
+                        f2 aa[4] = {0ull, 0ull, 0ull, 0ull}, bb[4] = {0ull, 0ull, 0ull, 0ull};
+#ifndef FWP_ABL_NODOTS
+#pragma unroll
+                        for (int i = 0; i < G::NP; i++) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                if constexpr (!SUM) aa[j] = ffma2(S[i], kk[j][i], aa[j]);
+                                bb[j] = ffma2(S[i], qq[j][i], bb[j]);
+                            }
+                        }
+#else
+#pragma unroll
+                        for (int j = 0; j < 4; j++) { aa[j] = kk[j][0]; bb[j] = qq[j][1]; }
+#endif
+                        float a[4], b[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) { a[j] = SUM ? 0.f : f2_hsum(aa[j]); b[j] = f2_hsum(bb[j]); }
+                        tail(4 * gi, a, b, [&](const float (&u)[4]) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) axpy2<G::NP>(S, kk[j], u[j]);
+                        });
+                    };
+                    f2 kA[4][G::NP], qA[4][G::NP], kB[4][G::NP], qB[4][G::NP];
+                    fetch(0, kA, qA);
+                    for (int gi = 0; gi < ng; gi += 2) {
+                        group(gi, kA, qA, kB, qB);
+                        if (gi + 1 < ng) group(gi + 1, kB, qB, kA, qA);
+                    }
+                } else {
+                    for (int gi = 0; gi < ng; gi++) {
+                        const int tb = 4 * gi;
+                        float a[4], b[4];
+                        f2 kk[KEEP ? 4 : 1][G::NP];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            f2 (&kj)[G::NP] = kk[KEEP ? j : 0];
+                            lds_slice<G::NR>(kj, s.k.f + (tb + j) * D + g.off);
+                            if constexpr (!SUM) a[j] = dot2_chain<G::NP>(S, kj); else a[j] = 0.f;
+                            f2 qq[G::NP];
+                            lds_slice<G::NR>(qq, s.q.f + (tb + j) * D + g.off);
+                            b[j] = dot2_chain<G::NP>(S, qq);
+                        }
+                        tail(tb, a, b, [&](const float (&u)[4]) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                if constexpr (KEEP) {
+                                    axpy2<G::NP>(S, kk[j], u[j]);
+                                } else {
+                                    lds_slice<G::NR>(kk[0], s.k.f + (tb + j) * D + g.off);
+                                    axpy2<G::NP>(S, kk[0], u[j]);
+                                }
+                            }
+                        });
                     }
                 }
-#pragma unroll
-                for (int j = 0; j < 4; j++) { a[j] = SUM ? 0.f : f2_hsum(aa[j]); b[j] = f2_hsum(bb[j]); }
-                FWP_PROF(9)
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    f2 (&kj)[G::NP] = kk[KEEP ? j : 0];
-                    lds_slice<G::NR>(kj, s.k.f + (tb + j) * D + g.off);
-                    if constexpr (!SUM) a[j] = dot2_chain<G::NP>(S, kj); else a[j] = 0.f;
-                    f2 qq[G::NP];
-                    lds_slice<G::NR>(qq, s.q.f + (tb + j) * D + g.off);
-                    b[j] = dot2_chain<G::NP>(S, qq);
-                }
             }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                if constexpr (!SUM) a[j] = reduce_split<SPLIT>(a[j]);
-                b[j] = reduce_split<SPLIT>(b[j]);
-            }
-            FWP_PROF(10)
-            float gs[16];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float4 t4 = *reinterpret_cast<const float4*>(gram + gi * 16 + 4 * i);
-                gs[4 * i] = t4.x; gs[4 * i + 1] = t4.y; gs[4 * i + 2] = t4.z; gs[4 * i + 3] = t4.w;
-            }
-            float be[4] = {1.f, 1.f, 1.f, 1.f};
-            if constexpr (!SUM) {
-                const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
-                be[0] = b4.x; be[1] = b4.y; be[2] = b4.z; be[3] = b4.w;
-            }
-            float u[4], vo[4], y[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float vv = s.v.f[(tb + j) * D + g.idx];
-                if constexpr (SUM) {
-                    vo[j] = 0.f;
-                    u[j] = vv;
-                } else {
-                    float acc = a[j];
-#pragma unroll
-                    for (int i = 0; i < j; i++) acc = fmaf(u[i], gs[gram_kk(i, j)], acc);
-                    vo[j] = acc;
-                    u[j] = be[j] * (vv - acc);
-                }
-                float yy = b[j];
-#pragma unroll
-                for (int i = 0; i <= j; i++) yy = fmaf(u[i], gs[gram_kq(i, j)], yy);
-                y[j] = yy;
-            }
-            FWP_PROF(11)
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                if constexpr (KEEP) {
-                    axpy2<G::NP>(S, kk[j], u[j]);
-                } else {
-                    lds_slice<G::NR>(kk[0], s.k.f + (tb + j) * D + g.off);
-                    axpy2<G::NP>(S, kk[0], u[j]);
-                }
-            }
-            FWP_PROF(12)
-            if (g.s == 0) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    oy[(tb + j) * D + g.idx] = y[j];
-                    if constexpr (!SUM) {
-                        ovo[(tb + j) * D + g.idx] = vo[j];
-                        ou[(tb + j) * D + g.idx] = u[j];
-                    }
-                }
-            }
-            FWP_PROF(13)
+            FWP_PROF(1)
+            __syncthreads();
+            FWP_PROF(2)
         }
-        __syncthreads();
-        FWP_PROF(4)
-        flush_rows<D, G::NT, T>(oy, p.out, n, h, t0, nt, p.M, g.tid);
-        if constexpr (!SUM) {
-            flush_rows<D, G::NT, float>(ovo, p.v_old, n, h, t0, nt, p.M, g.tid);
-            if (p.v_ins.p) flush_rows<D, G::NT, float>(ou, p.v_ins, n, h, t0, nt, p.M, g.tid);
-        }
-        FWP_PROF(5)
+        store_cols(g, S, W, p.wE, p.E, p.M);
+        FWP_PROF(3)
+        FWP_PROF_END(8, tid == 0)
     }
-    store_cols(g, S, W, p.wE, p.E, p.M);
-    FWP_PROF(6)
-    FWP_PROF_END
 }
 
 // ------------------------------------------------------------------ backward
 template <int D, int TC, typename T>
-struct BlkBwdStage {
+struct WsBwdStage {
     Tile<D, TC, T> q, k, v, gy;
     Tile<D, TC, float> vo;
     Tile<1, TC, T> b;
@@ -242,208 +340,254 @@ struct BlkBwdStage {
 };
 
 template <int D, int TC, typename T>
-struct BlkBwdSmem {
-    static constexpr int kStage = BlkBwdStage<D, TC, T>::kFloats;
+struct WsBwdSmem {
+    static constexpr int NS = 4;                       // in flight, prepared, column role, row role
+    static constexpr int kStage = WsBwdStage<D, TC, T>::kFloats;
     static constexpr int kGram = (TC / 4) * 16;
-    static constexpr int kOut = TC * D;
-    static constexpr int kXg = 8 * D + 32;          // per group parity: u[4][D], br[4][D], dbeta partials[4][8]
-    static constexpr int kFloats = 2 * kStage + kGram + 3 * kOut + r4(TC) + 2 * kXg;
+    static constexpr int kX = 2 * TC * D + TC * 8;     // u[TC][D], beta*r[TC][D] (= dv), dbeta partials[TC][8]
+    static constexpr int kO = 2 * TC * D;              // dq[TC][D], dk[TC][D]
+    static constexpr int kFloats = NS * kStage + 2 * kGram + 2 * kX + 2 * kO + r4(TC);
 };
 
 template <int D, int SPLIT, int TC, typename T>
-__global__ void __launch_bounds__(D * SPLIT) delta_bwd_kernel(const DeltaBwdParams p) {
+__global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) delta_bwd_kernel(const DeltaBwdParams p) {
     using G = Geo<D, SPLIT>;
-    using SM = BlkBwdSmem<D, TC, T>;
-    using Stage = BlkBwdStage<D, TC, T>;
+    using SM = WsBwdSmem<D, TC, T>;
+    using Stage = WsBwdStage<D, TC, T>;
     static_assert(TC % 4 == 0, "chunk must hold whole groups");
     constexpr bool KEEP = G::NR <= 8;
     constexpr int HS = sum4_stride<SPLIT>();
-    const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
-    for (int i = g.tid; i < SM::kFloats; i += G::NT) smem[i] = 0.f;
-    float* gram = smem + 2 * SM::kStage;
-    float* odq = gram + SM::kGram;
-    float* odk = odq + SM::kOut;
-    float* odv = odk + SM::kOut;
-    float* odb = odv + SM::kOut;
-    float* xch = odb + r4(TC);
-
-    Src<T> sq, sk, sv, sg, sb;
-    Src<float> so;
-    sq.init(p.q, n, h, p.E);
-    sk.init(p.k, n, h, p.E);
-    sv.init(p.v, n, h, p.M);
-    sg.init(p.gy, n, h, p.M);
-    so.init(p.v_old, n, h, p.M);
-    sb.init(p.beta, n, h, 1);
-
-    float* W = p.W + n * p.wN + h * p.wH;
-    f2 Sr[G::NP], Gr[G::NP], Gc[G::NP];
-    load_rows(g, Sr, W, p.wE, p.E, p.M);
-#pragma unroll
-    for (int i = 0; i < G::NP; i++) { Gr[i] = 0ull; Gc[i] = 0ull; }
-    __syncthreads();
-
+    constexpr int NSL = slots_for(G::NT);          // sequences per CTA
+    constexpr int NCONS = NSL * G::NT;             // column-role threads, then row-role threads, then producers
+    const int tid = threadIdx.x;
+    const int role = tid < NCONS ? 0 : (tid < 2 * NCONS ? 1 : 2);     // 0 column, 1 row, 2 producer
+    const int rtid = tid - role * NCONS;                               // index within the role
+    const int slot = role == 2 ? rtid >> 5 : rtid / G::NT;
+    const int seq = blockIdx.x * NSL + slot;
+    const int n = seq / p.H, h = seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    for (int i = tid; i < NSL * SM::kFloats; i += NSL * (2 * G::NT + 32)) smem_all[i] = 0.f;
+    float* smem = smem_all + slot * SM::kFloats;
+    float* gram0 = smem + SM::NS * SM::kStage;
+    float* x0 = gram0 + 2 * SM::kGram;
+    float* o0 = x0 + 2 * SM::kX;
+    float* dbt = o0 + 2 * SM::kO;       // dbeta of one chunk, assembled by the producer before its flush
     const int nchunks = (p.L + TC - 1) / TC;
-    auto issue = [&](int jc) {   // jc-th chunk counted from the end of the sequence
-        Stage s; s.bind(smem + (jc & 1) * SM::kStage);
-        const int c = nchunks - 1 - jc;
-        const int t0 = c * TC, nt = min(TC, p.L - t0);
-        s.q.template load<G::NT>(sq, t0, nt, g.tid);
-        s.k.template load<G::NT>(sk, t0, nt, g.tid);
-        s.v.template load<G::NT>(sv, t0, nt, g.tid);
-        s.gy.template load<G::NT>(sg, t0, nt, g.tid);
-        s.vo.template load<G::NT>(so, t0, nt, g.tid);
-        s.b.template load<G::NT>(sb, t0, nt, g.tid);
-        cp_async_commit();
-    };
-    issue(0);
-    int par = 0;
-    for (int jc = 0; jc < nchunks; jc++) {
-        if (jc + 1 < nchunks) { issue(jc + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-        __syncthreads();
-        Stage s; s.bind(smem + (jc & 1) * SM::kStage);
-        const int c = nchunks - 1 - jc;
-        const int t0 = c * TC, nt = min(TC, p.L - t0);
-        const int ng = (nt + 3) >> 2;
-        if constexpr (sizeof(T) != 4) {
-            s.q.widen(nt, p.E, g.tid, G::NT);
-            s.k.widen(nt, p.E, g.tid, G::NT);
-            s.v.widen(nt, p.M, g.tid, G::NT);
-            s.gy.widen(nt, p.M, g.tid, G::NT);
-            s.b.widen(nt, 1, g.tid, G::NT);
-        }
-        if (nt & 3) {
-            zero_rows<D>(s.q.f, nt, 4 * ng, g.tid, G::NT);
-            zero_rows<D>(s.k.f, nt, 4 * ng, g.tid, G::NT);
-            zero_rows<D>(s.v.f, nt, 4 * ng, g.tid, G::NT);
-            zero_rows<D>(s.gy.f, nt, 4 * ng, g.tid, G::NT);
-            zero_rows<D>(s.vo.f, nt, 4 * ng, g.tid, G::NT);
-            zero_rows<1>(s.b.f, nt, 4 * ng, g.tid, G::NT);
-        }
-        if ((sizeof(T) != 4) || (nt & 3)) __syncthreads();
-        gram_phase<D>(s.k.f, s.q.f, gram, ng, g.tid, G::NT);
-        __syncthreads();
-
-        for (int gi = ng - 1; gi >= 0; gi--) {
-            const int tb = 4 * gi;
-            const int nv = min(4, nt - tb);            // valid steps in this group
-            float* xu = xch + par * SM::kXg;           // [4][D]
-            float* xbr = xu + 4 * D;                   // [4][D]
-            float* xdb = xbr + 4 * D;                  // [4][8]
-            par ^= 1;
-            // ---------------- column role: one reduction round for the four steps
-            {
-                float a[4];
-                f2 kk[KEEP ? 4 : 1][G::NP];
-                if constexpr (KEEP) {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
-                    f2 aa[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-                    for (int i = 0; i < G::NP; i++) {
-#pragma unroll
-                        for (int j = 0; j < 4; j++) aa[j] = ffma2(Gc[i], kk[j][i], aa[j]);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; j++) a[j] = f2_hsum(aa[j]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        lds_slice<G::NR>(kk[0], s.k.f + (tb + j) * D + g.off);
-                        a[j] = dot2_chain<G::NP>(Gc, kk[0]);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 4; j++) a[j] = reduce_split<SPLIT>(a[j]);
-                float gs[16];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float4 t4 = *reinterpret_cast<const float4*>(gram + gi * 16 + 4 * i);
-                    gs[4 * i] = t4.x; gs[4 * i + 1] = t4.y; gs[4 * i + 2] = t4.z; gs[4 * i + 3] = t4.w;
-                }
-                const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
-                const float be[4] = {b4.x, b4.y, b4.z, b4.w};
-                float gy[4], w[4], r[4], br[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    gy[j] = s.gy.f[(tb + j) * D + g.idx];
-                    w[j] = s.v.f[(tb + j) * D + g.idx] - s.vo.f[(tb + j) * D + g.idx];
-                }
-#pragma unroll
-                for (int j = 3; j >= 0; j--) {          // time reversed
-                    float acc = fmaf(gy[j], gs[gram_kq(j, j)], a[j]);
-#pragma unroll
-                    for (int i = 3; i > j; i--) {
-                        acc = fmaf(gy[i], gs[gram_kq(j, i)], acc);
-                        acc = fmaf(-br[i], gs[gram_kk(j, i)], acc);
-                    }
-                    r[j] = acc;
-                    br[j] = be[j] * acc;
-                }
-#pragma unroll
-                for (int j = 3; j >= 0; j--) {
-                    f2 qq[G::NP];
-                    lds_slice<G::NR>(qq, s.q.f + (tb + j) * D + g.off);
-                    axpy2<G::NP>(Gc, qq, gy[j]);
-                    if constexpr (KEEP) {
-                        axpy2<G::NP>(Gc, kk[j], -br[j]);
-                    } else {
-                        lds_slice<G::NR>(kk[0], s.k.f + (tb + j) * D + g.off);
-                        axpy2<G::NP>(Gc, kk[0], -br[j]);
-                    }
-                }
-                const float tot = warp_sum4_idx<SPLIT>(r[0] * w[0], r[1] * w[1], r[2] * w[2], r[3] * w[3], g.lane);
-                if (g.s == 0) {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        xu[j * D + g.idx] = be[j] * w[j];
-                        xbr[j * D + g.idx] = br[j];
-                        odv[(tb + j) * D + g.idx] = br[j];
-                    }
-                    const int lm = g.lane % G::MC;
-                    if ((lm % HS) == 0 && lm / HS < 4) {
-                        if (G::WPS == 1) odb[tb + lm / HS] = tot; else xdb[(lm / HS) * 8 + g.warp] = tot;
-                    }
-                }
-            }
-            cta_sync<G::WPS>();
-            // ---------------- row role: per step, time reversed
-            for (int j = nv - 1; j >= 0; j--) {
-                const int t = tb + j;
-                f2 gr[G::NP], ur[G::NP], brr[G::NP];
-                lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
-                lds_slice<G::NR>(ur, xu + j * D + g.off);
-                lds_slice<G::NR>(brr, xbr + j * D + g.off);
-                const float qe = s.q.f[t * D + g.idx], ke = s.k.f[t * D + g.idx];
-                float dq = dot2<G::NP>(Sr, gr);
-                axpy2<G::NP>(Gr, gr, qe);
-                float dk = dot2<G::NP>(Gr, ur);
-                axpy2<G::NP>(Sr, ur, -ke);
-                dk -= dot2<G::NP>(Sr, brr);
-                axpy2<G::NP>(Gr, brr, -ke);
-                dq = reduce_split<SPLIT>(dq);
-                dk = reduce_split<SPLIT>(dk);
-                if (g.s == 0) {
-                    odq[t * D + g.idx] = dq;
-                    odk[t * D + g.idx] = dk;
-                }
-                if (G::WPS > 1 && g.tid == 0) {
-                    float db = xdb[j * 8];
-#pragma unroll
-                    for (int w2 = 1; w2 < G::WPS; w2++) db += xdb[j * 8 + w2];
-                    odb[t] = db;
-                }
-            }
-        }
-        __syncthreads();
-        flush_rows<D, G::NT, T>(odq, p.gq, n, h, t0, nt, p.E, g.tid);
-        flush_rows<D, G::NT, T>(odk, p.gk, n, h, t0, nt, p.E, g.tid);
-        flush_rows<D, G::NT, T>(odv, p.gv, n, h, t0, nt, p.M, g.tid);
-        flush_rows<1, G::NT, T>(odb, p.gb, n, h, t0, nt, 1, g.tid);
+    __syncthreads();
+    if (seq >= p.NH) {      // an empty slot of the last CTA only keeps the barrier count
+        for (int i = 0; i <= nchunks + 2; i++) __syncthreads();
+        return;
     }
-    store_rows(g, Sr, W, p.wE, p.E, p.M);
+    // chunk index jc counts from the end of the sequence; nchunks-1-jc is the time-order chunk
+    if (role == 2) {
+        // ===================================================== producer warp
+        const int ptid = rtid & 31;
+        Src<T> sq, sk, sv, sg, sb;
+        Src<float> so;
+        sq.init(p.q, n, h, p.E);
+        sk.init(p.k, n, h, p.E);
+        sv.init(p.v, n, h, p.M);
+        sg.init(p.gy, n, h, p.M);
+        so.init(p.v_old, n, h, p.M);
+        sb.init(p.beta, n, h, 1);
+        auto issue = [&](int jc) {
+            Stage s; s.bind(smem + (jc % SM::NS) * SM::kStage);
+            const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
+            s.q.template load<32>(sq, t0, nt, ptid);
+            s.k.template load<32>(sk, t0, nt, ptid);
+            s.v.template load<32>(sv, t0, nt, ptid);
+            s.gy.template load<32>(sg, t0, nt, ptid);
+            s.vo.template load<32>(so, t0, nt, ptid);
+            s.b.template load<32>(sb, t0, nt, ptid);
+            cp_async_commit();
+        };
+        auto prepare = [&](int jc) {
+            Stage s; s.bind(smem + (jc % SM::NS) * SM::kStage);
+            const int nt = min(TC, p.L - (nchunks - 1 - jc) * TC), ng = (nt + 3) >> 2;
+            __syncwarp();
+            if constexpr (sizeof(T) != 4) {
+                s.q.widen(nt, p.E, ptid, 32);
+                s.k.widen(nt, p.E, ptid, 32);
+                s.v.widen(nt, p.M, ptid, 32);
+                s.gy.widen(nt, p.M, ptid, 32);
+                s.b.widen(nt, 1, ptid, 32);
+            }
+            if (nt & 3) {
+                zero_rows<D>(s.q.f, nt, 4 * ng, ptid, 32);
+                zero_rows<D>(s.k.f, nt, 4 * ng, ptid, 32);
+                zero_rows<D>(s.v.f, nt, 4 * ng, ptid, 32);
+                zero_rows<D>(s.gy.f, nt, 4 * ng, ptid, 32);
+                zero_rows<D>(s.vo.f, nt, 4 * ng, ptid, 32);
+                zero_rows<1>(s.b.f, nt, 4 * ng, ptid, 32);
+            }
+            if ((sizeof(T) != 4) || (nt & 3)) __syncwarp();
+            gram_phase<D, 32, TC>(s.k.f, s.q.f, gram0 + (jc & 1) * SM::kGram, ng, ptid);
+        };
+        auto flush_col = [&](int jc) {      // dv = beta*r and dbeta of the chunk the column role just finished
+            const float* x = x0 + (jc & 1) * SM::kX;
+            const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
+            flush_rows<D, 32, T, TC>(x + TC * D, p.gv, n, h, t0, nt, p.M, ptid);
+            const float* part = x + 2 * TC * D;
+            for (int t = ptid; t < nt; t += 32) {
+                float db = part[t * 8];
+#pragma unroll
+                for (int w = 1; w < G::WPS; w++) db += part[t * 8 + w];
+                dbt[t] = db;
+            }
+            __syncwarp();
+            flush_rows<1, 32, T, 0>(dbt, p.gb, n, h, t0, nt, 1, ptid);
+            __syncwarp();
+        };
+        auto flush_row = [&](int jc) {
+            const float* o = o0 + (jc & 1) * SM::kO;
+            const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
+            flush_rows<D, 32, T, TC>(o, p.gq, n, h, t0, nt, p.E, ptid);
+            flush_rows<D, 32, T, TC>(o + TC * D, p.gk, n, h, t0, nt, p.E, ptid);
+        };
+        issue(0);
+        if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        prepare(0);
+        __syncthreads();
+        for (int i = 0; i <= nchunks + 1; i++) {
+            if (i + 2 < nchunks) issue(i + 2);      // lands while this iteration's other work runs
+            if (i >= 1 && i - 1 < nchunks) flush_col(i - 1);
+            if (i >= 2) flush_row(i - 2);
+            if (i + 1 < nchunks) {
+                if (i + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
+                prepare(i + 1);
+            }
+            __syncthreads();
+        }
+    } else if (role == 0) {
+        // ===================================================== column role: blocked chain on G
+        const G g(rtid);
+        f2 Gc[G::NP];
+#pragma unroll
+        for (int i = 0; i < G::NP; i++) Gc[i] = 0ull;
+        __syncthreads();
+        for (int i = 0; i <= nchunks + 1; i++) {
+            if (i < nchunks) {
+                const int jc = i;
+                Stage s; s.bind(smem + (jc % SM::NS) * SM::kStage);
+                const float* gram = gram0 + (jc & 1) * SM::kGram;
+                float* xu = x0 + (jc & 1) * SM::kX;
+                float* xbr = xu + TC * D;
+                float* xdb = xbr + TC * D;
+                const int nt = min(TC, p.L - (nchunks - 1 - jc) * TC), ng = (nt + 3) >> 2;
+                for (int gi = ng - 1; gi >= 0; gi--) {
+                    const int tb = 4 * gi;
+                    float a[4];
+                    f2 kk[KEEP ? 4 : 1][G::NP];
+                    if constexpr (KEEP) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                        f2 aa[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+                        for (int q = 0; q < G::NP; q++) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) aa[j] = ffma2(Gc[q], kk[j][q], aa[j]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; j++) a[j] = f2_hsum(aa[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            lds_slice<G::NR>(kk[0], s.k.f + (tb + j) * D + g.off);
+                            a[j] = dot2_chain<G::NP>(Gc, kk[0]);
+                        }
+                    }
+                    float gs[16];
+                    load16(gs, gram + gi * 16);
+                    const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
+                    const float be[4] = {b4.x, b4.y, b4.z, b4.w};
+                    float gy[4], w[4], r[4], br[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        gy[j] = s.gy.f[(tb + j) * D + g.idx];
+                        w[j] = s.v.f[(tb + j) * D + g.idx] - s.vo.f[(tb + j) * D + g.idx];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) a[j] = reduce_split<SPLIT>(a[j]);
+#pragma unroll
+                    for (int j = 3; j >= 0; j--) {          // time reversed
+                        float acc = fmaf(gy[j], gs[gram_kq(j, j)], a[j]);
+#pragma unroll
+                        for (int q = 3; q > j; q--) {
+                            acc = fmaf(gy[q], gs[gram_kq(j, q)], acc);
+                            acc = fmaf(-br[q], gs[gram_kk(j, q)], acc);
+                        }
+                        r[j] = acc;
+                        br[j] = be[j] * acc;
+                    }
+#pragma unroll
+                    for (int j = 3; j >= 0; j--) {
+                        f2 qq[G::NP];
+                        lds_slice<G::NR>(qq, s.q.f + (tb + j) * D + g.off);
+                        axpy2<G::NP>(Gc, qq, gy[j]);
+                        if constexpr (KEEP) {
+                            axpy2<G::NP>(Gc, kk[j], -br[j]);
+                        } else {
+                            lds_slice<G::NR>(kk[0], s.k.f + (tb + j) * D + g.off);
+                            axpy2<G::NP>(Gc, kk[0], -br[j]);
+                        }
+                    }
+                    const float tot = warp_sum4_idx<SPLIT>(r[0] * w[0], r[1] * w[1], r[2] * w[2], r[3] * w[3], g.lane);
+                    if (g.s == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            xu[(tb + j) * D + g.idx] = be[j] * w[j];
+                            xbr[(tb + j) * D + g.idx] = br[j];
+                        }
+                        const int lm = g.lane % G::MC;
+                        if ((lm % HS) == 0 && lm / HS < 4) xdb[(tb + lm / HS) * 8 + g.warp] = tot;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    } else {
+        // ===================================================== row role: per step, one chunk behind
+        const G g(rtid);
+        float* W = p.W + n * p.wN + h * p.wH;
+        f2 Sr[G::NP], Gr[G::NP];
+        load_rows(g, Sr, W, p.wE, p.E, p.M);
+#pragma unroll
+        for (int i = 0; i < G::NP; i++) Gr[i] = 0ull;
+        __syncthreads();
+        for (int i = 0; i <= nchunks + 1; i++) {
+            if (i >= 1 && i - 1 < nchunks) {
+                const int jc = i - 1;
+                Stage s; s.bind(smem + (jc % SM::NS) * SM::kStage);
+                const float* xu = x0 + (jc & 1) * SM::kX;
+                const float* xbr = xu + TC * D;
+                float* odq = o0 + (jc & 1) * SM::kO;
+                float* odk = odq + TC * D;
+                const int nt = min(TC, p.L - (nchunks - 1 - jc) * TC);
+#pragma unroll 2
+                for (int t = nt - 1; t >= 0; t--) {
+                    f2 gr[G::NP], ur[G::NP], brr[G::NP];
+                    lds_slice<G::NR>(gr, s.gy.f + t * D + g.off);
+                    lds_slice<G::NR>(ur, xu + t * D + g.off);
+                    lds_slice<G::NR>(brr, xbr + t * D + g.off);
+                    const float qe = s.q.f[t * D + g.idx], ke = s.k.f[t * D + g.idx];
+                    float dq = dot2<G::NP>(Sr, gr);
+                    axpy2<G::NP>(Gr, gr, qe);
+                    float dk = dot2<G::NP>(Gr, ur);
+                    axpy2<G::NP>(Sr, ur, -ke);
+                    dk -= dot2<G::NP>(Sr, brr);
+                    axpy2<G::NP>(Gr, brr, -ke);
+                    dq = reduce_split<SPLIT>(dq);
+                    dk = reduce_split<SPLIT>(dk);
+                    if (g.s == 0) {
+                        odq[t * D + g.idx] = dq;
+                        odk[t * D + g.idx] = dk;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        store_rows(g, Sr, W, p.wE, p.E, p.M);
+    }
 }
 
 }  // namespace fwp

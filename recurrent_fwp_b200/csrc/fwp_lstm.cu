@@ -43,11 +43,12 @@ struct LstmFwdStage {
 };
 
 template <int D, int SPLIT, int TC, int VAR>
-__global__ void __launch_bounds__(D * SPLIT) lstm_fwd_kernel(const LstmFwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) lstm_fwd_kernel(const LstmFwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = LstmFwdStage<D, TC>;
     constexpr int kX = D + 16;
     for (int i = g.tid; i < 2 * Stage::kFloats + 2 * kX; i += G::NT) smem[i] = 0.f;
@@ -186,11 +187,12 @@ struct LstmBwdStage {
 };
 
 template <int D, int SPLIT, int TC, int VAR>
-__global__ void __launch_bounds__(D * SPLIT) lstm_bwd_kernel(const LstmBwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) lstm_bwd_kernel(const LstmBwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = LstmBwdStage<D, TC>;
     constexpr int kXs = 9 * D + 48;      // per parity: dz[3][D], u[3][D], br[3][D], slots
     for (int i = g.tid; i < 2 * Stage::kFloats + 2 * kXs; i += G::NT) smem[i] = 0.f;
@@ -353,8 +355,10 @@ template <int D, int SPLIT, int TC, int VAR>
 static int launch_lstm_fwd(const LstmFwdParams& p, int nseq, cudaStream_t st) {
     auto kern = lstm_fwd_kernel<D, SPLIT, TC, VAR>;
     const size_t bytes = (2 * LstmFwdStage<D, TC>::kFloats + 2 * (D + 16)) * sizeof(float);
-    if (int rc = smem_optin(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    if (int rc = smem_optin(kern, bytes * slots)) return rc;
+    kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
@@ -364,8 +368,10 @@ template <int D, int SPLIT, int TC, int VAR>
 static int launch_lstm_bwd(const LstmBwdParams& p, int nseq, cudaStream_t st) {
     auto kern = lstm_bwd_kernel<D, SPLIT, TC, VAR>;
     const size_t bytes = (2 * LstmBwdStage<D, TC>::kFloats + 2 * (9 * D + 48)) * sizeof(float);
-    if (int rc = smem_optin(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    if (int rc = smem_optin(kern, bytes * slots)) return rc;
+    kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);

@@ -37,11 +37,12 @@ struct RecFwdStage {
 };
 
 template <int D, int SPLIT, int TC>
-__global__ void __launch_bounds__(D * SPLIT) rec_fwd_kernel(const RecFwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_fwd_kernel(const RecFwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = RecFwdStage<D, TC>;
     constexpr int kX = 3 * D + 32;        // per parity: ht[D], eq[D], ek[D], slots[4][8]
     for (int i = g.tid; i < 2 * Stage::kFloats + 2 * kX; i += G::NT) smem[i] = 0.f;
@@ -170,12 +171,13 @@ struct RecBwdSmem {
 };
 
 template <int D, int SPLIT, int TC>
-__global__ void __launch_bounds__(D * SPLIT) rec_bwd_kernel(const RecBwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_bwd_kernel(const RecBwdParams p) {
     using G = Geo<D, SPLIT>;
     using SM = RecBwdSmem<D>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = RecBwdStage<D, TC>;
     for (int i = g.tid; i < 2 * Stage::kFloats + 2 * SM::kXs + SM::kR; i += G::NT) smem[i] = 0.f;
     float* xch = smem + 2 * Stage::kFloats;
@@ -318,7 +320,7 @@ __global__ void __launch_bounds__(D * SPLIT) rec_bwd_kernel(const RecBwdParams p
     }
     store_rows(g, Sr, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
     // partial parameter gradients of this (n, h): [3][d][d] then [d]
-    float* out = p.scratch + (long long)blockIdx.x * (3 * p.D * p.D + p.D);
+    float* out = p.scratch + (long long)g.seq * (3 * p.D * p.D + p.D);
     store_cols(g, aq, out, p.D, p.D, p.D);
     store_cols(g, ak, out + p.D * p.D, p.D, p.D, p.D);
     store_cols(g, av, out + 2 * p.D * p.D, p.D, p.D, p.D);
@@ -358,8 +360,10 @@ template <int D, int SPLIT, int TC>
 static int launch_rec_fwd(const RecFwdParams& p, int nseq, cudaStream_t st) {
     auto kern = rec_fwd_kernel<D, SPLIT, TC>;
     const size_t bytes = (2 * RecFwdStage<D, TC>::kFloats + 2 * (3 * D + 32)) * sizeof(float);
-    if (int rc = smem_optin(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    if (int rc = smem_optin(kern, bytes * slots)) return rc;
+    kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
@@ -369,8 +373,10 @@ template <int D, int SPLIT, int TC>
 static int launch_rec_bwd(const RecBwdParams& p, int nseq, cudaStream_t st) {
     auto kern = rec_bwd_kernel<D, SPLIT, TC>;
     const size_t bytes = (2 * RecBwdStage<D, TC>::kFloats + 2 * RecBwdSmem<D>::kXs + RecBwdSmem<D>::kR) * sizeof(float);
-    if (int rc = smem_optin(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    if (int rc = smem_optin(kern, bytes * slots)) return rc;
+    kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);

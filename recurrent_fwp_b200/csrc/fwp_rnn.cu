@@ -35,11 +35,12 @@ struct RnnFwdStage {
 };
 
 template <int D, int SPLIT, int TC, bool V1>
-__global__ void __launch_bounds__(D * SPLIT) rnn_fwd_kernel(const RnnFwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rnn_fwd_kernel(const RnnFwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = RnnFwdStage<D, TC>;
     constexpr int kX = 2 * (D + 16);      // per parity: vector[D], reduction slots[2][8]
     for (int i = g.tid; i < 2 * Stage::kFloats + kX; i += G::NT) smem[i] = 0.f;
@@ -148,11 +149,12 @@ struct RnnBwdStage {
 // v2 step (time reversed): g = gy + g_h ; dz = g ; G += s (x) g ; gs = S_t g ; delta block ; g_h = s .* (gs - <s, gs>)
 // v1 step:                 g = gy + g_h ; dz = h_t .* (g - <h_t, g>) ; G += h_{t-1} (x) dz ; g_h = S_t dz ; delta block
 template <int D, int SPLIT, int TC, bool V1>
-__global__ void __launch_bounds__(D * SPLIT) rnn_bwd_kernel(const RnnBwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rnn_bwd_kernel(const RnnBwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
-    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
-    extern __shared__ __align__(16) float smem[];
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
     using Stage = RnnBwdStage<D, TC, V1>;
     constexpr int kXs = 3 * D + 24;       // per parity: g[D], u[D], br[D], slots[3][8]
     for (int i = g.tid; i < 2 * Stage::kFloats + 2 * kXs; i += G::NT) smem[i] = 0.f;
@@ -277,8 +279,10 @@ template <int D, int SPLIT, int TC, bool V1>
 static int launch_rnn_fwd(const RnnFwdParams& p, int nseq, cudaStream_t st) {
     auto kern = rnn_fwd_kernel<D, SPLIT, TC, V1>;
     const size_t bytes = (2 * RnnFwdStage<D, TC>::kFloats + 2 * (D + 16)) * sizeof(float);
-    if (int rc = smem_optin(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    if (int rc = smem_optin(kern, bytes * slots)) return rc;
+    kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
@@ -288,8 +292,10 @@ template <int D, int SPLIT, int TC, bool V1>
 static int launch_rnn_bwd(const RnnBwdParams& p, int nseq, cudaStream_t st) {
     auto kern = rnn_bwd_kernel<D, SPLIT, TC, V1>;
     const size_t bytes = (2 * RnnBwdStage<D, TC, V1>::kFloats + 2 * (3 * D + 24)) * sizeof(float);
-    if (int rc = smem_optin(kern, bytes)) return rc;
-    kern<<<nseq, D * SPLIT, bytes, st>>>(p);
+    int slots = slots_for(D * SPLIT);
+    while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    if (int rc = smem_optin(kern, bytes * slots)) return rc;
+    kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
