@@ -78,7 +78,7 @@ static inline int pad_dim(int d) { return d <= 16 ? 16 : (d <= 32 ? 32 : (d <= 6
 static __device__ long long fwp_prof_out[16];
 #define FWP_PROF_BEGIN long long _pt[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long _pc = clock64();
 #define FWP_PROF(i) { const long long _n = clock64(); _pt[i] += _n - _pc; _pc = _n; }
-#define FWP_PROF_END(base, cond) if (blockIdx.x == 0 && (cond)) { for (int _i = 0; _i < 8; _i++) fwp_prof_out[(base) + _i] = _pt[_i]; }
+#define FWP_PROF_END(base, cond) if (blockIdx.x == 0 && (cond)) { for (int _i = 0; _i < 8 && (base) + _i < 16; _i++) fwp_prof_out[(base) + _i] = _pt[_i]; }
 #else
 #define FWP_PROF_BEGIN
 #define FWP_PROF(i)

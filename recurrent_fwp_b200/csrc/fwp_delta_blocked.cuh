@@ -444,27 +444,37 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
             flush_rows<D, 32, T, TC>(o, p.gq, n, h, t0, nt, p.E, ptid);
             flush_rows<D, 32, T, TC>(o + TC * D, p.gk, n, h, t0, nt, p.E, ptid);
         };
+        FWP_PROF_BEGIN
         issue(0);
         if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         prepare(0);
         __syncthreads();
+        FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i + 2 < nchunks) issue(i + 2);      // lands while this iteration's other work runs
+            FWP_PROF(1)
             if (i >= 1 && i - 1 < nchunks) flush_col(i - 1);
             if (i >= 2) flush_row(i - 2);
+            FWP_PROF(2)
             if (i + 1 < nchunks) {
                 if (i + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
+                FWP_PROF(3)
                 prepare(i + 1);
             }
+            FWP_PROF(4)
             __syncthreads();
+            FWP_PROF(5)
         }
+        FWP_PROF_END(0, ptid == 0 && slot == 0)
     } else if (role == 0) {
         // ===================================================== column role: blocked chain on G
         const G g(rtid);
         f2 Gc[G::NP];
 #pragma unroll
         for (int i = 0; i < G::NP; i++) Gc[i] = 0ull;
+        FWP_PROF_BEGIN
         __syncthreads();
+        FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i < nchunks) {
                 const int jc = i;
@@ -543,8 +553,11 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                     }
                 }
             }
+            FWP_PROF(1)
             __syncthreads();
+            FWP_PROF(2)
         }
+        FWP_PROF_END(8, rtid == 0)
     } else {
         // ===================================================== row role: per step, one chunk behind
         const G g(rtid);
@@ -553,7 +566,9 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         load_rows(g, Sr, W, p.wE, p.E, p.M);
 #pragma unroll
         for (int i = 0; i < G::NP; i++) Gr[i] = 0ull;
+        FWP_PROF_BEGIN
         __syncthreads();
+        FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i >= 1 && i - 1 < nchunks) {
                 const int jc = i - 1;
@@ -584,9 +599,12 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                     }
                 }
             }
+            FWP_PROF(1)
             __syncthreads();
+            FWP_PROF(2)
         }
         store_rows(g, Sr, W, p.wE, p.E, p.M);
+        FWP_PROF_END(12, rtid == 0)
     }
 }
 
