@@ -54,7 +54,8 @@ enum fwp_status {
     FWP_ERR_UNSUPPORTED = 6,  /* head dimension beyond what the kernels cover */
     FWP_ERR_CUDA = 7,         /* a CUDA runtime call failed; see fwp_last_cuda_error */
     FWP_ERR_VARIANT = 8,      /* unknown LSTM variant */
-    FWP_ERR_SCRATCH = 9       /* scratch buffer missing or too small */
+    FWP_ERR_SCRATCH = 9,      /* scratch buffer missing or too small */
+    FWP_ERR_NOALLOC_TOO_LARGE = 10 /* problem needs more than FWP_NOALLOC_SCRATCH_FLOATS of built-in scratch */
 };
 
 /* Human-readable text for a status code.  Never NULL. */
@@ -151,6 +152,32 @@ int fwp_rec_update_fwm_tanh_backward(int N, int H, int L, int D,
                                      float* scratch, int64_t scratch_floats,
                                      int io_dtype, void* stream, int device);
 int64_t fwp_rec_update_fwm_tanh_scratch_floats(int N, int H, int D);
+
+/* Same backward for callers that cannot allocate device memory when they call it
+ * (a host bound to this ABI without a memory pool, or a process whose device memory
+ * was handed out completely at start-up).  No counterpart in the reference, whose
+ * wrapper always allocates with torch.  The scratch lives in a fixed array inside the
+ * library, FWP_NOALLOC_SCRATCH_FLOATS floats per GPU (held by every GPU that loads
+ * the library until the process exits), so N*H*(3*D*D+D) must not exceed it; larger
+ * problems return FWP_ERR_NOALLOC_TOO_LARGE and launch nothing.  The first call on a
+ * device looks up the array's device address (cudaGetSymbolAddress, that device
+ * current): make it before any stream capture.  All calls on a device share the
+ * array: calls that may overlap on the GPU race, calls ordered on one stream do not.
+ * Allocates nothing (no cudaMalloc / cudaFree / allocating library call). */
+#define FWP_NOALLOC_SCRATCH_FLOATS (2 * 1024 * 1024)
+int fwp_rec_update_fwm_tanh_backward_noalloc(int N, int H, int L, int D,
+                                             const fwp_tensor* q, const fwp_tensor* k,
+                                             const fwp_tensor* v, const fwp_tensor* beta,
+                                             const fwp_tensor* v_old, const fwp_tensor* o_delayed,
+                                             const fwp_tensor* grad_out,
+                                             const fwp_tensor* Rq, const fwp_tensor* Rk,
+                                             const fwp_tensor* Rv, const fwp_tensor* rb,
+                                             const fwp_tensor* fw_mem,
+                                             const fwp_tensor* grad_q, const fwp_tensor* grad_k,
+                                             const fwp_tensor* grad_v, const fwp_tensor* grad_beta,
+                                             const fwp_tensor* grad_Rq, const fwp_tensor* grad_Rk,
+                                             const fwp_tensor* grad_Rv, const fwp_tensor* grad_rb,
+                                             int io_dtype, void* stream, int device);
 
 /* ---- delta RNN v2 and v1 ---------------------------------------------------
  * replaces fast_rnn_v2_forward(Z,K,V,beta,v_old,states,kv,out,out_nmz),

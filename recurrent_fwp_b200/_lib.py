@@ -40,6 +40,7 @@ SIGNATURES = {
     'fwp_causal_dot_backward': [_i] * 5 + [_T] * 7 + [_i, _vp, _i],
     'fwp_rec_update_fwm_tanh_forward': [_i] * 4 + [_T] * 16 + [_i, _vp, _i],
     'fwp_rec_update_fwm_tanh_backward': [_i] * 4 + [_T] * 20 + [ctypes.POINTER(ctypes.c_float), _i64, _i, _vp, _i],
+    'fwp_rec_update_fwm_tanh_backward_noalloc': [_i] * 4 + [_T] * 20 + [_i, _vp, _i],
     'fwp_fast_rnn_v2_forward': [_i] * 4 + [_T] * 9 + [_i, _vp, _i],
     'fwp_fast_rnn_v2_backward': [_i] * 4 + [_T] * 12 + [_i, _vp, _i],
     'fwp_fast_rnn_forward': [_i] * 4 + [_T] * 8 + [_i, _vp, _i],

@@ -53,6 +53,7 @@ FWP_API const char* fwp_status_string(int status) {
         case FWP_ERR_CUDA: return "a CUDA runtime call failed (see fwp_last_cuda_error)";
         case FWP_ERR_VARIANT: return "unknown LSTM variant (must be 1..4)";
         case FWP_ERR_SCRATCH: return "scratch buffer missing, misaligned or too small";
+        case FWP_ERR_NOALLOC_TOO_LARGE: return "problem too large for the built-in scratch of the no-allocation entry point (N*H*(3*D*D+D) > FWP_NOALLOC_SCRATCH_FLOATS)";
     }
     return "unknown status";
 }

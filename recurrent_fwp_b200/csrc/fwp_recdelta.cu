@@ -9,6 +9,7 @@
 // parameter gradients dRq, dRk, dRv, drb are accumulated per (n, h) in registers,
 // written once to a scratch buffer and summed over n by a second kernel in a fixed
 // order (the reference adds them with global atomics every step).
+#include <mutex>
 #include "fwp_core.cuh"
 
 namespace fwp {
@@ -502,4 +503,73 @@ FWP_API int fwp_rec_update_fwm_tanh_backward(int N, int H, int L, int D,
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+
+// ---------------------------------------------------------------------------
+// Backward of the recurrent delta net for callers that cannot allocate.
+//
+// The regular entry point above takes a caller-allocated scratch buffer.  Some
+// hosts have nothing to allocate it with at the moment of the call: a plain C
+// or Fortran program bound to this ABI without a device memory pool, or a
+// process that has handed all device memory to another owner at start-up and
+// may not call cudaMalloc afterwards.  For them this variant keeps the scratch
+// in a fixed array inside the library image, FWP_NOALLOC_SCRATCH_FLOATS floats
+// (8 MiB) on every GPU that loads the library, held until the process exits.
+//
+// The array's name is only a host-side handle; its device address is looked up
+// once per device with cudaGetSymbolAddress, with that device current, on the
+// first call that targets the device.  Make that first call outside any stream
+// capture.  Every call on a device uses the same array, so two calls that can
+// overlap on the GPU (different streams, no ordering between them) race; calls
+// ordered on one stream are fine.  Nothing in the array has to start at zero:
+// each (batch, head) block overwrites its whole region before the reduction
+// kernel reads it.  This function calls no cudaMalloc, cudaFree or any other
+// allocating routine.
+namespace {
+static __device__ __align__(256) float g_noalloc_scratch[FWP_NOALLOC_SCRATCH_FLOATS];
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+float* g_noalloc_ptr[kMaxDevices] = {};
+}  // namespace
+
+FWP_API int fwp_rec_update_fwm_tanh_backward_noalloc(int N, int H, int L, int D,
+                                                     const fwp_tensor* q, const fwp_tensor* k,
+                                                     const fwp_tensor* v, const fwp_tensor* beta,
+                                                     const fwp_tensor* v_old, const fwp_tensor* o_delayed,
+                                                     const fwp_tensor* grad_out,
+                                                     const fwp_tensor* Rq, const fwp_tensor* Rk,
+                                                     const fwp_tensor* Rv, const fwp_tensor* rb,
+                                                     const fwp_tensor* fw_mem,
+                                                     const fwp_tensor* grad_q, const fwp_tensor* grad_k,
+                                                     const fwp_tensor* grad_v, const fwp_tensor* grad_beta,
+                                                     const fwp_tensor* grad_Rq, const fwp_tensor* grad_Rk,
+                                                     const fwp_tensor* grad_Rv, const fwp_tensor* grad_rb,
+                                                     int io_dtype, void* stream, int device) {
+    if (N <= 0 || H <= 0 || L <= 0 || D <= 0) return FWP_ERR_SHAPE;
+    if (fwp_rec_update_fwm_tanh_scratch_floats(N, H, D) > (int64_t)FWP_NOALLOC_SCRATCH_FLOATS)
+        return FWP_ERR_NOALLOC_TOO_LARGE;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    int dev = device;
+    if (dev < 0) {
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return set_cuda_error(e);
+    }
+    if (dev >= kMaxDevices) return FWP_ERR_SHAPE;
+    float* scratch;
+    {
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (!g_noalloc_ptr[dev]) {      // first call on this device: resolve the array's device address
+            void* ptr = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+            if (e != cudaSuccess) return set_cuda_error(e);
+            g_noalloc_ptr[dev] = static_cast<float*>(ptr);
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+    return fwp_rec_update_fwm_tanh_backward(N, H, L, D, q, k, v, beta, v_old, o_delayed, grad_out, Rq, Rk, Rv, rb,
+                                            fw_mem, grad_q, grad_k, grad_v, grad_beta, grad_Rq, grad_Rk, grad_Rv,
+                                            grad_rb, scratch, (int64_t)FWP_NOALLOC_SCRATCH_FLOATS, io_dtype, stream,
+                                            device);
 }
