@@ -46,6 +46,11 @@ WORKLOADS = {
 }
 
 
+# DRAM read+write bytes of one backward launch, from the ncu capture summarised in
+# profiles/delta_fwd_bwd_lm_shape_ncu.md (dram__bytes_read.sum + dram__bytes_write.sum)
+NCU_TRAFFIC_BWD = {'lm': 44262912}
+
+
 def peaks():
     p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(p):
@@ -405,7 +410,7 @@ def run_gpu_arm(args):
                        'l2': 'flushed between timed steps (256 MiB write)', 'cuda_graph': graph is not None,
                        'timing': 'CUDA events per step, summed; max over ranks'},
             'roofline': {'bound': 'hbm', 'kernel': 'delta_bwd_kernel', 'achieved': ach_b, 'peak': peak, 'unit': 'GB/s',
-                         'frac': ach_b / peak, 'peak_kind': peak_kind, 'traffic': None,
+                         'frac': ach_b / peak, 'peak_kind': peak_kind, 'traffic': NCU_TRAFFIC_BWD.get(args.workload),
                          'algorithmic_bytes_per_launch': bytes_bwd, 'launch_s': tb, 'launch_s_min': tb_min},
             'roofline_fwd_bwd': {'achieved': ach_fb, 'peak': peak, 'unit': 'GB/s', 'frac': ach_fb / peak,
                                  'algorithmic_bytes': bytes_fwd + bytes_bwd, 'fwd_s': tf, 'bwd_s': tb,
