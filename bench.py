@@ -255,6 +255,79 @@ def time_kernels(ds, flush, reps):
     return statistics.mean(tf) * 1e-3, statistics.mean(tb) * 1e-3, min(tf) * 1e-3, min(tb) * 1e-3
 
 
+# ---- the recurrent families (BASELINE configs[2] and configs[3]); timed through their autograd Functions
+FAMILY_SHAPES = {
+    'rec_delta': (64, 8, 256, 32),     # configs[2]
+    'rnn_v2': (128, 4, 512, 32),       # configs[3]
+    'rnn_v1': (128, 4, 512, 32),
+    'lstm_v1': (128, 4, 512, 32),
+    'lstm_v2': (128, 4, 512, 32),
+    'lstm_v3': (128, 4, 512, 32),
+    'lstm_v4': (128, 4, 512, 32),
+}
+
+
+def run_family(args):
+    """Forward and backward device time of one recurrent family at its BASELINE shape (fp32, W0 = h0 = 0),
+    CUDA events around the autograd Function's forward and around .backward(), L2 flushed before each."""
+    import recurrent_fwp_b200 as fwp
+    name = args.workload
+    B, H, L, d = FAMILY_SHAPES[name]
+    dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device='cpu')
+    g.manual_seed(7)
+    rn = lambda *s: torch.randn(*s, generator=g).to(dev)
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    z = lambda *s: torch.zeros(*s, device=dev)
+
+    def gate():
+        return [rn(B, H, L, d), torch.softmax(rn(B, H, L, d), -1), rn(B, H, L, d), torch.sigmoid(rn(B, H, L, 1))]
+
+    if name == 'rec_delta':
+        ins = [rn(B, H, L, d), rn(B, H, L, d), rn(B, H, L, d), rn(B, H, L, 1)] + \
+              [rn(1, H, d, d) / d ** 0.5 for _ in range(3)] + [rn(1, H, 1, d) / d ** 0.5]
+        call = lambda x: fwp.rec_update_fwm_tanh(*x, z(B, H, d, d), z(B, H, 1, d))
+        elems = 11 * d + 3
+    elif name.startswith('rnn'):
+        zz, k, v, b = gate()
+        ins = [zz, k, v, b]
+        op = fwp.fast_rnn_v2 if name == 'rnn_v2' else fwp.fast_rnn
+        call = lambda x: op(x[0], x[1], x[2], z(B, H, d, d), x[3], z(B, H, 1, d))
+        elems = 11 * d + 3
+    else:
+        ins = gate() + gate() + gate()
+        op = getattr(fwp, 'fast_lstm' if name == 'lstm_v1' else 'fast_lstm_' + name[-2:])
+        call = lambda x: op(x[0], x[1], x[2], x[3], z(B, H, d, d), x[4], x[5], x[6], x[7], z(B, H, d, d),
+                            x[8], x[9], x[10], x[11], z(B, H, d, d), z(B, H, 1, d), z(B, H, 1, d))[0]
+        elems = 29 * d + 9
+    gy = rn(B, H, L, d)
+    tf, tb = [], []
+    for i in range(3 + max(args.steps, 5)):
+        leaves = [t.detach().requires_grad_() for t in ins]
+        flush_buf.zero_()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        e[0].record()
+        y = call(leaves)
+        e[1].record()
+        flush_buf.zero_()
+        e[2].record()
+        y.backward(gy)
+        e[3].record()
+        torch.cuda.synchronize(dev)
+        if i >= 3:
+            tf.append(e[0].elapsed_time(e[1]) * 1e-3)
+            tb.append(e[2].elapsed_time(e[3]) * 1e-3)
+    peak, kind = peaks()
+    f, b_ = statistics.mean(tf), statistics.mean(tb)
+    nbytes = B * H * L * elems * 4
+    print(json.dumps({'workload': name, 'shape': {'B': B, 'H': H, 'L': L, 'd': d}, 'fwd_ms': f * 1e3, 'bwd_ms': b_ * 1e3,
+                      'tokens_per_s': B * L / (f + b_), 'algorithmic_bytes_fwd_bwd': nbytes,
+                      'hbm_frac_fwd_bwd': nbytes / (f + b_) / 1e9 / peak, 'peak_kind': kind,
+                      'timing': 'CUDA events around the autograd forward / backward calls, L2 flushed before each'}),
+          flush=True)
+
+
 def run_gpu_arm(args):
     rank = int(os.environ.get('RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -432,14 +505,16 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='fwp', choices=['fwp', 'reference'])
-    ap.add_argument('--workload', default='lm', choices=sorted(WORKLOADS))
+    ap.add_argument('--workload', default='lm', choices=sorted(WORKLOADS) + sorted(FAMILY_SHAPES))
     ap.add_argument('--no-graph', action='store_true')
     ap.add_argument('--skip-cpu', action='store_true')
     ap.add_argument('--kernels-only', action='store_true',
                     help='run the forward and backward kernels a few times and print their device times '
                          '(the command the ncu captures under profiles/ use)')
     args = ap.parse_args()
-    if args.impl == 'reference':
+    if args.workload in FAMILY_SHAPES:
+        run_family(args)
+    elif args.impl == 'reference':
         run_reference_arm(args)
     else:
         run_gpu_arm(args)
