@@ -237,7 +237,7 @@ def time_kernels(ds, flush, reps):
     stream_obj = torch.cuda.current_stream(ds.device)
     stream = ctypes.c_void_p(stream_obj.cuda_stream)
     tf, tb = [], []
-    for i in range(reps):
+    for i in range(reps + 2):     # the first two launches are warm-up (clock ramp, cold instruction cache)
         s = i % ds.segs
         ds.W.zero_()
         flush()
@@ -250,8 +250,9 @@ def time_kernels(ds, flush, reps):
         ds.bwd(s, stream)
         e3.record(stream_obj)
         torch.cuda.synchronize(ds.device)
-        tf.append(e0.elapsed_time(e1))
-        tb.append(e2.elapsed_time(e3))
+        if i >= 2:
+            tf.append(e0.elapsed_time(e1))
+            tb.append(e2.elapsed_time(e3))
     return statistics.mean(tf) * 1e-3, statistics.mean(tb) * 1e-3, min(tf) * 1e-3, min(tb) * 1e-3
 
 

@@ -352,6 +352,7 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) sum_bwd_kern
 }  // namespace fwp
 
 #include "fwp_delta_blocked.cuh"
+#include "fwp_delta_generic.cuh"
 
 namespace fwp {
 
@@ -408,6 +409,21 @@ static int launch_sum_bwd(const SumBwdParams& p, int nseq, cudaStream_t st) {
                   slots * 2 * SumStage<D, TC, T>::kFloats * sizeof(float), st);
 }
 
+// Shapes beyond the register-resident kernels: one CTA per sequence, matrices in shared memory.
+static const size_t kGenericSmemLimit = 227 * 1024;
+template <typename T, bool SUM>
+static int launch_fwd_generic(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
+    const size_t bytes = gen_fwd_floats(p.E, p.M) * sizeof(float);
+    if (bytes > kGenericSmemLimit) return FWP_ERR_UNSUPPORTED;
+    return launch(delta_fwd_generic_kernel<T, SUM>, p, nseq, kGenThreads, bytes, st);
+}
+template <typename T>
+static int launch_bwd_generic(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
+    const size_t bytes = gen_bwd_floats(p.E, p.M) * sizeof(float);
+    if (bytes > kGenericSmemLimit) return FWP_ERR_UNSUPPORTED;
+    return launch(delta_bwd_generic_kernel<T>, p, nseq, kGenThreads, bytes, st);
+}
+
 // "delta.blocked" = 0 selects the per-step kernels (kept as a cross-check of the blocked form).
 template <typename T, bool SUM>
 static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, const char* op) {
@@ -415,6 +431,7 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
     char key[48];
     snprintf(key, sizeof key, "%s.%d.split", op, D);
     const bool blocked = tune_get("delta.blocked", 1) != 0;
+    if (D == 0) return launch_fwd_generic<T, SUM>(p, nseq, st);
     switch (D) {
         case 16: {
             if (!blocked) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
@@ -444,6 +461,7 @@ static int dispatch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     char key[48];
     snprintf(key, sizeof key, "delta_bwd.%d.split", D);
     const bool blocked = tune_get("delta.blocked", 1) != 0;
+    if (D == 0) return launch_bwd_generic<T>(p, nseq, st);
     switch (D) {
         case 16: {
             if (!blocked) return launch_bwd_step<16, 2, 16, T>(p, nseq, st);
@@ -479,7 +497,8 @@ static int check_common(int N, int H, int L, int E, int M, int io_dtype) {
     if (N <= 0 || H <= 0 || L <= 0 || E <= 0 || M <= 0) return FWP_ERR_SHAPE;
     if ((long long)N * H > 0x7fffffffLL) return FWP_ERR_SHAPE;
     if (io_dtype != FWP_F32 && io_dtype != FWP_BF16) return FWP_ERR_DTYPE;
-    if (pad_dim(E > M ? E : M) == 0) return FWP_ERR_UNSUPPORTED;
+    if (pad_dim(E > M ? E : M) == 0 && gen_bwd_floats(E, M) * sizeof(float) > kGenericSmemLimit)
+        return FWP_ERR_UNSUPPORTED;     // beyond both the register-resident and the shared-memory kernels
     return FWP_OK;
 }
 

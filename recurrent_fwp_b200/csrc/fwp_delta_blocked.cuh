@@ -488,9 +488,13 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                     const int tb = 4 * gi;
                     float a[4];
                     f2 kk[KEEP ? 4 : 1][G::NP];
+                    f2 qk[KEEP ? 4 : 1][G::NP];     // query slices, fetched with the keys so their latency overlaps the chain
                     if constexpr (KEEP) {
 #pragma unroll
-                        for (int j = 0; j < 4; j++) lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                        for (int j = 0; j < 4; j++) {
+                            lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                            lds_slice<G::NR>(qk[j], s.q.f + (tb + j) * D + g.off);
+                        }
                         f2 aa[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
                         for (int q = 0; q < G::NP; q++) {
@@ -531,12 +535,12 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                     }
 #pragma unroll
                     for (int j = 3; j >= 0; j--) {
-                        f2 qq[G::NP];
-                        lds_slice<G::NR>(qq, s.q.f + (tb + j) * D + g.off);
-                        axpy2<G::NP>(Gc, qq, gy[j]);
                         if constexpr (KEEP) {
+                            axpy2<G::NP>(Gc, qk[j], gy[j]);
                             axpy2<G::NP>(Gc, kk[j], -br[j]);
                         } else {
+                            lds_slice<G::NR>(qk[0], s.q.f + (tb + j) * D + g.off);
+                            axpy2<G::NP>(Gc, qk[0], gy[j]);
                             lds_slice<G::NR>(kk[0], s.k.f + (tb + j) * D + g.off);
                             axpy2<G::NP>(Gc, kk[0], -br[j]);
                         }

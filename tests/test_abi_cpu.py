@@ -51,7 +51,7 @@ def test_host_validation_rejects_before_any_launch(L):
     before = L.launch_count()
     assert f(0, 8, 16, 16, 16, *args(), 0, None, -1) == 2          # shape
     assert f(2, 8, 16, 16, 16, *args(), 7, None, -1) == 5          # dtype
-    assert f(2, 8, 16, 128, 16, *args(), 0, None, -1) == 6         # unsupported head dim
+    assert f(2, 8, 16, 2048, 64, *args(), 0, None, -1) == 6        # beyond every kernel's head dimensions
     assert f(2, 8, 16, 16, 16, *args(Q=null), 0, None, -1) == 1    # NULL
     assert f(2, 8, 16, 16, 16, *args(K=_fake(stride3=2)), 0, None, -1) == 3   # stride
     assert f(2, 8, 16, 16, 16, *args(V=_fake(ptr=0x1002)), 0, None, -1) == 4  # alignment

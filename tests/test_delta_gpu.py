@@ -167,9 +167,28 @@ def test_sum_rule_golden_and_oracle(fwp):
 
 
 def test_unsupported_head_dim_is_an_error_not_a_fallback(fwp):
-    q = torch.rand(1, 1, 4, 128, device=DEV)
+    q = torch.rand(1, 1, 4, 512, device=DEV)
     with pytest.raises(RuntimeError, match='head dimension'):
-        fwp.fast_weight_delta(q, q, q, torch.rand(1, 1, 4, 1, device=DEV), torch.zeros(1, 1, 128, 128, device=DEV))
+        fwp.fast_weight_delta(q, q, q, torch.rand(1, 1, 4, 1, device=DEV), torch.zeros(1, 1, 512, 512, device=DEV))
+
+
+@pytest.mark.parametrize('B,H,L,E,M', [
+    (2, 2, 13, 128, 16),     # Performer / DPFP feature maps: wide keys, narrow values
+    (1, 2, 9, 96, 32),       # E = 2 * n_roll * d
+    (1, 2, 11, 16, 97),      # M = 3d+1 above the register-resident limit
+    (1, 1, 7, 200, 10),
+    (1, 2, 5, 128, 128),
+])
+def test_shapes_above_64_use_the_shared_memory_kernels(fwp, B, H, L, E, M):
+    q, k, v, b, gy = util.delta_inputs(61, B, H, L, E, M)
+    W0 = torch.randn(B, H, E, M, generator=util.gen(62)) * 0.1
+    W = W0.to(DEV)
+    y, grads, W_end = run_cuda(fwp, q, k, v, b, W, gy)
+    y64, g64, S64 = run_loop(q, k, v, b, W0, gy, torch.float64)
+    assert util.max_abs(y, y64) <= 1e-4 and util.max_abs(W_end, S64) <= 1e-4
+    for g, r in zip(grads, g64):
+        assert util.scaled_rel(g, r) <= 1e-3
+    assert util.max_abs(W, W0) <= 1e-5
 
 
 @pytest.mark.parametrize('B,H,L,d', [(2, 2, 37, 16), (1, 2, 21, 32), (1, 1, 13, 64)])
