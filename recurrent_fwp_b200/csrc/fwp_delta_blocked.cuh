@@ -181,11 +181,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                 // group's slices, whose loads are issued before this group's arithmetic.
                 auto tail = [&](int tb, float (&a)[4], float (&b)[4], auto&& update) {
                     float gs[16], vv[4];
-#ifdef FWP_ABL_NOGRAM
-                    for (int i = 0; i < 16; i++) gs[i] = 0.01f * i;
-#else
                     load16(gs, gram + (tb >> 2) * 16);
-#endif
                     float be[4] = {1.f, 1.f, 1.f, 1.f};
                     if constexpr (!SUM) {
                         const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
@@ -193,13 +189,11 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                     }
 #pragma unroll
                     for (int j = 0; j < 4; j++) vv[j] = s.v.f[(tb + j) * D + g.idx];
-#ifndef FWP_ABL_NOSHFL
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         if constexpr (!SUM) a[j] = reduce_split<SPLIT>(a[j]);
                         b[j] = reduce_split<SPLIT>(b[j]);
                     }
-#endif
                     float u[4], vo[4], y[4];
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -208,29 +202,18 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                             u[j] = vv[j];
                         } else {
                             float acc = a[j];
-#ifndef FWP_ABL_NOSCALAR
 #pragma unroll
                             for (int i = 0; i < j; i++) acc = fmaf(u[i], gs[gram_kk(i, j)], acc);
-#endif
                             vo[j] = acc;
                             u[j] = be[j] * (vv[j] - acc);
                         }
                         float yy = b[j];
-#ifndef FWP_ABL_NOSCALAR
 #pragma unroll
                         for (int i = 0; i <= j; i++) yy = fmaf(u[i], gs[gram_kq(i, j)], yy);
-#endif
                         y[j] = yy;
                     }
-#ifndef FWP_ABL_NOAXPY
                     update(u);
-#endif
-#ifdef FWP_ABL_NOSTS
-                    if (y[0] + y[1] + y[2] + y[3] + u[3] + vo[3] == 123.456f)
-#else
-                    if (g.s == 0)
-#endif
-                    {
+                    if (g.s == 0) {
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
                             oy[(tb + j) * D + g.idx] = y[j];
@@ -242,22 +225,18 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                     }
                 };
                 if constexpr (G::NR <= 8) {
-                    auto fetch = [&](int tb, f2 (&kk)[4][G::NP], f2 (&qq)[4][G::NP]) {
+                    // small slices: fetch all eight operand slices first, then run the eight dot-product
+                    // chains interleaved so that no FMA waits on its predecessor
+#pragma unroll 1
+                    for (int gi = 0; gi < ng; gi++) {
+                        const int tb = 4 * gi;
+                        f2 kk[4][G::NP], qq[4][G::NP];
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
-#ifdef FWP_ABL_NOFETCH
-                            for (int i = 0; i < G::NP; i++) { kk[j][i] = 0x3c23d70a3c23d70aull + tb; qq[j][i] = 0x3c23d70a3c23d70aull + j; }
-#else
-                            lds_slice_early<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
-                            lds_slice_early<G::NR>(qq[j], s.q.f + (tb + j) * D + g.off);
-#endif
+                            lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                            lds_slice<G::NR>(qq[j], s.q.f + (tb + j) * D + g.off);
                         }
-                    };
-                    auto group = [&](int gi, f2 (&kk)[4][G::NP], f2 (&qq)[4][G::NP],
-                                     f2 (&kn)[4][G::NP], f2 (&qn)[4][G::NP]) {
-                        if (gi + 1 < ng) fetch(4 * (gi + 1), kn, qn);
                         f2 aa[4] = {0ull, 0ull, 0ull, 0ull}, bb[4] = {0ull, 0ull, 0ull, 0ull};
-#ifndef FWP_ABL_NODOTS
 #pragma unroll
                         for (int i = 0; i < G::NP; i++) {
 #pragma unroll
@@ -266,23 +245,13 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                                 bb[j] = ffma2(S[i], qq[j][i], bb[j]);
                             }
                         }
-#else
-#pragma unroll
-                        for (int j = 0; j < 4; j++) { aa[j] = kk[j][0]; bb[j] = qq[j][1]; }
-#endif
                         float a[4], b[4];
 #pragma unroll
                         for (int j = 0; j < 4; j++) { a[j] = SUM ? 0.f : f2_hsum(aa[j]); b[j] = f2_hsum(bb[j]); }
-                        tail(4 * gi, a, b, [&](const float (&u)[4]) {
+                        tail(tb, a, b, [&](const float (&u)[4]) {
 #pragma unroll
                             for (int j = 0; j < 4; j++) axpy2<G::NP>(S, kk[j], u[j]);
                         });
-                    };
-                    f2 kA[4][G::NP], qA[4][G::NP], kB[4][G::NP], qB[4][G::NP];
-                    fetch(0, kA, qA);
-                    for (int gi = 0; gi < ng; gi += 2) {
-                        group(gi, kA, qA, kB, qB);
-                        if (gi + 1 < ng) group(gi + 1, kB, qB, kA, qA);
                     }
                 } else {
                     for (int gi = 0; gi < ng; gi++) {
