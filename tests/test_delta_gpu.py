@@ -193,7 +193,7 @@ def test_shapes_above_64_use_the_shared_memory_kernels(fwp, B, H, L, E, M):
 
 @pytest.mark.parametrize('B,H,L,d', [(2, 2, 37, 16), (1, 2, 21, 32), (1, 1, 13, 64)])
 def test_per_step_kernels_agree_with_blocked_form(fwp, B, H, L, d):
-    """The four-step blocked kernels (default) and the per-step kernels are two execution plans
+    """The four-step blocked kernels and the per-step kernels are two execution plans
     of the same recurrence; both must meet the oracle tolerance and agree with each other."""
     from recurrent_fwp_b200 import _lib
     q, k, v, b, gy = util.delta_inputs(51, B, H, L, d)
@@ -205,7 +205,7 @@ def test_per_step_kernels_agree_with_blocked_form(fwp, B, H, L, d):
             W = W0.to(DEV)
             res[blocked] = run_cuda(fwp, q, k, v, b, W, gy)
     finally:
-        _lib.tune('delta.blocked', 1)
+        _lib.tune('delta.blocked', -1)
     y64, g64, _ = run_loop(q, k, v, b, W0, gy, torch.float64)
     for blocked in (1, 0):
         y, grads, _ = res[blocked]
