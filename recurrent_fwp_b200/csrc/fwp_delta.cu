@@ -34,7 +34,8 @@ struct FwdStage {
 
 // SUM = true drops beta / v_old (sum rule): S_t = S_{t-1} + k_t (x) v_t.
 template <int D, int SPLIT, int TC, typename T, bool SUM>
-__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) delta_fwd_step_kernel(const DeltaFwdParams p) {
+__global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT), D == 64 ? 4 : 1)
+delta_fwd_step_kernel(const DeltaFwdParams p) {
     using G = Geo<D, SPLIT>;
     const G g;
     const int n = g.seq / p.H, h = g.seq - n * p.H;
