@@ -494,6 +494,8 @@ def run_gpu_arm(args):
                     'steps': e2e_steps, 'batch': Be, 'api': 'recurrent_fwp_b200.fast_weight_delta (autograd) + .backward()'},
             'gpu_launches': int(launches), 'clocks': clocks, 'wall_s_timed_region': t_wall,
         }
+        if _lib.device_fault() != 0:
+            raise SystemExit('bench.py: a bounded wait inside a kernel ran out; the numbers above are invalid')
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

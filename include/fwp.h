@@ -96,6 +96,12 @@ int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
                              const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
                              int io_dtype, void* stream, int device);
 
+/* The delta-rule kernels move contiguous chunks with bulk asynchronous copies whose completion
+ * waits are bounded.  Returns 1 if such a wait ever ran out on the current device since the last
+ * call (that launch then produced wrong numbers instead of hanging the GPU), 0 if not, -1 on a
+ * CUDA error.  Synchronises the device; reading clears the flag.  No counterpart in the reference. */
+int fwp_delta_device_fault(void);
+
 /* ---- sum rule (linear-transformer causal product with carried state) ----
  * replaces causal_dot_product(Q,K,V,kv,out),
  *   algorithmic/fast_transformers/causal_product_cuda.cu:98-140 */

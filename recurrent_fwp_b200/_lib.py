@@ -49,7 +49,7 @@ SIGNATURES = {
     'fwp_fast_lstm_backward': [_i] * 5 + [_T] + [_T3] * 4 + [_T] * 4 + [_T3] * 6 + [_i, _vp, _i],
 }
 OTHER_SYMBOLS = ['fwp_status_string', 'fwp_last_cuda_error', 'fwp_version', 'fwp_max_head_dim',
-                 'fwp_launch_count', 'fwp_tune', 'fwp_rec_update_fwm_tanh_scratch_floats']
+                 'fwp_launch_count', 'fwp_tune', 'fwp_rec_update_fwm_tanh_scratch_floats', 'fwp_delta_device_fault']
 
 for _name, _args in SIGNATURES.items():
     _f = getattr(lib, _name)
@@ -118,6 +118,11 @@ def check(rc, what):
         if rc == 7:
             msg += ' [cudaError %d]' % lib.fwp_last_cuda_error()
         raise RuntimeError('%s failed: %s' % (what, msg))
+
+
+def device_fault():
+    """1 if a bounded wait inside a delta-rule kernel ran out since the last call (synchronises the device)."""
+    return int(lib.fwp_delta_device_fault())
 
 
 def launch_count():

@@ -318,6 +318,62 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+
+// ---- bulk asynchronous copies (TMA, one instruction per contiguous chunk) ------------
+// A producer warp moves whole [rows x D] chunks between global and shared memory with
+// cp.async.bulk when the rows are contiguous and 16-byte aligned; loads complete on an
+// mbarrier (complete_tx), stores are tracked by bulk groups.  Every wait is bounded: after
+// kTmaSpinLimit failed polls the waiter records a fault and carries on, so a copy that never
+// completes yields wrong numbers and a raised flag, never a hung GPU.
+constexpr int kTmaSpinLimit = 1 << 16;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%1], %0;" ::"r"(count), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %0;" ::"r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred P1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P1;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// returns false when the limit ran out
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
+    for (int i = 0; i < kTmaSpinLimit; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, unsigned bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// generic-proxy writes to shared memory -> visible to the async proxy (before a bulk store / after zero fill)
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// whole rows of a chunk can go by one bulk copy: full-width, contiguous, 16-byte aligned
+template <int D, typename T>
+__device__ __forceinline__ bool bulk_rows_ok(const T* base, long long sL, int width) {
+    return width == D && sL == D && (reinterpret_cast<uintptr_t>(base) & 15) == 0 && (D * sizeof(T)) % 16 == 0;
+}
+template <typename T>
+__device__ __forceinline__ bool bulk_col_ok(const T* base, long long sL, int t0, int nt) {   // [L,1] tensors
+    return sL == 1 && (reinterpret_cast<uintptr_t>(base + t0) & 15) == 0 && (nt * sizeof(T)) % 16 == 0;
+}
+
 // One streamed tensor of one sequence: rows of `width` elements, row stride sL.
 template <typename T>
 struct Src {

@@ -383,6 +383,12 @@ static int launch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
                   NSL * WsFwdSmem<D, TC, T>::kFloats * sizeof(float), st);
 }
 template <int D, int SPLIT, int TC, typename T>
+static int launch_fwd3(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
+    constexpr int NSL = slots_for(D * SPLIT);
+    return launch(delta_fwd3_kernel<D, SPLIT, TC, T>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
+                  NSL * WsFwd3Smem<D, TC, T>::kFloats * sizeof(float), st);
+}
+template <int D, int SPLIT, int TC, typename T>
 static int launch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     constexpr int NSL = slots_for(D * SPLIT);
     return launch(delta_bwd_kernel<D, SPLIT, TC, T>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
@@ -443,6 +449,11 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
         case 16: {
             if (force == 0) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
+            if constexpr (!SUM) {
+                // opt-in chain / read-out split of the group loop with bulk-copy staging (measured slower
+                // than one consumer warp per sequence on the language-model shape)
+                if (tune_get("delta_fwd.roles", 2) == 3) return launch_fwd3<16, 2, 32, T>(p, nseq, st);
+            }
             return launch_fwd<16, 2, 32, T, SUM>(p, nseq, st);
         }
         case 32: {
@@ -612,4 +623,17 @@ FWP_API int fwp_causal_dot_backward(int N, int H, int L, int E, int M,
     cudaStream_t st = (cudaStream_t)stream;
     if (io_dtype == FWP_F32) return dispatch_sum_bwd<float>(p, N * H, st);
     return dispatch_sum_bwd<__nv_bfloat16>(p, N * H, st);
+}
+
+// 1 if a bounded wait on a bulk copy ever ran out on the current device since the last call
+// (the affected launch produced wrong numbers instead of hanging), 0 if not, -1 on a CUDA error.
+// Synchronises the device; reading clears the flag.
+FWP_API int fwp_delta_device_fault(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, fwp::g_delta_fault, sizeof v) != cudaSuccess) return -1;
+    if (v) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(fwp::g_delta_fault, &zero, sizeof zero);
+    }
+    return v;
 }

@@ -31,6 +31,9 @@
 
 namespace fwp {
 
+// raised (and left raised) when a bounded wait on a bulk copy ran out; read by fwp_delta_device_fault()
+static __device__ int g_delta_fault;
+
 template <int RL>
 __device__ __forceinline__ void zero_rows(float* tile, int r0, int r1, int tid, int nthreads) {
     for (int i = r0 * RL + tid; i < r1 * RL; i += nthreads) tile[i] = 0.f;
@@ -291,6 +294,269 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
     }
 }
 
+// ------------------------------------------------------------------ forward, three roles
+// Same algebra, but the group loop is split over two warps per sequence so that neither carries
+// the whole instruction stream: the "chain" warp owns S and produces v_old_j, u_j (the only part
+// the next group depends on); the "read-out" warp follows one chunk behind with its own copy of
+// the state, updated with the published u_j, and produces y_j = S^T q_j + sum_i u_i (k_i . q_j).
+template <int D, int TC, typename T>
+struct WsFwd3Smem {
+    static constexpr int NS = 4;                       // in flight, prepared, chain, read-out
+    static constexpr int NB = 3;                       // Gram / output buffers: chain, read-out, flush
+    static constexpr int kStage = WsFwdStage<D, TC, T>::kFloats;
+    static constexpr int kGram = (TC / 4) * 16;
+    static constexpr int kOut = 3 * TC * D;            // y, v_old, u
+    static constexpr int kBars = r4(2 * NS);           // one 8-byte mbarrier per stage
+    static constexpr int kFloats = NS * kStage + NB * kGram + NB * kOut + kBars;
+};
+
+template <int D, int SPLIT, int TC, typename T>
+__global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) delta_fwd3_kernel(const DeltaFwdParams p) {
+    using G = Geo<D, SPLIT>;
+    using SM = WsFwd3Smem<D, TC, T>;
+    using Stage = WsFwdStage<D, TC, T>;
+    static_assert(TC % 4 == 0 && G::NR <= 8, "three-role forward is for small slices");
+    constexpr int NSL = slots_for(G::NT);
+    constexpr int NCONS = NSL * G::NT;
+    const int tid = threadIdx.x;
+    const int role = tid < NCONS ? 0 : (tid < 2 * NCONS ? 1 : 2);     // 0 chain, 1 read-out, 2 producer
+    const int rtid = tid - role * NCONS;
+    const int slot = role == 2 ? rtid >> 5 : rtid / G::NT;
+    const int seq = blockIdx.x * NSL + slot;
+    const int n = seq / p.H, h = seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    for (int i = tid; i < NSL * SM::kFloats; i += NSL * (2 * G::NT + 32)) smem_all[i] = 0.f;
+    fence_async_smem();     // the zero fill is ordered before any bulk copy into the same tiles
+    float* smem = smem_all + slot * SM::kFloats;
+    float* gram0 = smem + SM::NS * SM::kStage;
+    float* out0 = gram0 + SM::NB * SM::kGram;
+    const int nchunks = (p.L + TC - 1) / TC;
+    __syncthreads();
+    if (seq >= p.NH) {
+        for (int c = 0; c <= nchunks + 2; c++) __syncthreads();
+        return;
+    }
+    if (role == 2) {
+        // ===================================================== producer warp
+        const int ptid = rtid & 31;
+        Src<T> sq, sk, sv, sb;
+        sq.init(p.q, n, h, p.E);
+        sk.init(p.k, n, h, p.E);
+        sv.init(p.v, n, h, p.M);
+        sb.init(p.beta, n, h, 1);
+        // rows that are contiguous and 16-byte aligned travel as one bulk copy per chunk, the rest by cp.async
+        unsigned long long* bars = reinterpret_cast<unsigned long long*>(out0 + SM::NB * SM::kOut);
+        if (ptid == 0) {
+            for (int i = 0; i < SM::NS; i++) mbar_init(&bars[i], 1);
+            mbar_fence_init();
+        }
+        __syncwarp();
+        const bool eq = bulk_rows_ok<D, T>(sq.base, sq.sL, sq.width), ek = bulk_rows_ok<D, T>(sk.base, sk.sL, sk.width),
+                   ev = bulk_rows_ok<D, T>(sv.base, sv.sL, sv.width);
+        unsigned phase = 0;
+        bool failed = false;
+        auto issue = [&](int c) {
+            Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
+            const int t0 = c * TC, nt = min(TC, p.L - t0);
+            const bool eb = bulk_col_ok<T>(sb.base, sb.sL, t0, nt);
+            if (ptid == 0 && (eq || ek || ev || eb)) {
+                unsigned long long* bar = &bars[c % SM::NS];
+                const unsigned rows = nt * D * sizeof(T), col = nt * sizeof(T);
+                mbar_arrive_expect_tx(bar, (eq ? rows : 0) + (ek ? rows : 0) + (ev ? rows : 0) + (eb ? col : 0));
+                if (eq) bulk_g2s(s.q.raw, sq.base + (long long)t0 * D, rows, bar);
+                if (ek) bulk_g2s(s.k.raw, sk.base + (long long)t0 * D, rows, bar);
+                if (ev) bulk_g2s(s.v.raw, sv.base + (long long)t0 * D, rows, bar);
+                if (eb) bulk_g2s(s.b.raw, sb.base + t0, col, bar);
+            }
+            if (!eq) s.q.template load<32>(sq, t0, nt, ptid);
+            if (!ek) s.k.template load<32>(sk, t0, nt, ptid);
+            if (!ev) s.v.template load<32>(sv, t0, nt, ptid);
+            if (!eb) s.b.template load<32>(sb, t0, nt, ptid);
+            cp_async_commit();
+        };
+        auto landed = [&](int c) {      // after the cp.async groups of chunk c were waited for: its bulk copies
+            const int t0 = c * TC, nt = min(TC, p.L - t0);
+            if (eq || ek || ev || bulk_col_ok<T>(sb.base, sb.sL, t0, nt)) {
+                const int st = c % SM::NS;
+                if (!failed && !mbar_wait_bounded(&bars[st], (phase >> st) & 1)) {
+                    failed = true;
+                    atomicExch(&g_delta_fault, 1);
+                }
+                phase ^= 1u << st;
+            }
+        };
+        auto prepare = [&](int c) {
+            Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
+            const int nt = min(TC, p.L - c * TC), ng = (nt + 3) >> 2;
+            __syncwarp();
+            if constexpr (sizeof(T) != 4) {
+                s.q.widen(nt, p.E, ptid, 32);
+                s.k.widen(nt, p.E, ptid, 32);
+                s.v.widen(nt, p.M, ptid, 32);
+                s.b.widen(nt, 1, ptid, 32);
+            }
+            if (nt & 3) {
+                zero_rows<D>(s.q.f, nt, 4 * ng, ptid, 32);
+                zero_rows<D>(s.k.f, nt, 4 * ng, ptid, 32);
+                zero_rows<D>(s.v.f, nt, 4 * ng, ptid, 32);
+                zero_rows<1>(s.b.f, nt, 4 * ng, ptid, 32);
+            }
+            if ((sizeof(T) != 4) || (nt & 3)) __syncwarp();
+            gram_phase<D, 32, TC>(s.k.f, s.q.f, gram0 + (c % SM::NB) * SM::kGram, ng, ptid);
+        };
+        // outputs: fp32 tiles whose destination rows are contiguous leave by one bulk store each
+        const Row4 ro[3] = {p.out, p.v_old, p.v_ins};
+        bool eo[3];
+        float* ob[3];
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            ob[i] = reinterpret_cast<float*>(ro[i].p) + n * ro[i].sN + h * ro[i].sH;
+            eo[i] = ro[i].p && (i > 0 || sizeof(T) == 4) && bulk_rows_ok<D, float>(ob[i], ro[i].sL, p.M);
+        }
+        auto flush = [&](int c) {
+            const float* o = out0 + (c % SM::NB) * SM::kOut;
+            const int t0 = c * TC, nt = min(TC, p.L - t0);
+            if (ptid == 0 && (eo[0] || eo[1] || eo[2])) {
+#pragma unroll
+                for (int i = 0; i < 3; i++)
+                    if (eo[i]) bulk_s2g(ob[i] + (long long)t0 * D, o + i * TC * D, nt * D * sizeof(float));
+                bulk_commit();
+            }
+            if (!eo[0]) flush_rows<D, 32, T, TC>(o, p.out, n, h, t0, nt, p.M, ptid);
+            if (!eo[1]) flush_rows<D, 32, float, TC>(o + TC * D, p.v_old, n, h, t0, nt, p.M, ptid);
+            if (!eo[2] && p.v_ins.p) flush_rows<D, 32, float, TC>(o + 2 * TC * D, p.v_ins, n, h, t0, nt, p.M, ptid);
+        };
+        issue(0);
+        if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        landed(0);
+        prepare(0);
+        __syncthreads();
+        for (int c = 0; c <= nchunks + 1; c++) {
+            if (c + 2 < nchunks) issue(c + 2);
+            if (c >= 2) flush(c - 2);
+            if (c + 1 < nchunks) {
+                if (c + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
+                landed(c + 1);
+                prepare(c + 1);
+            }
+            if (ptid == 0) bulk_wait_read_all();     // the flushed tiles may be rewritten after the barrier
+            __syncthreads();
+        }
+        if (ptid == 0) bulk_wait_all();
+    } else if (role == 0) {
+        // ===================================================== chain warp: v_old, u, state update
+        const G g(rtid);
+        float* W = p.W + n * p.wN + h * p.wH;
+        f2 S[G::NP];
+        load_cols(g, S, W, p.wE, p.E, p.M);
+        __syncthreads();
+        for (int c = 0; c <= nchunks + 1; c++) {
+            if (c < nchunks) {
+                Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
+                const float* gram = gram0 + (c % SM::NB) * SM::kGram;
+                float* ovo = out0 + (c % SM::NB) * SM::kOut + TC * D;
+                float* ou = ovo + TC * D;
+                const int nt = min(TC, p.L - c * TC), ng = (nt + 3) >> 2;
+#pragma unroll 1
+                for (int gi = 0; gi < ng; gi++) {
+                    const int tb = 4 * gi;
+                    f2 kk[4][G::NP];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                    f2 aa[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+                    for (int i = 0; i < G::NP; i++) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) aa[j] = ffma2(S[i], kk[j][i], aa[j]);
+                    }
+                    // the six key-key Gram scalars sit in the first two float4 of the group's block
+                    const float4 g0 = *reinterpret_cast<const float4*>(gram + gi * 16);
+                    const float4 g1 = *reinterpret_cast<const float4*>(gram + gi * 16 + 4);
+                    const float gk[6] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y};
+                    const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
+                    const float be[4] = {b4.x, b4.y, b4.z, b4.w};
+                    float vv[4], a[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) vv[j] = s.v.f[(tb + j) * D + g.idx];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) a[j] = reduce_split<SPLIT>(f2_hsum(aa[j]));
+                    float u[4], vo[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        float acc = a[j];
+#pragma unroll
+                        for (int i = 0; i < j; i++) acc = fmaf(u[i], gk[gram_kk(i, j)], acc);
+                        vo[j] = acc;
+                        u[j] = be[j] * (vv[j] - acc);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) axpy2<G::NP>(S, kk[j], u[j]);
+                    if (g.s == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            ovo[(tb + j) * D + g.idx] = vo[j];
+                            ou[(tb + j) * D + g.idx] = u[j];
+                        }
+                    }
+                }
+                fence_async_smem();      // the staged outputs are read by a bulk store
+            }
+            __syncthreads();
+        }
+        store_cols(g, S, W, p.wE, p.E, p.M);
+    } else {
+        // ===================================================== read-out warp: y, one chunk behind
+        const G g(rtid);
+        const float* W = p.W + n * p.wN + h * p.wH;
+        f2 S[G::NP];
+        load_cols(g, S, W, p.wE, p.E, p.M);      // start-of-segment state, read before the chain warp writes it back
+        __syncthreads();
+        for (int c = 0; c <= nchunks + 1; c++) {
+            if (c >= 1 && c - 1 < nchunks) {
+                const int cc = c - 1;
+                Stage s; s.bind(smem + (cc % SM::NS) * SM::kStage);
+                const float* gram = gram0 + (cc % SM::NB) * SM::kGram;
+                float* oy = out0 + (cc % SM::NB) * SM::kOut;
+                const float* ou = oy + 2 * TC * D;
+                const int nt = min(TC, p.L - cc * TC), ng = (nt + 3) >> 2;
+#pragma unroll 1
+                for (int gi = 0; gi < ng; gi++) {
+                    const int tb = 4 * gi;
+                    f2 kk[4][G::NP], qq[4][G::NP];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        lds_slice<G::NR>(qq[j], s.q.f + (tb + j) * D + g.off);
+                        lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
+                    }
+                    f2 bb[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+                    for (int i = 0; i < G::NP; i++) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) bb[j] = ffma2(S[i], qq[j][i], bb[j]);
+                    }
+                    float gs[16], u[4], b[4];
+                    load16(gs, gram + gi * 16);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) u[j] = ou[(tb + j) * D + g.idx];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) b[j] = reduce_split<SPLIT>(f2_hsum(bb[j]));
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        float yy = b[j];
+#pragma unroll
+                        for (int i = 0; i <= j; i++) yy = fmaf(u[i], gs[gram_kq(i, j)], yy);
+                        if (g.s == 0) oy[(tb + j) * D + g.idx] = yy;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) axpy2<G::NP>(S, kk[j], u[j]);
+                }
+                fence_async_smem();
+            }
+            __syncthreads();
+        }
+    }
+}
+
 // ------------------------------------------------------------------ backward
 template <int D, int TC, typename T>
 struct WsBwdStage {
@@ -315,7 +581,8 @@ struct WsBwdSmem {
     static constexpr int kGram = (TC / 4) * 16;
     static constexpr int kX = 2 * TC * D + TC * 8;     // u[TC][D], beta*r[TC][D] (= dv), dbeta partials[TC][8]
     static constexpr int kO = 2 * TC * D;              // dq[TC][D], dk[TC][D]
-    static constexpr int kFloats = NS * kStage + 2 * kGram + 2 * kX + 2 * kO + r4(TC);
+    static constexpr int kBars = r4(2 * NS);           // one 8-byte mbarrier per stage
+    static constexpr int kFloats = NS * kStage + 2 * kGram + 2 * kX + 2 * kO + r4(TC) + kBars;
 };
 
 template <int D, int SPLIT, int TC, typename T>
@@ -336,6 +603,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
     const int n = seq / p.H, h = seq - n * p.H;
     extern __shared__ __align__(16) float smem_all[];
     for (int i = tid; i < NSL * SM::kFloats; i += NSL * (2 * G::NT + 32)) smem_all[i] = 0.f;
+    fence_async_smem();     // the zero fill is ordered before any bulk copy into the same tiles
     float* smem = smem_all + slot * SM::kFloats;
     float* gram0 = smem + SM::NS * SM::kStage;
     float* x0 = gram0 + 2 * SM::kGram;
@@ -359,16 +627,51 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         sg.init(p.gy, n, h, p.M);
         so.init(p.v_old, n, h, p.M);
         sb.init(p.beta, n, h, 1);
+        unsigned long long* bars = reinterpret_cast<unsigned long long*>(dbt + r4(TC));
+        if (ptid == 0) {
+            for (int i = 0; i < SM::NS; i++) mbar_init(&bars[i], 1);
+            mbar_fence_init();
+        }
+        __syncwarp();
+        const bool eq = bulk_rows_ok<D, T>(sq.base, sq.sL, sq.width), ek = bulk_rows_ok<D, T>(sk.base, sk.sL, sk.width),
+                   ev = bulk_rows_ok<D, T>(sv.base, sv.sL, sv.width), eg = bulk_rows_ok<D, T>(sg.base, sg.sL, sg.width),
+                   eo = bulk_rows_ok<D, float>(so.base, so.sL, so.width);
+        unsigned phase = 0;
+        bool failed = false;
         auto issue = [&](int jc) {
             Stage s; s.bind(smem + (jc % SM::NS) * SM::kStage);
             const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
-            s.q.template load<32>(sq, t0, nt, ptid);
-            s.k.template load<32>(sk, t0, nt, ptid);
-            s.v.template load<32>(sv, t0, nt, ptid);
-            s.gy.template load<32>(sg, t0, nt, ptid);
-            s.vo.template load<32>(so, t0, nt, ptid);
-            s.b.template load<32>(sb, t0, nt, ptid);
+            const bool eb = bulk_col_ok<T>(sb.base, sb.sL, t0, nt);
+            if (ptid == 0 && (eq || ek || ev || eg || eo || eb)) {
+                unsigned long long* bar = &bars[jc % SM::NS];
+                const unsigned rows = nt * D * sizeof(T), rowsf = nt * D * sizeof(float), col = nt * sizeof(T);
+                mbar_arrive_expect_tx(bar, (eq ? rows : 0) + (ek ? rows : 0) + (ev ? rows : 0) + (eg ? rows : 0) +
+                                               (eo ? rowsf : 0) + (eb ? col : 0));
+                if (eq) bulk_g2s(s.q.raw, sq.base + (long long)t0 * D, rows, bar);
+                if (ek) bulk_g2s(s.k.raw, sk.base + (long long)t0 * D, rows, bar);
+                if (ev) bulk_g2s(s.v.raw, sv.base + (long long)t0 * D, rows, bar);
+                if (eg) bulk_g2s(s.gy.raw, sg.base + (long long)t0 * D, rows, bar);
+                if (eo) bulk_g2s(s.vo.raw, so.base + (long long)t0 * D, rowsf, bar);
+                if (eb) bulk_g2s(s.b.raw, sb.base + t0, col, bar);
+            }
+            if (!eq) s.q.template load<32>(sq, t0, nt, ptid);
+            if (!ek) s.k.template load<32>(sk, t0, nt, ptid);
+            if (!ev) s.v.template load<32>(sv, t0, nt, ptid);
+            if (!eg) s.gy.template load<32>(sg, t0, nt, ptid);
+            if (!eo) s.vo.template load<32>(so, t0, nt, ptid);
+            if (!eb) s.b.template load<32>(sb, t0, nt, ptid);
             cp_async_commit();
+        };
+        auto landed = [&](int jc) {
+            const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
+            if (eq || ek || ev || eg || eo || bulk_col_ok<T>(sb.base, sb.sL, t0, nt)) {
+                const int st = jc % SM::NS;
+                if (!failed && !mbar_wait_bounded(&bars[st], (phase >> st) & 1)) {
+                    failed = true;
+                    atomicExch(&g_delta_fault, 1);
+                }
+                phase ^= 1u << st;
+            }
         };
         auto prepare = [&](int jc) {
             Stage s; s.bind(smem + (jc % SM::NS) * SM::kStage);
@@ -392,10 +695,23 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
             if ((sizeof(T) != 4) || (nt & 3)) __syncwarp();
             gram_phase<D, 32, TC>(s.k.f, s.q.f, gram0 + (jc & 1) * SM::kGram, ng, ptid);
         };
+        // gradients: fp32 tiles whose destination rows are contiguous leave by one bulk store each
+        const Row4 rg[3] = {p.gv, p.gq, p.gk};
+        bool es[3];
+        float* gbase[3];
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            gbase[i] = reinterpret_cast<float*>(rg[i].p) + n * rg[i].sN + h * rg[i].sH;
+            es[i] = sizeof(T) == 4 && bulk_rows_ok<D, float>(gbase[i], rg[i].sL, i == 0 ? p.M : p.E);
+        }
         auto flush_col = [&](int jc) {      // dv = beta*r and dbeta of the chunk the column role just finished
             const float* x = x0 + (jc & 1) * SM::kX;
             const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
-            flush_rows<D, 32, T, TC>(x + TC * D, p.gv, n, h, t0, nt, p.M, ptid);
+            if (es[0]) {
+                if (ptid == 0) { bulk_s2g(gbase[0] + (long long)t0 * D, x + TC * D, nt * D * sizeof(float)); bulk_commit(); }
+            } else {
+                flush_rows<D, 32, T, TC>(x + TC * D, p.gv, n, h, t0, nt, p.M, ptid);
+            }
             const float* part = x + 2 * TC * D;
             for (int t = ptid; t < nt; t += 32) {
                 float db = part[t * 8];
@@ -410,12 +726,18 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         auto flush_row = [&](int jc) {
             const float* o = o0 + (jc & 1) * SM::kO;
             const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
-            flush_rows<D, 32, T, TC>(o, p.gq, n, h, t0, nt, p.E, ptid);
-            flush_rows<D, 32, T, TC>(o + TC * D, p.gk, n, h, t0, nt, p.E, ptid);
+            if (ptid == 0 && (es[1] || es[2])) {
+                if (es[1]) bulk_s2g(gbase[1] + (long long)t0 * D, o, nt * D * sizeof(float));
+                if (es[2]) bulk_s2g(gbase[2] + (long long)t0 * D, o + TC * D, nt * D * sizeof(float));
+                bulk_commit();
+            }
+            if (!es[1]) flush_rows<D, 32, T, TC>(o, p.gq, n, h, t0, nt, p.E, ptid);
+            if (!es[2]) flush_rows<D, 32, T, TC>(o + TC * D, p.gk, n, h, t0, nt, p.E, ptid);
         };
         FWP_PROF_BEGIN
         issue(0);
         if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        landed(0);
         prepare(0);
         __syncthreads();
         FWP_PROF(0)
@@ -427,13 +749,16 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
             FWP_PROF(2)
             if (i + 1 < nchunks) {
                 if (i + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
+                landed(i + 1);
                 FWP_PROF(3)
                 prepare(i + 1);
             }
             FWP_PROF(4)
+            if (ptid == 0) bulk_wait_read_all();     // the flushed tiles may be rewritten after the barrier
             __syncthreads();
             FWP_PROF(5)
         }
+        if (ptid == 0) bulk_wait_all();
         FWP_PROF_END(0, ptid == 0 && slot == 0)
     } else if (role == 0) {
         // ===================================================== column role: blocked chain on G
@@ -525,6 +850,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                         if ((lm % HS) == 0 && lm / HS < 4) xdb[(tb + lm / HS) * 8 + g.warp] = tot;
                     }
                 }
+                fence_async_smem();      // beta*r (= dv) is read by a bulk store
             }
             FWP_PROF(1)
             __syncthreads();
@@ -571,6 +897,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                         odk[t * D + g.idx] = dk;
                     }
                 }
+                fence_async_smem();
             }
             FWP_PROF(1)
             __syncthreads();

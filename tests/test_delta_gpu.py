@@ -213,3 +213,24 @@ def test_per_step_kernels_agree_with_blocked_form(fwp, B, H, L, d):
         for g, r in zip(grads, g64):
             assert util.scaled_rel(g, r) <= 1e-3
     assert util.max_abs(res[1][0], res[0][0]) <= 1e-5
+
+
+@pytest.mark.parametrize('B,H,L', [(2, 3, 37), (1, 5, 256), (3, 1, 5)])
+def test_three_role_forward_with_bulk_copies_meets_the_oracle(fwp, B, H, L):
+    """Opt-in execution plan for d = 16: chain / read-out / producer warps, chunks staged by
+    bulk copies with bounded waits.  Same tolerance as the default plan; no wait may run out."""
+    from recurrent_fwp_b200 import _lib
+    d = 16
+    q, k, v, b, gy = util.delta_inputs(71, B, H, L, d)
+    W0 = torch.randn(B, H, d, d, generator=util.gen(72)) * 0.1
+    try:
+        _lib.tune('delta_fwd.roles', 3)
+        W = W0.to(DEV)
+        y, grads, W_end = run_cuda(fwp, q, k, v, b, W, gy)
+    finally:
+        _lib.tune('delta_fwd.roles', 2)
+    y64, g64, S64 = run_loop(q, k, v, b, W0, gy, torch.float64)
+    assert util.max_abs(y, y64) <= 1e-4 and util.max_abs(W_end, S64) <= 1e-4
+    for g, r in zip(grads, g64):
+        assert util.scaled_rel(g, r) <= 1e-3
+    assert _lib.device_fault() == 0

@@ -83,3 +83,9 @@ def test_noalloc_refuses_oversized_problem(fwp):
     rc = L_.lib.fwp_rec_update_fwm_tanh_backward_noalloc(N, H, T, d, *([t] * 20), L_.F32, None, 0)
     assert rc == 10 and b'built-in scratch' in L_.lib.fwp_status_string(rc)
     assert L_.launch_count() == before
+
+
+def test_no_bounded_wait_ran_out_during_the_gpu_tests(fwp):
+    """The delta-rule kernels bound every wait on their bulk copies; a wait that ran out would have raised this flag."""
+    from recurrent_fwp_b200 import _lib as L_
+    assert L_.device_fault() == 0
