@@ -204,21 +204,24 @@ class DeltaStep:
         self.d_vi = [D(t) for t in self.vi]
         self.d_g = [[D(t) for t in seg] for seg in self.g]
         self.dev_index = device.index
+        # workspaces of the chunkwise plan (null for shapes that have none)
+        self.ws_f, self.ws_f_n, self._ws_f_keep = _lib.delta_workspace(B, H, L, d, d, self.inp[0][0], backward=False)
+        self.ws_b, self.ws_b_n, self._ws_b_keep = _lib.delta_workspace(B, H, L, d, d, self.inp[0][0], backward=True)
 
     def fwd(self, s, stream):
         B, H, L, d = self.shape
         q, k, v, b, _ = self.d_in[s]
-        self.L_.check(self.L_.lib.fwp_fast_weight_forward(
+        self.L_.check(self.L_.lib.fwp_fast_weight_forward_ws(
             B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], self.d_W, self.d_y[s],
-            self.code, stream, self.dev_index), 'fwd')
+            self.code, stream, self.dev_index, self.ws_f, self.ws_f_n), 'fwd')
 
     def bwd(self, s, stream):
         B, H, L, d = self.shape
         q, k, v, b, gy = self.d_in[s]
         gq, gk, gv, gb = self.d_g[s]
-        self.L_.check(self.L_.lib.fwp_fast_weight_backward(
+        self.L_.check(self.L_.lib.fwp_fast_weight_backward_ws(
             B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], gy, self.d_W, gq, gk, gv, gb,
-            self.code, stream, self.dev_index), 'bwd')
+            self.code, stream, self.dev_index, self.ws_b, self.ws_b_n), 'bwd')
 
     def step(self):
         """fwd, keep a clone of the end state (the carried memory), bwd (rewinds W), restore the carried state."""
@@ -329,6 +332,81 @@ def run_family(args):
           flush=True)
 
 
+# ---- BASELINE configs[4], second part: end-to-end forward of a 16-layer delta-rule language model
+LM_E2E = dict(n_token=32768, n_layer=16, n_head=8, d_model=256, d_head=32, d_inner=1024, batch=32, seq_len=512)
+
+
+def run_lm_e2e(args):
+    """Forward of the delta-rule language model (recurrent_fwp_b200/lm_harness.py: the reference's
+    MemTransformerLM with attn_type 24, random-init weights, uniform random token ids, fp32), B=32, L=512.
+    Each step copies the step's token ids from pinned host memory, runs the forward under no_grad and reads the
+    mean loss back.  With N > 1 ranks the batch rows are split over ranks and the per-token losses are
+    all-gathered over NCCL (the only collective; it is outside the fast-weight op)."""
+    import torch.distributed as dist
+    from recurrent_fwp_b200 import _lib
+    from recurrent_fwp_b200.lm_harness import DeltaNetLM
+    from recurrent_fwp_b200 import sharding
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    c = LM_E2E
+    torch.manual_seed(11)
+    model = DeltaNetLM(c['n_token'], c['n_layer'], c['n_head'], c['d_model'], c['d_head'], c['d_inner']).to(dev).eval()
+    B, L = c['batch'], c['seq_len']
+    rows = sharding.batch_slice(B, rank, world)
+    g = torch.Generator().manual_seed(5)
+    host = [torch.randint(0, c['n_token'], (L + 1, B), generator=g)[:, rows].contiguous().pin_memory()
+            for _ in range(4)]
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    times, launches, loss_mean = [], 0, None
+    sampler = None
+    for i in range(args.warmup + args.steps):
+        if i == args.warmup:
+            sampler = ClockSampler(dev.index)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+        flush_buf.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0 = _lib.launch_count()
+        e0.record()
+        tok = host[i % len(host)].to(dev, non_blocking=True)
+        with torch.no_grad():
+            loss, _ = model(tok[:-1], tok[1:])
+            if world > 1:
+                loss = sharding.gather_outputs(loss.t().contiguous(), B).t()
+            loss_mean = loss.mean().item()        # device -> host read of the step's result
+        e1.record()
+        torch.cuda.synchronize(dev)
+        if i >= args.warmup:
+            times.append(e0.elapsed_time(e1) * 1e-3)
+            launches += _lib.launch_count() - n0
+    clocks = sampler.stop() if sampler else None
+    tsum = torch.tensor([sum(times)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tsum, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    if rank == 0:
+        sec = tsum.item() / args.steps
+        tps = B * L / sec
+        print(json.dumps({
+            'metric': 'delta-net language model forward tokens/s', 'value': tps, 'unit': 'tokens/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': sec * 1e3, 'higher_is_better': True,
+            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'fp32', 'data': 'synthetic',
+            'config': {'workload': 'end-to-end forward, 16-layer delta-rule LM (attn_type 24), d_model 256, 8 heads of 32, '
+                                   'FF 1024, vocab 32768, B=32, L=512, random-init weights, uniform random token ids',
+                       'sharding': 'batch rows split over ranks; per-token losses all-gathered (NCCL) outside the op',
+                       'l2': 'flushed between timed steps (256 MiB write)'},
+            'e2e': {'value': tps, 'unit': 'tokens/s', 'h2d_bytes_per_step': int(host[0].numel() * 8),
+                    'd2h_bytes_per_step': 4, 'api': 'recurrent_fwp_b200.lm_harness.DeltaNetLM.forward'},
+            'gpu_launches': int(launches), 'mean_loss': loss_mean, 'clocks': clocks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_gpu_arm(args):
     rank = int(os.environ.get('RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -343,6 +421,9 @@ def run_gpu_arm(args):
     import recurrent_fwp_b200 as fwp
     from recurrent_fwp_b200 import _lib
 
+    for kv in args.tune:      # execution-plan switches of the library, e.g. delta.chunk=1
+        key, _, val = kv.partition('=')
+        _lib.tune(key, int(val))
     B, H, L, d, segs, dts = WORKLOADS[args.workload]
     dtype = torch.float32 if dts == 'fp32' else torch.bfloat16
     esz = 4 if dts == 'fp32' else 2
@@ -362,7 +443,9 @@ def run_gpu_arm(args):
     use_graph = not args.no_graph
     graph = None
     for _ in range(2):
+        n0 = _lib.launch_count()
         ds.step()
+        per_step_launches = _lib.launch_count() - n0
     torch.cuda.synchronize(device)
     if use_graph:
         try:
@@ -406,7 +489,7 @@ def run_gpu_arm(args):
     t_wall = time.perf_counter() - t_wall0
     launches = _lib.launch_count() - launches0
     if graph is not None:
-        launches = 2 * segs * args.steps      # replays re-issue the captured launches: fwd+bwd per segment
+        launches = per_step_launches * args.steps      # replays re-issue the launches counted in one eager step
     dev_s = sum(a.elapsed_time(b_) for a, b_ in evs) * 1e-3
     tmax = torch.tensor([dev_s], device=device, dtype=torch.float64)
     if world > 1:
@@ -508,14 +591,18 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='fwp', choices=['fwp', 'reference'])
-    ap.add_argument('--workload', default='lm', choices=sorted(WORKLOADS) + sorted(FAMILY_SHAPES))
+    ap.add_argument('--workload', default='lm', choices=sorted(WORKLOADS) + sorted(FAMILY_SHAPES) + ['lm_e2e'])
     ap.add_argument('--no-graph', action='store_true')
+    ap.add_argument('--tune', action='append', default=[], metavar='KEY=INT',
+                    help='set an execution-plan switch of the library before the run (repeatable), e.g. delta.chunk=1')
     ap.add_argument('--skip-cpu', action='store_true')
     ap.add_argument('--kernels-only', action='store_true',
                     help='run the forward and backward kernels a few times and print their device times '
                          '(the command the ncu captures under profiles/ use)')
     args = ap.parse_args()
-    if args.workload in FAMILY_SHAPES:
+    if args.workload == 'lm_e2e':
+        run_lm_e2e(args)
+    elif args.workload in FAMILY_SHAPES:
         run_family(args)
     elif args.impl == 'reference':
         run_reference_arm(args)

@@ -31,6 +31,7 @@
 #ifndef FWP_H_
 #define FWP_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -95,6 +96,31 @@ int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
                              const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
                              const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
                              int io_dtype, void* stream, int device);
+
+/* Chunkwise plan of the delta rule (fp32 streams, E and M up to 16): 16 steps per chunk, every chunk
+ * of every sequence prepared and finished in parallel, one small product per chunk on the
+ * sequential chain.  It needs device scratch, which the caller owns: ask for the size, allocate
+ * (16-byte aligned), and call the *_ws variants, which take the same arguments as the two entry
+ * points above plus the workspace.  backward != 0 asks for the backward pass's size.  A shape
+ * without such a plan reports 0; a null or short workspace makes the *_ws call behave exactly like
+ * the plain entry point.  The workspace is only used during the call's own launches.
+ * No counterpart in the reference, which has no scratch (fast_weight_cuda.cu:182-240, :564-664). */
+size_t fwp_fast_weight_workspace_floats(int N, int H, int L, int E, int M, int io_dtype, int backward);
+int fwp_fast_weight_forward_ws(int N, int H, int L, int E, int M,
+                               const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                               const fwp_tensor* beta, const fwp_tensor* v_old,
+                               const fwp_tensor* v_insert, const fwp_tensor* kv,
+                               const fwp_tensor* out, int io_dtype, void* stream, int device,
+                               float* workspace, size_t workspace_floats);
+int fwp_fast_weight_backward_ws(int N, int H, int L, int E, int M,
+                                const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                const fwp_tensor* beta, const fwp_tensor* v_old,
+                                const fwp_tensor* v_insert, const fwp_tensor* grad_out,
+                                const fwp_tensor* fw_mem,
+                                const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
+                                const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
+                                int io_dtype, void* stream, int device,
+                                float* workspace, size_t workspace_floats);
 
 /* The delta-rule kernels move contiguous chunks with bulk asynchronous copies whose completion
  * waits are bounded.  Returns 1 if such a wait ever ran out on the current device since the last

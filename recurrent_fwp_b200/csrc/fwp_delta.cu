@@ -8,16 +8,10 @@
 // at most two shuffles, outputs are plain stores, and the backward is one pass.
 // The same file holds the sum rule (causal_product_cuda.cu), which is the delta
 // rule without beta and v_old.
-#include "fwp_core.cuh"
+#include "fwp_delta_params.cuh"
 
 namespace fwp {
 
-struct DeltaFwdParams {
-    Row4 q, k, v, beta, v_old, v_ins, out;
-    float* W; long long wN, wH, wE;
-    int H, L, E, M;
-    int NH;     // number of sequences (N*H)
-};
 
 template <int D, int TC, typename T>
 struct FwdStage {
@@ -108,12 +102,6 @@ delta_fwd_step_kernel(const DeltaFwdParams p) {
 }
 
 // ------------------------------------------------------------------ backward
-struct DeltaBwdParams {
-    Row4 q, k, v, beta, v_old, gy, gq, gk, gv, gb;
-    float* W; long long wN, wH, wE;
-    int H, L, E, M;
-    int NH;     // number of sequences (N*H)
-};
 
 template <int D, int TC, typename T>
 struct BwdStage {
@@ -358,24 +346,6 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) sum_bwd_kern
 namespace fwp {
 
 // ------------------------------------------------------------------ launchers
-template <typename K>
-static int set_smem(K kernel, size_t bytes) {
-    if (bytes > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-        if (e != cudaSuccess) return set_cuda_error(e);
-    }
-    return FWP_OK;
-}
-
-template <typename K, typename P>
-static int launch(K kern, const P& p, int grid, int threads, size_t bytes, cudaStream_t st) {
-    if (int rc = set_smem(kern, bytes)) return rc;
-    kern<<<grid, threads, bytes, st>>>(p);
-    count_launch();
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
-}
-
 template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     constexpr int NSL = slots_for(D * SPLIT);
@@ -447,6 +417,12 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
     if (D == 0) return launch_fwd_generic<T, SUM>(p, nseq, st);
     switch (D) {
         case 16: {
+            if constexpr (!SUM && sizeof(T) == 4) {
+                // opt-in chunkwise tensor-core form ("delta.chunk" = 1 and a workspace): three launches, every
+                // chunk in parallel; measured issue-bound and behind the recurrent plan on B200 (48 vs 35 us
+                // forward, 76 vs 61 us backward at 512 sequences of 256 steps)
+                if (p.ws && force == -1 && tune_get("delta.chunk", 0) == 1) return launch_fwd_chunk(p, nseq, st);
+            }
             if (force == 0) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
             if constexpr (!SUM) {
@@ -481,6 +457,9 @@ static int dispatch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     if (D == 0) return launch_bwd_generic<T>(p, nseq, st);
     switch (D) {
         case 16: {
+            if constexpr (sizeof(T) == 4) {
+                if (p.ws && force == -1 && tune_get("delta.chunk", 0) == 1) return launch_bwd_chunk(p, nseq, st);
+            }
             if (force == 0) return launch_bwd_step<16, 2, 16, T>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_bwd<16, 4, 16, T>(p, nseq, st);
             return launch_bwd<16, 2, 16, T>(p, nseq, st);
@@ -524,11 +503,17 @@ static int check_common(int N, int H, int L, int E, int M, int io_dtype) {
 
 using namespace fwp;
 
-FWP_API int fwp_fast_weight_forward(int N, int H, int L, int E, int M,
-                                       const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
-                                       const fwp_tensor* beta, const fwp_tensor* v_old,
-                                       const fwp_tensor* v_insert, const fwp_tensor* kv,
-                                       const fwp_tensor* out, int io_dtype, void* stream, int device) {
+FWP_API size_t fwp_fast_weight_workspace_floats(int N, int H, int L, int E, int M, int io_dtype, int backward) {
+    if (N < 1 || H < 1) return 0;
+    return chunk_ws_floats((long long)N * H, L, E, M, io_dtype, backward != 0);
+}
+
+static int fast_weight_forward_impl(int N, int H, int L, int E, int M,
+                                    const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                    const fwp_tensor* beta, const fwp_tensor* v_old,
+                                    const fwp_tensor* v_insert, const fwp_tensor* kv,
+                                    const fwp_tensor* out, int io_dtype, void* stream, int device,
+                                    float* workspace, size_t workspace_floats) {
     if (int rc = check_common(N, H, L, E, M, io_dtype)) return rc;
     const int eb = io_dtype == FWP_F32 ? 4 : 2;
     int rc;
@@ -545,18 +530,41 @@ FWP_API int fwp_fast_weight_forward(int N, int H, int L, int E, int M,
     p.W = (float*)kv->data; p.wN = kv->stride[0]; p.wH = kv->stride[1]; p.wE = kv->stride[2];
     p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
+    const size_t need = chunk_ws_floats((long long)N * H, L, E, M, io_dtype, false);
+    if (workspace && need && workspace_floats >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) p.ws = workspace;
     if (io_dtype == FWP_F32) return dispatch_fwd<float, false>(p, N * H, st, "delta_fwd");
     return dispatch_fwd<__nv_bfloat16, false>(p, N * H, st, "delta_fwd");
 }
 
-FWP_API int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
+FWP_API int fwp_fast_weight_forward(int N, int H, int L, int E, int M,
+                                       const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                       const fwp_tensor* beta, const fwp_tensor* v_old,
+                                       const fwp_tensor* v_insert, const fwp_tensor* kv,
+                                       const fwp_tensor* out, int io_dtype, void* stream, int device) {
+    return fast_weight_forward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, kv, out, io_dtype, stream, device, nullptr, 0);
+}
+
+// Same call with a caller-provided workspace (fwp_fast_weight_workspace_floats): shapes that have a
+// chunkwise plan use it; a null or short workspace, or any other shape, takes the plain entry point's path.
+FWP_API int fwp_fast_weight_forward_ws(int N, int H, int L, int E, int M,
+                                       const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                       const fwp_tensor* beta, const fwp_tensor* v_old,
+                                       const fwp_tensor* v_insert, const fwp_tensor* kv,
+                                       const fwp_tensor* out, int io_dtype, void* stream, int device,
+                                       float* workspace, size_t workspace_floats) {
+    return fast_weight_forward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, kv, out, io_dtype, stream, device,
+                                    workspace, workspace_floats);
+}
+
+static int fast_weight_backward_impl(int N, int H, int L, int E, int M,
                                         const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
                                         const fwp_tensor* beta, const fwp_tensor* v_old,
                                         const fwp_tensor* v_insert, const fwp_tensor* grad_out,
                                         const fwp_tensor* fw_mem,
                                         const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
                                         const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
-                                        int io_dtype, void* stream, int device) {
+                                        int io_dtype, void* stream, int device,
+                                        float* workspace, size_t workspace_floats) {
     (void)v_insert;
     if (int rc = check_common(N, H, L, E, M, io_dtype)) return rc;
     const int eb = io_dtype == FWP_F32 ? 4 : 2;
@@ -575,8 +583,35 @@ FWP_API int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
     p.W = (float*)fw_mem->data; p.wN = fw_mem->stride[0]; p.wH = fw_mem->stride[1]; p.wE = fw_mem->stride[2];
     p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
+    const size_t need = chunk_ws_floats((long long)N * H, L, E, M, io_dtype, true);
+    if (workspace && need && workspace_floats >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) p.ws = workspace;
     if (io_dtype == FWP_F32) return dispatch_bwd<float>(p, N * H, st);
     return dispatch_bwd<__nv_bfloat16>(p, N * H, st);
+}
+
+FWP_API int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
+                                        const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                        const fwp_tensor* beta, const fwp_tensor* v_old,
+                                        const fwp_tensor* v_insert, const fwp_tensor* grad_out,
+                                        const fwp_tensor* fw_mem,
+                                        const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
+                                        const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
+                                        int io_dtype, void* stream, int device) {
+    return fast_weight_backward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, grad_out, fw_mem, grad_Q, grad_K, grad_V,
+                                     grad_beta, io_dtype, stream, device, nullptr, 0);
+}
+
+FWP_API int fwp_fast_weight_backward_ws(int N, int H, int L, int E, int M,
+                                        const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
+                                        const fwp_tensor* beta, const fwp_tensor* v_old,
+                                        const fwp_tensor* v_insert, const fwp_tensor* grad_out,
+                                        const fwp_tensor* fw_mem,
+                                        const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
+                                        const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
+                                        int io_dtype, void* stream, int device,
+                                        float* workspace, size_t workspace_floats) {
+    return fast_weight_backward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, grad_out, fw_mem, grad_Q, grad_K, grad_V,
+                                     grad_beta, io_dtype, stream, device, workspace, workspace_floats);
 }
 
 FWP_API int fwp_causal_dot_product(int N, int H, int L, int E, int M,

@@ -1,0 +1,47 @@
+// Kernel parameter blocks of the delta rule and the launch helper, shared by the translation
+// units that hold the recurrent plans and the chunkwise plan.
+#pragma once
+#include "fwp_core.cuh"
+
+namespace fwp {
+
+struct DeltaFwdParams {
+    Row4 q, k, v, beta, v_old, v_ins, out;
+    float* W; long long wN, wH, wE;
+    int H, L, E, M;
+    int NH;     // number of sequences (N*H)
+    float* ws = nullptr;    // caller-provided workspace of the chunkwise plan (null: recurrent plans only)
+};
+
+struct DeltaBwdParams {
+    Row4 q, k, v, beta, v_old, gy, gq, gk, gv, gb;
+    float* W; long long wN, wH, wE;
+    int H, L, E, M;
+    int NH;     // number of sequences (N*H)
+    float* ws = nullptr;    // caller-provided workspace of the chunkwise plan (null: recurrent plans only)
+};
+
+template <typename K>
+static int set_smem(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return set_cuda_error(e);
+    }
+    return FWP_OK;
+}
+
+template <typename K, typename P>
+static int launch(K kern, const P& p, int grid, int threads, size_t bytes, cudaStream_t st) {
+    if (int rc = set_smem(kern, bytes)) return rc;
+    kern<<<grid, threads, bytes, st>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+// chunkwise plan (fwp_delta_chunk.cu): three launches each; p.ws must hold chunk_ws_floats() floats
+size_t chunk_ws_floats(long long nseq, int L, int E, int M, int io_dtype, bool backward);
+int launch_fwd_chunk(const DeltaFwdParams& p, int nseq, cudaStream_t st);
+int launch_bwd_chunk(const DeltaBwdParams& p, int nseq, cudaStream_t st);
+
+}  // namespace fwp

@@ -234,3 +234,32 @@ def test_three_role_forward_with_bulk_copies_meets_the_oracle(fwp, B, H, L):
     for g, r in zip(grads, g64):
         assert util.scaled_rel(g, r) <= 1e-3
     assert _lib.device_fault() == 0
+
+
+@pytest.mark.parametrize('B,H,L,E,M', [
+    (2, 3, 16, 16, 16), (1, 2, 64, 16, 16), (2, 2, 37, 16, 16), (1, 3, 100, 16, 16), (1, 1, 1, 16, 16),
+    (1, 2, 300, 16, 16), (2, 1, 45, 9, 16), (1, 2, 33, 16, 5), (1, 2, 50, 12, 10), (1, 1, 129, 3, 2),
+])
+def test_chunkwise_tensor_core_plan_meets_the_oracle(fwp, B, H, L, E, M):
+    """Opt-in plan for head dims up to 16 in fp32: 16-step chunks, error-compensated TF32 products on the
+    tensor cores, three launches over a workspace.  Checked against the fp64 loop at the fp32 tolerance,
+    and against the recurrent plan."""
+    from recurrent_fwp_b200 import _lib
+    q, k, v, b, gy = util.delta_inputs(81, B, H, L, E, M)
+    W0 = torch.randn(B, H, E, M, generator=util.gen(82)) * 0.1
+    res = {}
+    try:
+        for chunk in (1, 0):
+            _lib.tune('delta.chunk', chunk)
+            W = W0.to(DEV)
+            res[chunk] = run_cuda(fwp, q, k, v, b, W, gy) + (W,)
+    finally:
+        _lib.tune('delta.chunk', 0)
+    y64, g64, S64 = run_loop(q, k, v, b, W0, gy, torch.float64)
+    for chunk in (1, 0):
+        y, grads, W_end, W_back = res[chunk]
+        assert util.max_abs(y, y64) <= 1e-4 and util.max_abs(W_end, S64) <= 1e-4
+        for g, r in zip(grads, g64):
+            assert util.scaled_rel(g, r) <= 1e-3
+        assert util.max_abs(W_back, W0) <= 1e-5
+    assert util.max_abs(res[1][0], res[0][0]) <= 2e-5
