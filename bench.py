@@ -421,9 +421,6 @@ def run_gpu_arm(args):
     import recurrent_fwp_b200 as fwp
     from recurrent_fwp_b200 import _lib
 
-    for kv in args.tune:      # execution-plan switches of the library, e.g. delta.chunk=1
-        key, _, val = kv.partition('=')
-        _lib.tune(key, int(val))
     B, H, L, d, segs, dts = WORKLOADS[args.workload]
     dtype = torch.float32 if dts == 'fp32' else torch.bfloat16
     esz = 4 if dts == 'fp32' else 2
@@ -600,6 +597,11 @@ def main():
                     help='run the forward and backward kernels a few times and print their device times '
                          '(the command the ncu captures under profiles/ use)')
     args = ap.parse_args()
+    if args.tune and args.impl != 'reference':      # execution-plan switches of the library, e.g. delta.chunk=1
+        from recurrent_fwp_b200 import _lib
+        for kv in args.tune:
+            key, _, val = kv.partition('=')
+            _lib.tune(key, int(val))
     if args.workload == 'lm_e2e':
         run_lm_e2e(args)
     elif args.workload in FAMILY_SHAPES:

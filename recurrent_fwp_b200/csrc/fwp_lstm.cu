@@ -381,7 +381,13 @@ template <int VAR>
 static int dispatch_lstm_fwd(const LstmFwdParams& p, int nseq, cudaStream_t st) {
     switch (pad_dim(p.D)) {
         case 16: return launch_lstm_fwd<16, 2, 16, VAR>(p, nseq, st);
-        case 32: return launch_lstm_fwd<32, 2, 8, VAR>(p, nseq, st);
+        case 32: {
+            const int sp = tune_get("lstm_fwd.32.split", 1);
+            // measured (512 sequences x 512 steps): 1 -> 0.78 ms, 4 -> 0.83 ms, 2 -> 0.85 ms
+            if (sp == 2) return launch_lstm_fwd<32, 2, 8, VAR>(p, nseq, st);
+            if (sp == 4) return launch_lstm_fwd<32, 4, 8, VAR>(p, nseq, st);
+            return launch_lstm_fwd<32, 1, 8, VAR>(p, nseq, st);
+        }
         case 64: return launch_lstm_fwd<64, 4, 4, VAR>(p, nseq, st);
     }
     return FWP_ERR_UNSUPPORTED;
@@ -391,7 +397,12 @@ template <int VAR>
 static int dispatch_lstm_bwd(const LstmBwdParams& p, int nseq, cudaStream_t st) {
     switch (pad_dim(p.D)) {
         case 16: return launch_lstm_bwd<16, 2, 8, VAR>(p, nseq, st);
-        case 32: return launch_lstm_bwd<32, 4, 4, VAR>(p, nseq, st);
+        case 32: {
+            const int sp = tune_get("lstm_bwd.32.split", 2);
+            // measured: 2 -> 1.37 ms, 4 -> 2.14 ms
+            if (sp == 4) return launch_lstm_bwd<32, 4, 4, VAR>(p, nseq, st);
+            return launch_lstm_bwd<32, 2, 4, VAR>(p, nseq, st);
+        }
         case 64: return launch_lstm_bwd<64, 4, 2, VAR>(p, nseq, st);
     }
     return FWP_ERR_UNSUPPORTED;

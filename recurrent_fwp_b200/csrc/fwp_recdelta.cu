@@ -440,7 +440,13 @@ FWP_API int fwp_rec_update_fwm_tanh_forward(int N, int H, int L, int D,
     cudaStream_t st = (cudaStream_t)stream;
     switch (DP) {
         case 16: return launch_rec_fwd<16, 2, 32>(p, N * H, st);
-        case 32: return launch_rec_fwd<32, 2, 16>(p, N * H, st);
+        case 32: {
+            const int sp = tune_get("rec_fwd.32.split", 1);
+            // measured on B200 (512 sequences x 256 steps): 1 -> 0.36 ms, 2 -> 0.38 ms, 4 -> 0.41 ms
+            if (sp == 2) return launch_rec_fwd<32, 2, 16>(p, N * H, st);
+            if (sp == 4) return launch_rec_fwd<32, 4, 16>(p, N * H, st);
+            return launch_rec_fwd<32, 1, 16>(p, N * H, st);
+        }
         case 64: return launch_rec_fwd<64, 4, 8>(p, N * H, st);
     }
     return FWP_ERR_UNSUPPORTED;
@@ -491,7 +497,14 @@ FWP_API int fwp_rec_update_fwm_tanh_backward(int N, int H, int L, int D,
     cudaStream_t st = (cudaStream_t)stream;
     switch (DP) {
         case 16: rc = launch_rec_bwd<16, 2, 16>(p, N * H, st); break;
-        case 32: rc = launch_rec_bwd<32, 4, 8>(p, N * H, st); break;
+        case 32: {
+            const int sp = tune_get("rec_bwd.32.split", 2);
+            // measured: 2 -> 0.36 ms, 4 -> 0.40 ms, 1 -> 0.43 ms (spills)
+            if (sp == 4) rc = launch_rec_bwd<32, 4, 8>(p, N * H, st);
+            else if (sp == 1) rc = launch_rec_bwd<32, 1, 8>(p, N * H, st);
+            else rc = launch_rec_bwd<32, 2, 8>(p, N * H, st);
+            break;
+        }
         case 64: rc = launch_rec_bwd<64, 4, 4>(p, N * H, st); break;
         default: rc = FWP_ERR_UNSUPPORTED;
     }
