@@ -49,10 +49,13 @@ __device__ __forceinline__ void frag_zero(Frag& f) {
         for (int i = 0; i < 4; i++) f.c[j][i] = 0.f;
 }
 
+// x = hi + lo with hi and lo valid TF32 bit patterns (10 explicit mantissa bits, the low 13 bits zero).  Both
+// parts are taken by truncation: hi is within one TF32 ulp of x, lo carries the next 11 bits, and what is
+// dropped is below 2^-20 |x|.  Two logic operations and one subtraction; the rounding conversion of the ISA
+// costs several times that on this part and the products are issue-bound.
 __device__ __forceinline__ void tf32_split(float x, unsigned& hi, unsigned& lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-    const float r = x - __uint_as_float(hi);
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi)) & 0xffffe000u;
 }
 
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
@@ -84,6 +87,72 @@ __device__ __forceinline__ void mm16(Frag& acc, FA a, FB b, int g, int t) {
             mma_tf32(acc.c[j], ah, bh);
         }
     }
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc.c[j][i] += lo.c[j][i];
+}
+
+// Operand fragments of a 16x16 matrix, split once into TF32 hi/lo parts, so that a matrix that feeds several
+// products is loaded and split a single time.
+struct AFr { unsigned h[2][4], l[2][4]; };            // [k-step][m16n8k8 A registers]
+struct BFr { unsigned h[2][2][2], l[2][2][2]; };      // [k-step][n-tile][B registers]
+
+template <class FA>
+__device__ __forceinline__ void load_a(AFr& f, FA a, int g, int t) {
+#pragma unroll
+    for (int ks = 0; ks < 2; ks++) {
+        const int k0 = ks * 8 + t;
+        tf32_split(a(g, k0), f.h[ks][0], f.l[ks][0]);
+        tf32_split(a(g + 8, k0), f.h[ks][1], f.l[ks][1]);
+        tf32_split(a(g, k0 + 4), f.h[ks][2], f.l[ks][2]);
+        tf32_split(a(g + 8, k0 + 4), f.h[ks][3], f.l[ks][3]);
+    }
+}
+template <class FB>
+__device__ __forceinline__ void load_b(BFr& f, FB b, int g, int t) {
+#pragma unroll
+    for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            tf32_split(b(ks * 8 + t, 8 * j + g), f.h[ks][j][0], f.l[ks][j][0]);
+            tf32_split(b(ks * 8 + t + 4, 8 * j + g), f.h[ks][j][1], f.l[ks][j][1]);
+        }
+}
+// An accumulator fragment used as the left operand of the next product: k-step j takes the accumulator's
+// column tile j with the contraction index relabelled (slot t <-> column 8j+2t, slot t+4 <-> column 8j+2t+1);
+// the right operand must then be loaded with load_b_relabelled.
+__device__ __forceinline__ void a_from_acc(AFr& f, const Frag& c) {
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        tf32_split(c.c[j][0], f.h[j][0], f.l[j][0]);
+        tf32_split(c.c[j][2], f.h[j][1], f.l[j][1]);
+        tf32_split(c.c[j][1], f.h[j][2], f.l[j][2]);
+        tf32_split(c.c[j][3], f.h[j][3], f.l[j][3]);
+    }
+}
+template <class FB>
+__device__ __forceinline__ void load_b_relabelled(BFr& f, FB b, int g, int t) {
+#pragma unroll
+    for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            tf32_split(b(ks * 8 + 2 * t, 8 * j + g), f.h[ks][j][0], f.l[ks][j][0]);
+            tf32_split(b(ks * 8 + 2 * t + 1, 8 * j + g), f.h[ks][j][1], f.l[ks][j][1]);
+        }
+}
+// acc += A B
+__device__ __forceinline__ void mma16(Frag& acc, const AFr& a, const BFr& b) {
+    Frag lo;
+    frag_zero(lo);
+#pragma unroll
+    for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            mma_tf32(lo.c[j], a.l[ks], b.h[ks][j]);
+            mma_tf32(lo.c[j], a.h[ks], b.l[ks][j]);
+            mma_tf32(acc.c[j], a.h[ks], b.h[ks][j]);
+        }
 #pragma unroll
     for (int j = 0; j < 2; j++)
 #pragma unroll
@@ -180,13 +249,12 @@ __device__ __forceinline__ void ck_store_frag(const CkDst& d, const Frag& a, int
 // ------------------------------------------------------------------ workspace layout
 // Per chunk, in floats; every piece is a 16x16 tile stored without padding.
 struct CkWs {
-    static constexpr int kWt = 0;         // Wt, row-major [t][e]
-    static constexpr int kUt = 256;       // Ut, row-major [t][m]
-    static constexpr int kAk = 512;       // strict_lower(K K^T), row-major
-    static constexpr int kT = 768;        // chain operator T = Wt^T K, in the B-fragment order of the scan
-    static constexpr int kR = 1024;       // chain offset R = Ut^T K, in accumulator-fragment order
-    static constexpr int kS0 = 1280;      // S0^T, row-major [m][e], written by the scan
-    static constexpr int kFwd = 1536;
+    static constexpr int kCk = 0;         // Ck = Wt / beta (the solve before the scaling by beta), row-major [t][e]
+    static constexpr int kCv = 256;       // Cv = Ut / beta, row-major [t][m]
+    static constexpr int kT = 512;        // chain operator T = Wt^T K, in the B-fragment order of the scan
+    static constexpr int kR = 768;        // chain offset R = Ut^T K, in accumulator-fragment order
+    static constexpr int kS0 = 1024;      // S0^T, row-major [m][e], written by the scan
+    static constexpr int kFwd = 1280;
     // backward
     static constexpr int kLt = 0;         // Lt, row-major [t][m]
     static constexpr int kKt = 256;       // Kt, row-major [t][e]
@@ -217,14 +285,15 @@ __device__ __forceinline__ void ck_store_ws_frag(float* dst, const Frag& a, int 
 
 // ------------------------------------------------------------------ forward
 // Three launches.  (1) one warp per chunk, all chunks of all sequences in parallel: Akk, the
-// triangular solve, and the chunk's transition in the form  S1^T = S0^T + R - S0^T T  with
-// T = Wt^T K and R = Ut^T K (the identity part of the transition stays an exact fp32 add).  (2) one warp per sequence walks its chunks: one product per
+// triangular solve (kept before its scaling by beta: Ut = beta Cv, Wt = beta Ck), and the chunk's transition in
+// the form  S1^T = S0^T + R - S0^T T  with T = Wt^T K and R = Ut^T K (the identity part of the transition stays
+// an exact fp32 add).  (2) one warp per sequence walks its chunks: one product per
 // chunk, with the state kept in the accumulator fragment, which is also the A-operand fragment
 // of the next product once the contraction index is relabelled (slot t <-> column 2t, slot
 // t+4 <-> column 2t+1), so nothing on the chain goes through shared memory.  (3) one warp per
-// chunk again: u = Ut - Wt S0, y, v_old from S0 and u.
-struct CkFwdPrep { static constexpr int kTiles = 6; static constexpr int kWarp = kTiles * kCkTile + 16; };   // K, V, Akk, Ut, Wt, T
-struct CkFwdPost { static constexpr int kTiles = 7; static constexpr int kWarp = kTiles * kCkTile; };        // Q, K, Akk, Ut, Wt, S0^T, Aqk
+// chunk again: u, v_old and y from S0 (four products, see the kernel).
+struct CkFwdPrep { static constexpr int kTiles = 5; static constexpr int kWarp = kTiles * kCkTile + 16; };   // K, V, Akk (-> T), Cv, Ck
+struct CkFwdPost { static constexpr int kTiles = 6; static constexpr int kWarp = kTiles * kCkTile + 16; };   // Q, K, V, Cv (-> u), Ck, S0^T
 
 __global__ void __launch_bounds__(kCkWarps * 32) delta_fwd_chunk_prep_kernel(const DeltaFwdParams p) {
     constexpr int LD = kCkLd;
@@ -236,8 +305,8 @@ __global__ void __launch_bounds__(kCkWarps * 32) delta_fwd_chunk_prep_kernel(con
     const int seq = (int)(cid / nchunks), c = (int)(cid - (long long)seq * nchunks);
     const int n = seq / p.H, h = seq - n * p.H, t0 = c * 16, nt = min(16, p.L - t0);
     float* base = smem + warp * CkFwdPrep::kWarp;
-    float* Ks = base; float* Vs = base + kCkTile; float* AK = base + 2 * kCkTile; float* UT = base + 3 * kCkTile;
-    float* WT = base + 4 * kCkTile; float* TT = base + 5 * kCkTile; float* bs = base + 6 * kCkTile;
+    float* Ks = base; float* Vs = base + kCkTile; float* AK = base + 2 * kCkTile; float* CV = base + 3 * kCkTile;
+    float* CK = base + 4 * kCkTile; float* bs = base + 5 * kCkTile;
     float* ws = p.ws + cid * CkWs::kFwd;
     CkSrc sk, sv;
     sk.init(p.k, n, h, p.E);
@@ -250,23 +319,22 @@ __global__ void __launch_bounds__(kCkWarps * 32) delta_fwd_chunk_prep_kernel(con
     cp_async_wait<0>();
     __syncwarp();
     Frag a;
-    frag_zero(a);
-    mm16(a, [&](int m, int k) { return Ks[m * LD + k]; }, [&](int k, int nn) { return Ks[nn * LD + k]; }, g, t);
-#pragma unroll
-    for (int j = 0; j < 2; j++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int r = g + 8 * (i >> 1), cc = 8 * j + 2 * t + (i & 1);
-            if (cc >= r) a.c[j][i] = 0.f;
-        }
-    frag_store(AK, a, g, t);
-    ck_store_ws_frag(ws + CkWs::kAk, a, g, t);
+    {
+        AFr ka;
+        BFr kt;
+        load_a(ka, [&](int m, int k) { return Ks[m * LD + k]; }, g, t);
+        load_b(kt, [&](int k, int nn) { return Ks[nn * LD + k]; }, g, t);
+        frag_zero(a);
+        mma16(a, ka, kt);
+    }
+    frag_store(AK, a, g, t, [](int r, int cc, float x) { return cc < r ? x : 0.f; });
     __syncwarp();
-    {   // unit lower triangular solve, one right-hand column per lane: lanes 0-15 the columns of V, 16-31 of K
+    {   // unit lower triangular solve, one right-hand column per lane: lanes 0-15 the columns of V, 16-31 of K.
+        // c_t = rhs_t - sum_{i<t} Akk[t,i] beta_i c_i ; [Cv | Ck] keeps c, and Ut = beta Cv, Wt = beta Ck.
         const int col = lane & 15;
         const float* rhs = (lane < 16 ? Vs : Ks) + col;
-        float* dst = (lane < 16 ? UT : WT) + col;
-        float* gdst = ws + (lane < 16 ? CkWs::kUt : CkWs::kWt) + col;
+        float* dst = (lane < 16 ? CV : CK) + col;
+        float* gdst = ws + (lane < 16 ? CkWs::kCv : CkWs::kCk) + col;
         float x[16];
 #pragma unroll
         for (int tt = 0; tt < 16; tt++) {
@@ -280,29 +348,33 @@ __global__ void __launch_bounds__(kCkWarps * 32) delta_fwd_chunk_prep_kernel(con
                 if (4 * i4 + 3 < tt) acc = fmaf(-a4.w, x[4 * i4 + 3], acc);
             }
             x[tt] = bs[tt] * acc;
-            dst[tt * LD] = x[tt];
-            gdst[tt * 16] = x[tt];
+            dst[tt * LD] = acc;
+            gdst[tt * 16] = acc;
         }
     }
     __syncwarp();
-    auto kB = [&](int k, int nn) { return Ks[k * LD + nn]; };
+    BFr kb;
+    load_b(kb, [&](int k, int nn) { return Ks[k * LD + nn]; }, g, t);
+    AFr lhs;
     // R = Ut^T K, already in the order the scan's accumulator wants
+    load_a(lhs, [&](int m, int k) { return bs[k] * CV[k * LD + m]; }, g, t);
     frag_zero(a);
-    mm16(a, [&](int m, int k) { return UT[k * LD + m]; }, kB, g, t);
+    mma16(a, lhs, kb);
     *reinterpret_cast<float4*>(ws + CkWs::kR + lane * 8) = make_float4(a.c[0][0], a.c[0][1], a.c[0][2], a.c[0][3]);
     *reinterpret_cast<float4*>(ws + CkWs::kR + lane * 8 + 4) = make_float4(a.c[1][0], a.c[1][1], a.c[1][2], a.c[1][3]);
-    // T = Wt^T K, re-ordered through shared memory into the scan's B fragments
+    // T = Wt^T K, re-ordered through shared memory (the Akk tile is free) into the scan's B fragments
+    load_a(lhs, [&](int m, int k) { return bs[k] * CK[k * LD + m]; }, g, t);
     frag_zero(a);
-    mm16(a, [&](int m, int k) { return WT[k * LD + m]; }, kB, g, t);
-    frag_store(TT, a, g, t);
+    mma16(a, lhs, kb);
+    frag_store(AK, a, g, t);
     __syncwarp();
     float tf[8];
 #pragma unroll
     for (int j = 0; j < 2; j++)
 #pragma unroll
         for (int jn = 0; jn < 2; jn++) {
-            tf[(j * 2 + jn) * 2] = TT[(8 * j + 2 * t) * LD + 8 * jn + g];
-            tf[(j * 2 + jn) * 2 + 1] = TT[(8 * j + 2 * t + 1) * LD + 8 * jn + g];
+            tf[(j * 2 + jn) * 2] = AK[(8 * j + 2 * t) * LD + 8 * jn + g];
+            tf[(j * 2 + jn) * 2 + 1] = AK[(8 * j + 2 * t + 1) * LD + 8 * jn + g];
         }
     *reinterpret_cast<float4*>(ws + CkWs::kT + lane * 8) = make_float4(tf[0], tf[1], tf[2], tf[3]);
     *reinterpret_cast<float4*>(ws + CkWs::kT + lane * 8 + 4) = make_float4(tf[4], tf[5], tf[6], tf[7]);
@@ -408,6 +480,9 @@ __global__ void __launch_bounds__(32) delta_fwd_chunk_scan_kernel(const DeltaFwd
     ck_store_state_t(X, W, p.wE, p.E, p.M, g, t);
 }
 
+// With c = [Cv | Ck] from the solve and P = Ck S0:  u = beta (Cv - P),  v_old = V - Cv + P  (the identity
+// K S0 + Akk u = V - u / beta, taken before the scaling by beta so that nothing is divided), and
+// y = Q S0 + lower(Q K^T) u.  Four products; Q and S0 are split once and used twice.
 __global__ void __launch_bounds__(kCkWarps * 32) delta_fwd_chunk_post_kernel(const DeltaFwdParams p) {
     constexpr int LD = kCkLd;
     extern __shared__ __align__(16) float smem[];
@@ -418,54 +493,81 @@ __global__ void __launch_bounds__(kCkWarps * 32) delta_fwd_chunk_post_kernel(con
     const int seq = (int)(cid / nchunks), c = (int)(cid - (long long)seq * nchunks);
     const int n = seq / p.H, h = seq - n * p.H, t0 = c * 16, nt = min(16, p.L - t0);
     float* base = smem + warp * CkFwdPost::kWarp;
-    float* Qs = base; float* Ks = base + kCkTile; float* AK = base + 2 * kCkTile; float* UT = base + 3 * kCkTile;
-    float* WT = base + 4 * kCkTile; float* XT = base + 5 * kCkTile; float* AQ = base + 6 * kCkTile;
+    float* Qs = base; float* Ks = base + kCkTile; float* Vs = base + 2 * kCkTile; float* CV = base + 3 * kCkTile;
+    float* CK = base + 4 * kCkTile; float* XT = base + 5 * kCkTile; float* bs = base + 6 * kCkTile;
     const float* ws = p.ws + cid * CkWs::kFwd;
-    CkSrc sq, sk;
+    CkSrc sq, sk, sv;
     sq.init(p.q, n, h, p.E);
     sk.init(p.k, n, h, p.E);
+    sv.init(p.v, n, h, p.M);
+    const float* bsrc = reinterpret_cast<const float*>(p.beta.p) + n * p.beta.sN + h * p.beta.sH;
     CkDst dy, dvo, dvi;
     dy.init(p.out, n, h, p.M);
     dvo.init(p.v_old, n, h, p.M);
     dvi.init(p.v_ins, n, h, p.M);
     ck_load_tile(Qs, sq, t0, nt, lane);
     ck_load_tile(Ks, sk, t0, nt, lane);
-    ck_load_ws_tile(AK, ws + CkWs::kAk, lane);
-    ck_load_ws_tile(UT, ws + CkWs::kUt, lane);
-    ck_load_ws_tile(WT, ws + CkWs::kWt, lane);
+    ck_load_tile(Vs, sv, t0, nt, lane);
+    ck_load_ws_tile(CV, ws + CkWs::kCv, lane);
+    ck_load_ws_tile(CK, ws + CkWs::kCk, lane);
     ck_load_ws_tile(XT, ws + CkWs::kS0, lane);
     cp_async_commit();
+    if (lane < 16) bs[lane] = lane < nt ? bsrc[(long long)(t0 + lane) * p.beta.sL] : 0.f;
     cp_async_wait<0>();
     __syncwarp();
-    auto s0 = [&](int k, int nn) { return XT[nn * LD + k]; };       // S0[e][m] from the transposed tile
-    Frag u;
-    frag_load(u, UT, g, t);
+    BFr s0;
+    load_b(s0, [&](int k, int nn) { return XT[nn * LD + k]; }, g, t);       // S0[e][m] from the transposed tile
+    Frag pf;
     {
-        Frag ws0;
-        frag_zero(ws0);
-        mm16(ws0, [&](int m, int k) { return WT[m * LD + k]; }, s0, g, t);
-#pragma unroll
-        for (int j = 0; j < 2; j++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) u.c[j][i] -= ws0.c[j][i];
+        AFr ck;
+        load_a(ck, [&](int m, int k) { return CK[m * LD + k]; }, g, t);
+        frag_zero(pf);
+        mma16(pf, ck, s0);
     }
-    Frag a;
-    frag_zero(a);
-    mm16(a, [&](int m, int k) { return Qs[m * LD + k]; }, [&](int k, int nn) { return Ks[nn * LD + k]; }, g, t);
-    __syncwarp();       // every lane has read Ut before u replaces it
-    frag_store(UT, u, g, t);
-    frag_store(AQ, a, g, t, [](int r, int cc, float x) { return cc <= r ? x : 0.f; });
-    __syncwarp();
+    Frag u, vo;
+    frag_load(u, CV, g, t);
+    frag_load(vo, Vs, g, t);
+    const float b0 = bs[g], b1 = bs[g + 8];
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float d = u.c[j][i] - pf.c[j][i];
+            vo.c[j][i] -= d;
+            u.c[j][i] = (i < 2 ? b0 : b1) * d;
+        }
+    __syncwarp();       // every lane has read Cv before u replaces it
+    frag_store(CV, u, g, t);
+    ck_store_frag(dvo, vo, t0, nt, g, t);
     if (p.v_ins.p) ck_store_frag(dvi, u, t0, nt, g, t);
-    auto uu = [&](int k, int nn) { return UT[k * LD + nn]; };
-    frag_zero(a);
-    mm16(a, [&](int m, int k) { return Qs[m * LD + k]; }, s0, g, t);
-    mm16(a, [&](int m, int k) { return AQ[m * LD + k]; }, uu, g, t);
-    ck_store_frag(dy, a, t0, nt, g, t);
-    frag_zero(a);
-    mm16(a, [&](int m, int k) { return Ks[m * LD + k]; }, s0, g, t);
-    mm16(a, [&](int m, int k) { return AK[m * LD + k]; }, uu, g, t);
-    ck_store_frag(dvo, a, t0, nt, g, t);
+    AFr qa;
+    load_a(qa, [&](int m, int k) { return Qs[m * LD + k]; }, g, t);
+    Frag aqk;
+    {
+        BFr kt;
+        load_b(kt, [&](int k, int nn) { return Ks[nn * LD + k]; }, g, t);
+        frag_zero(aqk);
+        mma16(aqk, qa, kt);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = g + 8 * (i >> 1), cc = 8 * j + 2 * t + (i & 1);
+            if (cc > r) aqk.c[j][i] = 0.f;
+        }
+    Frag y;
+    frag_zero(y);
+    mma16(y, qa, s0);
+    __syncwarp();       // u is visible
+    {
+        AFr am;
+        BFr ub;
+        a_from_acc(am, aqk);
+        load_b_relabelled(ub, [&](int k, int nn) { return CV[k * LD + nn]; }, g, t);
+        mma16(y, am, ub);
+    }
+    ck_store_frag(dy, y, t0, nt, g, t);
 }
 
 // ------------------------------------------------------------------ backward
