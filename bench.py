@@ -354,7 +354,8 @@ def run_lm_e2e(args):
         dist.init_process_group('nccl', device_id=dev)
     c = LM_E2E
     torch.manual_seed(11)
-    model = DeltaNetLM(c['n_token'], c['n_layer'], c['n_head'], c['d_model'], c['d_head'], c['d_inner']).to(dev).eval()
+    model = DeltaNetLM(c['n_token'], c['n_layer'], c['n_head'], c['d_model'], c['d_head'], c['d_inner'],
+                       fused_io=not args.unfused_layer_io).to(dev).eval()
     B, L = c['batch'], c['seq_len']
     rows = sharding.batch_slice(B, rank, world)
     g = torch.Generator().manual_seed(5)
@@ -398,6 +399,7 @@ def run_lm_e2e(args):
             'scaling': 'strong', 'vs_baseline': None, 'dtype': 'fp32', 'data': 'synthetic',
             'config': {'workload': 'end-to-end forward, 16-layer delta-rule LM (attn_type 24), d_model 256, 8 heads of 32, '
                                    'FF 1024, vocab 32768, B=32, L=512, random-init weights, uniform random token ids',
+                       'layer_io': 'torch elementwise chain' if args.unfused_layer_io else 'one-launch prologue and epilogue',
                        'sharding': 'batch rows split over ranks; per-token losses all-gathered (NCCL) outside the op',
                        'l2': 'flushed between timed steps (256 MiB write)'},
             'e2e': {'value': tps, 'unit': 'tokens/s', 'h2d_bytes_per_step': int(host[0].numel() * 8),
@@ -593,6 +595,8 @@ def main():
     ap.add_argument('--tune', action='append', default=[], metavar='KEY=INT',
                     help='set an execution-plan switch of the library before the run (repeatable), e.g. delta.chunk=1')
     ap.add_argument('--skip-cpu', action='store_true')
+    ap.add_argument('--unfused-layer-io', action='store_true',
+                    help='lm_e2e: run the chain of torch ops around the op instead of the fused prologue / epilogue')
     ap.add_argument('--kernels-only', action='store_true',
                     help='run the forward and backward kernels a few times and print their device times '
                          '(the command the ncu captures under profiles/ use)')

@@ -128,6 +128,22 @@ int fwp_fast_weight_backward_ws(int N, int H, int L, int E, int M,
  * CUDA error.  Synchronises the device; reading clears the flag.  No counterpart in the reference. */
 int fwp_delta_device_fault(void);
 
+/* ---- input prologue / output epilogue of the delta-rule attention layer ----
+ * One pass each for what the reference's layers do with a chain of elementwise and permute launches around the
+ * op (language_modeling/src/utils/cuda_fast_weight_layer.py:106-125 and :152-163, algorithmic/layers.py:110-137).
+ * All tensors fp32 and contiguous; D <= 128.
+ *   prologue_forward:  qkvb (L,B,H,3D+1) -> q, k (elu+1, normalised to sum 1 over D), v, beta = sigmoid, each (B,H,L,.)
+ *   prologue_backward: gradients of q, k, v, beta (B,H,L,.) and the same qkvb -> gradient of qkvb (L,B,H,3D+1)
+ *   transpose:         to_len_major != 0: dst (L,B,H,D) = scale * src (B,H,L,D)  (the layer's output path);
+ *                      to_len_major == 0: dst (B,H,L,D) = scale * src (L,B,H,D)  (its gradient) */
+int fwp_delta_layer_prologue_forward(int L, int B, int H, int D, const float* qkvb,
+                                     float* q, float* k, float* v, float* beta, void* stream, int device);
+int fwp_delta_layer_prologue_backward(int L, int B, int H, int D, const float* qkvb,
+                                      const float* grad_q, const float* grad_k, const float* grad_v,
+                                      const float* grad_beta, float* grad_qkvb, void* stream, int device);
+int fwp_delta_layer_transpose(int L, int B, int H, int D, const float* src, float* dst, float scale,
+                              int to_len_major, void* stream, int device);
+
 /* ---- sum rule (linear-transformer causal product with carried state) ----
  * replaces causal_dot_product(Q,K,V,kv,out),
  *   algorithmic/fast_transformers/causal_product_cuda.cu:98-140 */

@@ -407,7 +407,11 @@ static int launch_bwd_generic(const DeltaBwdParams& p, int nseq, cudaStream_t st
 //   D=32: forward per-step 62 us vs blocked 64-72 us, backward blocked 145 us vs per-step 178 us;
 //   D=64: forward per-step 158 us vs blocked 213 us; backward fp32 blocked 481 us vs per-step 588 us,
 //         bf16 streams per-step 2.35 ms vs blocked 3.10 ms (the producer warp's widening pass).
+// Short segments (the reinforcement-learning callers step the op with L = 1, reinforcement_learning/torchbeast/
+// layer.py:143-186) take the per-step plan, whose CTAs start faster: at L <= 16 it measures 10-12 us against
+// 12-15 us per launch (32 x 8 sequences), and the d=64 fp32 backward only pays off beyond 64 steps.
 // "delta.blocked" = 0 / 1 forces the per-step / blocked plan (tests cross-check one against the other).
+constexpr int kShortSeq = 16;
 template <typename T, bool SUM>
 static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, const char* op) {
     const int D = pad_dim(p.E > p.M ? p.E : p.M);
@@ -423,7 +427,7 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
                 // forward, 76 vs 61 us backward at 512 sequences of 256 steps)
                 if (p.ws && force == -1 && tune_get("delta.chunk", 0) == 1) return launch_fwd_chunk(p, nseq, st);
             }
-            if (force == 0) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
+            if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
             if constexpr (!SUM) {
                 // opt-in chain / read-out split of the group loop with bulk-copy staging (measured slower
@@ -460,17 +464,17 @@ static int dispatch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
             if constexpr (sizeof(T) == 4) {
                 if (p.ws && force == -1 && tune_get("delta.chunk", 0) == 1) return launch_bwd_chunk(p, nseq, st);
             }
-            if (force == 0) return launch_bwd_step<16, 2, 16, T>(p, nseq, st);
+            if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_bwd_step<16, 2, 16, T>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_bwd<16, 4, 16, T>(p, nseq, st);
             return launch_bwd<16, 2, 16, T>(p, nseq, st);
         }
         case 32: {
-            if (force == 0) return launch_bwd_step<32, 2, 8, T>(p, nseq, st);
+            if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_bwd_step<32, 2, 8, T>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_bwd<32, 4, 8, T>(p, nseq, st);
             return launch_bwd<32, 2, 8, T>(p, nseq, st);
         }
         case 64: {
-            const bool blocked = force == 1 || (force == -1 && sizeof(T) == 4);
+            const bool blocked = force == 1 || (force == -1 && sizeof(T) == 4 && p.L > 4 * kShortSeq);
             if (!blocked) return launch_bwd_step<64, 4, 4, T>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_bwd<64, 4, 4, T>(p, nseq, st);
             return launch_bwd<64, 2, 4, T>(p, nseq, st);

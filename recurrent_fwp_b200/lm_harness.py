@@ -20,7 +20,9 @@ loop (language_modeling/src/eval.py:97-118), including the ``[:bsz]`` slice for 
 
 Parameter names equal the reference's ``state_dict`` keys, so weights exported from the reference
 load with ``load_state_dict``.  The op is injectable (``delta_fn``) so that tests can run the same
-module on the CPU with a checker in place of the CUDA op; the default is the CUDA op.
+module on the CPU with a checker in place of the CUDA op; the default is the CUDA op.  ``fused_io=True``
+replaces the elementwise chain around the op by the one-launch prologue and epilogue of
+``recurrent_fwp_b200/delta_layer_io.py``.
 """
 import math
 
@@ -34,9 +36,10 @@ class _Named(nn.Module):
 
 
 class _DeltaAttention(nn.Module):
-    def __init__(self, n_head, d_model, d_head, delta_fn):
+    def __init__(self, n_head, d_model, d_head, delta_fn, fused_io):
         super().__init__()
         self.n_head, self.d_head = n_head, d_head
+        self.fused_io = fused_io
         self.qkvb_net = nn.Linear(d_model, n_head * (3 * d_head + 1), bias=False)
         self.o_net = nn.Linear(n_head * d_head, d_model, bias=False)
         self.layer_norm = nn.LayerNorm(d_model)
@@ -47,6 +50,14 @@ class _DeltaAttention(nn.Module):
         slen, bsz, _ = h.shape
         x = self.layer_norm(h)
         qkvb = self.qkvb_net(x).view(slen, bsz, self.n_head, 3 * self.d_head + 1)
+        if mem is None:
+            W = torch.zeros(bsz, self.n_head, self.d_head, self.d_head, device=h.device, dtype=torch.float32)
+        else:
+            W = mem[0][:bsz]
+        if self.fused_io:       # one launch before and one after the op instead of the chain below
+            from recurrent_fwp_b200.delta_layer_io import delta_attention
+            y = x + self.o_net(delta_attention(qkvb, W, self.scale))
+            return y, ((W.clone().detach(), None) if carry else None)
         q, k, v, beta = torch.split(qkvb, (self.d_head, self.d_head, self.d_head, 1), dim=-1)
         # (len, B, H, d) -> (B, H, len, d); the op takes these strided views as they are
         q, k, v, beta = (t.permute(1, 2, 0, 3) for t in (q, k, v, torch.sigmoid(beta)))
@@ -54,10 +65,6 @@ class _DeltaAttention(nn.Module):
         k = F.elu(k) + 1.0
         q = q / q.sum(-1, keepdim=True)
         k = k / k.sum(-1, keepdim=True)
-        if mem is None:
-            W = torch.zeros(bsz, self.n_head, self.d_head, self.d_head, device=h.device, dtype=torch.float32)
-        else:
-            W = mem[0][:bsz]
         out = self.delta_fn(q, k, v, beta, W)                       # W now holds the end-of-segment state
         out = (self.scale * out).transpose(1, 2).reshape(bsz, slen, self.n_head * self.d_head).transpose(0, 1)
         y = x + self.o_net(out)     # the reference adds the *normalised* input back (cuda_fast_weight_layer.py:100-102,171-173)
@@ -78,21 +85,23 @@ class _FeedForward(nn.Module):
 
 
 class _Layer(nn.Module):
-    def __init__(self, n_head, d_model, d_head, d_inner, delta_fn):
+    def __init__(self, n_head, d_model, d_head, d_inner, delta_fn, fused_io):
         super().__init__()
-        self.dec_attn = _DeltaAttention(n_head, d_model, d_head, delta_fn)
+        self.dec_attn = _DeltaAttention(n_head, d_model, d_head, delta_fn, fused_io)
         self.pos_ff = _FeedForward(d_model, d_inner)
 
 
 class DeltaNetLM(nn.Module):
-    def __init__(self, n_token, n_layer, n_head, d_model, d_head, d_inner, delta_fn=None, init_std=0.02):
+    def __init__(self, n_token, n_layer, n_head, d_model, d_head, d_inner, delta_fn=None, init_std=0.02, fused_io=False):
         super().__init__()
+        if fused_io and delta_fn is not None:
+            raise ValueError('the fused prologue / epilogue belongs to the CUDA op')
         if delta_fn is None:
             from recurrent_fwp_b200.fast_weight import fast_weight_delta as delta_fn
         self.d_model = d_model
         self.word_emb = _Named()
         self.word_emb.emb_layers = nn.ModuleList([nn.Embedding(n_token, d_model)])
-        self.layers = nn.ModuleList([_Layer(n_head, d_model, d_head, d_inner, delta_fn) for _ in range(n_layer)])
+        self.layers = nn.ModuleList([_Layer(n_head, d_model, d_head, d_inner, delta_fn, fused_io) for _ in range(n_layer)])
         self.crit = _Named()
         self.crit.out_layers = nn.ModuleList([nn.Linear(d_model, n_token)])
         self.crit.out_layers[0].weight = self.word_emb.emb_layers[0].weight         # tied
