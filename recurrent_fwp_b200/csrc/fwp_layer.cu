@@ -8,148 +8,201 @@
 // Here each direction is one pass: a projected row is read once and q, k, v, beta leave in the (B, H, len, .)
 // layout with aligned, contiguous rows (which is also what lets the op stage them with 16-byte and bulk
 // copies); the backward pass recomputes the normalisation from the same row and writes the gradient row once.
-// All four kernels are plain streaming kernels: one warp per (len, batch, head) row, rows visited in the order
-// of the projected tensor so that reads are fully contiguous and writes are whole aligned rows.
+// All kernels are plain streaming kernels.  The prologue kernels give 8, 16 or 32 lanes to a (len, batch, head) row,
+// visit rows in the order of the projected tensor so that reads are fully contiguous and writes are whole aligned
+// rows, and issue every load before the first use; the transpose moves 16-byte pieces, four per thread.
 #include "fwp_core.cuh"
 
 namespace fwp {
 
-constexpr int kLayerWarps = 8;          // rows per CTA
-constexpr int kLayerMaxPerLane = 4;     // head dimension up to 128
+constexpr int kLayerWarps = 8;          // warps per CTA
+constexpr int kLayerRows = 4;           // pieces per thread of the transpose, all loads issued before the first use
+constexpr int kLayerMaxD = 128;
 
 struct LayerDims {
     int L, B, H, D;
     long long rows;     // L * B * H
 };
 
-__device__ __forceinline__ float warp_sum(float x) {
+// elu(x) + 1 = x + 1 for x > 0, exp(x) otherwise
+__device__ __forceinline__ float elu_p1(float x) { return x > 0.f ? x + 1.f : expf(x); }
+
+// row r of the projected (len, B, H, .) tensor -> row of the (B, H, len, .) tensors (rows fit 31 bits: 32-bit divisions)
+__device__ __forceinline__ long long bhl_row(const LayerDims& d, long long r) {
+    const unsigned r32 = (unsigned)r;
+    const unsigned lb = r32 / (unsigned)d.H, h = r32 - lb * (unsigned)d.H;
+    const unsigned l = lb / (unsigned)d.B, b = lb - l * (unsigned)d.B;
+    return ((long long)b * d.H + h) * d.L + l;
+}
+
+// sum over the LPR consecutive lanes that share a row
+template <int LPR>
+__device__ __forceinline__ float row_sum(float x) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    for (int o = LPR / 2; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
     return x;
 }
 
-// phi(x) = (elu(x) + 1) / sum: returns the un-normalised p and accumulates nothing; elu(x)+1 = x+1 for x > 0, exp(x) otherwise
-__device__ __forceinline__ float elu_p1(float x) { return x > 0.f ? x + 1.f : expf(x); }
+// LPR lanes share a row (8, 16 or 32 for D up to 32, 64, 128); lane `sub` of a row holds elements sub + LPR*j,
+// j < 4, of each of q, k, v, so that one load instruction covers 32/LPR rows with contiguous 4*LPR-byte pieces.
+constexpr int kLayerPer = 4;
 
+template <int LPR, int PASSES>
 __global__ void __launch_bounds__(kLayerWarps * 32) layer_prologue_fwd_kernel(const float* __restrict__ qkvb, float* __restrict__ q,
                                                                                float* __restrict__ k, float* __restrict__ v,
                                                                                float* __restrict__ beta, const LayerDims d) {
-    const int lane = threadIdx.x & 31;
-    const long long r = (long long)blockIdx.x * kLayerWarps + (threadIdx.x >> 5);     // row of the projected tensor
-    if (r >= d.rows) return;
-    const int h = (int)(r % d.H);
-    const long long lb = r / d.H;
-    const int b = (int)(lb % d.B), l = (int)(lb / d.B);
-    const int D = d.D;
-    const float* x = qkvb + r * (3 * D + 1);
-    const long long o = (((long long)b * d.H + h) * d.L + l);      // row of the (B, H, len, .) tensors
-    float pq[kLayerMaxPerLane], pk[kLayerMaxPerLane];
-    float sq = 0.f, sk = 0.f;
+    constexpr int RPW = 32 / LPR;       // rows per warp and pass
+    const int lane = threadIdx.x & 31, sub = lane % LPR, D = d.D;
+    const long long r0 = ((long long)blockIdx.x * kLayerWarps + (threadIdx.x >> 5)) * (RPW * PASSES) + lane / LPR;
+    float xq[PASSES][kLayerPer], xk[PASSES][kLayerPer], xv[PASSES][kLayerPer], xb[PASSES];
 #pragma unroll
-    for (int j = 0; j < kLayerMaxPerLane; j++) {
-        const int i = lane + 32 * j;
-        pq[j] = pk[j] = 0.f;
-        if (i < D) {
-            pq[j] = elu_p1(x[i]);
-            pk[j] = elu_p1(x[D + i]);
-            v[o * D + i] = x[2 * D + i];
-        }
-        sq += pq[j];
-        sk += pk[j];
-    }
-    const float iq = 1.f / warp_sum(sq), ik = 1.f / warp_sum(sk);
+    for (int a = 0; a < PASSES; a++) {
+        const long long r = r0 + a * RPW;
+        const float* x = qkvb + r * (3 * D + 1);
+        const bool live = r < d.rows;
 #pragma unroll
-    for (int j = 0; j < kLayerMaxPerLane; j++) {
-        const int i = lane + 32 * j;
-        if (i < D) {
-            q[o * D + i] = pq[j] * iq;
-            k[o * D + i] = pk[j] * ik;
+        for (int j = 0; j < kLayerPer; j++) {
+            const int i = sub + LPR * j;
+            const bool ok = live && i < D;
+            xq[a][j] = ok ? x[i] : 0.f;
+            xk[a][j] = ok ? x[D + i] : 0.f;
+            xv[a][j] = ok ? x[2 * D + i] : 0.f;
         }
+        xb[a] = (live && sub == 0) ? x[3 * D] : 0.f;
     }
-    if (lane == 0) beta[o] = 1.f / (1.f + expf(-x[3 * D]));
+#pragma unroll
+    for (int a = 0; a < PASSES; a++) {
+        const long long r = r0 + a * RPW;
+        const bool live = r < d.rows;
+        const long long o = live ? bhl_row(d, r) : 0;
+        float sq = 0.f, sk = 0.f;
+#pragma unroll
+        for (int j = 0; j < kLayerPer; j++) {
+            const bool ok = sub + LPR * j < D;
+            xq[a][j] = ok ? elu_p1(xq[a][j]) : 0.f;
+            xk[a][j] = ok ? elu_p1(xk[a][j]) : 0.f;
+            sq += xq[a][j];
+            sk += xk[a][j];
+        }
+        const float iq = 1.f / row_sum<LPR>(sq), ik = 1.f / row_sum<LPR>(sk);
+        if (!live) continue;
+#pragma unroll
+        for (int j = 0; j < kLayerPer; j++) {
+            const int i = sub + LPR * j;
+            if (i < D) {
+                q[o * D + i] = xq[a][j] * iq;
+                k[o * D + i] = xk[a][j] * ik;
+                v[o * D + i] = xv[a][j];
+            }
+        }
+        if (sub == 0) beta[o] = 1.f / (1.f + expf(-xb[a]));
+    }
 }
 
 // y = p / s with p = elu(x)+1:  dL/dx_i = (g_i - sum_j g_j y_j) / s * (x_i > 0 ? 1 : p_i);  sigmoid: g * b * (1 - b)
+template <int LPR>
 __global__ void __launch_bounds__(kLayerWarps * 32) layer_prologue_bwd_kernel(const float* __restrict__ qkvb, const float* __restrict__ gq,
                                                                                const float* __restrict__ gk, const float* __restrict__ gv,
                                                                                const float* __restrict__ gbeta, float* __restrict__ gx,
                                                                                const LayerDims d) {
-    const int lane = threadIdx.x & 31;
-    const long long r = (long long)blockIdx.x * kLayerWarps + (threadIdx.x >> 5);
-    if (r >= d.rows) return;
-    const int h = (int)(r % d.H);
-    const long long lb = r / d.H;
-    const int b = (int)(lb % d.B), l = (int)(lb / d.B);
-    const int D = d.D;
+    constexpr int RPW = 32 / LPR;
+    const int lane = threadIdx.x & 31, sub = lane % LPR, D = d.D;
+    const long long r = ((long long)blockIdx.x * kLayerWarps + (threadIdx.x >> 5)) * RPW + lane / LPR;
+    const bool live = r < d.rows;
+    const long long o = live ? bhl_row(d, r) : 0;
     const float* x = qkvb + r * (3 * D + 1);
-    float* y = gx + r * (3 * D + 1);
-    const long long o = (((long long)b * d.H + h) * d.L + l);
-    float xq[kLayerMaxPerLane], xk[kLayerMaxPerLane], pq[kLayerMaxPerLane], pk[kLayerMaxPerLane], aq[kLayerMaxPerLane], ak[kLayerMaxPerLane];
+    float xq[kLayerPer], xk[kLayerPer], aq[kLayerPer], ak[kLayerPer], av[kLayerPer];
+#pragma unroll
+    for (int j = 0; j < kLayerPer; j++) {
+        const int i = sub + LPR * j;
+        const bool ok = live && i < D;
+        xq[j] = ok ? x[i] : 0.f;
+        xk[j] = ok ? x[D + i] : 0.f;
+        aq[j] = ok ? gq[o * D + i] : 0.f;
+        ak[j] = ok ? gk[o * D + i] : 0.f;
+        av[j] = ok ? gv[o * D + i] : 0.f;
+    }
+    const float xb = (live && sub == 0) ? x[3 * D] : 0.f;
+    const float ab = (live && sub == 0) ? gbeta[o] : 0.f;
+    float pq[kLayerPer], pk[kLayerPer];
     float sq = 0.f, sk = 0.f, dq = 0.f, dk = 0.f;
 #pragma unroll
-    for (int j = 0; j < kLayerMaxPerLane; j++) {
-        const int i = lane + 32 * j;
-        xq[j] = xk[j] = pq[j] = pk[j] = aq[j] = ak[j] = 0.f;
-        if (i < D) {
-            xq[j] = x[i];
-            xk[j] = x[D + i];
-            pq[j] = elu_p1(xq[j]);
-            pk[j] = elu_p1(xk[j]);
-            aq[j] = gq[o * D + i];
-            ak[j] = gk[o * D + i];
-            y[2 * D + i] = gv[o * D + i];
-        }
+    for (int j = 0; j < kLayerPer; j++) {
+        const bool ok = sub + LPR * j < D;
+        pq[j] = ok ? elu_p1(xq[j]) : 0.f;
+        pk[j] = ok ? elu_p1(xk[j]) : 0.f;
         sq += pq[j];
         sk += pk[j];
         dq = fmaf(aq[j], pq[j], dq);
         dk = fmaf(ak[j], pk[j], dk);
     }
-    const float iq = 1.f / warp_sum(sq), ik = 1.f / warp_sum(sk);
-    dq = warp_sum(dq) * iq;     // sum_j g_j y_j
-    dk = warp_sum(dk) * ik;
+    const float iq = 1.f / row_sum<LPR>(sq), ik = 1.f / row_sum<LPR>(sk);
+    dq = row_sum<LPR>(dq) * iq;     // sum_j g_j y_j
+    dk = row_sum<LPR>(dk) * ik;
+    if (!live) return;
+    float* y = gx + r * (3 * D + 1);
 #pragma unroll
-    for (int j = 0; j < kLayerMaxPerLane; j++) {
-        const int i = lane + 32 * j;
+    for (int j = 0; j < kLayerPer; j++) {
+        const int i = sub + LPR * j;
         if (i < D) {
             y[i] = (aq[j] - dq) * iq * (xq[j] > 0.f ? 1.f : pq[j]);
             y[D + i] = (ak[j] - dk) * ik * (xk[j] > 0.f ? 1.f : pk[j]);
+            y[2 * D + i] = av[j];
         }
     }
-    if (lane == 0) {
-        const float s = 1.f / (1.f + expf(-x[3 * D]));
-        y[3 * D] = gbeta[o] * s * (1.f - s);
+    if (sub == 0) {
+        const float sg = 1.f / (1.f + expf(-xb));
+        y[3 * D] = ab * sg * (1.f - sg);
     }
 }
 
-// (B, H, len, D) <-> (len, B, H, D) with a scale: dst row of one side = scale * src row of the other
-__global__ void __launch_bounds__(kLayerWarps * 32) layer_transpose_kernel(const float* __restrict__ src, float* __restrict__ dst,
-                                                                            const LayerDims d, float scale, int to_len_major) {
-    const int lane = threadIdx.x & 31;
-    const long long r = (long long)blockIdx.x * kLayerWarps + (threadIdx.x >> 5);     // row in (len, B, H) order
-    if (r >= d.rows) return;
-    const int h = (int)(r % d.H);
-    const long long lb = r / d.H;
-    const int b = (int)(lb % d.B), l = (int)(lb / d.B);
-    const long long o = (((long long)b * d.H + h) * d.L + l);
-    const float* s = src + (to_len_major ? o : r) * d.D;
-    float* t = dst + (to_len_major ? r : o) * d.D;
-    if ((d.D & 3) == 0) {
-        for (int i = lane * 4; i < d.D; i += 128) {
-            float4 x = *reinterpret_cast<const float4*>(s + i);
-            x.x *= scale; x.y *= scale; x.z *= scale; x.w *= scale;
-            *reinterpret_cast<float4*>(t + i) = x;
+// (B, H, len, D) <-> (len, B, H, D) with a scale: dst row of one side = scale * src row of the other.
+// One thread per 16-byte piece (4-byte piece when D is not a multiple of 4), kLayerRows pieces per thread.
+template <typename V>
+__global__ void __launch_bounds__(kLayerWarps * 32) layer_transpose_kernel(const V* __restrict__ src, V* __restrict__ dst,
+                                                                            const LayerDims d, int per_row, float scale, int to_len_major) {
+    const long long total = d.rows * per_row;
+    const long long i0 = ((long long)blockIdx.x * kLayerRows) * (kLayerWarps * 32) + threadIdx.x;
+    V x[kLayerRows];
+    long long to[kLayerRows];
+#pragma unroll
+    for (int a = 0; a < kLayerRows; a++) {
+        const long long i = i0 + (long long)a * (kLayerWarps * 32);      // piece index in (len, B, H, .) order
+        to[a] = -1;
+        if (i < total) {
+            long long r;
+            int c;
+            if (total <= 0x7fffffffLL) {
+                const unsigned q32 = (unsigned)i / (unsigned)per_row;
+                r = q32;
+                c = (int)((unsigned)i - q32 * (unsigned)per_row);
+            } else {
+                r = i / per_row;
+                c = (int)(i - r * per_row);
+            }
+            const long long j = bhl_row(d, r) * per_row + c;
+            x[a] = src[to_len_major ? j : i];
+            to[a] = to_len_major ? i : j;
         }
-    } else {
-        for (int i = lane; i < d.D; i += 32) t[i] = scale * s[i];
+    }
+#pragma unroll
+    for (int a = 0; a < kLayerRows; a++) {
+        if (to[a] < 0) continue;
+        if constexpr (sizeof(V) == 16) {
+            x[a].x *= scale; x[a].y *= scale; x[a].z *= scale; x[a].w *= scale;
+        } else {
+            x[a] *= scale;
+        }
+        dst[to[a]] = x[a];
     }
 }
 
 static int layer_dims(int L, int B, int H, int D, LayerDims& d) {
     if (L <= 0 || B <= 0 || H <= 0 || D <= 0) return FWP_ERR_SHAPE;
-    if (D > 32 * kLayerMaxPerLane) return FWP_ERR_UNSUPPORTED;
+    if (D > kLayerMaxD) return FWP_ERR_UNSUPPORTED;
     d.L = L; d.B = B; d.H = H; d.D = D;
     d.rows = (long long)L * B * H;
-    if ((d.rows + kLayerWarps - 1) / kLayerWarps > 0x7fffffffLL) return FWP_ERR_SHAPE;
+    if (d.rows > 0x7fffffffLL) return FWP_ERR_SHAPE;
     return FWP_OK;
 }
 
@@ -172,8 +225,11 @@ FWP_API int fwp_delta_layer_prologue_forward(int L, int B, int H, int D, const f
          reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(beta)) & 3) return FWP_ERR_ALIGN;
     DeviceGuard guard(device);
     if (guard.status) return guard.status;
-    const int grid = (int)((d.rows + kLayerWarps - 1) / kLayerWarps);
-    layer_prologue_fwd_kernel<<<grid, kLayerWarps * 32, 0, (cudaStream_t)stream>>>(qkvb, q, k, v, beta, d);
+    cudaStream_t st = (cudaStream_t)stream;
+    auto grid = [&](int rows_per_warp) { return (int)((d.rows + kLayerWarps * rows_per_warp - 1) / (kLayerWarps * rows_per_warp)); };
+    if (D <= 32) layer_prologue_fwd_kernel<8, 2><<<grid(8), kLayerWarps * 32, 0, st>>>(qkvb, q, k, v, beta, d);
+    else if (D <= 64) layer_prologue_fwd_kernel<16, 2><<<grid(4), kLayerWarps * 32, 0, st>>>(qkvb, q, k, v, beta, d);
+    else layer_prologue_fwd_kernel<32, 2><<<grid(2), kLayerWarps * 32, 0, st>>>(qkvb, q, k, v, beta, d);
     return finish_launch();
 }
 
@@ -188,8 +244,11 @@ FWP_API int fwp_delta_layer_prologue_backward(int L, int B, int H, int D, const 
         return FWP_ERR_ALIGN;
     DeviceGuard guard(device);
     if (guard.status) return guard.status;
-    const int grid = (int)((d.rows + kLayerWarps - 1) / kLayerWarps);
-    layer_prologue_bwd_kernel<<<grid, kLayerWarps * 32, 0, (cudaStream_t)stream>>>(qkvb, grad_q, grad_k, grad_v, grad_beta, grad_qkvb, d);
+    cudaStream_t st = (cudaStream_t)stream;
+    auto grid = [&](int rows_per_warp) { return (int)((d.rows + kLayerWarps * rows_per_warp - 1) / (kLayerWarps * rows_per_warp)); };
+    if (D <= 32) layer_prologue_bwd_kernel<8><<<grid(4), kLayerWarps * 32, 0, st>>>(qkvb, grad_q, grad_k, grad_v, grad_beta, grad_qkvb, d);
+    else if (D <= 64) layer_prologue_bwd_kernel<16><<<grid(2), kLayerWarps * 32, 0, st>>>(qkvb, grad_q, grad_k, grad_v, grad_beta, grad_qkvb, d);
+    else layer_prologue_bwd_kernel<32><<<grid(1), kLayerWarps * 32, 0, st>>>(qkvb, grad_q, grad_k, grad_v, grad_beta, grad_qkvb, d);
     return finish_launch();
 }
 
@@ -202,7 +261,15 @@ FWP_API int fwp_delta_layer_transpose(int L, int B, int H, int D, const float* s
     if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & mask) return FWP_ERR_ALIGN;
     DeviceGuard guard(device);
     if (guard.status) return guard.status;
-    const int grid = (int)((d.rows + kLayerWarps - 1) / kLayerWarps);
-    layer_transpose_kernel<<<grid, kLayerWarps * 32, 0, (cudaStream_t)stream>>>(src, dst, d, scale, to_len_major ? 1 : 0);
+    const int per_row = (D & 3) == 0 ? D / 4 : D;
+    const long long per_cta = (long long)kLayerWarps * 32 * kLayerRows;
+    const long long ctas = (d.rows * per_row + per_cta - 1) / per_cta;
+    if (ctas > 0x7fffffffLL) return FWP_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((D & 3) == 0)
+        layer_transpose_kernel<float4><<<(int)ctas, kLayerWarps * 32, 0, st>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(dst),
+                                                                              d, per_row, scale, to_len_major ? 1 : 0);
+    else
+        layer_transpose_kernel<float><<<(int)ctas, kLayerWarps * 32, 0, st>>>(src, dst, d, per_row, scale, to_len_major ? 1 : 0);
     return finish_launch();
 }
