@@ -156,6 +156,11 @@ struct Geo {
     }
 };
 
+// Barrier among the warps that serve one sequence slot of a CTA (named barriers 1..15; 0 is __syncthreads).
+__device__ __forceinline__ void slot_barrier(int slot, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "r"(nthreads) : "memory");
+}
+
 // sequences per CTA that fill four warps
 __host__ __device__ constexpr int slots_for(int threads_per_seq) { return threads_per_seq >= 128 ? 1 : 128 / threads_per_seq; }
 

@@ -19,7 +19,7 @@
 // Warp specialisation.  With a few hundred sequences there is about one warp per
 // SM sub-partition, so anything a warp does besides the dependency chain is
 // exposed latency.  Each CTA therefore runs separate warps in lock step, one
-// __syncthreads() per chunk:
+// named barrier per sequence and chunk (the sequences of a CTA do not wait for each other):
 //   * a producer warp: cp.async staging two chunks ahead, Gram scalars one chunk
 //     ahead, and the 16-byte flush of the previous chunk's outputs;
 //   * forward: the consumer warps own the state columns and only run the group loop;
@@ -92,10 +92,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
     float* out0 = gram0 + 2 * SM::kGram;
     const int nchunks = (p.L + TC - 1) / TC;
     __syncthreads();
-    if (seq >= p.NH) {      // an empty slot of the last CTA only keeps the barrier count
-        for (int c = 0; c <= nchunks + 1; c++) __syncthreads();
-        return;
-    }
+    if (seq >= p.NH) return;      // an empty slot of the last CTA: nobody waits on its barrier
 
     if (producer) {
         // ===================================================== producer warp
@@ -145,7 +142,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
         issue(0);
         if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         prepare(0);
-        __syncthreads();
+        slot_barrier(slot, G::NT + 32);
         FWP_PROF(0)
         for (int c = 0; c <= nchunks; c++) {
             if (c + 2 < nchunks) issue(c + 2);      // lands while this iteration's other work runs
@@ -158,7 +155,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                 prepare(c + 1);
             }
             FWP_PROF(2)
-            __syncthreads();
+            slot_barrier(slot, G::NT + 32);
             FWP_PROF(5)
         }
         FWP_PROF_END(0, ptid == 0 && slot == 0)
@@ -169,7 +166,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
         f2 S[G::NP];
         FWP_PROF_BEGIN
         load_cols(g, S, W, p.wE, p.E, p.M);
-        __syncthreads();
+        slot_barrier(slot, G::NT + 32);
         FWP_PROF(0)
         for (int c = 0; c <= nchunks; c++) {
             if (c < nchunks) {
@@ -285,7 +282,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                 }
             }
             FWP_PROF(1)
-            __syncthreads();
+            slot_barrier(slot, G::NT + 32);
             FWP_PROF(2)
         }
         store_cols(g, S, W, p.wE, p.E, p.M);
@@ -332,10 +329,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
     float* out0 = gram0 + SM::NB * SM::kGram;
     const int nchunks = (p.L + TC - 1) / TC;
     __syncthreads();
-    if (seq >= p.NH) {
-        for (int c = 0; c <= nchunks + 2; c++) __syncthreads();
-        return;
-    }
+    if (seq >= p.NH) return;      // an empty slot of the last CTA: nobody waits on its barrier
     if (role == 2) {
         // ===================================================== producer warp
         const int ptid = rtid & 31;
@@ -430,7 +424,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         landed(0);
         prepare(0);
-        __syncthreads();
+        slot_barrier(slot, 2 * G::NT + 32);
         for (int c = 0; c <= nchunks + 1; c++) {
             if (c + 2 < nchunks) issue(c + 2);
             if (c >= 2) flush(c - 2);
@@ -440,7 +434,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                 prepare(c + 1);
             }
             if (ptid == 0) bulk_wait_read_all();     // the flushed tiles may be rewritten after the barrier
-            __syncthreads();
+            slot_barrier(slot, 2 * G::NT + 32);
         }
         if (ptid == 0) bulk_wait_all();
     } else if (role == 0) {
@@ -449,7 +443,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         float* W = p.W + n * p.wN + h * p.wH;
         f2 S[G::NP];
         load_cols(g, S, W, p.wE, p.E, p.M);
-        __syncthreads();
+        slot_barrier(slot, 2 * G::NT + 32);
         for (int c = 0; c <= nchunks + 1; c++) {
             if (c < nchunks) {
                 Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
@@ -501,7 +495,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                 }
                 fence_async_smem();      // the staged outputs are read by a bulk store
             }
-            __syncthreads();
+            slot_barrier(slot, 2 * G::NT + 32);
         }
         store_cols(g, S, W, p.wE, p.E, p.M);
     } else {
@@ -510,7 +504,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         const float* W = p.W + n * p.wN + h * p.wH;
         f2 S[G::NP];
         load_cols(g, S, W, p.wE, p.E, p.M);      // start-of-segment state, read before the chain warp writes it back
-        __syncthreads();
+        slot_barrier(slot, 2 * G::NT + 32);
         for (int c = 0; c <= nchunks + 1; c++) {
             if (c >= 1 && c - 1 < nchunks) {
                 const int cc = c - 1;
@@ -552,7 +546,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                 }
                 fence_async_smem();
             }
-            __syncthreads();
+            slot_barrier(slot, 2 * G::NT + 32);
         }
     }
 }
@@ -611,10 +605,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
     float* dbt = o0 + 2 * SM::kO;       // dbeta of one chunk, assembled by the producer before its flush
     const int nchunks = (p.L + TC - 1) / TC;
     __syncthreads();
-    if (seq >= p.NH) {      // an empty slot of the last CTA only keeps the barrier count
-        for (int i = 0; i <= nchunks + 2; i++) __syncthreads();
-        return;
-    }
+    if (seq >= p.NH) return;      // an empty slot of the last CTA: nobody waits on its barrier
     // chunk index jc counts from the end of the sequence; nchunks-1-jc is the time-order chunk
     if (role == 2) {
         // ===================================================== producer warp
@@ -739,7 +730,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         landed(0);
         prepare(0);
-        __syncthreads();
+        slot_barrier(slot, 2 * G::NT + 32);
         FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i + 2 < nchunks) issue(i + 2);      // lands while this iteration's other work runs
@@ -755,7 +746,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
             }
             FWP_PROF(4)
             if (ptid == 0) bulk_wait_read_all();     // the flushed tiles may be rewritten after the barrier
-            __syncthreads();
+            slot_barrier(slot, 2 * G::NT + 32);
             FWP_PROF(5)
         }
         if (ptid == 0) bulk_wait_all();
@@ -767,7 +758,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
 #pragma unroll
         for (int i = 0; i < G::NP; i++) Gc[i] = 0ull;
         FWP_PROF_BEGIN
-        __syncthreads();
+        slot_barrier(slot, 2 * G::NT + 32);
         FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i < nchunks) {
@@ -853,7 +844,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                 fence_async_smem();      // beta*r (= dv) is read by a bulk store
             }
             FWP_PROF(1)
-            __syncthreads();
+            slot_barrier(slot, 2 * G::NT + 32);
             FWP_PROF(2)
         }
         FWP_PROF_END(8, rtid == 0)
@@ -866,7 +857,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
 #pragma unroll
         for (int i = 0; i < G::NP; i++) Gr[i] = 0ull;
         FWP_PROF_BEGIN
-        __syncthreads();
+        slot_barrier(slot, 2 * G::NT + 32);
         FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i >= 1 && i - 1 < nchunks) {
@@ -900,7 +891,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                 fence_async_smem();
             }
             FWP_PROF(1)
-            __syncthreads();
+            slot_barrier(slot, 2 * G::NT + 32);
             FWP_PROF(2)
         }
         store_rows(g, Sr, W, p.wE, p.E, p.M);
