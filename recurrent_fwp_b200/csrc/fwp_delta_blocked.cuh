@@ -589,6 +589,10 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
     constexpr int HS = sum4_stride<SPLIT>();
     constexpr int NSL = slots_for(G::NT);          // sequences per CTA
     constexpr int NCONS = NSL * G::NT;             // column-role threads, then row-role threads, then producers
+    // Gradients leave by 16-byte stores of the producer warp.  Bulk stores from shared memory are implemented
+    // (set to true) but need a generic-to-async proxy fence in the compute roles before every chunk's barrier,
+    // which measured about 1900 cycles per chunk on the column role's critical path.
+    constexpr bool kBulkStores = false;
     const int tid = threadIdx.x;
     const int role = tid < NCONS ? 0 : (tid < 2 * NCONS ? 1 : 2);     // 0 column, 1 row, 2 producer
     const int rtid = tid - role * NCONS;                               // index within the role
@@ -693,7 +697,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
 #pragma unroll
         for (int i = 0; i < 3; i++) {
             gbase[i] = reinterpret_cast<float*>(rg[i].p) + n * rg[i].sN + h * rg[i].sH;
-            es[i] = sizeof(T) == 4 && bulk_rows_ok<D, float>(gbase[i], rg[i].sL, i == 0 ? p.M : p.E);
+            es[i] = kBulkStores && sizeof(T) == 4 && bulk_rows_ok<D, float>(gbase[i], rg[i].sL, i == 0 ? p.M : p.E);
         }
         auto flush_col = [&](int jc) {      // dv = beta*r and dbeta of the chunk the column role just finished
             const float* x = x0 + (jc & 1) * SM::kX;
@@ -841,7 +845,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                         if ((lm % HS) == 0 && lm / HS < 4) xdb[(tb + lm / HS) * 8 + g.warp] = tot;
                     }
                 }
-                fence_async_smem();      // beta*r (= dv) is read by a bulk store
+                if (kBulkStores) fence_async_smem();      // beta*r (= dv) is read by a bulk store
             }
             FWP_PROF(1)
             slot_barrier(slot, 2 * G::NT + 32);
@@ -888,7 +892,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                         odk[t * D + g.idx] = dk;
                     }
                 }
-                fence_async_smem();
+                if (kBulkStores) fence_async_smem();
             }
             FWP_PROF(1)
             slot_barrier(slot, 2 * G::NT + 32);
