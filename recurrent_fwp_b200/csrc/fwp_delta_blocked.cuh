@@ -18,10 +18,13 @@
 //
 // Warp specialisation.  With a few hundred sequences there is about one warp per
 // SM sub-partition, so anything a warp does besides the dependency chain is
-// exposed latency.  Each CTA therefore runs separate warps in lock step, one
-// named barrier per sequence and chunk (the sequences of a CTA do not wait for each other):
-//   * a producer warp: cp.async staging two chunks ahead, Gram scalars one chunk
-//     ahead, and the 16-byte flush of the previous chunk's outputs;
+// exposed latency.  Each sequence is therefore served by separate warps that meet
+// at a named barrier of their own once per chunk (several sequences share a CTA
+// without waiting for each other):
+//   * a producer warp: staging two chunks ahead (forward: cp.async; backward: one
+//     1-D bulk copy per tensor and chunk completing on an mbarrier whose wait is
+//     bounded, cp.async for rows that are strided or unaligned), Gram scalars one
+//     chunk ahead, and the 16-byte flush of the previous chunk's outputs;
 //   * forward: the consumer warps own the state columns and only run the group loop;
 //   * backward: "column" warps run the blocked chain on G and publish u_t, beta_t r_t
 //     for a whole chunk; "row" warps follow one chunk behind with the per-step part

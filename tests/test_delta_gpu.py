@@ -263,3 +263,32 @@ def test_chunkwise_tensor_core_plan_meets_the_oracle(fwp, B, H, L, E, M):
             assert util.scaled_rel(g, r) <= 1e-3
         assert util.max_abs(W_back, W0) <= 1e-5
     assert util.max_abs(res[1][0], res[0][0]) <= 2e-5
+
+
+def test_chunkwise_plan_on_strided_views_of_a_fused_projection(fwp):
+    """The opt-in chunkwise plan reads the (B,H,L,d) views of a fused (L,B,H,3d+1) projection (rows 4-byte
+    aligned, not contiguous) through its element-wise load path; same result as the contiguous copies."""
+    from recurrent_fwp_b200 import _lib
+    L, B, H, d = 45, 2, 3, 16
+    g = util.gen(91)
+    qkvb = torch.randn(L, B, H, 3 * d + 1, generator=g).to(DEV)
+    q, k, v, beta = torch.split(qkvb, (d, d, d, 1), dim=-1)
+    q, k, v, beta = (t.permute(1, 2, 0, 3) for t in (q, k, v, torch.sigmoid(beta)))
+    q = torch.softmax(q, -1)
+    k = torch.softmax(k, -1)
+    gy = torch.randn(B, H, L, d, generator=g).to(DEV)
+    res = []
+    try:
+        _lib.tune('delta.chunk', 1)
+        for contiguous in (False, True):
+            leaves = [(t.contiguous() if contiguous else t).detach().requires_grad_() for t in (q, k, v, beta)]
+            assert contiguous or not leaves[2].is_contiguous()
+            W = torch.zeros(B, H, d, d, device=DEV)
+            y = fwp.fast_weight_delta(*leaves, W)
+            W_end = W.clone()
+            y.backward(gy)
+            res.append([y.detach(), W_end] + [t.grad for t in leaves])
+    finally:
+        _lib.tune('delta.chunk', 0)
+    for a, b in zip(*res):
+        assert torch.equal(a.contiguous(), b.contiguous())
