@@ -188,8 +188,10 @@ class DeltaStep:
         self.inp = [make_inputs(seed + s, B, H, L, d, dtype, device) for s in range(segs)]
         f32 = dict(device=device, dtype=torch.float32)
         io = dict(device=device, dtype=dtype)
-        self.W = torch.zeros(B, H, d, d, **f32)
-        self.W_keep = [torch.empty(B, H, d, d, **f32) for _ in range(segs)]
+        # Ws[s] is the state segment s starts from; its forward leaves the end state there, a clone of it becomes
+        # Ws[s+1] (the carried memory, as the reference's layers hand it on) and its backward rewinds Ws[s] in place.
+        self.Ws = [torch.zeros(B, H, d, d, **f32) for _ in range(segs + 1)]
+        self.W = self.Ws[0]
         self.y = [torch.empty(B, H, L, d, **io) for _ in range(segs)]
         self.vo = [torch.empty(B, H, L, d, **f32) for _ in range(segs)]
         self.vi = [torch.empty(B, H, L, d, **f32) for _ in range(segs)]
@@ -198,7 +200,7 @@ class DeltaStep:
         self.code = _lib.io_dtype(self.inp[0][0])
         D = _lib.desc
         self.d_in = [[D(t) for t in seg] for seg in self.inp]
-        self.d_W = D(self.W)
+        self.d_Ws = [D(t) for t in self.Ws]
         self.d_y = [D(t) for t in self.y]
         self.d_vo = [D(t) for t in self.vo]
         self.d_vi = [D(t) for t in self.vi]
@@ -212,7 +214,7 @@ class DeltaStep:
         B, H, L, d = self.shape
         q, k, v, b, _ = self.d_in[s]
         self.L_.check(self.L_.lib.fwp_fast_weight_forward_ws(
-            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], self.d_W, self.d_y[s],
+            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], self.d_Ws[s], self.d_y[s],
             self.code, stream, self.dev_index, self.ws_f, self.ws_f_n), 'fwd')
 
     def bwd(self, s, stream):
@@ -220,42 +222,46 @@ class DeltaStep:
         q, k, v, b, gy = self.d_in[s]
         gq, gk, gv, gb = self.d_g[s]
         self.L_.check(self.L_.lib.fwp_fast_weight_backward_ws(
-            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], gy, self.d_W, gq, gk, gv, gb,
+            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], gy, self.d_Ws[s], gq, gk, gv, gb,
             self.code, stream, self.dev_index, self.ws_b, self.ws_b_n), 'bwd')
 
     def step(self):
-        """fwd, keep a clone of the end state (the carried memory), bwd (rewinds W), restore the carried state."""
+        """Per segment: fwd, clone the end state as the next segment's start state (the carried memory; the reference's
+        layers do the same clone because the backward rewinds the state in place), bwd."""
         stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        self.W.zero_()
+        self.Ws[0].zero_()
         for s in range(self.segs):
             self.fwd(s, stream)
-            self.W_keep[s].copy_(self.W)
+            self.Ws[s + 1].copy_(self.Ws[s])
             self.bwd(s, stream)
-            self.W.copy_(self.W_keep[s])
 
 
 def time_kernels(ds, flush, reps):
-    """Average device time of one forward and one backward launch (CUDA events on the launching stream,
-    L2 flushed before each launch)."""
+    """Average device time of one forward and one backward launch: CUDA events on the launching stream around the
+    launches of all segments back to back (their inputs are distinct tensors: 4 x 35 MB forward, 4 x 61 MB backward
+    at the LM shape, more than the 126 MB L2), L2 flushed before each event pair.  Events are created before the
+    flush so that the host is ahead of the device when the first launch is due."""
     stream_obj = torch.cuda.current_stream(ds.device)
     stream = ctypes.c_void_p(stream_obj.cuda_stream)
     tf, tb = [], []
-    for i in range(reps + 2):     # the first two launches are warm-up (clock ramp, cold instruction cache)
-        s = i % ds.segs
-        ds.W.zero_()
-        flush()
+    for i in range(reps + 2):     # the first two rounds are warm-up (clock ramp, cold instruction cache)
         e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        for W in ds.Ws:
+            W.zero_()
+        flush()
         e0.record(stream_obj)
-        ds.fwd(s, stream)
+        for s in range(ds.segs):
+            ds.fwd(s, stream)
         e1.record(stream_obj)
         flush()
         e2.record(stream_obj)
-        ds.bwd(s, stream)
+        for s in range(ds.segs):
+            ds.bwd(s, stream)
         e3.record(stream_obj)
         torch.cuda.synchronize(ds.device)
         if i >= 2:
-            tf.append(e0.elapsed_time(e1))
-            tb.append(e2.elapsed_time(e3))
+            tf.append(e0.elapsed_time(e1) / ds.segs)
+            tb.append(e2.elapsed_time(e3) / ds.segs)
     return statistics.mean(tf) * 1e-3, statistics.mean(tb) * 1e-3, min(tf) * 1e-3, min(tb) * 1e-3
 
 
@@ -567,7 +573,9 @@ def run_gpu_arm(args):
                        'timing': 'CUDA events per step, summed; max over ranks'},
             'roofline': {'bound': 'hbm', 'kernel': 'delta_bwd_kernel', 'achieved': ach_b, 'peak': peak, 'unit': 'GB/s',
                          'frac': ach_b / peak, 'peak_kind': peak_kind, 'traffic': NCU_TRAFFIC_BWD.get(args.workload),
-                         'algorithmic_bytes_per_launch': bytes_bwd, 'launch_s': tb, 'launch_s_min': tb_min},
+                         'algorithmic_bytes_per_launch': bytes_bwd, 'launch_s': tb, 'launch_s_min': tb_min,
+                         'timing': 'CUDA events around the %d segments launched back to back (distinct inputs, '
+                                   'L2 flushed before the first), divided by %d' % (segs, segs)},
             'roofline_fwd_bwd': {'achieved': ach_fb, 'peak': peak, 'unit': 'GB/s', 'frac': ach_fb / peak,
                                  'algorithmic_bytes': bytes_fwd + bytes_bwd, 'fwd_s': tf, 'bwd_s': tb,
                                  'fwd_s_min': tf_min, 'bwd_s_min': tb_min},

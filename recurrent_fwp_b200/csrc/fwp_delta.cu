@@ -352,6 +352,12 @@ static int launch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     return launch(delta_fwd_kernel<D, SPLIT, TC, T, SUM>, p, (nseq + NSL - 1) / NSL, NSL * (D * SPLIT + 32),
                   NSL * WsFwdSmem<D, TC, T>::kFloats * sizeof(float), st);
 }
+template <int TC, typename T>
+static int launch_fwd_mma(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
+    constexpr int NSL = slots_for(32);
+    return launch(delta_fwd_kernel<16, 2, TC, T, false, true>, p, (nseq + NSL - 1) / NSL, NSL * 64,
+                  NSL * WsFwdSmem<16, TC, T>::kFloats * sizeof(float), st);
+}
 template <int D, int SPLIT, int TC, typename T>
 static int launch_fwd3(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     constexpr int NSL = slots_for(D * SPLIT);
@@ -430,6 +436,8 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
             if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
             if constexpr (!SUM) {
+                // tensor-core group loop ("delta_fwd.mma"); the streams may be fp32 or bf16, the math is the same
+                if (force == -1 && tune_get("delta_fwd.mma", 0) == 1) return launch_fwd_mma<32, T>(p, nseq, st);
                 // opt-in chain / read-out split of the group loop with bulk-copy staging (measured slower
                 // than one consumer warp per sequence on the language-model shape)
                 if (tune_get("delta_fwd.roles", 2) == 3) return launch_fwd3<16, 2, 32, T>(p, nseq, st);

@@ -31,6 +31,7 @@
 //     (dq, dk, in-place rewind of S).
 #pragma once
 #include "fwp_core.cuh"
+#include "fwp_mma.cuh"
 
 namespace fwp {
 
@@ -73,9 +74,10 @@ struct WsFwdSmem {
     static constexpr int kFloats = NS * kStage + 2 * kGram + 2 * kOut;
 };
 
-template <int D, int SPLIT, int TC, typename T, bool SUM>
+template <int D, int SPLIT, int TC, typename T, bool SUM, bool MMA = false>
 __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta_fwd_kernel(const DeltaFwdParams p) {
     using G = Geo<D, SPLIT>;
+    static_assert(!MMA || (D == 16 && SPLIT == 2 && !SUM), "the tensor-core group loop is written for one warp per 16x16 state");
     using SM = WsFwdSmem<D, TC, T>;
     using Stage = WsFwdStage<D, TC, T>;
     static_assert(TC % 4 == 0, "chunk must hold whole groups");
@@ -162,6 +164,121 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
             FWP_PROF(5)
         }
         FWP_PROF_END(0, ptid == 0 && slot == 0)
+    } else if constexpr (MMA) {
+        // ===================================================== consumer warp, tensor-core group loop
+        // The state is kept transposed, X = S^T (rows m, columns e), as an mma accumulator fragment: lane
+        // (g = lane/4, t = lane%4) holds rows m = g, g+8 and columns e = 8j+2t, 8j+2t+1.  Per group of four steps:
+        //   P = X [k_0 q_0 k_1 q_1 k_2 q_2 k_3 q_3]     one m16n8k8 product over e (X is the A operand after
+        //                                               relabelling the contraction index); lane t receives
+        //                                               a_t = S0^T k_t and b_t = S0^T q_t for its two rows m
+        //   d_t = v_t - a_t, exchanged inside the quad; every lane runs the scalar recurrence
+        //   u_s = beta_s (d_s - sum_{i<s} u_i k_i.k_s) for both rows; lane t keeps v_old_t, u_t, y_t
+        //   X += U^T K                                  one m16n8k4 product per column tile over the four steps
+        // Operands are split into two TF32 parts (three MMAs per tile), so the result keeps fp32 accuracy.  Against
+        // the FMA loop this needs 11 instead of 25 shared-memory loads per group, none of them a 16-fold broadcast.
+        const int lane = tid & 31, g = lane >> 2, t = lane & 3;
+        float* W = p.W + n * p.wN + h * p.wH;
+        Frag X;
+        ck_load_state_t(X, W, p.wE, p.E, p.M, g, t);
+        slot_barrier(slot, G::NT + 32);
+        for (int c = 0; c <= nchunks; c++) {
+            if (c < nchunks) {
+                Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
+                const float* gram = gram0 + (c & 1) * SM::kGram;
+                float* oy = out0 + (c & 1) * SM::kOut;
+                float* ovo = oy + TC * D;
+                float* ou = ovo + TC * D;
+                const int nt = min(TC, p.L - c * TC), ng = (nt + 3) >> 2;
+                const float* vec0 = ((g & 1) ? s.q.f : s.k.f) + (g >> 1) * D + 2 * t;      // column g of [k_0 q_0 k_1 q_1 ...]
+#pragma unroll 1
+                for (int gi = 0; gi < ng; gi++) {
+                    const int tb = 4 * gi;
+                    // ---- operands that do not depend on the state
+                    const float2 e0 = *reinterpret_cast<const float2*>(vec0 + tb * D);
+                    const float2 e1 = *reinterpret_cast<const float2*>(vec0 + tb * D + 8);
+                    const float vt0 = s.v.f[(tb + t) * D + g], vt1 = s.v.f[(tb + t) * D + g + 8];
+                    const float kt0 = s.k.f[(tb + t) * D + g], kt1 = s.k.f[(tb + t) * D + g + 8];
+                    float gs[16];
+                    load16(gs, gram + gi * 16);
+                    const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
+                    const float be[4] = {b4.x, b4.y, b4.z, b4.w};
+                    unsigned bh[2][2], bl[2][2];
+                    tf32_split(e0.x, bh[0][0], bl[0][0]);
+                    tf32_split(e0.y, bh[0][1], bl[0][1]);
+                    tf32_split(e1.x, bh[1][0], bl[1][0]);
+                    tf32_split(e1.y, bh[1][1], bl[1][1]);
+                    unsigned kh[2], kl[2];
+                    tf32_split(kt0, kh[0], kl[0]);
+                    tf32_split(kt1, kh[1], kl[1]);
+                    // ---- P = X [k q ...]
+                    AFr xa;
+                    a_from_acc(xa, X);
+                    float ph[4] = {0.f, 0.f, 0.f, 0.f}, pl[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int ks = 0; ks < 2; ks++) {
+                        mma_tf32(pl, xa.l[ks], bh[ks]);
+                        mma_tf32(pl, xa.h[ks], bl[ks]);
+                        mma_tf32(ph, xa.h[ks], bh[ks]);
+                    }
+                    const float a0 = ph[0] + pl[0], q0 = ph[1] + pl[1], a1 = ph[2] + pl[2], q1 = ph[3] + pl[3];
+                    // ---- d_s for all four steps, rows m = g (suffix 0) and m = g + 8 (suffix 1)
+                    const float d0 = vt0 - a0, d1 = vt1 - a1;
+                    float ds0[4], ds1[4];
+#pragma unroll
+                    for (int sidx = 0; sidx < 4; sidx++) {
+                        ds0[sidx] = __shfl_sync(0xffffffffu, d0, (lane & ~3) | sidx);
+                        ds1[sidx] = __shfl_sync(0xffffffffu, d1, (lane & ~3) | sidx);
+                    }
+                    float u0[4], u1[4], c0[4], c1[4];       // c = the value before the scaling by beta: v_old_s = v_s - c_s
+#pragma unroll
+                    for (int sidx = 0; sidx < 4; sidx++) {
+                        float x0 = ds0[sidx], x1 = ds1[sidx];
+#pragma unroll
+                        for (int i = 0; i < sidx; i++) {
+                            x0 = fmaf(-u0[i], gs[gram_kk(i, sidx)], x0);
+                            x1 = fmaf(-u1[i], gs[gram_kk(i, sidx)], x1);
+                        }
+                        c0[sidx] = x0; c1[sidx] = x1;
+                        u0[sidx] = be[sidx] * x0; u1[sidx] = be[sidx] * x1;
+                    }
+                    // ---- this lane's step t: u_t, v_old_t, y_t = b_t + sum_{i<=t} u_i (k_i . q_t)
+                    const float ut0 = t == 0 ? u0[0] : t == 1 ? u0[1] : t == 2 ? u0[2] : u0[3];
+                    const float ut1 = t == 0 ? u1[0] : t == 1 ? u1[1] : t == 2 ? u1[2] : u1[3];
+                    const float ct0 = t == 0 ? c0[0] : t == 1 ? c0[1] : t == 2 ? c0[2] : c0[3];
+                    const float ct1 = t == 0 ? c1[0] : t == 1 ? c1[1] : t == 2 ? c1[2] : c1[3];
+                    float cq[4];
+                    cq[0] = t == 0 ? gs[gram_kq(0, 0)] : t == 1 ? gs[gram_kq(0, 1)] : t == 2 ? gs[gram_kq(0, 2)] : gs[gram_kq(0, 3)];
+                    cq[1] = t == 0 ? 0.f : t == 1 ? gs[gram_kq(1, 1)] : t == 2 ? gs[gram_kq(1, 2)] : gs[gram_kq(1, 3)];
+                    cq[2] = t <= 1 ? 0.f : t == 2 ? gs[gram_kq(2, 2)] : gs[gram_kq(2, 3)];
+                    cq[3] = t <= 2 ? 0.f : gs[gram_kq(3, 3)];
+                    float y0 = q0, y1 = q1;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        y0 = fmaf(u0[i], cq[i], y0);
+                        y1 = fmaf(u1[i], cq[i], y1);
+                    }
+                    const int o0 = (tb + t) * D + g;
+                    oy[o0] = y0; oy[o0 + 8] = y1;
+                    ovo[o0] = vt0 - ct0; ovo[o0 + 8] = vt1 - ct1;
+                    ou[o0] = ut0; ou[o0 + 8] = ut1;
+                    // ---- X += U^T K over the four steps (contraction slot t <-> step t)
+                    unsigned uh[2], ul[2];
+                    tf32_split(ut0, uh[0], ul[0]);
+                    tf32_split(ut1, uh[1], ul[1]);
+                    float lo0[4] = {0.f, 0.f, 0.f, 0.f}, lo1[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_tf32_k4(lo0, ul, kh[0]);
+                    mma_tf32_k4(lo0, uh, kl[0]);
+                    mma_tf32_k4(X.c[0], uh, kh[0]);
+                    mma_tf32_k4(lo1, ul, kh[1]);
+                    mma_tf32_k4(lo1, uh, kl[1]);
+                    mma_tf32_k4(X.c[1], uh, kh[1]);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) { X.c[0][i] += lo0[i]; X.c[1][i] += lo1[i]; }
+                }
+            }
+            slot_barrier(slot, G::NT + 32);
+        }
+        ck_store_state_t(X, W, p.wE, p.E, p.M, g, t);
     } else {
         // ===================================================== consumer warps: the group loop
         const G g(tid);

@@ -31,38 +31,13 @@
 // chunk of one sequence does not fill it.)
 #pragma once
 #include "fwp_delta_params.cuh"
+#include "fwp_mma.cuh"
 
 namespace fwp {
 
 constexpr int kCkLd = 20;                 // tile row stride in floats: rows stay 16-byte aligned, row-fragment loads hit 32 banks
 constexpr int kCkTile = 16 * kCkLd;       // one 16x16 tile
 constexpr int kCkWarps = 4;               // warps per CTA = chunks per super-chunk
-
-struct Frag {                             // 16x16 fp32 accumulator of one warp: lane (g = lane/4, t = lane%4) holds
-    float c[2][4];                        // c[j][0..1] = (row g, cols 8j+2t, +1), c[j][2..3] = (row g+8, same cols)
-};
-
-__device__ __forceinline__ void frag_zero(Frag& f) {
-#pragma unroll
-    for (int j = 0; j < 2; j++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) f.c[j][i] = 0.f;
-}
-
-// x = hi + lo with hi and lo valid TF32 bit patterns (10 explicit mantissa bits, the low 13 bits zero).  Both
-// parts are taken by truncation: hi is within one TF32 ulp of x, lo carries the next 11 bits, and what is
-// dropped is below 2^-20 |x|.  Two logic operations and one subtraction; the rounding conversion of the ISA
-// costs several times that on this part and the products are issue-bound.
-__device__ __forceinline__ void tf32_split(float x, unsigned& hi, unsigned& lo) {
-    hi = __float_as_uint(x) & 0xffffe000u;
-    lo = __float_as_uint(x - __uint_as_float(hi)) & 0xffffe000u;
-}
-
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
-    asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
 
 // acc += A B for 16x16 operands given as element functors a(m, k) and b(k, n)
 template <class FA, class FB>
@@ -93,11 +68,6 @@ __device__ __forceinline__ void mm16(Frag& acc, FA a, FB b, int g, int t) {
         for (int i = 0; i < 4; i++) acc.c[j][i] += lo.c[j][i];
 }
 
-// Operand fragments of a 16x16 matrix, split once into TF32 hi/lo parts, so that a matrix that feeds several
-// products is loaded and split a single time.
-struct AFr { unsigned h[2][4], l[2][4]; };            // [k-step][m16n8k8 A registers]
-struct BFr { unsigned h[2][2][2], l[2][2][2]; };      // [k-step][n-tile][B registers]
-
 template <class FA>
 __device__ __forceinline__ void load_a(AFr& f, FA a, int g, int t) {
 #pragma unroll
@@ -118,18 +88,6 @@ __device__ __forceinline__ void load_b(BFr& f, FB b, int g, int t) {
             tf32_split(b(ks * 8 + t, 8 * j + g), f.h[ks][j][0], f.l[ks][j][0]);
             tf32_split(b(ks * 8 + t + 4, 8 * j + g), f.h[ks][j][1], f.l[ks][j][1]);
         }
-}
-// An accumulator fragment used as the left operand of the next product: k-step j takes the accumulator's
-// column tile j with the contraction index relabelled (slot t <-> column 8j+2t, slot t+4 <-> column 8j+2t+1);
-// the right operand must then be loaded with load_b_relabelled.
-__device__ __forceinline__ void a_from_acc(AFr& f, const Frag& c) {
-#pragma unroll
-    for (int j = 0; j < 2; j++) {
-        tf32_split(c.c[j][0], f.h[j][0], f.l[j][0]);
-        tf32_split(c.c[j][2], f.h[j][1], f.l[j][1]);
-        tf32_split(c.c[j][1], f.h[j][2], f.l[j][2]);
-        tf32_split(c.c[j][3], f.h[j][3], f.l[j][3]);
-    }
 }
 template <class FB>
 __device__ __forceinline__ void load_b_relabelled(BFr& f, FB b, int g, int t) {
@@ -412,25 +370,6 @@ __device__ __forceinline__ void ck_scan_step(Frag& X, const float (&tf)[8], cons
             X.c[jn][i] = (X.c[jn][i] + rf[jn * 4 + i]) - ((lo[0].c[jn][i] + lo[1].c[jn][i]) + (hi[0].c[jn][i] + hi[1].c[jn][i]));
 }
 
-// transposed state fragment <-> the E x M state in global memory
-__device__ __forceinline__ void ck_load_state_t(Frag& X, const float* W, long long wE, int E, int M, int g, int t) {
-#pragma unroll
-    for (int j = 0; j < 2; j++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int m = g + 8 * (i >> 1), e = 8 * j + 2 * t + (i & 1);
-            X.c[j][i] = (e < E && m < M) ? W[e * wE + m] : 0.f;
-        }
-}
-__device__ __forceinline__ void ck_store_state_t(const Frag& X, float* W, long long wE, int E, int M, int g, int t) {
-#pragma unroll
-    for (int j = 0; j < 2; j++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int m = g + 8 * (i >> 1), e = 8 * j + 2 * t + (i & 1);
-            if (e < E && m < M) W[e * wE + m] = X.c[j][i];
-        }
-}
 __device__ __forceinline__ void ck_load8(float (&d)[8], const float* src) {
     const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
     d[0] = a.x; d[1] = a.y; d[2] = a.z; d[3] = a.w; d[4] = b.x; d[5] = b.y; d[6] = b.z; d[7] = b.w;

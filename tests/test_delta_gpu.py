@@ -292,3 +292,33 @@ def test_chunkwise_plan_on_strided_views_of_a_fused_projection(fwp):
         _lib.tune('delta.chunk', 0)
     for a, b in zip(*res):
         assert torch.equal(a.contiguous(), b.contiguous())
+
+
+@pytest.mark.parametrize('B,H,L,E,M', [
+    (2, 3, 16, 16, 16), (1, 2, 64, 16, 16), (2, 2, 37, 16, 16), (1, 3, 100, 16, 16), (1, 2, 300, 16, 16),
+    (2, 1, 45, 9, 16), (1, 2, 33, 16, 5), (1, 2, 50, 12, 10), (3, 5, 256, 16, 16),
+])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_tensor_core_group_loop_of_the_forward_meets_the_oracle(fwp, B, H, L, E, M, dtype):
+    """Forward plan for head dims up to 16 whose group products run on the tensor cores (TF32 hi/lo split):
+    same tolerances as the FMA plan, and the backward (which consumes its v_old) still meets the oracle."""
+    from recurrent_fwp_b200 import _lib
+    q, k, v, b, gy = util.delta_inputs(95, B, H, L, E, M, dtype=dtype)
+    W0 = torch.randn(B, H, E, M, generator=util.gen(96)) * 0.1
+    res = {}
+    try:
+        for mma in (1, 0):
+            _lib.tune('delta_fwd.mma', mma)
+            W = W0.to(DEV)
+            res[mma] = run_cuda(fwp, q, k, v, b, W, gy) + (W,)
+    finally:
+        _lib.tune('delta_fwd.mma', -1)
+    y64, g64, S64 = run_loop(q.float(), k.float(), v.float(), b.float(), W0, gy.float(), torch.float64)
+    ytol, gtol = (1e-4, 1e-3) if dtype == torch.float32 else (2e-2 * y64.abs().max().item(), 3e-2)
+    for mma in (1, 0):
+        y, grads, W_end, W_back = res[mma]
+        assert util.max_abs(y.float(), y64) <= ytol and util.max_abs(W_end, S64) <= 1e-4
+        for g, r in zip(grads, g64):
+            assert util.scaled_rel(g.float(), r) <= gtol
+    if dtype == torch.float32:
+        assert util.max_abs(res[1][0], res[0][0]) <= 2e-5
