@@ -409,10 +409,10 @@ static int launch_bwd_generic(const DeltaBwdParams& p, int nseq, cudaStream_t st
 
 // Which execution plan runs by default was picked per head dimension from measurements on B200
 // (forward / backward device time, 512 sequences):
-//   D=16: blocked + warp-specialised wins both ways (34.8 / 58.3 us vs 45.0 / 112.6 us per-step);
-//   D=32: forward per-step 62 us vs blocked 64-72 us, backward blocked 145 us vs per-step 178 us;
-//   D=64: forward per-step 158 us vs blocked 213 us; backward fp32 blocked 481 us vs per-step 588 us,
-//         bf16 streams per-step 2.35 ms vs blocked 3.10 ms (the producer warp's widening pass).
+//   D=16: blocked + warp-specialised wins both ways (28.3 / 48.5 us vs 41.7 / 103.7 us per-step);
+//   D=32: forward per-step 55 us vs blocked 56-71 us, backward blocked 138 us vs per-step 175 us;
+//   D=64: forward per-step 161 us vs blocked 208 us; backward fp32 blocked 479 us vs per-step 584 us,
+//         bf16 streams (1024 steps) per-step 2.35 ms vs blocked 3.12 ms (the producer warp's widening pass).
 // Short segments (the reinforcement-learning callers step the op with L = 1, reinforcement_learning/torchbeast/
 // layer.py:143-186) take the per-step plan, whose CTAs start faster: at L <= 16 it measures 10-12 us against
 // 12-15 us per launch (32 x 8 sequences), and the d=64 fp32 backward only pays off beyond 64 steps.
@@ -429,14 +429,14 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
         case 16: {
             if constexpr (!SUM && sizeof(T) == 4) {
                 // opt-in chunkwise tensor-core form ("delta.chunk" = 1 and a workspace): three launches, every
-                // chunk in parallel; measured issue-bound and behind the recurrent plan on B200 (48 vs 35 us
-                // forward, 76 vs 61 us backward at 512 sequences of 256 steps)
+                // chunk in parallel; measured issue-bound and behind the recurrent plan on B200 (40 vs 28 us
+                // forward, 65 vs 48 us backward at 512 sequences of 256 steps)
                 if (p.ws && force == -1 && tune_get("delta.chunk", 0) == 1) return launch_fwd_chunk(p, nseq, st);
             }
             if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
             if constexpr (!SUM) {
-                // tensor-core group loop ("delta_fwd.mma"); the streams may be fp32 or bf16, the math is the same
+                // opt-in tensor-core group loop ("delta_fwd.mma" = 1; fp32 or bf16 streams): 30.5 us against 28.4 us
                 if (force == -1 && tune_get("delta_fwd.mma", 0) == 1) return launch_fwd_mma<32, T>(p, nseq, st);
                 // opt-in chain / read-out split of the group loop with bulk-copy staging (measured slower
                 // than one consumer warp per sequence on the language-model shape)
@@ -445,7 +445,8 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
             return launch_fwd<16, 2, 32, T, SUM>(p, nseq, st);
         }
         case 32: {
-            if (force != 1) return launch_fwd_step<32, 1, 16, T, SUM>(p, nseq, st);
+            // fp32 streams: per-step 55 us vs blocked 56 us; bf16 streams: blocked 80 us vs per-step 87 us
+            if (force == 0 || (force == -1 && (sizeof(T) == 4 || p.L <= kShortSeq))) return launch_fwd_step<32, 1, 16, T, SUM>(p, nseq, st);
             const int sp = tune_get(key, 1);
             if (sp == 2) return launch_fwd<32, 2, 16, T, SUM>(p, nseq, st);
             if (sp == 4) return launch_fwd<32, 4, 16, T, SUM>(p, nseq, st);
@@ -477,7 +478,8 @@ static int dispatch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
             return launch_bwd<16, 2, 16, T>(p, nseq, st);
         }
         case 32: {
-            if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_bwd_step<32, 2, 8, T>(p, nseq, st);
+            // fp32 streams: blocked 138 us vs per-step 175 us; bf16 streams: per-step 201 us vs blocked 207 us
+            if (force == 0 || (force == -1 && (p.L <= kShortSeq || sizeof(T) != 4))) return launch_bwd_step<32, 2, 8, T>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_bwd<32, 4, 8, T>(p, nseq, st);
             return launch_bwd<32, 2, 8, T>(p, nseq, st);
         }

@@ -748,15 +748,19 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
             mbar_fence_init();
         }
         __syncwarp();
-        const bool eq = bulk_rows_ok<D, T>(sq.base, sq.sL, sq.width), ek = bulk_rows_ok<D, T>(sk.base, sk.sL, sk.width),
-                   ev = bulk_rows_ok<D, T>(sv.base, sv.sL, sv.width), eg = bulk_rows_ok<D, T>(sg.base, sg.sL, sg.width),
-                   eo = bulk_rows_ok<D, float>(so.base, so.sL, so.width);
+        // One bulk copy per tensor and chunk pays off only when a chunk is long: at d = 32 / 64 a chunk is 8 / 4
+        // steps, six copies per chunk cost more to issue than the cp.async pieces they replace (measured 159 vs
+        // 145 us at d = 32 and 588 vs 481 us at d = 64 for 512 sequences of 256 steps), so those sizes keep cp.async.
+        constexpr bool kBulkLoads = D <= 16;
+        const bool eq = kBulkLoads && bulk_rows_ok<D, T>(sq.base, sq.sL, sq.width), ek = kBulkLoads && bulk_rows_ok<D, T>(sk.base, sk.sL, sk.width),
+                   ev = kBulkLoads && bulk_rows_ok<D, T>(sv.base, sv.sL, sv.width), eg = kBulkLoads && bulk_rows_ok<D, T>(sg.base, sg.sL, sg.width),
+                   eo = kBulkLoads && bulk_rows_ok<D, float>(so.base, so.sL, so.width);
         unsigned phase = 0;
         bool failed = false;
         auto issue = [&](int jc) {
             Stage s; s.bind(smem + (jc % SM::NS) * SM::kStage);
             const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
-            const bool eb = bulk_col_ok<T>(sb.base, sb.sL, t0, nt);
+            const bool eb = kBulkLoads && bulk_col_ok<T>(sb.base, sb.sL, t0, nt);
             if (ptid == 0 && (eq || ek || ev || eg || eo || eb)) {
                 unsigned long long* bar = &bars[jc % SM::NS];
                 const unsigned rows = nt * D * sizeof(T), rowsf = nt * D * sizeof(float), col = nt * sizeof(T);
@@ -779,7 +783,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         };
         auto landed = [&](int jc) {
             const int t0 = (nchunks - 1 - jc) * TC, nt = min(TC, p.L - t0);
-            if (eq || ek || ev || eg || eo || bulk_col_ok<T>(sb.base, sb.sL, t0, nt)) {
+            if (eq || ek || ev || eg || eo || (kBulkLoads && bulk_col_ok<T>(sb.base, sb.sL, t0, nt))) {
                 const int st = jc % SM::NS;
                 if (!failed && !mbar_wait_bounded(&bars[st], (phase >> st) & 1)) {
                     failed = true;
