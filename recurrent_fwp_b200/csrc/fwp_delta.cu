@@ -462,7 +462,9 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
 }
 
 template <typename T>
-static int dispatch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
+static int dispatch_bwd(const DeltaBwdParams& p0, int nseq, cudaStream_t st) {
+    DeltaBwdParams p = p0;
+    p.bulk = tune_get("delta_bwd.bulk", 1);
     const int D = pad_dim(p.E > p.M ? p.E : p.M);
     char key[48];
     snprintf(key, sizeof key, "delta_bwd.%d.split", D);

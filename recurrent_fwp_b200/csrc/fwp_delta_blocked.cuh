@@ -750,8 +750,9 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         __syncwarp();
         // One bulk copy per tensor and chunk pays off only when a chunk is long: at d = 32 / 64 a chunk is 8 / 4
         // steps, six copies per chunk cost more to issue than the cp.async pieces they replace (measured 159 vs
-        // 145 us at d = 32 and 588 vs 481 us at d = 64 for 512 sequences of 256 steps), so those sizes keep cp.async.
-        constexpr bool kBulkLoads = D <= 16;
+        // 138 us at d = 32 and 588 vs 479 us at d = 64 for 512 sequences of 256 steps), so those sizes keep cp.async.
+        // Issuing the six copies from six lanes of one instruction instead of one lane in turn was slower (50 us).
+        const bool kBulkLoads = D <= 16 && p.bulk;      // "delta_bwd.bulk" = 0 keeps cp.async (48.4 vs 46.3 us at d = 16)
         const bool eq = kBulkLoads && bulk_rows_ok<D, T>(sq.base, sq.sL, sq.width), ek = kBulkLoads && bulk_rows_ok<D, T>(sk.base, sk.sL, sk.width),
                    ev = kBulkLoads && bulk_rows_ok<D, T>(sv.base, sv.sL, sv.width), eg = kBulkLoads && bulk_rows_ok<D, T>(sg.base, sg.sL, sg.width),
                    eo = kBulkLoads && bulk_rows_ok<D, float>(so.base, so.sL, so.width);

@@ -18,6 +18,7 @@ struct DeltaBwdParams {
     float* W; long long wN, wH, wE;
     int H, L, E, M;
     int NH;     // number of sequences (N*H)
+    int bulk = 1;           // stage contiguous chunks with bulk copies where the kernel supports it
     float* ws = nullptr;    // caller-provided workspace of the chunkwise plan (null: recurrent plans only)
 };
 
