@@ -364,11 +364,11 @@ static int launch_fwd3(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     return launch(delta_fwd3_kernel<D, SPLIT, TC, T>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
                   NSL * WsFwd3Smem<D, TC, T>::kFloats * sizeof(float), st);
 }
-template <int D, int SPLIT, int TC, typename T>
+template <int D, int SPLIT, int TC, typename T, int PF = 2>
 static int launch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     constexpr int NSL = slots_for(D * SPLIT);
-    return launch(delta_bwd_kernel<D, SPLIT, TC, T>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
-                  NSL * WsBwdSmem<D, TC, T>::kFloats * sizeof(float), st);
+    return launch(delta_bwd_kernel<D, SPLIT, TC, T, PF>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
+                  NSL * WsBwdSmem<D, TC, T, PF>::kFloats * sizeof(float), st);
 }
 template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd_step(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
@@ -477,7 +477,11 @@ static int dispatch_bwd(const DeltaBwdParams& p0, int nseq, cudaStream_t st) {
             }
             if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_bwd_step<16, 2, 16, T>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_bwd<16, 4, 16, T>(p, nseq, st);
-            return launch_bwd<16, 2, 16, T>(p, nseq, st);
+            // 32-step chunks staged one chunk ahead (three stages; 203 KB of shared memory for four sequences) against
+            // 16-step chunks staged two ahead: 45.3 vs 46.3 us at 256 steps, 149.8 vs 155.4 us at 1024
+            // (fp32 streams only: the 16-bit staging copies of bf16 streams do not fit next to 32-step chunks)
+            if (sizeof(T) != 4 || tune_get("delta_bwd.16.chunk", 32) == 16) return launch_bwd<16, 2, 16, T>(p, nseq, st);
+            return launch_bwd<16, 2, 32, float, 1>(p, nseq, st);
         }
         case 32: {
             // fp32 streams: blocked 138 us vs per-step 175 us; bf16 streams: per-step 201 us vs blocked 207 us

@@ -688,9 +688,9 @@ struct WsBwdStage {
     }
 };
 
-template <int D, int TC, typename T>
+template <int D, int TC, typename T, int PF = 2>
 struct WsBwdSmem {
-    static constexpr int NS = 4;                       // in flight, prepared, column role, row role
+    static constexpr int NS = PF + 2;                  // PF chunks ahead (in flight / prepared), column role, row role
     static constexpr int kStage = WsBwdStage<D, TC, T>::kFloats;
     static constexpr int kGram = (TC / 4) * 16;
     static constexpr int kX = 2 * TC * D + TC * 8;     // u[TC][D], beta*r[TC][D] (= dv), dbeta partials[TC][8]
@@ -699,10 +699,13 @@ struct WsBwdSmem {
     static constexpr int kFloats = NS * kStage + 2 * kGram + 2 * kX + 2 * kO + r4(TC) + kBars;
 };
 
-template <int D, int SPLIT, int TC, typename T>
+// PF = how many chunks ahead the producer stages: 2 hides the memory latency behind a whole iteration; 1 needs one
+// stage less, which is what lets a chunk of 32 steps fit four sequences into the shared memory of an SM.
+template <int D, int SPLIT, int TC, typename T, int PF = 2>
 __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) delta_bwd_kernel(const DeltaBwdParams p) {
     using G = Geo<D, SPLIT>;
-    using SM = WsBwdSmem<D, TC, T>;
+    using SM = WsBwdSmem<D, TC, T, PF>;
+    static_assert(PF == 1 || PF == 2, "prefetch distance");
     using Stage = WsBwdStage<D, TC, T>;
     static_assert(TC % 4 == 0, "chunk must hold whole groups");
     constexpr bool KEEP = G::NR <= 8;
@@ -856,19 +859,19 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         };
         FWP_PROF_BEGIN
         issue(0);
-        if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        if (PF == 2 && nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         landed(0);
         prepare(0);
         slot_barrier(slot, 2 * G::NT + 32);
         FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
-            if (i + 2 < nchunks) issue(i + 2);      // lands while this iteration's other work runs
+            if (i + PF < nchunks) issue(i + PF);    // lands while this iteration's other work runs
             FWP_PROF(1)
             if (i >= 1 && i - 1 < nchunks) flush_col(i - 1);
             if (i >= 2) flush_row(i - 2);
             FWP_PROF(2)
             if (i + 1 < nchunks) {
-                if (i + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
+                if (PF == 2 && i + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
                 landed(i + 1);
                 FWP_PROF(3)
                 prepare(i + 1);
