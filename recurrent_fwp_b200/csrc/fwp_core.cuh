@@ -553,9 +553,12 @@ __device__ __forceinline__ void gram_phase(const float* ktile, const float* qtil
         const int a = (IA >> (2 * pidx)) & 3, b = (IB >> (2 * pidx)) & 3;
         const float* x = ktile + (4 * gi + a) * D;
         const float* y = (pidx < 6 ? ktile : qtile) + (4 * gi + b) * D;
+        // rows two apart start in the same bank: each lane walks its rows from a different 16-byte piece
+        const int rot = ((4 * gi + a) >> 1) + ((4 * gi + b) >> 1);
         f2 acc0 = 0ull, acc1 = 0ull;
 #pragma unroll
-        for (int i = 0; i < D / 4; i++) {
+        for (int ii = 0; ii < D / 4; ii++) {
+            const int i = (ii + rot) & (D / 4 - 1);
             const ulonglong2 xa = *reinterpret_cast<const ulonglong2*>(x + 4 * i);
             const ulonglong2 ya = *reinterpret_cast<const ulonglong2*>(y + 4 * i);
             acc0 = ffma2(xa.x, ya.x, acc0);
