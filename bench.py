@@ -48,7 +48,7 @@ WORKLOADS = {
 
 # DRAM read+write bytes of one backward launch, from the ncu capture summarised in
 # profiles/delta_fwd_bwd_lm_shape_ncu.md (dram__bytes_read.sum + dram__bytes_write.sum)
-NCU_TRAFFIC_BWD = {'lm': 44262912}
+NCU_TRAFFIC_BWD = {'lm': 44221312}
 
 
 def peaks():
