@@ -322,3 +322,27 @@ def test_tensor_core_group_loop_of_the_forward_meets_the_oracle(fwp, B, H, L, E,
             assert util.scaled_rel(g.float(), r) <= gtol
     if dtype == torch.float32:
         assert util.max_abs(res[1][0], res[0][0]) <= 2e-5
+
+
+@pytest.mark.parametrize('key,value', [('delta_bwd.bulk', 0), ('delta_bwd.16.chunk', 16)])
+@pytest.mark.parametrize('B,H,L', [(2, 3, 100), (1, 2, 257)])
+def test_alternative_backward_staging_plans_give_the_same_bits(fwp, key, value, B, H, L):
+    """d = 16 backward: cp.async instead of bulk-copy staging, and 16-step chunks staged two ahead instead of
+    32-step chunks staged one ahead.  Staging does not touch the arithmetic: results are bit-identical."""
+    from recurrent_fwp_b200 import _lib
+    d = 16
+    q, k, v, b, gy = util.delta_inputs(97, B, H, L, d)
+    W0 = torch.randn(B, H, d, d, generator=util.gen(98)) * 0.1
+    res = []
+    try:
+        for setting in (None, value):
+            if setting is not None:
+                _lib.tune(key, setting)
+            W = W0.to(DEV)
+            y, grads, W_end = run_cuda(fwp, q, k, v, b, W, gy)
+            res.append([y, W_end, W] + grads)
+    finally:
+        _lib.tune(key, 1 if key.endswith('bulk') else 32)
+    for a, c in zip(*res):
+        assert torch.equal(a, c)
+    assert _lib.device_fault() == 0
