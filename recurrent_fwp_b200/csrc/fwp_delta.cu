@@ -453,6 +453,11 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
             return launch_fwd<32, 1, 16, T, SUM>(p, nseq, st);
         }
         case 64: {
+            if constexpr (!SUM && sizeof(T) == 2) {
+                // chunkwise tensor-core form for bf16 streams ("delta.chunk64" = 0 switches it off)
+                if (force == -1 && p.L > kShortSeq && tune_get("delta.chunk64", 1) == 1 && chunk_bf16_applies(p))
+                    return launch_fwd_chunk_bf16(p, nseq, st);
+            }
             if (force != 1) return launch_fwd_step<64, 2, 8, T, SUM>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_fwd<64, 4, 8, T, SUM>(p, nseq, st);
             return launch_fwd<64, 2, 8, T, SUM>(p, nseq, st);

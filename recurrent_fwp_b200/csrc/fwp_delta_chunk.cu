@@ -1,5 +1,6 @@
 // Chunkwise plan of the delta rule: kernels in fwp_delta_chunk.cuh, launch sequence here.
 #include "fwp_delta_chunk.cuh"
+#include "fwp_delta_chunk_bf16.cuh"
 
 namespace fwp {
 
@@ -25,6 +26,21 @@ int launch_bwd_chunk(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     if (int rc = launch(delta_bwd_chunk_prep_kernel, p, grid, kCkWarps * 32, kCkWarps * CkBwdPrep::kWarp * sizeof(float), st)) return rc;
     if (int rc = launch(delta_bwd_chunk_scan_kernel, p, nseq, 32, kCkScanDepth * 3 * 256 * sizeof(float), st)) return rc;
     return launch(delta_bwd_chunk_post_kernel, p, grid, kCkWarps * 32, kCkWarps * CkBwdPost::kWarp * sizeof(float), st);
+}
+
+// ---- bf16 streams, E = M = 64: one fused launch per direction, no workspace
+static bool rows_ok(const Row4& r, int elem_bytes) {
+    const long long per16 = 16 / elem_bytes;
+    return (reinterpret_cast<uintptr_t>(r.p) & 15) == 0 && r.sN % per16 == 0 && r.sH % per16 == 0 && r.sL % per16 == 0;
+}
+
+bool chunk_bf16_applies(const DeltaFwdParams& p) {
+    return p.E == cb::D && p.M == cb::D && rows_ok(p.q, 2) && rows_ok(p.k, 2) && rows_ok(p.v, 2) && rows_ok(p.out, 2) &&
+           rows_ok(p.v_old, 4) && (!p.v_ins.p || rows_ok(p.v_ins, 4));
+}
+
+int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
+    return launch(delta_fwd_chunk_bf16_kernel, p, nseq, cb::NT, sizeof(cb::Smem), st);
 }
 
 }  // namespace fwp

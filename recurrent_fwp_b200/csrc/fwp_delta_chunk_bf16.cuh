@@ -1,0 +1,315 @@
+// Delta rule in chunkwise (WY / UT-transform) form for 16-bit streams and head dimension 64 (sm_100a).
+//
+// At d = 64 the per-step kernels are bound by fp32 FMA issue and by the delivery of every operand
+// vector to all columns (12 d^2 FMAs per step forward).  Here one CTA of four warps walks a sequence
+// in chunks of 16 steps, and every d-sized contraction is a warp-level bf16 tensor-core product
+// (mma.sync.m16n8k16, fp32 accumulation).  With S0 the state before the chunk, K, Q, V the chunk's
+// rows and b = beta:
+//
+//   Akk = strict_lower(K K^T), Aqk = lower(Q K^T)                          (bf16 products)
+//   [Cv | Ck] : c_t = rhs_t - sum_{i<t} Akk[t,i] b_i c_i  for rhs = [V | K] (fp32 substitution,
+//               one right-hand column per thread: 64 + 64 columns = 128 threads)
+//   w = Cv - Ck S0  (= v - v_old),  u = b w,  v_old = (V - Cv) + Ck S0
+//   y = Q S0 + Aqk u,   S1 = S0 + K^T u
+//
+// (the same recurrence as algorithmic/fast_weight/fast_weight_cuda.cu:107-180, regrouped).
+// The state is kept transposed, S^T (value index m by key index e): warp w owns the 16 rows
+// m in [16w, 16w+16) as a 16 x 64 fp32 accumulator.  That choice keeps the chain in registers:
+// the accumulator fragments of S^T, rounded to bf16, are the left operand of S^T Ck^T and S^T Q^T,
+// the accumulator fragment of u^T is the left operand of u^T Aqk^T and of the update u^T K, and
+// every right operand is a row-major shared-memory tile read with ldmatrix (transposed for K in
+// the update).  Outputs leave through shared-memory tiles as 16-byte row pieces.
+//
+// Rounding: the streams are bf16 already; S, Ck and u are rounded to bf16 only as product
+// operands, the state itself and all sums stay fp32, and the state update takes u as two bf16 parts.
+#pragma once
+#include "fwp_delta_params.cuh"
+
+namespace fwp {
+
+namespace cb {
+
+constexpr int D = 64;                   // E = M = 64
+constexpr int C = 16;                   // steps per chunk
+constexpr int NT = 128;                 // threads: four warps, and one thread per column of [V | K]
+constexpr int LDT = 72;                 // row stride of the 16 x 64 bf16 tiles (144 B: ldmatrix rows hit distinct banks)
+constexpr int LDA = 20;                 // row stride of Akk (fp32; 16-byte aligned rows)
+constexpr int LDQ = 24;                 // row stride of Aqk (bf16; 48 B)
+constexpr int LDC = 18;                 // row stride of the transposed fp32 tiles Cv^T, (V - Cv)^T  [m][t]
+constexpr int LDO = 68;                 // row stride of the fp32 output tiles [t][m]
+
+struct Smem {
+    __nv_bfloat16 k[2][C * LDT], v[2][C * LDT], q[2][C * LDT];    // input stages
+    __nv_bfloat16 ck[C * LDT];          // Ck, [t][e]
+    __nv_bfloat16 aqk[C * LDQ];         // Aqk, [t][i], zero above the diagonal
+    __nv_bfloat16 ys[C * LDT];          // y, [t][m]
+    float akk[C * LDA];                 // Akk, [t][i], zero on and above the diagonal
+    float cvT[D * LDC];                 // Cv^T, [m][t]
+    float vmcT[D * LDC];                // (V - Cv)^T, [m][t]
+    float vo[C * LDO];                  // v_old, [t][m]
+    float ui[C * LDO];                  // u, [t][m] (only when the caller asks for v_insert)
+    float b[2][C];
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void ldsm4(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)) : "memory");
+}
+__device__ __forceinline__ void ldsm4t(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)) : "memory");
+}
+// d += a b, a: 16 x 16 (row), b: 16 x 8 (col), bf16 operands, fp32 accumulation
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&h);
+}
+
+// Left-operand fragments of a 16 x 16 row-major bf16 block at `tile` (row stride ld elements):
+// lane l supplies the address of row (l & 15), column 8 (l >> 4).
+__device__ __forceinline__ void lda_rowmajor(unsigned (&a)[4], const __nv_bfloat16* tile, int ld, int lane) {
+    ldsm4(a, tile + (lane & 15) * ld + 8 * (lane >> 4));
+}
+// Right-operand fragments B[k][n] = X[n][k] from a row-major X (rows n, k contiguous), 16 (n) x 16 (k) block:
+// r[0], r[1] = b0, b1 of the n-tile 0..7, r[2], r[3] of the n-tile 8..15.
+__device__ __forceinline__ void ldb_nk(unsigned (&r)[4], const __nv_bfloat16* tile, int ld, int lane) {
+    ldsm4(r, tile + ((lane & 7) + 8 * (lane >> 4)) * ld + 8 * ((lane >> 3) & 1));
+}
+// Right-operand fragments B[k][n] = X[k][n] from a row-major X (rows k, n contiguous), 16 (k) x 16 (n) block:
+// r[0], r[1] = b0, b1 of the n-tile 0..7, r[2], r[3] of the n-tile 8..15.
+__device__ __forceinline__ void ldb_kn(unsigned (&r)[4], const __nv_bfloat16* tile, int ld, int lane) {
+    ldsm4t(r, tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ld + 8 * (lane >> 4));
+}
+
+// rows [t0, t0 + nt) of a (N,H,L,64) bf16 tensor into a tile, one 16-byte piece per thread; rows past nt become zero
+__device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat16* base, long long sL, int t0, int nt, int tid) {
+    const int row = tid >> 3, part = (tid & 7) * 8;
+    __nv_bfloat16* dst = tile + row * LDT + part;
+    if (row < nt) cp_async16(dst, base + (long long)(t0 + row) * sL + part);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+}
+
+}  // namespace cb
+
+// ------------------------------------------------------------------ forward
+// One CTA per sequence, four warps.  Per chunk: (1) the two Gram products, one 16 x 8 tile per warp;
+// (2) the triangular solve, one column of [V | K] per thread; (3) the chain, warp w on rows
+// m in [16w, 16w+16) of S^T; (4) coalesced stores of y, v_old (and u).  Input tiles of the next
+// chunk are in flight (cp.async) meanwhile.
+__global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_kernel(const DeltaFwdParams p) {
+    using namespace cb;
+    using bf16 = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char cb_smem[];
+    Smem& s = *reinterpret_cast<Smem*>(cb_smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int seq = blockIdx.x, n = seq / p.H, h = seq - n * p.H;
+    const bf16* qb = reinterpret_cast<const bf16*>(p.q.p) + n * p.q.sN + h * p.q.sH;
+    const bf16* kb = reinterpret_cast<const bf16*>(p.k.p) + n * p.k.sN + h * p.k.sH;
+    const bf16* vb = reinterpret_cast<const bf16*>(p.v.p) + n * p.v.sN + h * p.v.sH;
+    const bf16* bb = reinterpret_cast<const bf16*>(p.beta.p) + n * p.beta.sN + h * p.beta.sH;
+    bf16* yb = reinterpret_cast<bf16*>(p.out.p) + n * p.out.sN + h * p.out.sH;
+    float* vob = reinterpret_cast<float*>(p.v_old.p) + n * p.v_old.sN + h * p.v_old.sH;
+    float* uib = p.v_ins.p ? reinterpret_cast<float*>(p.v_ins.p) + n * p.v_ins.sN + h * p.v_ins.sH : nullptr;
+    float* W = p.W + n * p.wN + h * p.wH;
+    const int m0 = 16 * warp;
+
+    // S^T rows m0+g, m0+g+8; tile j holds the key indices 8j + 2 t4, +1
+    float S[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) S[j][i] = W[(long long)(8 * j + 2 * t4 + (i & 1)) * p.wE + m0 + g + 8 * (i >> 1)];
+
+    const int nchunks = (p.L + C - 1) / C;
+    {
+        const int nt = min(C, p.L);
+        load_tile(s.k[0], kb, p.k.sL, 0, nt, tid);
+        load_tile(s.v[0], vb, p.v.sL, 0, nt, tid);
+        load_tile(s.q[0], qb, p.q.sL, 0, nt, tid);
+        cp_async_commit();
+        if (tid < C) s.b[0][tid] = tid < nt ? __bfloat162float(bb[(long long)tid * p.beta.sL]) : 0.f;
+    }
+    for (int c = 0; c < nchunks; c++) {
+        const int cur = c & 1, t0 = c * C, nt = min(C, p.L - t0);
+        float bnext = 0.f;
+        if (c + 1 < nchunks) {
+            const int t1 = t0 + C, nt1 = min(C, p.L - t1);
+            load_tile(s.k[cur ^ 1], kb, p.k.sL, t1, nt1, tid);
+            load_tile(s.v[cur ^ 1], vb, p.v.sL, t1, nt1, tid);
+            load_tile(s.q[cur ^ 1], qb, p.q.sL, t1, nt1, tid);
+            cp_async_commit();
+            if (tid < nt1) bnext = __bfloat162float(bb[(long long)(t1 + tid) * p.beta.sL]);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const bf16* Ks = s.k[cur];
+        const bf16* Qs = s.q[cur];
+        const float* bs = s.b[cur];
+
+        {   // (1) Gram tiles: warps 0, 1 the two column tiles of K K^T, warps 2, 3 of Q K^T
+            const bf16* X = warp < 2 ? Ks : Qs;
+            const int j = warp & 1;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int kp = 0; kp < 2; kp++) {
+                unsigned bfr[4];
+                ldsm4(bfr, Ks + (8 * j + (lane & 7)) * LDT + 8 * (lane >> 3) + 32 * kp);
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    unsigned a[4];
+                    lda_rowmajor(a, X + 16 * (2 * kp + kk), LDT, lane);
+                    mma_bf16(acc, a, bfr[2 * kk], bfr[2 * kk + 1]);
+                }
+            }
+            const int col = 8 * j + 2 * t4;
+            if (warp < 2) {
+                *reinterpret_cast<float2*>(s.akk + g * LDA + col) =
+                    make_float2(col < g ? acc[0] : 0.f, col + 1 < g ? acc[1] : 0.f);
+                *reinterpret_cast<float2*>(s.akk + (g + 8) * LDA + col) =
+                    make_float2(col < g + 8 ? acc[2] : 0.f, col + 1 < g + 8 ? acc[3] : 0.f);
+            } else {
+                *reinterpret_cast<unsigned*>(s.aqk + g * LDQ + col) =
+                    pack_bf16(col <= g ? acc[0] : 0.f, col + 1 <= g ? acc[1] : 0.f);
+                *reinterpret_cast<unsigned*>(s.aqk + (g + 8) * LDQ + col) =
+                    pack_bf16(col <= g + 8 ? acc[2] : 0.f, col + 1 <= g + 8 ? acc[3] : 0.f);
+            }
+        }
+        __syncthreads();
+
+        {   // (2) unit lower triangular solve, one right-hand column per thread
+            const int col = tid & 63;
+            const bool is_v = tid < 64;
+            const bf16* rhs = (is_v ? s.v[cur] : Ks) + col;
+            float x[C];
+#pragma unroll
+            for (int t = 0; t < C; t++) {
+                const float r = __bfloat162float(rhs[t * LDT]);
+                float a0 = r, a1 = 0.f;
+#pragma unroll
+                for (int i4 = 0; i4 * 4 < t; i4++) {
+                    const float4 a = *reinterpret_cast<const float4*>(s.akk + t * LDA + 4 * i4);
+                    a0 = fmaf(-a.x, x[4 * i4], a0);
+                    if (4 * i4 + 1 < t) a1 = fmaf(-a.y, x[4 * i4 + 1], a1);
+                    if (4 * i4 + 2 < t) a0 = fmaf(-a.z, x[4 * i4 + 2], a0);
+                    if (4 * i4 + 3 < t) a1 = fmaf(-a.w, x[4 * i4 + 3], a1);
+                }
+                const float cc = a0 + a1;
+                x[t] = bs[t] * cc;
+                if (is_v) {
+                    s.cvT[col * LDC + t] = cc;
+                    s.vmcT[col * LDC + t] = r - cc;
+                } else {
+                    s.ck[t * LDT + col] = __float2bfloat16_rn(cc);
+                }
+            }
+        }
+        __syncthreads();
+
+        {   // (3) chain
+            unsigned sa[4][4];
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                sa[ks][0] = pack_bf16(S[2 * ks][0], S[2 * ks][1]);
+                sa[ks][1] = pack_bf16(S[2 * ks][2], S[2 * ks][3]);
+                sa[ks][2] = pack_bf16(S[2 * ks + 1][0], S[2 * ks + 1][1]);
+                sa[ks][3] = pack_bf16(S[2 * ks + 1][2], S[2 * ks + 1][3]);
+            }
+            float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float Y[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                unsigned bc[4], bq[4];
+                ldb_nk(bc, s.ck + 16 * ks, LDT, lane);
+                ldb_nk(bq, Qs + 16 * ks, LDT, lane);
+                mma_bf16(P[0], sa[ks], bc[0], bc[1]);
+                mma_bf16(P[1], sa[ks], bc[2], bc[3]);
+                mma_bf16(Y[0], sa[ks], bq[0], bq[1]);
+                mma_bf16(Y[1], sa[ks], bq[2], bq[3]);
+            }
+            float u[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++) {
+                    const int m = m0 + g + 8 * hr, t = 8 * j + 2 * t4;
+                    const float2 cv = *reinterpret_cast<const float2*>(s.cvT + m * LDC + t);
+                    const float2 vm = *reinterpret_cast<const float2*>(s.vmcT + m * LDC + t);
+                    const float w0 = cv.x - P[j][2 * hr], w1 = cv.y - P[j][2 * hr + 1];
+                    u[j][2 * hr] = bs[t] * w0;
+                    u[j][2 * hr + 1] = bs[t + 1] * w1;
+                    s.vo[t * LDO + m] = vm.x + P[j][2 * hr];
+                    s.vo[(t + 1) * LDO + m] = vm.y + P[j][2 * hr + 1];
+                    if (uib) {
+                        s.ui[t * LDO + m] = u[j][2 * hr];
+                        s.ui[(t + 1) * LDO + m] = u[j][2 * hr + 1];
+                    }
+                }
+            unsigned ua[4] = {pack_bf16(u[0][0], u[0][1]), pack_bf16(u[0][2], u[0][3]),
+                              pack_bf16(u[1][0], u[1][1]), pack_bf16(u[1][2], u[1][3])};
+            {
+                unsigned ba[4];
+                ldb_nk(ba, s.aqk, LDQ, lane);
+                mma_bf16(Y[0], ua, ba[0], ba[1]);
+                mma_bf16(Y[1], ua, ba[2], ba[3]);
+            }
+            // the state takes u as hi + lo (two bf16 parts, 16 mantissa bits): the saved v_old lets the
+            // backward rebuild u in fp32, and the rewind S0 = S1 - K^T u must undo this update
+            unsigned ul[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const float x0 = u[r >> 1][2 * (r & 1)], x1 = u[r >> 1][2 * (r & 1) + 1];
+                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&ua[r]);
+                ul[r] = pack_bf16(x0 - __low2float(hi), x1 - __high2float(hi));
+            }
+#pragma unroll
+            for (int jp = 0; jp < 4; jp++) {
+                unsigned bk[4];
+                ldb_kn(bk, Ks + 16 * jp, LDT, lane);
+                mma_bf16(S[2 * jp], ua, bk[0], bk[1]);
+                mma_bf16(S[2 * jp + 1], ua, bk[2], bk[3]);
+                mma_bf16(S[2 * jp], ul, bk[0], bk[1]);
+                mma_bf16(S[2 * jp + 1], ul, bk[2], bk[3]);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    s.ys[(8 * j + 2 * t4 + (i & 1)) * LDT + m0 + g + 8 * (i >> 1)] = __float2bfloat16_rn(Y[j][i]);
+        }
+        __syncthreads();
+
+        {   // (4) stores: 16-byte row pieces
+            const int row = tid >> 3, part = (tid & 7) * 8;
+            if (row < nt)
+                *reinterpret_cast<uint4*>(yb + (long long)(t0 + row) * p.out.sL + part) =
+                    *reinterpret_cast<const uint4*>(s.ys + row * LDT + part);
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int idx = tid + NT * i, r = idx >> 4, pc = (idx & 15) * 4;
+                if (r < nt) {
+                    *reinterpret_cast<float4*>(vob + (long long)(t0 + r) * p.v_old.sL + pc) =
+                        *reinterpret_cast<const float4*>(s.vo + r * LDO + pc);
+                    if (uib)
+                        *reinterpret_cast<float4*>(uib + (long long)(t0 + r) * p.v_ins.sL + pc) =
+                            *reinterpret_cast<const float4*>(s.ui + r * LDO + pc);
+                }
+            }
+            if (tid < C && c + 1 < nchunks) s.b[cur ^ 1][tid] = bnext;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) W[(long long)(8 * j + 2 * t4 + (i & 1)) * p.wE + m0 + g + 8 * (i >> 1)] = S[j][i];
+}
+
+}  // namespace fwp

@@ -45,4 +45,8 @@ size_t chunk_ws_floats(long long nseq, int L, int E, int M, int io_dtype, bool b
 int launch_fwd_chunk(const DeltaFwdParams& p, int nseq, cudaStream_t st);
 int launch_bwd_chunk(const DeltaBwdParams& p, int nseq, cudaStream_t st);
 
+// chunkwise plan for bf16 streams with E = M = 64 (fwp_delta_chunk_bf16.cuh): applies when every row is 16-byte aligned
+bool chunk_bf16_applies(const DeltaFwdParams& p);
+int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st);
+
 }  // namespace fwp
