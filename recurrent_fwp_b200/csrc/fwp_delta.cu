@@ -495,6 +495,11 @@ static int dispatch_bwd(const DeltaBwdParams& p0, int nseq, cudaStream_t st) {
             return launch_bwd<32, 2, 8, T>(p, nseq, st);
         }
         case 64: {
+            if constexpr (sizeof(T) == 2) {
+                // chunkwise tensor-core form for bf16 streams ("delta.chunk64" = 0 switches it off)
+                if (force == -1 && p.L > kShortSeq && tune_get("delta.chunk64", 1) == 1 && chunk_bf16_applies(p))
+                    return launch_bwd_chunk_bf16(p, nseq, st);
+            }
             const bool blocked = force == 1 || (force == -1 && sizeof(T) == 4 && p.L > 4 * kShortSeq);
             if (!blocked) return launch_bwd_step<64, 4, 4, T>(p, nseq, st);
             if (tune_get(key, 2) == 4) return launch_bwd<64, 4, 4, T>(p, nseq, st);

@@ -43,4 +43,14 @@ int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     return launch(delta_fwd_chunk_bf16_kernel, p, nseq, cb::NT, sizeof(cb::Smem), st);
 }
 
+bool chunk_bf16_applies(const DeltaBwdParams& p) {
+    return p.E == cb::D && p.M == cb::D && rows_ok(p.q, 2) && rows_ok(p.k, 2) && rows_ok(p.v, 2) && rows_ok(p.gy, 2) &&
+           rows_ok(p.v_old, 4) && rows_ok(p.gq, 2) && rows_ok(p.gk, 2) && rows_ok(p.gv, 2) &&
+           (reinterpret_cast<uintptr_t>(p.W) & 7) == 0 && p.wN % 2 == 0 && p.wH % 2 == 0 && p.wE % 2 == 0;
+}
+
+int launch_bwd_chunk_bf16(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
+    return launch(delta_bwd_chunk_bf16_kernel, p, nseq, cb::NT, sizeof(cb::SmemB), st);
+}
+
 }  // namespace fwp

@@ -48,5 +48,7 @@ int launch_bwd_chunk(const DeltaBwdParams& p, int nseq, cudaStream_t st);
 // chunkwise plan for bf16 streams with E = M = 64 (fwp_delta_chunk_bf16.cuh): applies when every row is 16-byte aligned
 bool chunk_bf16_applies(const DeltaFwdParams& p);
 int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st);
+bool chunk_bf16_applies(const DeltaBwdParams& p);
+int launch_bwd_chunk_bf16(const DeltaBwdParams& p, int nseq, cudaStream_t st);
 
 }  // namespace fwp

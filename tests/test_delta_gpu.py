@@ -346,3 +346,62 @@ def test_alternative_backward_staging_plans_give_the_same_bits(fwp, key, value, 
     for a, c in zip(*res):
         assert torch.equal(a, c)
     assert _lib.device_fault() == 0
+
+
+@pytest.mark.parametrize('B,H,L', [(2, 3, 100), (1, 2, 17), (1, 2, 300), (3, 1, 64)])
+def test_chunkwise_bf16_plan_at_d64_meets_the_oracle(fwp, B, H, L):
+    """Default plan for bf16 streams at E = M = 64 beyond 16 steps: 16-step chunks, bf16 tensor-core products,
+    fp32 state, one launch per direction.  Checked against the fp64 loop on the bf16-rounded inputs and
+    against the per-step plan ('delta.chunk64' = 0).  Bounds: |dy| <= 2e-2 max|y|, gradients scaled-rel
+    <= 3e-2 (the stated bf16-stream bounds), end state 2e-4, rewound start state 1e-5."""
+    from recurrent_fwp_b200 import _lib
+    d = 64
+    q, k, v, b, gy = [t.to(torch.bfloat16) for t in util.delta_inputs(301, B, H, L, d)]
+    W0 = torch.randn(B, H, d, d, generator=util.gen(302)) * 0.1
+    res = {}
+    try:
+        for chunk in (1, 0):
+            _lib.tune('delta.chunk64', chunk)
+            before = _lib.lib.fwp_launch_count()
+            W = W0.to(DEV)
+            res[chunk] = run_cuda(fwp, q, k, v, b, W, gy) + (W, _lib.lib.fwp_launch_count() - before)
+    finally:
+        _lib.tune('delta.chunk64', 1)
+    y64, g64, S64 = run_loop(q.float(), k.float(), v.float(), b.float(), W0, gy.float(), torch.float64)
+    for chunk in (1, 0):
+        y, grads, W_end, W_back, launches = res[chunk]
+        assert launches == 2
+        assert util.max_abs(y.float(), y64) <= 2e-2 * y64.abs().max().item()
+        assert util.max_abs(W_end, S64) <= 2e-4
+        for g, r in zip(grads, g64):
+            assert util.scaled_rel(g.float(), r) <= 3e-2
+        assert util.max_abs(W_back, W0) <= 1e-5
+    # the two plans agree far inside the bf16 output rounding
+    assert util.max_abs(res[1][0].float(), res[0][0].float()) <= 1e-2 * y64.abs().max().item()
+
+
+def test_chunkwise_bf16_plan_leaves_unaligned_rows_to_the_per_step_plan(fwp):
+    """Views of a fused (L,B,H,3d+1) projection have rows that are not 16-byte aligned: the chunkwise bf16 plan
+    does not apply and the call takes the per-step kernels; same numbers as on contiguous copies within the
+    bf16 bounds."""
+    L, B, H, d = 40, 2, 2, 64
+    g = util.gen(303)
+    qkvb = torch.randn(L, B, H, 3 * d + 1, generator=g).to(DEV)
+    q, k, v, beta = torch.split(qkvb, (d, d, d, 1), dim=-1)
+    q, k, v, beta = (t.permute(1, 2, 0, 3) for t in (q, k, v, torch.sigmoid(beta)))
+    fused = torch.cat([torch.softmax(q, -1), torch.softmax(k, -1), v, beta], -1).to(torch.bfloat16)
+    q, k, v, beta = torch.split(fused, (d, d, d, 1), dim=-1)
+    gy = torch.randn(B, H, L, d, generator=g).to(DEV).to(torch.bfloat16)
+    res = []
+    for contiguous in (False, True):
+        leaves = [(t.contiguous() if contiguous else t).detach().requires_grad_() for t in (q, k, v, beta)]
+        W = torch.zeros(B, H, d, d, device=DEV)
+        y = fwp.fast_weight_delta(*leaves, W)
+        W_end = W.clone()
+        y.backward(gy)
+        res.append([y.detach(), W_end] + [t.grad for t in leaves])
+    ym = res[1][0].float().abs().max().item()
+    assert util.max_abs(res[0][0].float(), res[1][0].float()) <= 2e-2 * ym
+    assert util.max_abs(res[0][1], res[1][1]) <= 2e-4
+    for a, c in zip(res[0][2:], res[1][2:]):
+        assert util.scaled_rel(a.float(), c.float()) <= 3e-2
