@@ -48,7 +48,12 @@ WORKLOADS = {
 
 # DRAM read+write bytes of one backward launch, from the ncu capture summarised in
 # profiles/delta_fwd_bwd_lm_shape_ncu.md (dram__bytes_read.sum + dram__bytes_write.sum)
-NCU_TRAFFIC_BWD = {'lm': 44221312}
+NCU_TRAFFIC_BWD = {'lm': 44221312,
+                   # profiles/delta_chunkwise_bf16_d64_ncu.md: captured on long_slice (512 sequences); 'long' has 8x
+                   # the sequences and its traffic grows in proportion
+                   'long_slice': 2430927000, 'long': 8 * 2430927000}
+# the kernel the backward launch runs, per workload (the dispatch picks it from head dimension and stream type)
+BWD_KERNEL = {'long': 'delta_bwd_chunk_bf16_kernel', 'long_slice': 'delta_bwd_chunk_bf16_kernel'}
 
 
 def peaks():
@@ -600,7 +605,7 @@ def run_gpu_arm(args):
                        'sharding': 'batch x head units split over ranks, no collective on the data path',
                        'l2': 'flushed between timed steps (256 MiB write)', 'cuda_graph': graph is not None,
                        'timing': 'CUDA events per step, summed; max over ranks'},
-            'roofline': {'bound': 'hbm', 'kernel': 'delta_bwd_kernel', 'achieved': ach_b, 'peak': peak, 'unit': 'GB/s',
+            'roofline': {'bound': 'hbm', 'kernel': BWD_KERNEL.get(args.workload, 'delta_bwd_kernel'), 'achieved': ach_b, 'peak': peak, 'unit': 'GB/s',
                          'frac': ach_b / peak, 'peak_kind': peak_kind, 'traffic': NCU_TRAFFIC_BWD.get(args.workload),
                          'algorithmic_bytes_per_launch': bytes_bwd, 'launch_s': tb, 'launch_s_min': tb_min,
                          'timing': 'CUDA events around the %d segments launched back to back (distinct inputs, '
