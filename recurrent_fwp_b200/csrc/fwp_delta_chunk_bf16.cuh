@@ -18,7 +18,7 @@
 // the accumulator fragments of S^T, rounded to bf16, are the left operand of S^T Ck^T and S^T Q^T,
 // the accumulator fragment of u^T is the left operand of u^T Aqk^T and of the update u^T K, and
 // every right operand is a row-major shared-memory tile read with ldmatrix (transposed for K in
-// the update).  Outputs leave through shared-memory tiles as 16-byte row pieces.
+// the update).  y leaves through a shared-memory tile as 16-byte row pieces, v_old and u straight from the fragments.
 //
 // Rounding: the streams are bf16 already; S, Ck and u are rounded to bf16 only as product
 // operands, the state itself and all sums stay fp32, and the state update takes u as two bf16 parts.
@@ -46,8 +46,6 @@ struct Smem {
     float akk[C * LDA];                 // Akk, [t][i], zero on and above the diagonal
     float cvT[D * LDC];                 // Cv^T, [m][t]
     float vmcT[D * LDC];                // (V - Cv)^T, [m][t]
-    float vo[C * LDO];                  // v_old, [t][m]
-    float ui[C * LDO];                  // u, [t][m] (only when the caller asks for v_insert)
     float b[2][C];
 };
 
@@ -101,7 +99,7 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat
 // ------------------------------------------------------------------ forward
 // One CTA per sequence, four warps.  Per chunk: (1) the two Gram products, one 16 x 8 tile per warp;
 // (2) the triangular solve, one column of [V | K] per thread; (3) the chain, warp w on rows
-// m in [16w, 16w+16) of S^T; (4) coalesced stores of y, v_old (and u).  Input tiles of the next
+// m in [16w, 16w+16) of S^T; (4) 16-byte stores of y.  Input tiles of the next
 // chunk are in flight (cp.async) meanwhile.
 __global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_kernel(const DeltaFwdParams p) {
     using namespace cb;
@@ -246,11 +244,14 @@ __global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_kernel(const D
                     const float w0 = cv.x - P[j][2 * hr], w1 = cv.y - P[j][2 * hr + 1];
                     u[j][2 * hr] = bs[t] * w0;
                     u[j][2 * hr + 1] = bs[t + 1] * w1;
-                    s.vo[t * LDO + m] = vm.x + P[j][2 * hr];
-                    s.vo[(t + 1) * LDO + m] = vm.y + P[j][2 * hr + 1];
-                    if (uib) {
-                        s.ui[t * LDO + m] = u[j][2 * hr];
-                        s.ui[(t + 1) * LDO + m] = u[j][2 * hr + 1];
+                    // fp32 rows go straight to global memory: the eight lanes of a quad column fill one 32-byte sector
+                    if (t < nt) {
+                        vob[(long long)(t0 + t) * p.v_old.sL + m] = vm.x + P[j][2 * hr];
+                        if (uib) uib[(long long)(t0 + t) * p.v_ins.sL + m] = u[j][2 * hr];
+                    }
+                    if (t + 1 < nt) {
+                        vob[(long long)(t0 + t + 1) * p.v_old.sL + m] = vm.y + P[j][2 * hr + 1];
+                        if (uib) uib[(long long)(t0 + t + 1) * p.v_ins.sL + m] = u[j][2 * hr + 1];
                     }
                 }
             unsigned ua[4] = {pack_bf16(u[0][0], u[0][1]), pack_bf16(u[0][2], u[0][3]),
@@ -292,17 +293,6 @@ __global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_kernel(const D
             if (row < nt)
                 *reinterpret_cast<uint4*>(yb + (long long)(t0 + row) * p.out.sL + part) =
                     *reinterpret_cast<const uint4*>(s.ys + row * LDT + part);
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const int idx = tid + NT * i, r = idx >> 4, pc = (idx & 15) * 4;
-                if (r < nt) {
-                    *reinterpret_cast<float4*>(vob + (long long)(t0 + r) * p.v_old.sL + pc) =
-                        *reinterpret_cast<const float4*>(s.vo + r * LDO + pc);
-                    if (uib)
-                        *reinterpret_cast<float4*>(uib + (long long)(t0 + r) * p.v_ins.sL + pc) =
-                            *reinterpret_cast<const float4*>(s.ui + r * LDO + pc);
-                }
-            }
             if (tid < C && c + 1 < nchunks) s.b[cur ^ 1][tid] = bnext;
         }
     }
@@ -702,6 +692,283 @@ __global__ void __launch_bounds__(cb::NT, 3) delta_bwd_chunk_bf16_kernel(const D
         for (int hr = 0; hr < 2; hr++)
             *reinterpret_cast<float2*>(W + (long long)(e0 + g + 8 * hr) * p.wE + 8 * j + 2 * t4) =
                 make_float2(S[j][2 * hr], S[j][2 * hr + 1]);
+}
+
+// ------------------------------------------------------------------ forward, register-resident solve
+// Same algebra as delta_fwd_chunk_bf16_kernel with the triangular solve replaced by the explicit inverse
+// T = (I + N)^-1, N = Akk diag(b) strictly lower and therefore nilpotent:
+//   T = (I - N)(I + N^2)(I + N^4)(I + N^8)
+// Every warp builds Akk, Aqk and T for itself in accumulator fragments (six 16 x 16 x 16 products whose right
+// operands are transposed in registers with movmatrix), so the Gram tiles, the solve and Cv never touch shared
+// memory: Cv^T = V^T T^T and (V - Cv)^T = -V^T (T - I)^T are two products of the chain warp with T taken from
+// its own fragments, and only Ck = T K (16 columns per warp) is exchanged through shared memory.
+namespace cb {
+
+struct SmemI {
+    __nv_bfloat16 k[2][C * LDT], v[2][C * LDT], q[2][C * LDT];    // input stages
+    __nv_bfloat16 ck[C * LDT];          // Ck, [t][e]
+    __nv_bfloat16 ys[C * LDT];          // y, [t][m]
+    float b[2][C];
+};
+
+__device__ __forceinline__ unsigned movm(unsigned x) {
+    unsigned r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
+}
+// a 16 x 16 matrix held as an accumulator fragment, as the left operand of a product
+__device__ __forceinline__ void a_of(unsigned (&a)[4], const float (&x)[2][4]) {
+    a[0] = pack_bf16(x[0][0], x[0][1]); a[1] = pack_bf16(x[0][2], x[0][3]);
+    a[2] = pack_bf16(x[1][0], x[1][1]); a[3] = pack_bf16(x[1][2], x[1][3]);
+}
+// ... as the right operand B[k][n] = X[k][n]: b[2j], b[2j+1] for the column tile j
+__device__ __forceinline__ void b_of(unsigned (&b)[4], const float (&x)[2][4]) {
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        b[2 * j] = movm(pack_bf16(x[j][0], x[j][1]));
+        b[2 * j + 1] = movm(pack_bf16(x[j][2], x[j][3]));
+    }
+}
+// ... as the right operand B[k][n] = X[n][k] (the transposed matrix), in two bf16 parts: no data movement
+__device__ __forceinline__ void bt_of(unsigned (&hi)[4], unsigned (&lo)[4], const float (&x)[2][4]) {
+    split_bf16(x[0][0], x[0][1], hi[0], lo[0]);   // column tile 0 (n = g): k = 2 t4, +1
+    split_bf16(x[1][0], x[1][1], hi[1], lo[1]);   //                        k = 8 + 2 t4, +1
+    split_bf16(x[0][2], x[0][3], hi[2], lo[2]);   // column tile 1 (n = 8 + g)
+    split_bf16(x[1][2], x[1][3], hi[3], lo[3]);
+}
+// out += A B for 16 x 16 fragments
+__device__ __forceinline__ void mm(float (&out)[2][4], const unsigned (&a)[4], const unsigned (&b)[4]) {
+    mma_bf16(out[0], a, b[0], b[1]);
+    mma_bf16(out[1], a, b[2], b[3]);
+}
+
+}  // namespace cb
+
+__global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_inv_kernel(const DeltaFwdParams p) {
+    using namespace cb;
+    using bf16 = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char cb_smem[];
+    SmemI& s = *reinterpret_cast<SmemI*>(cb_smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int seq = blockIdx.x, n = seq / p.H, h = seq - n * p.H;
+    const bf16* qb = reinterpret_cast<const bf16*>(p.q.p) + n * p.q.sN + h * p.q.sH;
+    const bf16* kb = reinterpret_cast<const bf16*>(p.k.p) + n * p.k.sN + h * p.k.sH;
+    const bf16* vb = reinterpret_cast<const bf16*>(p.v.p) + n * p.v.sN + h * p.v.sH;
+    const bf16* bb = reinterpret_cast<const bf16*>(p.beta.p) + n * p.beta.sN + h * p.beta.sH;
+    bf16* yb = reinterpret_cast<bf16*>(p.out.p) + n * p.out.sN + h * p.out.sH;
+    float* vob = reinterpret_cast<float*>(p.v_old.p) + n * p.v_old.sN + h * p.v_old.sH;
+    float* uib = p.v_ins.p ? reinterpret_cast<float*>(p.v_ins.p) + n * p.v_ins.sN + h * p.v_ins.sH : nullptr;
+    float* W = p.W + n * p.wN + h * p.wH;
+    const int m0 = 16 * warp;
+
+    float S[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) S[j][i] = W[(long long)(8 * j + 2 * t4 + (i & 1)) * p.wE + m0 + g + 8 * (i >> 1)];
+
+    const int nchunks = (p.L + C - 1) / C;
+    {
+        const int nt = min(C, p.L);
+        load_tile(s.k[0], kb, p.k.sL, 0, nt, tid);
+        load_tile(s.v[0], vb, p.v.sL, 0, nt, tid);
+        load_tile(s.q[0], qb, p.q.sL, 0, nt, tid);
+        cp_async_commit();
+        if (tid < C) s.b[0][tid] = tid < nt ? __bfloat162float(bb[(long long)tid * p.beta.sL]) : 0.f;
+    }
+    for (int c = 0; c < nchunks; c++) {
+        const int cur = c & 1, t0 = c * C, nt = min(C, p.L - t0);
+        float bnext = 0.f;
+        if (c + 1 < nchunks) {
+            const int t1 = t0 + C, nt1 = min(C, p.L - t1);
+            load_tile(s.k[cur ^ 1], kb, p.k.sL, t1, nt1, tid);
+            load_tile(s.v[cur ^ 1], vb, p.v.sL, t1, nt1, tid);
+            load_tile(s.q[cur ^ 1], qb, p.q.sL, t1, nt1, tid);
+            cp_async_commit();
+            if (tid < nt1) bnext = __bfloat162float(bb[(long long)(t1 + tid) * p.beta.sL]);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const bf16* Ks = s.k[cur];
+        const bf16* Qs = s.q[cur];
+        const float* bs = s.b[cur];
+
+        // (1) per warp: Akk, Aqk, T; the warp's 16 columns of Ck = T K
+        unsigned th[4], tl[4], yh[4], yl[4], qk[4];     // right operands T^T, (T - I)^T (two parts each), Aqk^T
+        {
+            float akk[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float aqk[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int kp = 0; kp < 2; kp++) {
+                unsigned b0[4], b1[4];
+                ldsm4(b0, Ks + (lane & 7) * LDT + 8 * (lane >> 3) + 32 * kp);
+                ldsm4(b1, Ks + (8 + (lane & 7)) * LDT + 8 * (lane >> 3) + 32 * kp);
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    unsigned ak[4], aq[4];
+                    lda_rowmajor(ak, Ks + 16 * (2 * kp + kk), LDT, lane);
+                    lda_rowmajor(aq, Qs + 16 * (2 * kp + kk), LDT, lane);
+                    mma_bf16(akk[0], ak, b0[2 * kk], b0[2 * kk + 1]);
+                    mma_bf16(akk[1], ak, b1[2 * kk], b1[2 * kk + 1]);
+                    mma_bf16(aqk[0], aq, b0[2 * kk], b0[2 * kk + 1]);
+                    mma_bf16(aqk[1], aq, b1[2 * kk], b1[2 * kk + 1]);
+                }
+            }
+            float N1[2][4], Y[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int r = g + 8 * (i >> 1), cc = 8 * j + 2 * t4 + (i & 1);
+                    N1[j][i] = cc < r ? akk[j][i] * bs[cc] : 0.f;
+                    aqk[j][i] = cc <= r ? aqk[j][i] : 0.f;
+                    Y[j][i] = -N1[j][i];
+                }
+            {
+                unsigned lo[4];
+                bt_of(qk, lo, aqk);
+            }
+            unsigned a[4], bN[4], b2[4];
+            float N2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            a_of(a, N1);
+            b_of(bN, N1);
+            mm(N2, a, bN);                                  // N^2
+            b_of(b2, N2);
+            {
+                float N3[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                mm(N3, a, b2);                              // N^3
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N2[j][i] - N3[j][i];
+            }
+            float N4[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            a_of(a, N2);
+            mm(N4, a, b2);                                  // N^4
+            unsigned b4[4];
+            b_of(b4, N4);
+            {
+                float Z1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                a_of(a, Y);
+                mm(Z1, a, b4);                              // Y N^4
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N4[j][i] + Z1[j][i];
+            }
+            float N8[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            a_of(a, N4);
+            mm(N8, a, b4);                                  // N^8
+            {
+                unsigned b8[4];
+                b_of(b8, N8);
+                float Z2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                a_of(a, Y);
+                mm(Z2, a, b8);                              // Y N^8
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N8[j][i] + Z2[j][i];
+            }
+            // Y = T - I (strictly lower).  Ck[:, 16w..16w+15] = T K
+            float T[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) T[j][i] = Y[j][i] + ((8 * j + 2 * t4 + (i & 1)) == (g + 8 * (i >> 1)) ? 1.f : 0.f);
+            bt_of(th, tl, T);
+            bt_of(yh, yl, Y);
+            unsigned ah[4], al[4], bK[4];
+            split_bf16(T[0][0], T[0][1], ah[0], al[0]); split_bf16(T[0][2], T[0][3], ah[1], al[1]);
+            split_bf16(T[1][0], T[1][1], ah[2], al[2]); split_bf16(T[1][2], T[1][3], ah[3], al[3]);
+            ldb_kn(bK, Ks + m0, LDT, lane);
+            float ck[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            mm(ck, ah, bK);
+            mm(ck, al, bK);
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                *reinterpret_cast<unsigned*>(s.ck + g * LDT + m0 + 8 * j + 2 * t4) = pack_bf16(ck[j][0], ck[j][1]);
+                *reinterpret_cast<unsigned*>(s.ck + (g + 8) * LDT + m0 + 8 * j + 2 * t4) = pack_bf16(ck[j][2], ck[j][3]);
+            }
+        }
+        __syncthreads();
+
+        {   // (2) chain
+            unsigned sa[4][4];
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                sa[ks][0] = pack_bf16(S[2 * ks][0], S[2 * ks][1]);
+                sa[ks][1] = pack_bf16(S[2 * ks][2], S[2 * ks][3]);
+                sa[ks][2] = pack_bf16(S[2 * ks + 1][0], S[2 * ks + 1][1]);
+                sa[ks][3] = pack_bf16(S[2 * ks + 1][2], S[2 * ks + 1][3]);
+            }
+            float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float Yo[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                unsigned bc[4], bq[4];
+                ldb_nk(bc, s.ck + 16 * ks, LDT, lane);
+                ldb_nk(bq, Qs + 16 * ks, LDT, lane);
+                mm(P, sa[ks], bc);
+                mm(Yo, sa[ks], bq);
+            }
+            float cv[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float py[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            {
+                unsigned va[4];
+                lda_trans(va, s.v[cur] + m0, LDT, lane);
+                mm(cv, va, th);
+                mm(cv, va, tl);
+                mm(py, va, yh);
+                mm(py, va, yl);
+            }
+            float u[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int m = m0 + g + 8 * (i >> 1), t = 8 * j + 2 * t4 + (i & 1);
+                    u[j][i] = bs[t] * (cv[j][i] - P[j][i]);
+                    if (t < nt) {
+                        vob[(long long)(t0 + t) * p.v_old.sL + m] = P[j][i] - py[j][i];
+                        if (uib) uib[(long long)(t0 + t) * p.v_ins.sL + m] = u[j][i];
+                    }
+                }
+            unsigned ua[4], ul[4];
+            split_bf16(u[0][0], u[0][1], ua[0], ul[0]); split_bf16(u[0][2], u[0][3], ua[1], ul[1]);
+            split_bf16(u[1][0], u[1][1], ua[2], ul[2]); split_bf16(u[1][2], u[1][3], ua[3], ul[3]);
+            mm(Yo, ua, qk);
+#pragma unroll
+            for (int jp = 0; jp < 4; jp++) {
+                unsigned bk[4];
+                ldb_kn(bk, Ks + 16 * jp, LDT, lane);
+                mma_bf16(S[2 * jp], ua, bk[0], bk[1]);
+                mma_bf16(S[2 * jp + 1], ua, bk[2], bk[3]);
+                mma_bf16(S[2 * jp], ul, bk[0], bk[1]);
+                mma_bf16(S[2 * jp + 1], ul, bk[2], bk[3]);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    s.ys[(8 * j + 2 * t4 + (i & 1)) * LDT + m0 + g + 8 * (i >> 1)] = __float2bfloat16_rn(Yo[j][i]);
+        }
+        __syncthreads();
+
+        {   // (3) y: 16-byte row pieces
+            const int row = tid >> 3, part = (tid & 7) * 8;
+            if (row < nt)
+                *reinterpret_cast<uint4*>(yb + (long long)(t0 + row) * p.out.sL + part) =
+                    *reinterpret_cast<const uint4*>(s.ys + row * LDT + part);
+            if (tid < C && c + 1 < nchunks) s.b[cur ^ 1][tid] = bnext;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) W[(long long)(8 * j + 2 * t4 + (i & 1)) * p.wE + m0 + g + 8 * (i >> 1)] = S[j][i];
 }
 
 }  // namespace fwp

@@ -360,15 +360,19 @@ def test_chunkwise_bf16_plan_at_d64_meets_the_oracle(fwp, B, H, L):
     W0 = torch.randn(B, H, d, d, generator=util.gen(302)) * 0.1
     res = {}
     try:
-        for chunk in (1, 0):
-            _lib.tune('delta.chunk64', chunk)
+        # 1: chunkwise with the solve as an explicit inverse in registers (the default); 2: chunkwise with the
+        # per-thread substitution; 0: per-step plan
+        for chunk in (1, 2, 0):
+            _lib.tune('delta.chunk64', min(chunk, 1))
+            _lib.tune('delta_fwd.chunk64.solve', 1 if chunk == 2 else 0)
             before = _lib.lib.fwp_launch_count()
             W = W0.to(DEV)
             res[chunk] = run_cuda(fwp, q, k, v, b, W, gy) + (W, _lib.lib.fwp_launch_count() - before)
     finally:
         _lib.tune('delta.chunk64', 1)
+        _lib.tune('delta_fwd.chunk64.solve', 0)
     y64, g64, S64 = run_loop(q.float(), k.float(), v.float(), b.float(), W0, gy.float(), torch.float64)
-    for chunk in (1, 0):
+    for chunk in (1, 2, 0):
         y, grads, W_end, W_back, launches = res[chunk]
         assert launches == 2
         assert util.max_abs(y.float(), y64) <= 2e-2 * y64.abs().max().item()
@@ -378,6 +382,7 @@ def test_chunkwise_bf16_plan_at_d64_meets_the_oracle(fwp, B, H, L):
         assert util.max_abs(W_back, W0) <= 1e-5
     # the two plans agree far inside the bf16 output rounding
     assert util.max_abs(res[1][0].float(), res[0][0].float()) <= 1e-2 * y64.abs().max().item()
+    assert util.max_abs(res[2][0].float(), res[0][0].float()) <= 1e-2 * y64.abs().max().item()
 
 
 def test_chunkwise_bf16_plan_leaves_unaligned_rows_to_the_per_step_plan(fwp):
