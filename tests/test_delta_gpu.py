@@ -365,12 +365,14 @@ def test_chunkwise_bf16_plan_at_d64_meets_the_oracle(fwp, B, H, L):
         for chunk in (1, 2, 0):
             _lib.tune('delta.chunk64', min(chunk, 1))
             _lib.tune('delta_fwd.chunk64.solve', 1 if chunk == 2 else 0)
+            _lib.tune('delta_bwd.chunk64.solve', 1 if chunk == 2 else 0)
             before = _lib.lib.fwp_launch_count()
             W = W0.to(DEV)
             res[chunk] = run_cuda(fwp, q, k, v, b, W, gy) + (W, _lib.lib.fwp_launch_count() - before)
     finally:
         _lib.tune('delta.chunk64', 1)
         _lib.tune('delta_fwd.chunk64.solve', 0)
+        _lib.tune('delta_bwd.chunk64.solve', 0)
     y64, g64, S64 = run_loop(q.float(), k.float(), v.float(), b.float(), W0, gy.float(), torch.float64)
     for chunk in (1, 2, 0):
         y, grads, W_end, W_back, launches = res[chunk]
