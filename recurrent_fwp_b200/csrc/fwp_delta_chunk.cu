@@ -57,7 +57,9 @@ int launch_bwd_chunk_bf16(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     // "delta_bwd.chunk64.solve" = 1: per-thread substitution through shared memory (2.55 ms at 512 sequences of 4096
     // steps); 0, the default: explicit inverse in registers (1.82 ms; 2.69 against 3.80 ms at 4096 sequences of 1024)
     if (tune_get("delta_bwd.chunk64.solve", 0) == 0)
-        return launch(delta_bwd_chunk_bf16_inv_kernel, p, nseq, cb::NT, sizeof(cb::SmemB2), st);
+        return tune_get("delta_bwd.chunk64.ctas", 3) == 4
+                   ? launch(delta_bwd_chunk_bf16_inv_kernel<4>, p, nseq, cb::NT, sizeof(cb::SmemB2), st)
+                   : launch(delta_bwd_chunk_bf16_inv_kernel<3>, p, nseq, cb::NT, sizeof(cb::SmemB2), st);
     return launch(delta_bwd_chunk_bf16_kernel, p, nseq, cb::NT, sizeof(cb::SmemB), st);
 }
 

@@ -992,7 +992,8 @@ struct SmemB2 {
 };
 }  // namespace cb
 
-__global__ void __launch_bounds__(cb::NT, 3) delta_bwd_chunk_bf16_inv_kernel(const DeltaBwdParams p) {
+template <int MINB>
+__global__ void __launch_bounds__(cb::NT, MINB) delta_bwd_chunk_bf16_inv_kernel(const DeltaBwdParams p) {
     using namespace cb;
     using bf16 = __nv_bfloat16;
     extern __shared__ __align__(16) unsigned char cb_smem[];
