@@ -43,7 +43,12 @@ int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     // "delta_fwd.chunk64.solve" = 1: per-thread substitution through shared memory (0.93 ms at 512 sequences of 4096
     // steps); 0, the default: explicit inverse in registers (0.86 ms; 1.43 against 1.75 ms at 4096 sequences of 1024)
     if (tune_get("delta_fwd.chunk64.solve", 0) == 0)
-        return launch(delta_fwd_chunk_bf16_inv_kernel, p, nseq, cb::NT, sizeof(cb::SmemI), st);
+    {
+        const int ctas = tune_get("delta_fwd.chunk64.ctas", 4);     // resident CTAs per SM the kernel is compiled for
+        if (ctas == 5) return launch(delta_fwd_chunk_bf16_inv_kernel<5>, p, nseq, cb::NT, sizeof(cb::SmemI), st);
+        if (ctas == 6) return launch(delta_fwd_chunk_bf16_inv_kernel<6>, p, nseq, cb::NT, sizeof(cb::SmemI), st);
+        return launch(delta_fwd_chunk_bf16_inv_kernel<4>, p, nseq, cb::NT, sizeof(cb::SmemI), st);
+    }
     return launch(delta_fwd_chunk_bf16_kernel, p, nseq, cb::NT, sizeof(cb::Smem), st);
 }
 

@@ -744,7 +744,8 @@ __device__ __forceinline__ void mm(float (&out)[2][4], const unsigned (&a)[4], c
 
 }  // namespace cb
 
-__global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_inv_kernel(const DeltaFwdParams p) {
+template <int MINB>
+__global__ void __launch_bounds__(cb::NT, MINB) delta_fwd_chunk_bf16_inv_kernel(const DeltaFwdParams p) {
     using namespace cb;
     using bf16 = __nv_bfloat16;
     extern __shared__ __align__(16) unsigned char cb_smem[];
