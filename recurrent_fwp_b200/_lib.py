@@ -86,6 +86,44 @@ def require_cuda(*tensors):
                                'there is no CPU path' % t.device.type)
 
 
+def require_streams(ref, shape_by_name):
+    """Every stream handed to a kernel is read with the element type of the first one and with the sizes
+    (N, H, L, D) passed beside the pointers, so a stream of another dtype, device or shape would be read out of
+    bounds.  ``shape_by_name`` maps an argument name to ``(tensor, expected shape)``; raises ``TypeError`` for a
+    dtype mismatch (the reference raises from ``data_ptr<float>()``) and ``RuntimeError`` otherwise."""
+    for name, (t, shape) in shape_by_name.items():
+        if t is None:
+            continue
+        if t.dtype != ref.dtype:
+            raise TypeError('%s is %s but the first stream is %s: all streams of one call share a dtype'
+                            % (name, t.dtype, ref.dtype))
+        if t.device != ref.device:
+            raise RuntimeError('%s is on %s but the first stream is on %s' % (name, t.device, ref.device))
+        if tuple(t.shape) != tuple(shape):
+            raise RuntimeError('%s has shape %s, expected %s' % (name, tuple(t.shape), tuple(shape)))
+
+
+def require_f32(ref, shape_by_name):
+    """States, recurrent parameters and initial hidden vectors are float32 on the streams' device."""
+    for name, (t, shape) in shape_by_name.items():
+        if t.dtype != torch.float32:
+            raise TypeError('%s must be float32, got %s' % (name, t.dtype))
+        if t.device != ref.device:
+            raise RuntimeError('%s is on %s but the streams are on %s' % (name, t.device, ref.device))
+        if tuple(t.shape) != tuple(shape):
+            raise RuntimeError('%s has shape %s, expected %s' % (name, tuple(t.shape), tuple(shape)))
+
+
+def grad_like(grad_out, ref, shape):
+    """The incoming gradient in the streams' dtype with a unit inner stride; its device and shape are checked."""
+    if grad_out.device != ref.device or tuple(grad_out.shape) != tuple(shape):
+        raise RuntimeError('grad_out is %s on %s, expected %s on %s'
+                           % (tuple(grad_out.shape), grad_out.device, tuple(shape), ref.device))
+    if grad_out.dtype != ref.dtype:
+        grad_out = grad_out.to(ref.dtype)
+    return unit_inner(grad_out)
+
+
 def desc(t):
     """Descriptor of a CUDA tensor viewed as 4-D (N, H, L, D); ``None`` -> NULL data."""
     d = FwpTensor()

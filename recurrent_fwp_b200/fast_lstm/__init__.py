@@ -17,7 +17,6 @@ from recurrent_fwp_b200 import _lib
 
 def make_lstm_function(variant, name):
     def forward(ctx, Zi, Ki, Vi, bi, Wi, Zu, Ku, Vu, bu, Wu, Zo, Ko, Vo, bo, Wo, h0, c0):
-        _lib.require_cuda(Zi, Ki, Vi, bi, Wi, Zu, Ku, Vu, bu, Wu, Zo, Ko, Vo, bo, Wo, h0, c0)
         N, H, L, _ = Zi.shape
         M = Vi.shape[3]
         assert Ki.shape == (N, H, L, M)
@@ -26,6 +25,14 @@ def make_lstm_function(variant, name):
         assert Wi.shape == (N, H, M, M)
         if Zi.dtype != torch.float32:
             raise TypeError('the recurrent fast-weight kernels take float32 tensors')
+        for g, (z, k, v, b, w) in zip('iuo', ((Zi, Ki, Vi, bi, Wi), (Zu, Ku, Vu, bu, Wu), (Zo, Ko, Vo, bo, Wo))):
+            _lib.require_streams(Zi, {'Z' + g: (z, (N, H, L, M)), 'K' + g: (k, (N, H, L, M)),
+                                      'V' + g: (v, (N, H, L, M)), 'b' + g: (b, (N, H, L, 1))})
+            _lib.require_f32(Zi, {'W' + g: (w, (N, H, M, M))})
+            if w.stride(3) != 1:
+                raise RuntimeError('the fast matrices must have a unit innermost stride (they are updated in place)')
+        _lib.require_f32(Zi, {'h0': (h0, (N, H, 1, M)), 'c0': (c0, (N, H, 1, M))})
+        _lib.require_cuda(Zi, Ki, Vi, bi, Wi, Zu, Ku, Vu, bu, Wu, Zo, Ko, Vo, bo, Wo, h0, c0)
         Z = [_lib.unit_inner(t.detach()) for t in (Zi, Zu, Zo)]
         K = [_lib.unit_inner(t.detach()) for t in (Ki, Ku, Ko)]
         V = [_lib.unit_inner(t.detach()) for t in (Vi, Vu, Vo)]
@@ -57,7 +64,7 @@ def make_lstm_function(variant, name):
         gates, K, V, B, W, v_old = list(t[2:5]), list(t[5:8]), list(t[8:11]), list(t[11:14]), list(t[14:17]), list(t[17:20])
         h0, c0 = t[20], t[21]
         N, H, L, M = rnn_out.shape
-        grad_out = _lib.unit_inner(grad_out)
+        grad_out = _lib.grad_like(grad_out, rnn_out, (N, H, L, M))
         if variant == 1:
             out_delayed = torch.cat([h0, rnn_out[:, :, :-1]], dim=2)
         else:

@@ -16,11 +16,12 @@ class FastWeightSum(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, Q, K, V, W):
-        _lib.require_cuda(Q, K, V, W)
         N, H, L, E = Q.shape
         M = V.shape[3]
-        if W.dtype != torch.float32 or W.shape != (N, H, E, M):
-            raise RuntimeError('W must be float32 of shape (N, H, E, M)')
+        _lib.io_dtype(Q)
+        _lib.require_streams(Q, {'K': (K, (N, H, L, E)), 'V': (V, (N, H, L, M))})
+        _lib.require_f32(Q, {'W': (W, (N, H, E, M))})
+        _lib.require_cuda(Q, K, V, W)
         Qc, Kc, Vc = (_lib.unit_inner(t.detach()) for t in (Q, K, V))
         out = torch.empty((N, H, L, M), device=Q.device, dtype=Q.dtype)
         stream, dev = _lib.stream_and_device(Q)
@@ -35,9 +36,7 @@ class FastWeightSum(torch.autograd.Function):
         Q, K, V = ctx.saved_tensors
         N, H, L, E = Q.shape
         M = V.shape[3]
-        grad_out = _lib.unit_inner(grad_out)
-        if grad_out.dtype != Q.dtype:
-            grad_out = grad_out.to(Q.dtype)
+        grad_out = _lib.grad_like(grad_out, Q, (N, H, L, M))
         grad_Q = torch.empty_like(Q, memory_format=torch.contiguous_format)
         grad_K = torch.empty_like(K, memory_format=torch.contiguous_format)
         grad_V = torch.empty_like(V, memory_format=torch.contiguous_format)

@@ -25,24 +25,27 @@ class DeltaFastWeight(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, Q, K, V, beta, W):
-        _lib.require_cuda(Q, K, V, W)
         N, H, L, E = Q.shape
         M = V.shape[3]
-        if W.dtype != torch.float32 or W.shape != (N, H, E, M):
-            raise RuntimeError('W must be float32 of shape (N, H, E, M)')
         dt = _lib.io_dtype(Q)
+        _lib.require_streams(Q, {'K': (K, (N, H, L, E)), 'V': (V, (N, H, L, M)), 'beta': (beta, (N, H, L, 1))})
+        _lib.require_f32(Q, {'W': (W, (N, H, E, M))})
+        _lib.require_cuda(Q, K, V, beta, W)
         Qc, Kc, Vc, bc = (_lib.unit_inner(t.detach()) for t in (Q, K, V, beta))
         Wd = W.detach()
         if Wd.stride(3) != 1:
             raise RuntimeError('W must have a unit innermost stride (it is updated in place)')
         out = torch.empty((N, H, L, M), device=Q.device, dtype=Q.dtype)
         V_old = torch.empty((N, H, L, M), device=Q.device, dtype=torch.float32)
-        V_insert = torch.empty((N, H, L, M), device=Q.device, dtype=torch.float32)
+        # The reference also stores u_t = beta_t (v_t - v_old_t) ("V_insert"); the backward here rebuilds it from
+        # V, V_old and beta, so that tensor is neither allocated nor written (an empty placeholder keeps the
+        # reference's saved-tensor order).
+        V_insert = torch.empty(0, device=Q.device, dtype=torch.float32)
         stream, dev = _lib.stream_and_device(Q)
         ws, ws_floats, _keep = _lib.delta_workspace(N, H, L, E, M, Qc, backward=False)
         _lib.check(_lib.lib.fwp_fast_weight_forward_ws(
             N, H, L, E, M, _lib.desc(Qc), _lib.desc(Kc), _lib.desc(Vc), _lib.desc(bc),
-            _lib.desc(V_old), _lib.desc(V_insert), _lib.desc(Wd), _lib.desc(out),
+            _lib.desc(V_old), _lib.desc(None), _lib.desc(Wd), _lib.desc(out),
             dt, stream, dev, ws, ws_floats), 'fast_weight_forward')
         ctx.save_for_backward(Qc, Kc, Vc, bc, V_old, V_insert, W)
         return out
@@ -52,9 +55,7 @@ class DeltaFastWeight(torch.autograd.Function):
         Q, K, V, beta, V_old, V_insert, W = ctx.saved_tensors
         N, H, L, E = Q.shape
         M = V.shape[3]
-        grad_out = _lib.unit_inner(grad_out)
-        if grad_out.dtype != Q.dtype:
-            grad_out = grad_out.to(Q.dtype)
+        grad_out = _lib.grad_like(grad_out, Q, (N, H, L, M))
         grad_Q = torch.empty_like(Q, memory_format=torch.contiguous_format)
         grad_K = torch.empty_like(K, memory_format=torch.contiguous_format)
         grad_V = torch.empty_like(V, memory_format=torch.contiguous_format)
@@ -63,7 +64,7 @@ class DeltaFastWeight(torch.autograd.Function):
         ws, ws_floats, _keep = _lib.delta_workspace(N, H, L, E, M, Q, backward=True)
         _lib.check(_lib.lib.fwp_fast_weight_backward_ws(
             N, H, L, E, M, _lib.desc(Q), _lib.desc(K), _lib.desc(V), _lib.desc(beta),
-            _lib.desc(V_old), _lib.desc(V_insert), _lib.desc(grad_out), _lib.desc(W.detach()),
+            _lib.desc(V_old), _lib.desc(None), _lib.desc(grad_out), _lib.desc(W.detach()),
             _lib.desc(grad_Q), _lib.desc(grad_K), _lib.desc(grad_V), _lib.desc(grad_beta),
             _lib.io_dtype(Q), stream, dev, ws, ws_floats), 'fast_weight_backward')
         return grad_Q, grad_K, grad_V, grad_beta, None

@@ -34,7 +34,7 @@ class FastRNN(torch.autograd.Function):
     def backward(ctx, grad_out):
         rnn_out, K, V, beta, V_old, W, h0 = ctx.saved_tensors
         N, H, L, M = K.shape
-        grad_out = _lib.unit_inner(grad_out)
+        grad_out = _lib.grad_like(grad_out, rnn_out, (N, H, L, M))
         rnn_out_delayed = torch.cat([h0, rnn_out[:, :, :-1]], dim=2)
         grad_Z = torch.empty_like(rnn_out)
         grad_K = torch.empty_like(rnn_out)

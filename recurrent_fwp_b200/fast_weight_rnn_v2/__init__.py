@@ -13,7 +13,6 @@ from recurrent_fwp_b200 import _lib
 
 
 def _check(Z, K, V, W, beta, h0):
-    _lib.require_cuda(Z, K, V, W, beta, h0)
     N, H, L, _ = Z.shape
     M = V.shape[3]
     assert K.shape == (N, H, L, M)
@@ -22,6 +21,10 @@ def _check(Z, K, V, W, beta, h0):
     assert W.shape == (N, H, M, M)
     if Z.dtype != torch.float32:
         raise TypeError('the recurrent fast-weight kernels take float32 tensors')
+    _lib.require_streams(Z, {'Z': (Z, (N, H, L, M)), 'K': (K, (N, H, L, M)), 'V': (V, (N, H, L, M)),
+                             'beta': (beta, (N, H, L, 1))})
+    _lib.require_f32(Z, {'W': (W, (N, H, M, M)), 'h0': (h0, (N, H, 1, M))})
+    _lib.require_cuda(Z, K, V, W, beta, h0)
     if W.stride(3) != 1 or h0.stride(3) != 1:
         raise RuntimeError('W and h0 must have a unit innermost stride (they are updated in place)')
     return N, H, L, M
@@ -50,7 +53,7 @@ class FastRNNv2(torch.autograd.Function):
     def backward(ctx, grad_out):
         rnn_out, rnn_out_nmz, K, V, beta, V_old, W = ctx.saved_tensors
         N, H, L, M = K.shape
-        grad_out = _lib.unit_inner(grad_out)
+        grad_out = _lib.grad_like(grad_out, rnn_out, (N, H, L, M))
         grad_Z = torch.empty_like(rnn_out)
         grad_K = torch.empty_like(rnn_out)
         grad_V = torch.empty_like(rnn_out)

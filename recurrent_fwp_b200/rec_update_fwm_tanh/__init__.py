@@ -18,7 +18,6 @@ class FastWeightRecUpdateTanh(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qx, kx, vx, bx, R_q, R_k, R_v, r_b, W, h0):
-        _lib.require_cuda(qx, kx, vx, bx, R_q, R_k, R_v, r_b, W, h0)
         N, H, L, E = qx.shape
         M = vx.shape[3]
         assert E == M, "Current kernel only support this case."
@@ -28,6 +27,10 @@ class FastWeightRecUpdateTanh(torch.autograd.Function):
         assert r_b.shape == (1, H, 1, M), "Reshape/unsqueeze if needed."
         if qx.dtype != torch.float32:
             raise TypeError('the recurrent fast-weight kernels take float32 tensors')
+        _lib.require_streams(qx, {'kx': (kx, (N, H, L, E)), 'vx': (vx, (N, H, L, M)), 'bx': (bx, (N, H, L, 1))})
+        _lib.require_f32(qx, {'R_q': (R_q, (1, H, M, M)), 'R_k': (R_k, (1, H, M, M)), 'R_v': (R_v, (1, H, M, M)),
+                              'r_b': (r_b, (1, H, 1, M)), 'W': (W, (N, H, E, M)), 'h0': (h0, (N, H, 1, M))})
+        _lib.require_cuda(qx, kx, vx, bx, R_q, R_k, R_v, r_b, W, h0)
         if W.stride(3) != 1 or h0.stride(3) != 1:
             raise RuntimeError('W and h0 must have a unit innermost stride (they are updated in place)')
         qc, kc, vc, bc = (_lib.unit_inner(t.detach()) for t in (qx, kx, vx, bx))
@@ -54,7 +57,7 @@ class FastWeightRecUpdateTanh(torch.autograd.Function):
     def backward(ctx, grad_out):
         (out, Q, K, V, beta, V_old, R_q, R_k, R_v, r_b, W, h0) = ctx.saved_tensors
         N, H, L, M = out.shape
-        grad_out = _lib.unit_inner(grad_out)
+        grad_out = _lib.grad_like(grad_out, out, (N, H, L, M))
         grad_Q = torch.empty_like(Q)
         grad_K = torch.empty_like(K)
         grad_V = torch.empty_like(V)
