@@ -18,9 +18,16 @@ The line printed by rank 0 carries, besides the contract keys:
   e2e           the same metric through the public autograd API with pinned host buffers,
                 host->device copies of the inputs and device->host copies of the results timed
 
+  configs       (N = 1) every other benchmark shape timed in the same run: the small delta-rule case, the
+                scale-out delta-rule shape, the recurrent delta net, the fast-weight RNN and LSTM, and the
+                end-to-end language-model forward -- forward / backward ms, tokens/s, fraction of the HBM roofline
+  long_strong   (every N) the scale-out delta-rule shape with its FIXED batch of 256 split over the ranks
+                (256/N batch rows per rank, no collective): ms per fwd+bwd step (max over ranks) and tokens/s, so
+                that value(N) / value(1) is the strong-scaling speed-up
+
 `--impl reference` times the reference's CPU formulation (the oracle's per-timestep
-loops, forward+backward through autograd) on all host threads; a step there is a
-bounded sample of the workload (one segment).
+loops, forward+backward through autograd) on all host threads, on the same step: four
+carried segments of the language-model shape.
 """
 import argparse
 import ctypes
@@ -39,21 +46,30 @@ sys.path.insert(0, ROOT)
 
 WORKLOADS = {
     # name: (B, H, L, d, segments, dtype)
-    'lm': (64, 8, 256, 16, 4, 'fp32'),            # BASELINE configs[1]
-    'small': (2, 8, 256, 16, 1, 'fp32'),          # BASELINE configs[0]
-    'long': (256, 16, 4096, 64, 1, 'bf16'),       # BASELINE configs[4], kernel part
+    'lm': (64, 8, 256, 16, 4, 'fp32'),            # language-model training shape, four carried segments
+    'small': (2, 8, 256, 16, 1, 'fp32'),          # the reference's own CPU-runnable case
+    'long': (256, 16, 4096, 64, 1, 'bf16'),       # scale-out shape, kernel part
     'long_slice': (32, 16, 4096, 64, 1, 'bf16'),  # an eighth of it (one GPU's shard at N=8)
 }
 
+# DRAM read+write bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture), keyed by
+# the kernel the dispatch picked (fwp_last_kernel) and the number of (batch, head) sequences and steps captured.
+# Traffic of these kernels grows in proportion to sequences x steps, so a capture is scaled to the timed launch
+# by that product; a kernel without a capture reports null.  Each entry names where its capture is summarised.
+NCU_TRAFFIC = {
+    'delta_bwd_kernel': dict(bytes=44221312, seqs=512, steps=256, d=16, dtype='fp32',
+                             source='profiles/delta_fwd_bwd_lm_shape_ncu.md'),
+    'delta_bwd_chunk_bf16_inv_kernel': dict(bytes=2430927000, seqs=512, steps=4096, d=64, dtype='bf16',
+                                            source='profiles/delta_chunkwise_bf16_d64_ncu.md'),
+}
 
-# DRAM read+write bytes of one backward launch, from the ncu capture summarised in
-# profiles/delta_fwd_bwd_lm_shape_ncu.md (dram__bytes_read.sum + dram__bytes_write.sum)
-NCU_TRAFFIC_BWD = {'lm': 44221312,
-                   # profiles/delta_chunkwise_bf16_d64_ncu.md: captured on long_slice (512 sequences); 'long' has 8x
-                   # the sequences and its traffic grows in proportion
-                   'long_slice': 2430927000, 'long': 8 * 2430927000}
-# the kernel the backward launch runs, per workload (the dispatch picks it from head dimension and stream type)
-BWD_KERNEL = {'long': 'delta_bwd_chunk_bf16_kernel', 'long_slice': 'delta_bwd_chunk_bf16_kernel'}
+
+def ncu_traffic(kernel, seqs, steps, d, dts):
+    """Per-launch DRAM traffic of `kernel` from its ncu capture, scaled by sequences x steps; None without one."""
+    e = NCU_TRAFFIC.get(kernel)
+    if not e or e['d'] != d or e['dtype'] != dts:
+        return None, None
+    return int(e['bytes'] * (seqs * steps) / (e['seqs'] * e['steps'])), e['source']
 
 
 def peaks():
@@ -136,41 +152,64 @@ def make_inputs(seed, B, H, L, d, dtype, device=None, pin=False):
     return out
 
 
+def workload_config(name, B, H, L, d, segs, dts, **extra):
+    """The `config` object of the JSON line; both arms print the same `workload` string for the same step."""
+    cfg = {'workload': 'delta-rule fast weight memory fwd+bwd, B=%d,H=%d,L=%d,d_k=d_v=%d, %d carried segment(s) per '
+                       'step, %s streams, fp32 state' % (B, H, L, d, segs, dts),
+           'name': name, 'tokens_per_step_per_gpu': segs * B * L}
+    cfg.update(extra)
+    return cfg
+
+
+def delta_bytes(B, H, L, d, esz):
+    """Algorithmic bytes of one forward and one backward launch: the streams that cross the autograd boundary
+    ((4d+1) and (7d+2) elements per (batch, head, step)) plus the fp32 state read and written once per launch."""
+    units = B * H * L
+    state = B * H * 2 * d * d * 4
+    return units * (4 * d + 1) * esz + state, units * (7 * d + 2) * esz + state
+
+
 # ----------------------------------------------------------------------- CPU arm
-def cpu_loop_tokens_per_s(B, H, L, d, reps, warm=1):
-    """The reference's CPU path: per-timestep PyTorch loop, fp32, forward+backward by autograd."""
+def cpu_loop_tokens_per_s(B, H, L, d, reps, warm=1, segs=1):
+    """The reference's CPU path: per-timestep PyTorch loop, fp32, forward+backward by autograd, over `segs`
+    carried segments per step (the end state of one segment is the detached start state of the next, as the
+    reference's layers hand it on)."""
     from oracle import loops
     torch.set_num_threads(os.cpu_count() or 1)
     times = []
     for i in range(warm + reps):
-        q, k, v, beta, gy = make_inputs(1000 + i, B, H, L, d, torch.float32)
-        leaves = [t.requires_grad_() for t in (q, k, v, beta)]
+        inputs = [make_inputs(1000 + 10 * i + s, B, H, L, d, torch.float32) for s in range(segs)]
         t0 = time.perf_counter()
-        y, _ = loops.delta_rule(*leaves, torch.zeros(B, H, d, d))
-        (y * gy).sum().backward()
+        W = torch.zeros(B, H, d, d)
+        for q, k, v, beta, gy in inputs:
+            leaves = [t.requires_grad_() for t in (q, k, v, beta)]
+            y, S = loops.delta_rule(*leaves, W)
+            W = S.detach()
+            (y * gy).sum().backward()
         dt = time.perf_counter() - t0
         if i >= warm:
             times.append(dt)
-    return B * L / statistics.mean(times), statistics.mean(times)
+    return segs * B * L / statistics.mean(times), statistics.mean(times)
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
-    B, H, L, d, segs, dt = WORKLOADS[args.workload]
-    # bounded sample: one segment of the workload per step, batch capped so a step stays ~1 s
+    B, H, L, d, segs, dts = WORKLOADS[args.workload]
+    # the same step as the GPU arm (all carried segments); shapes too large for the host are capped and say so
     Bs = min(B, 64)
     Ls = min(L, 256)
-    tps, sec = cpu_loop_tokens_per_s(Bs, H, Ls, d, reps=args.steps, warm=max(1, min(args.warmup, 2)))
+    steps = max(1, min(args.steps, 8))          # about 3.5 s per step on 16 cores: keeps the run within minutes
+    warm = max(1, min(args.warmup, 1))
+    tps, sec = cpu_loop_tokens_per_s(Bs, H, Ls, d, reps=steps, warm=warm, segs=segs)
     sample = 'per-timestep PyTorch loop (oracle port of the reference formulation), fwd+bwd by autograd, fp32, ' \
-             'one segment B=%d,H=%d,L=%d,d=%d per step' % (Bs, H, Ls, d)
+             '%d carried segment(s) of B=%d,H=%d,L=%d,d=%d per step, %d timed steps' % (segs, Bs, H, Ls, d, steps)
     line = {
         'impl': 'reference', 'metric': 'fast-weight fwd+bwd tokens/s', 'value': tps, 'unit': 'tokens/s',
-        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': sec * 1e3,
-        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp32', 'data': 'synthetic',
-        'config': {'workload': 'delta-rule fwd+bwd, %s shape B=%d,H=%d,L=%d,d=%d' % (args.workload, B, H, L, d),
-                   'sample': sample},
+        'n_gpus': args.gpus, 'steps': steps, 'warmup': warm, 'ms_per_step': sec * 1e3,
+        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': dts, 'data': 'synthetic',
+        'config': workload_config(args.workload, B, H, L, d, segs, dts, sample=sample),
         'cpu_baseline': {'value': tps, 'unit': 'tokens/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                          'sample': sample},
         'e2e': {'value': tps, 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
@@ -199,7 +238,6 @@ class DeltaStep:
         self.W = self.Ws[0]
         self.y = [torch.empty(B, H, L, d, **io) for _ in range(segs)]
         self.vo = [torch.empty(B, H, L, d, **f32) for _ in range(segs)]
-        self.vi = [torch.empty(B, H, L, d, **f32) for _ in range(segs)]
         self.g = [[torch.empty(B, H, L, d, **io) for _ in range(3)] + [torch.empty(B, H, L, 1, **io)]
                   for _ in range(segs)]
         self.code = _lib.io_dtype(self.inp[0][0])
@@ -208,27 +246,27 @@ class DeltaStep:
         self.d_Ws = [D(t) for t in self.Ws]
         self.d_y = [D(t) for t in self.y]
         self.d_vo = [D(t) for t in self.vo]
-        self.d_vi = [D(t) for t in self.vi]
+        self.d_none = D(None)     # u_t ("v_insert") is rebuilt by the backward: not stored
         self.d_g = [[D(t) for t in seg] for seg in self.g]
         self.dev_index = device.index
-        # workspaces of the chunkwise plan (null for shapes that have none)
-        self.ws_f, self.ws_f_n, self._ws_f_keep = _lib.delta_workspace(B, H, L, d, d, self.inp[0][0], backward=False)
-        self.ws_b, self.ws_b_n, self._ws_b_keep = _lib.delta_workspace(B, H, L, d, d, self.inp[0][0], backward=True)
+        self.kernels = {}
 
     def fwd(self, s, stream):
         B, H, L, d = self.shape
         q, k, v, b, _ = self.d_in[s]
-        self.L_.check(self.L_.lib.fwp_fast_weight_forward_ws(
-            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], self.d_Ws[s], self.d_y[s],
-            self.code, stream, self.dev_index, self.ws_f, self.ws_f_n), 'fwd')
+        self.L_.check(self.L_.lib.fwp_fast_weight_forward(
+            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_none, self.d_Ws[s], self.d_y[s],
+            self.code, stream, self.dev_index), 'fwd')
+        self.kernels['fwd'] = self.L_.last_kernel()
 
     def bwd(self, s, stream):
         B, H, L, d = self.shape
         q, k, v, b, gy = self.d_in[s]
         gq, gk, gv, gb = self.d_g[s]
-        self.L_.check(self.L_.lib.fwp_fast_weight_backward_ws(
-            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_vi[s], gy, self.d_Ws[s], gq, gk, gv, gb,
-            self.code, stream, self.dev_index, self.ws_b, self.ws_b_n), 'bwd')
+        self.L_.check(self.L_.lib.fwp_fast_weight_backward(
+            B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_none, gy, self.d_Ws[s], gq, gk, gv, gb,
+            self.code, stream, self.dev_index), 'bwd')
+        self.kernels['bwd'] = self.L_.last_kernel()
 
     def step(self):
         """Per segment: fwd, clone the end state as the next segment's start state (the carried memory; the reference's
@@ -270,10 +308,10 @@ def time_kernels(ds, flush, reps):
     return statistics.mean(tf) * 1e-3, statistics.mean(tb) * 1e-3, min(tf) * 1e-3, min(tb) * 1e-3
 
 
-# ---- the recurrent families (BASELINE configs[2] and configs[3]); timed through their autograd Functions
+# ---- the recurrent families at their benchmark shapes; timed through their autograd Functions
 FAMILY_SHAPES = {
-    'rec_delta': (64, 8, 256, 32),     # configs[2]
-    'rnn_v2': (128, 4, 512, 32),       # configs[3]
+    'rec_delta': (64, 8, 256, 32),     # recurrent delta net
+    'rnn_v2': (128, 4, 512, 32),       # fast-weight RNN / LSTM shape
     'rnn_v1': (128, 4, 512, 32),
     'lstm_v1': (128, 4, 512, 32),
     'lstm_v2': (128, 4, 512, 32),
@@ -282,18 +320,15 @@ FAMILY_SHAPES = {
 }
 
 
-def run_family(args):
-    """Forward and backward device time of one recurrent family at its BASELINE shape (fp32, W0 = h0 = 0),
+def time_family(name, steps, dev, flush_buf):
+    """Forward and backward device time of one recurrent family at its benchmark shape (fp32, W0 = h0 = 0),
     CUDA events around the autograd Function's forward and around .backward(), L2 flushed before each."""
     import recurrent_fwp_b200 as fwp
-    name = args.workload
+    from recurrent_fwp_b200 import _lib
     B, H, L, d = FAMILY_SHAPES[name]
-    dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
-    torch.cuda.set_device(dev)
     g = torch.Generator(device='cpu')
     g.manual_seed(7)
     rn = lambda *s: torch.randn(*s, generator=g).to(dev)
-    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     z = lambda *s: torch.zeros(*s, device=dev)
 
     def gate():
@@ -317,11 +352,12 @@ def run_family(args):
                             x[8], x[9], x[10], x[11], z(B, H, d, d), z(B, H, 1, d), z(B, H, 1, d))[0]
         elems = 29 * d + 9
     gy = rn(B, H, L, d)
-    tf, tb = [], []
-    for i in range(3 + max(args.steps, 5)):
+    tf, tb, launches = [], [], 0
+    for i in range(3 + max(steps, 5)):
         leaves = [t.detach().requires_grad_() for t in ins]
         flush_buf.zero_()
         e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        n0 = _lib.launch_count()
         e[0].record()
         y = call(leaves)
         e[1].record()
@@ -330,24 +366,53 @@ def run_family(args):
         y.backward(gy)
         e[3].record()
         torch.cuda.synchronize(dev)
+        launches = _lib.launch_count() - n0
         if i >= 3:
             tf.append(e[0].elapsed_time(e[1]) * 1e-3)
             tb.append(e[2].elapsed_time(e[3]) * 1e-3)
     peak, kind = peaks()
     f, b_ = statistics.mean(tf), statistics.mean(tb)
     nbytes = B * H * L * elems * 4
-    print(json.dumps({'workload': name, 'shape': {'B': B, 'H': H, 'L': L, 'd': d}, 'fwd_ms': f * 1e3, 'bwd_ms': b_ * 1e3,
-                      'tokens_per_s': B * L / (f + b_), 'algorithmic_bytes_fwd_bwd': nbytes,
-                      'hbm_frac_fwd_bwd': nbytes / (f + b_) / 1e9 / peak, 'peak_kind': kind,
-                      'timing': 'CUDA events around the autograd forward / backward calls, L2 flushed before each'}),
-          flush=True)
+    return {'workload': name, 'shape': {'B': B, 'H': H, 'L': L, 'd': d}, 'dtype': 'fp32', 'fwd_ms': f * 1e3,
+            'bwd_ms': b_ * 1e3, 'tokens_per_s': B * L / (f + b_), 'algorithmic_bytes_fwd_bwd': nbytes,
+            'frac': nbytes / (f + b_) / 1e9 / peak, 'peak_kind': kind, 'launches_per_step': int(launches),
+            'timing': 'CUDA events around the autograd forward / backward calls (the wrappers\' small torch ops '
+                      'included), L2 flushed before each'}
 
 
-# ---- BASELINE configs[4], second part: end-to-end forward of a 16-layer delta-rule language model
+def run_family(args):
+    dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
+    torch.cuda.set_device(dev)
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    print(json.dumps(time_family(args.workload, args.steps, dev, flush_buf)), flush=True)
+
+
+def time_delta(name, device, flush, reps, B=None, seed=77):
+    """Forward and backward kernel time of one delta-rule workload (all of its segments launched back to back),
+    with the kernels the dispatch picked and the fraction of the HBM roofline of both launches together."""
+    Bw, H, L, d, segs, dts = WORKLOADS[name]
+    B = Bw if B is None else B
+    dtype = torch.float32 if dts == 'fp32' else torch.bfloat16
+    esz = 4 if dts == 'fp32' else 2
+    ds = DeltaStep(B, H, L, d, segs, dtype, device, seed=seed)
+    tf, tb, tf_min, tb_min = time_kernels(ds, flush, reps=reps)
+    peak, kind = peaks()
+    bf, bb = delta_bytes(B, H, L, d, esz)
+    out = {'workload': name, 'shape': {'B': B, 'H': H, 'L': L, 'd': d}, 'dtype': dts, 'fwd_ms': tf * 1e3,
+           'bwd_ms': tb * 1e3, 'tokens_per_s': B * L / (tf + tb), 'algorithmic_bytes_fwd_bwd': bf + bb,
+           'frac': (bf + bb) / (tf + tb) / 1e9 / peak, 'frac_fwd': bf / tf / 1e9 / peak, 'frac_bwd': bb / tb / 1e9 / peak,
+           'peak_kind': kind, 'kernels': dict(ds.kernels),
+           'timing': 'CUDA events around the launches, L2 flushed before each direction'}
+    del ds
+    torch.cuda.empty_cache()
+    return out
+
+
+# ---- end-to-end forward of a 16-layer delta-rule language model (second part of the scale-out configuration)
 LM_E2E = dict(n_token=32768, n_layer=16, n_head=8, d_model=256, d_head=32, d_inner=1024, batch=32, seq_len=512)
 
 
-def run_lm_e2e(args):
+def time_lm_e2e(steps, warmup, dev, rank=0, world=1, fused_io=True, sample_clocks=False):
     """Forward of the delta-rule language model (recurrent_fwp_b200/lm_harness.py: the reference's
     MemTransformerLM with attn_type 24, random-init weights, uniform random token ids, fp32), B=32, L=512.
     Each step copies the step's token ids from pinned host memory, runs the forward under no_grad and reads the
@@ -357,16 +422,10 @@ def run_lm_e2e(args):
     from recurrent_fwp_b200 import _lib
     from recurrent_fwp_b200.lm_harness import DeltaNetLM
     from recurrent_fwp_b200 import sharding
-    rank = int(os.environ.get('RANK', '0'))
-    world = int(os.environ.get('WORLD_SIZE', '1'))
-    dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group('nccl', device_id=dev)
     c = LM_E2E
     torch.manual_seed(11)
     model = DeltaNetLM(c['n_token'], c['n_layer'], c['n_head'], c['d_model'], c['d_head'], c['d_inner'],
-                       fused_io=not args.unfused_layer_io).to(dev).eval()
+                       fused_io=fused_io).to(dev).eval()
     B, L = c['batch'], c['seq_len']
     rows = sharding.batch_slice(B, rank, world)
     g = torch.Generator().manual_seed(5)
@@ -375,9 +434,9 @@ def run_lm_e2e(args):
     flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     times, launches, loss_mean = [], 0, None
     sampler = None
-    for i in range(args.warmup + args.steps):
-        if i == args.warmup:
-            sampler = ClockSampler(dev.index)
+    for i in range(warmup + steps):
+        if i == warmup:
+            sampler = ClockSampler(dev.index) if sample_clocks else None
             if world > 1:
                 dist.barrier()
             torch.cuda.synchronize(dev)
@@ -393,7 +452,7 @@ def run_lm_e2e(args):
             loss_mean = loss.mean().item()        # device -> host read of the step's result
         e1.record()
         torch.cuda.synchronize(dev)
-        if i >= args.warmup:
+        if i >= warmup:
             times.append(e0.elapsed_time(e1) * 1e-3)
             launches += _lib.launch_count() - n0
     clocks = sampler.stop() if sampler else None
@@ -401,23 +460,80 @@ def run_lm_e2e(args):
     if world > 1:
         dist.all_reduce(tsum, op=dist.ReduceOp.MAX)
         dist.barrier()
+    sec = tsum.item() / steps
+    del model
+    torch.cuda.empty_cache()
+    return {'ms_per_step': sec * 1e3, 'tokens_per_s': B * L / sec, 'launches': int(launches), 'mean_loss': loss_mean,
+            'h2d_bytes_per_step': int(host[0].numel() * 8), 'clocks': clocks}
+
+
+LM_E2E_WORKLOAD = ('end-to-end forward, 16-layer delta-rule LM (attn_type 24), d_model 256, 8 heads of 32, FF 1024, '
+                   'vocab 32768, B=32, L=512, random-init weights, uniform random token ids')
+
+
+def run_lm_e2e(args):
+    import torch.distributed as dist
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    r = time_lm_e2e(args.steps, args.warmup, dev, rank, world, fused_io=not args.unfused_layer_io, sample_clocks=True)
     if rank == 0:
-        sec = tsum.item() / args.steps
-        tps = B * L / sec
         print(json.dumps({
-            'metric': 'delta-net language model forward tokens/s', 'value': tps, 'unit': 'tokens/s', 'n_gpus': world,
-            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': sec * 1e3, 'higher_is_better': True,
-            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'fp32', 'data': 'synthetic',
-            'config': {'workload': 'end-to-end forward, 16-layer delta-rule LM (attn_type 24), d_model 256, 8 heads of 32, '
-                                   'FF 1024, vocab 32768, B=32, L=512, random-init weights, uniform random token ids',
+            'metric': 'delta-net language model forward tokens/s', 'value': r['tokens_per_s'], 'unit': 'tokens/s',
+            'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': r['ms_per_step'],
+            'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'fp32', 'data': 'synthetic',
+            'config': {'workload': LM_E2E_WORKLOAD,
                        'layer_io': 'torch elementwise chain' if args.unfused_layer_io else 'one-launch prologue and epilogue',
                        'sharding': 'batch rows split over ranks; per-token losses all-gathered (NCCL) outside the op',
                        'l2': 'flushed between timed steps (256 MiB write)'},
-            'e2e': {'value': tps, 'unit': 'tokens/s', 'h2d_bytes_per_step': int(host[0].numel() * 8),
+            'e2e': {'value': r['tokens_per_s'], 'unit': 'tokens/s', 'h2d_bytes_per_step': r['h2d_bytes_per_step'],
                     'd2h_bytes_per_step': 4, 'api': 'recurrent_fwp_b200.lm_harness.DeltaNetLM.forward'},
-            'gpu_launches': int(launches), 'mean_loss': loss_mean, 'clocks': clocks}), flush=True)
+            'gpu_launches': r['launches'], 'mean_loss': r['mean_loss'], 'clocks': r['clocks']}), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def long_strong(device, flush, rank, world, barrier, steps=5, warmup=3):
+    """The scale-out delta-rule shape with its fixed batch of 256 split over the ranks (256 / N batch rows each,
+    all 16 heads, no collective): fwd+bwd device time per step, max over ranks."""
+    import torch.distributed as dist
+    Bw, H, L, d, segs, dts = WORKLOADS['long']
+    if Bw % world:
+        return None
+    B = Bw // world
+    ds = DeltaStep(B, H, L, d, segs, torch.bfloat16, device, seed=900 + rank)
+    tot = []
+    for i in range(warmup + steps):
+        if i == warmup:
+            torch.cuda.synchronize(device)
+            barrier()
+        flush()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        ds.step()
+        b_.record()
+        torch.cuda.synchronize(device)
+        if i >= warmup:
+            tot.append(a.elapsed_time(b_) * 1e-3)
+    t = torch.tensor([sum(tot)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sec = float(t.item()) / steps
+    kernels = dict(ds.kernels)
+    del ds
+    torch.cuda.empty_cache()
+    peak, kind = peaks()
+    bf, bb = delta_bytes(Bw, H, L, d, 2)
+    return {'workload': 'delta-rule fwd+bwd, B=%d (fixed, %d per rank),H=%d,L=%d,d=%d, bf16 streams, fp32 state'
+                        % (Bw, B, H, L, d),
+            'scaling': 'strong', 'n_gpus': world, 'ms_per_step': sec * 1e3, 'tokens_per_s': Bw * L / sec,
+            'frac_of_n_gpu_hbm': (bf + bb) / sec / 1e9 / (peak * world), 'peak_kind': kind, 'steps': steps,
+            'kernels': kernels,
+            'timing': 'CUDA events around forward, state copy and backward of each step, L2 flushed between steps, '
+                      'summed, max over ranks'}
 
 
 def run_gpu_arm(args):
@@ -577,47 +693,63 @@ def run_gpu_arm(args):
     e2e_value = world * segs * Be * L * e2e_steps / float(te.item())
     clocks = sampler.stop() if sampler else None
 
+    # ---- the scale-out shape with its fixed batch split over the ranks (every N)
+    strong = None
+    if args.workload == 'lm' and not args.skip_configs:
+        strong = long_strong(device, flush, rank, world, barrier)
+
     # ---- per-kernel timing for the roofline (rank 0 only; separate from the step timing)
-    line = None
     if rank == 0:
         tf, tb, tf_min, tb_min = time_kernels(ds, flush, reps=max(10, min(4 * args.steps, 40)))
         peak, peak_kind = peaks()
-        units = B * H * L
-        bytes_fwd = units * (2 * d + d + 1 + d) * esz + B * H * 2 * d * d * 4
-        bytes_bwd = units * ((2 * d + 2 * d + 1) + (2 * d + d + 1)) * esz + B * H * 2 * d * d * 4
+        bytes_fwd, bytes_bwd = delta_bytes(B, H, L, d, esz)
         ach_b = bytes_bwd / tb / 1e9
         ach_fb = (bytes_fwd + bytes_bwd) / (tf + tb) / 1e9
+        bwd_kernel = ds.kernels.get('bwd')
+        traffic, traffic_src = ncu_traffic(bwd_kernel, B * H, L, d, dts)
+        configs = None
+        if world == 1 and args.workload == 'lm' and not args.skip_configs:
+            configs = {'small': time_delta('small', device, flush, reps=10),
+                       'long': time_delta('long', device, flush, reps=3)}
+            for fam in ('rec_delta', 'rnn_v2', 'lstm_v1'):
+                configs[fam] = time_family(fam, 5, device, flush_buf)
+            r = time_lm_e2e(5, 3, device)
+            configs['lm_e2e'] = {'workload': LM_E2E_WORKLOAD, 'fwd_ms': r['ms_per_step'], 'bwd_ms': None,
+                                 'tokens_per_s': r['tokens_per_s'], 'frac': None, 'launches_per_step': r['launches'] // 5,
+                                 'h2d_bytes_per_step': r['h2d_bytes_per_step'], 'd2h_bytes_per_step': 4,
+                                 'timing': 'CUDA events around token upload, forward under no_grad and the read of '
+                                           'the mean loss; L2 flushed between steps'}
         cpu = None
         if world == 1 and not args.skip_cpu:
             Bs, Ls = min(B, 64), min(L, 256)
-            tps, sec = cpu_loop_tokens_per_s(Bs, H, Ls, d, reps=8, warm=1)
+            tps, sec = cpu_loop_tokens_per_s(Bs, H, Ls, d, reps=6, warm=1, segs=segs)
             cpu = {'value': tps, 'unit': 'tokens/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                    'sample': 'per-timestep PyTorch loop (oracle port of the reference formulation), fwd+bwd by '
-                             'autograd, fp32, 8 repetitions of one segment B=%d,H=%d,L=%d,d=%d (%.2f s each)'
-                             % (Bs, H, Ls, d, sec)}
+                             'autograd, fp32, 6 repetitions of the step (%d carried segment(s) of B=%d,H=%d,L=%d,d=%d; '
+                             '%.2f s each)' % (segs, Bs, H, Ls, d, sec)}
         line = {
             'metric': 'fast-weight fwd+bwd tokens/s', 'value': value, 'unit': 'tokens/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': dev_s / args.steps * 1e3,
             'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': dts, 'data': 'synthetic',
-            'config': {'workload': 'delta-rule fast weight memory fwd+bwd, B=%d,H=%d,L=%d,d_k=d_v=%d, %d carried '
-                                   'segment(s) per step, %s streams, fp32 state' % (B, H, L, d, segs, dts),
-                       'name': args.workload, 'tokens_per_step_per_gpu': tokens_per_step,
-                       'sharding': 'batch x head units split over ranks, no collective on the data path',
-                       'l2': 'flushed between timed steps (256 MiB write)', 'cuda_graph': graph is not None,
-                       'timing': 'CUDA events per step, summed; max over ranks'},
-            'roofline': {'bound': 'hbm', 'kernel': BWD_KERNEL.get(args.workload, 'delta_bwd_kernel'), 'achieved': ach_b, 'peak': peak, 'unit': 'GB/s',
-                         'frac': ach_b / peak, 'peak_kind': peak_kind, 'traffic': NCU_TRAFFIC_BWD.get(args.workload),
+            'config': workload_config(
+                args.workload, B, H, L, d, segs, dts,
+                sharding='batch x head units split over ranks, no collective on the data path',
+                l2='flushed between timed steps (256 MiB write)', cuda_graph=graph is not None,
+                timing='CUDA events per step, summed; max over ranks'),
+            'roofline': {'bound': 'hbm', 'kernel': bwd_kernel, 'achieved': ach_b, 'peak': peak, 'unit': 'GB/s',
+                         'frac': ach_b / peak, 'peak_kind': peak_kind, 'traffic': traffic, 'traffic_source': traffic_src,
                          'algorithmic_bytes_per_launch': bytes_bwd, 'launch_s': tb, 'launch_s_min': tb_min,
                          'timing': 'CUDA events around the %d segments launched back to back (distinct inputs, '
                                    'L2 flushed before the first), divided by %d' % (segs, segs)},
             'roofline_fwd_bwd': {'achieved': ach_fb, 'peak': peak, 'unit': 'GB/s', 'frac': ach_fb / peak,
                                  'algorithmic_bytes': bytes_fwd + bytes_bwd, 'fwd_s': tf, 'bwd_s': tb,
-                                 'fwd_s_min': tf_min, 'bwd_s_min': tb_min},
+                                 'fwd_s_min': tf_min, 'bwd_s_min': tb_min, 'kernels': dict(ds.kernels)},
             'cpu_baseline': cpu,
             'e2e': {'value': e2e_value, 'unit': 'tokens/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
                     'steps': e2e_steps, 'batch': Be, 'api': 'recurrent_fwp_b200.fast_weight_delta (autograd) + .backward()',
                     'pipeline': 'uploads, compute and downloads on three streams; pinned host buffers'},
             'gpu_launches': int(launches), 'clocks': clocks, 'wall_s_timed_region': t_wall,
+            'long_strong': strong, 'configs': configs,
         }
         if _lib.device_fault() != 0:
             raise SystemExit('bench.py: a bounded wait inside a kernel ran out; the numbers above are invalid')
@@ -638,6 +770,8 @@ def main():
     ap.add_argument('--tune', action='append', default=[], metavar='KEY=INT',
                     help='set an execution-plan switch of the library before the run (repeatable), e.g. delta.chunk=1')
     ap.add_argument('--skip-cpu', action='store_true')
+    ap.add_argument('--skip-configs', action='store_true',
+                    help='leave out the `configs` and `long_strong` objects (the other benchmark shapes)')
     ap.add_argument('--unfused-layer-io', action='store_true',
                     help='lm_e2e: run the chain of torch ops around the op instead of the fused prologue / epilogue')
     ap.add_argument('--kernels-only', action='store_true',

@@ -26,7 +26,12 @@
  * them, the backward rewinds them in place to the start-of-segment state.
  *
  * Ownership: the caller allocates everything, including scratch; the library
- * allocates nothing, keeps no pointer after a call returns, and is re-entrant.
+ * allocates nothing and keeps no pointer after a call returns.  Calls may be made
+ * from several host threads and on several devices at once.  Three pieces of
+ * process-wide state exist and are shared by all of them: the execution-plan
+ * switches set by fwp_tune (atomic integers), the built-in scratch array of the
+ * no-allocation entry point (one per GPU), and the per-GPU flag that
+ * fwp_delta_device_fault reads.
  */
 #ifndef FWP_H_
 #define FWP_H_
@@ -69,9 +74,15 @@ int fwp_version(void);
 int fwp_max_head_dim(void);
 /* Number of kernels this library has launched in this process (all threads). */
 unsigned long long fwp_launch_count(void);
-/* Tuning knob for experiments: key is "<op>.<D>.split" or "<op>.<D>.chunk";
- * returns 0 if the key/value pair is accepted. */
+/* Execution-plan switch for experiments and cross-checks (process-wide, atomic):
+ * "delta.blocked" (-1 automatic, 0 per-step kernels, 1 four-step blocked kernels),
+ * "delta.chunk64" (1 / 0: chunkwise tensor-core plan for bf16 streams at E = M = 64),
+ * "delta.tc64" (1 / 0: tcgen05 forward of that plan), "<op>.<D>.split", "delta_bwd.bulk",
+ * "delta_bwd.16.chunk".  Returns 0 if accepted, FWP_ERR_UNSUPPORTED for an unknown key. */
 int fwp_tune(const char* key, int value);
+/* Name of the kernel this host thread launched last through the library ("" before the
+ * first launch): lets a benchmark label its numbers with the plan the dispatch picked. */
+const char* fwp_last_kernel(void);
 
 /* ---- delta rule --------------------------------------------------------
  * replaces fast_weight_forward(Q,K,V,beta,v_old,v_insert,kv,out),
@@ -96,31 +107,6 @@ int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
                              const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
                              const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
                              int io_dtype, void* stream, int device);
-
-/* Chunkwise plan of the delta rule (fp32 streams, E and M up to 16): 16 steps per chunk, every chunk
- * of every sequence prepared and finished in parallel, one small product per chunk on the
- * sequential chain.  It needs device scratch, which the caller owns: ask for the size, allocate
- * (16-byte aligned), and call the *_ws variants, which take the same arguments as the two entry
- * points above plus the workspace.  backward != 0 asks for the backward pass's size.  A shape
- * without such a plan reports 0; a null or short workspace makes the *_ws call behave exactly like
- * the plain entry point.  The workspace is only used during the call's own launches.
- * No counterpart in the reference, which has no scratch (fast_weight_cuda.cu:182-240, :564-664). */
-size_t fwp_fast_weight_workspace_floats(int N, int H, int L, int E, int M, int io_dtype, int backward);
-int fwp_fast_weight_forward_ws(int N, int H, int L, int E, int M,
-                               const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
-                               const fwp_tensor* beta, const fwp_tensor* v_old,
-                               const fwp_tensor* v_insert, const fwp_tensor* kv,
-                               const fwp_tensor* out, int io_dtype, void* stream, int device,
-                               float* workspace, size_t workspace_floats);
-int fwp_fast_weight_backward_ws(int N, int H, int L, int E, int M,
-                                const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
-                                const fwp_tensor* beta, const fwp_tensor* v_old,
-                                const fwp_tensor* v_insert, const fwp_tensor* grad_out,
-                                const fwp_tensor* fw_mem,
-                                const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
-                                const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
-                                int io_dtype, void* stream, int device,
-                                float* workspace, size_t workspace_floats);
 
 /* The delta-rule kernels move contiguous chunks with bulk asynchronous copies whose completion
  * waits are bounded.  Returns 1 if such a wait ever ran out on the current device since the last

@@ -14,7 +14,9 @@ gradients are taken from the executed module's globals and stored under
 ``tests/golden/<op>.npz``; the test-suite checks both oracle layers and the
 CUDA path against these files without needing the reference checkout.
 
-Usage:  python -m oracle.pin_against_reference /path/to/reference
+Usage:  python -m oracle.pin_against_reference /path/to/reference [--out DIR]
+(``--out`` writes the fixtures to DIR instead of ``tests/golden``, e.g. to compare a fresh run with the
+committed files.)
 """
 import contextlib
 import io
@@ -135,10 +137,16 @@ def capture(family, env):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get('FWP_REFERENCE_ROOT', '')
+    argv = list(sys.argv[1:])
+    out_dir = GOLDEN
+    if '--out' in argv:
+        i = argv.index('--out')
+        out_dir = os.path.abspath(argv[i + 1])
+        del argv[i:i + 2]
+    ref_root = argv[0] if argv else os.environ.get('FWP_REFERENCE_ROOT', '')
     if not os.path.isdir(ref_root):
         raise SystemExit('reference checkout not found: pass its root as the first argument')
-    os.makedirs(GOLDEN, exist_ok=True)
+    os.makedirs(out_dir, exist_ok=True)
     for family in FAMILIES:
         try:
             env = run_selftest(ref_root, family)
@@ -148,9 +156,9 @@ def main():
         rec = capture(family, env)
         note = ''
         if rec is not None:
-            out = os.path.join(GOLDEN, family + '.npz')
+            out = os.path.join(out_dir, family + '.npz')
             np.savez_compressed(out, **rec)
-            note = ' -> %s (%d KB)' % (os.path.relpath(out, REPO), os.path.getsize(out) // 1024)
+            note = ' -> %s (%d KB)' % (out, os.path.getsize(out) // 1024)
         print('%-10s reference self-test passed with the oracle as the kernel%s' % (family, note))
 
 

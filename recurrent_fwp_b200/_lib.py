@@ -36,8 +36,6 @@ _i, _vp, _i64 = ctypes.c_int, ctypes.c_void_p, ctypes.c_int64
 SIGNATURES = {
     'fwp_fast_weight_forward': [_i] * 5 + [_T] * 8 + [_i, _vp, _i],
     'fwp_fast_weight_backward': [_i] * 5 + [_T] * 12 + [_i, _vp, _i],
-    'fwp_fast_weight_forward_ws': [_i] * 5 + [_T] * 8 + [_i, _vp, _i, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t],
-    'fwp_fast_weight_backward_ws': [_i] * 5 + [_T] * 12 + [_i, _vp, _i, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t],
     'fwp_causal_dot_product': [_i] * 5 + [_T] * 5 + [_i, _vp, _i],
     'fwp_causal_dot_backward': [_i] * 5 + [_T] * 7 + [_i, _vp, _i],
     'fwp_rec_update_fwm_tanh_forward': [_i] * 4 + [_T] * 16 + [_i, _vp, _i],
@@ -55,7 +53,7 @@ SIGNATURES = {
 }
 OTHER_SYMBOLS = ['fwp_status_string', 'fwp_last_cuda_error', 'fwp_version', 'fwp_max_head_dim',
                  'fwp_launch_count', 'fwp_tune', 'fwp_rec_update_fwm_tanh_scratch_floats', 'fwp_delta_device_fault',
-                 'fwp_fast_weight_workspace_floats']
+                 'fwp_last_kernel']
 
 for _name, _args in SIGNATURES.items():
     _f = getattr(lib, _name)
@@ -67,8 +65,7 @@ lib.fwp_launch_count.restype = ctypes.c_ulonglong
 lib.fwp_tune.argtypes = [ctypes.c_char_p, _i]
 lib.fwp_rec_update_fwm_tanh_scratch_floats.argtypes = [_i, _i, _i]
 lib.fwp_rec_update_fwm_tanh_scratch_floats.restype = _i64
-lib.fwp_fast_weight_workspace_floats.argtypes = [_i] * 7
-lib.fwp_fast_weight_workspace_floats.restype = ctypes.c_size_t
+lib.fwp_last_kernel.restype = ctypes.c_char_p
 
 
 def io_dtype(t):
@@ -166,19 +163,6 @@ def check(rc, what):
         raise RuntimeError('%s failed: %s' % (what, msg))
 
 
-def delta_workspace(N, H, L, E, M, like, backward):
-    """(pointer, floats) of a workspace for the chunkwise delta-rule plan on ``like``'s device, allocated from
-    torch's caching allocator on the current stream, plus the tensor that keeps it alive; (None, 0, None)
-    for shapes without such a plan or while the plan is not switched on (``tune('delta.chunk', 1)``)."""
-    if _tuned.get('delta.chunk', 0) != 1:
-        return None, 0, None
-    n = int(lib.fwp_fast_weight_workspace_floats(N, H, L, E, M, io_dtype(like), 1 if backward else 0))
-    if n == 0:
-        return None, 0, None
-    buf = torch.empty(n, device=like.device, dtype=torch.float32)
-    return ctypes.cast(ctypes.c_void_p(buf.data_ptr()), ctypes.POINTER(ctypes.c_float)), n, buf
-
-
 def device_fault():
     """1 if a bounded wait inside a delta-rule kernel ran out since the last call (synchronises the device)."""
     return int(lib.fwp_delta_device_fault())
@@ -188,9 +172,10 @@ def launch_count():
     return int(lib.fwp_launch_count())
 
 
-_tuned = {}     # mirror of the keys set through tune(), for host-side decisions
+def last_kernel():
+    """Name of the kernel the calling thread launched last through the library."""
+    return lib.fwp_last_kernel().decode()
 
 
 def tune(key, value):
-    check(lib.fwp_tune(key.encode(), int(value)), 'fwp_tune')
-    _tuned[key] = int(value)
+    check(lib.fwp_tune(key.encode(), int(value)), 'fwp_tune(%r)' % key)

@@ -1,21 +1,30 @@
 // Host-side plumbing shared by every entry point: argument validation, status
 // strings, the per-thread CUDA error slot, the launch counter and the tuning table.
 #include <atomic>
+#include <climits>
 #include <cstring>
-#include <map>
-#include <mutex>
-#include <string>
 #include "fwp_core.cuh"
 
 namespace fwp {
 
 static thread_local int g_last_cuda_error = 0;
 static std::atomic<unsigned long long> g_launches{0};
-static std::mutex g_tune_mu;
-static std::map<std::string, int>& tune_table() {
-    static std::map<std::string, int> t;
-    return t;
-}
+static thread_local const char* g_last_kernel = "";
+
+// Process-wide execution-plan switches: one atomic per key, INT_MIN = not set.
+static const char* const kTuneNames[T_COUNT] = {
+    "delta.blocked", "delta.chunk64", "delta.tc64",
+    "delta_fwd.16.split", "delta_fwd.32.split", "delta_fwd.64.split",
+    "sum_fwd.16.split", "sum_fwd.32.split", "sum_fwd.64.split",
+    "delta_bwd.16.split", "delta_bwd.32.split", "delta_bwd.64.split",
+    "delta_bwd.bulk", "delta_bwd.16.chunk",
+    "lstm_fwd.32.split", "lstm_bwd.32.split", "rnn_fwd.32.split", "rnn_bwd.32.split", "rec_fwd.32.split", "rec_bwd.32.split",
+};
+struct TuneTable {
+    std::atomic<int> v[T_COUNT];
+    TuneTable() { for (auto& x : v) x.store(INT_MIN, std::memory_order_relaxed); }
+};
+static TuneTable g_tune;
 
 int set_cuda_error(cudaError_t e) {
     g_last_cuda_error = (int)e;
@@ -24,10 +33,11 @@ int set_cuda_error(cudaError_t e) {
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
-int tune_get(const char* key, int fallback) {
-    std::lock_guard<std::mutex> lk(g_tune_mu);
-    auto it = tune_table().find(key);
-    return it == tune_table().end() ? fallback : it->second;
+void note_kernel(const char* name) { g_last_kernel = name; }
+
+int tune_get(TuneKey key, int fallback) {
+    const int v = g_tune.v[key].load(std::memory_order_relaxed);
+    return v == INT_MIN ? fallback : v;
 }
 
 int check_tensor(const fwp_tensor* t, int elem_bytes, bool required) {
@@ -63,9 +73,15 @@ FWP_API int fwp_version(void) { return 100; }
 FWP_API int fwp_max_head_dim(void) { return 64; }
 FWP_API unsigned long long fwp_launch_count(void) { return fwp::g_launches.load(); }
 
+FWP_API const char* fwp_last_kernel(void) { return fwp::g_last_kernel; }
+
 FWP_API int fwp_tune(const char* key, int value) {
-    if (!key || std::strlen(key) > 40) return FWP_ERR_NULL;
-    std::lock_guard<std::mutex> lk(fwp::g_tune_mu);
-    fwp::tune_table()[key] = value;
-    return FWP_OK;
+    if (!key) return FWP_ERR_NULL;
+    if (value == INT_MIN) return FWP_ERR_SHAPE;
+    for (int i = 0; i < fwp::T_COUNT; i++)
+        if (std::strcmp(key, fwp::kTuneNames[i]) == 0) {
+            fwp::g_tune.v[i].store(value, std::memory_order_relaxed);
+            return FWP_OK;
+        }
+    return FWP_ERR_UNSUPPORTED;     // not a switch of this library
 }

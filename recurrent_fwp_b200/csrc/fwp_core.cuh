@@ -43,7 +43,23 @@ static inline Row4 row4(const fwp_tensor* t) {
 int check_tensor(const fwp_tensor* t, int elem_bytes, bool required);
 int set_cuda_error(cudaError_t e);
 void count_launch(int n = 1);
-int tune_get(const char* key, int fallback);
+void note_kernel(const char* name);     // remembers, per host thread, the kernel launched last (fwp_last_kernel)
+
+// Execution-plan switches (fwp_tune).  Each is one atomic integer looked up by index, so the dispatch of a
+// call reads a few relaxed atomics: no string handling, no lock.
+enum TuneKey {
+    T_DELTA_BLOCKED,        // "delta.blocked": -1 automatic, 0 per-step kernels, 1 four-step blocked kernels
+    T_DELTA_CHUNK64,        // "delta.chunk64": 1 chunkwise tensor-core plan for bf16 streams at E = M = 64, 0 off
+    T_DELTA_TC64,           // "delta.tc64": 1 tcgen05 forward of that plan, 0 the warp-level mma forward
+    T_DELTA_FWD_SPLIT16, T_DELTA_FWD_SPLIT32, T_DELTA_FWD_SPLIT64,      // "delta_fwd.<D>.split"
+    T_SUM_FWD_SPLIT16, T_SUM_FWD_SPLIT32, T_SUM_FWD_SPLIT64,            // "sum_fwd.<D>.split"
+    T_DELTA_BWD_SPLIT16, T_DELTA_BWD_SPLIT32, T_DELTA_BWD_SPLIT64,      // "delta_bwd.<D>.split"
+    T_DELTA_BWD_BULK,       // "delta_bwd.bulk": 1 bulk-copy staging in the d = 16 backward, 0 cp.async
+    T_DELTA_BWD_CHUNK16,    // "delta_bwd.16.chunk": 32 or 16 steps per staged chunk
+    T_LSTM_FWD_SPLIT32, T_LSTM_BWD_SPLIT32, T_RNN_FWD_SPLIT32, T_RNN_BWD_SPLIT32, T_REC_FWD_SPLIT32, T_REC_BWD_SPLIT32,
+    T_COUNT
+};
+int tune_get(TuneKey key, int fallback);
 
 struct DeviceGuard {
     int prev = -1;
@@ -71,19 +87,6 @@ static inline int pad_dim(int d) { return d <= 16 ? 16 : (d <= 32 ? 32 : (d <= 6
 
 // ---------------------------------------------------------------- device side
 #ifdef __CUDACC__
-
-// Optional phase timers (cycles of thread 0 of CTA 0), compiled in only for
-// development builds with -DFWP_PROFILE; they expand to nothing otherwise.
-#ifdef FWP_PROFILE
-static __device__ long long fwp_prof_out[16];
-#define FWP_PROF_BEGIN long long _pt[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long _pc = clock64();
-#define FWP_PROF(i) { const long long _n = clock64(); _pt[i] += _n - _pc; _pc = _n; }
-#define FWP_PROF_END(base, cond) if (blockIdx.x == 0 && (cond)) { for (int _i = 0; _i < 8 && (base) + _i < 16; _i++) fwp_prof_out[(base) + _i] = _pt[_i]; }
-#else
-#define FWP_PROF_BEGIN
-#define FWP_PROF(i)
-#define FWP_PROF_END(base, cond)
-#endif
 
 // Two fp32 values packed in one 64-bit register.  Everything that lives across
 // time steps (the matrices, operand slices, dot-product accumulators) stays in

@@ -350,46 +350,34 @@ template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     constexpr int NSL = slots_for(D * SPLIT);
     return launch(delta_fwd_kernel<D, SPLIT, TC, T, SUM>, p, (nseq + NSL - 1) / NSL, NSL * (D * SPLIT + 32),
-                  NSL * WsFwdSmem<D, TC, T>::kFloats * sizeof(float), st);
-}
-template <int TC, typename T>
-static int launch_fwd_mma(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
-    constexpr int NSL = slots_for(32);
-    return launch(delta_fwd_kernel<16, 2, TC, T, false, true>, p, (nseq + NSL - 1) / NSL, NSL * 64,
-                  NSL * WsFwdSmem<16, TC, T>::kFloats * sizeof(float), st);
-}
-template <int D, int SPLIT, int TC, typename T>
-static int launch_fwd3(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
-    constexpr int NSL = slots_for(D * SPLIT);
-    return launch(delta_fwd3_kernel<D, SPLIT, TC, T>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
-                  NSL * WsFwd3Smem<D, TC, T>::kFloats * sizeof(float), st);
+                  NSL * WsFwdSmem<D, TC, T>::kFloats * sizeof(float), st, "delta_fwd_kernel");
 }
 template <int D, int SPLIT, int TC, typename T, int PF = 2>
 static int launch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     constexpr int NSL = slots_for(D * SPLIT);
     return launch(delta_bwd_kernel<D, SPLIT, TC, T, PF>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
-                  NSL * WsBwdSmem<D, TC, T, PF>::kFloats * sizeof(float), st);
+                  NSL * WsBwdSmem<D, TC, T, PF>::kFloats * sizeof(float), st, "delta_bwd_kernel");
 }
 template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd_step(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     int slots = slots_for(D * SPLIT);
     while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
     return launch(delta_fwd_step_kernel<D, SPLIT, TC, T, SUM>, p, nseq / slots, D * SPLIT * slots,
-                  slots * 2 * FwdStage<D, TC, T>::kFloats * sizeof(float), st);
+                  slots * 2 * FwdStage<D, TC, T>::kFloats * sizeof(float), st, "delta_fwd_step_kernel");
 }
 template <int D, int SPLIT, int TC, typename T>
 static int launch_bwd_step(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     int slots = slots_for(D * SPLIT);
     while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
     return launch(delta_bwd_step_kernel<D, SPLIT, TC, T>, p, nseq / slots, D * SPLIT * slots,
-                  slots * (2 * BwdStage<D, TC, T>::kFloats + 2 * (2 * D + 8)) * sizeof(float), st);
+                  slots * (2 * BwdStage<D, TC, T>::kFloats + 2 * (2 * D + 8)) * sizeof(float), st, "delta_bwd_step_kernel");
 }
 template <int D, int SPLIT, int TC, typename T>
 static int launch_sum_bwd(const SumBwdParams& p, int nseq, cudaStream_t st) {
     int slots = slots_for(D * SPLIT);
     while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
     return launch(sum_bwd_kernel<D, SPLIT, TC, T>, p, nseq / slots, D * SPLIT * slots,
-                  slots * 2 * SumStage<D, TC, T>::kFloats * sizeof(float), st);
+                  slots * 2 * SumStage<D, TC, T>::kFloats * sizeof(float), st, "sum_bwd_kernel");
 }
 
 // Shapes beyond the register-resident kernels: one CTA per sequence, matrices in shared memory.
@@ -398,13 +386,19 @@ template <typename T, bool SUM>
 static int launch_fwd_generic(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     const size_t bytes = gen_fwd_floats(p.E, p.M) * sizeof(float);
     if (bytes > kGenericSmemLimit) return FWP_ERR_UNSUPPORTED;
-    return launch(delta_fwd_generic_kernel<T, SUM>, p, nseq, kGenThreads, bytes, st);
+    return launch(delta_fwd_generic_kernel<T, SUM>, p, nseq, kGenThreads, bytes, st, "delta_fwd_generic_kernel");
 }
 template <typename T>
 static int launch_bwd_generic(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     const size_t bytes = gen_bwd_floats(p.E, p.M) * sizeof(float);
     if (bytes > kGenericSmemLimit) return FWP_ERR_UNSUPPORTED;
-    return launch(delta_bwd_generic_kernel<T>, p, nseq, kGenThreads, bytes, st);
+    return launch(delta_bwd_generic_kernel<T>, p, nseq, kGenThreads, bytes, st, "delta_bwd_generic_kernel");
+}
+template <typename T>
+static int launch_sum_bwd_generic(const SumBwdParams& p, int nseq, cudaStream_t st) {
+    const size_t bytes = gen_sum_bwd_floats(p.E, p.M) * sizeof(float);
+    if (bytes > kGenericSmemLimit) return FWP_ERR_UNSUPPORTED;
+    return launch(sum_bwd_generic_kernel<T>, p, nseq, kGenThreads, bytes, st, "sum_bwd_generic_kernel");
 }
 
 // Which execution plan runs by default was picked per head dimension from measurements on B200
@@ -419,35 +413,20 @@ static int launch_bwd_generic(const DeltaBwdParams& p, int nseq, cudaStream_t st
 // "delta.blocked" = 0 / 1 forces the per-step / blocked plan (tests cross-check one against the other).
 constexpr int kShortSeq = 16;
 template <typename T, bool SUM>
-static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, const char* op) {
+static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     const int D = pad_dim(p.E > p.M ? p.E : p.M);
-    char key[48];
-    snprintf(key, sizeof key, "%s.%d.split", op, D);
-    const int force = tune_get("delta.blocked", -1);
+    const int force = tune_get(T_DELTA_BLOCKED, -1);
     if (D == 0) return launch_fwd_generic<T, SUM>(p, nseq, st);
     switch (D) {
         case 16: {
-            if constexpr (!SUM && sizeof(T) == 4) {
-                // opt-in chunkwise tensor-core form ("delta.chunk" = 1 and a workspace): three launches, every
-                // chunk in parallel; measured issue-bound and behind the recurrent plan on B200 (40 vs 28 us
-                // forward, 65 vs 48 us backward at 512 sequences of 256 steps)
-                if (p.ws && force == -1 && tune_get("delta.chunk", 0) == 1) return launch_fwd_chunk(p, nseq, st);
-            }
             if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_fwd_step<16, 2, 32, T, SUM>(p, nseq, st);
-            if (tune_get(key, 2) == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
-            if constexpr (!SUM) {
-                // opt-in tensor-core group loop ("delta_fwd.mma" = 1; fp32 or bf16 streams): 30.5 us against 28.4 us
-                if (force == -1 && tune_get("delta_fwd.mma", 0) == 1) return launch_fwd_mma<32, T>(p, nseq, st);
-                // opt-in chain / read-out split of the group loop with bulk-copy staging (measured slower
-                // than one consumer warp per sequence on the language-model shape)
-                if (tune_get("delta_fwd.roles", 2) == 3) return launch_fwd3<16, 2, 32, T>(p, nseq, st);
-            }
+            if (tune_get(SUM ? T_SUM_FWD_SPLIT16 : T_DELTA_FWD_SPLIT16, 2) == 4) return launch_fwd<16, 4, 32, T, SUM>(p, nseq, st);
             return launch_fwd<16, 2, 32, T, SUM>(p, nseq, st);
         }
         case 32: {
             // fp32 streams: per-step 55 us vs blocked 56 us; bf16 streams: blocked 80 us vs per-step 87 us
             if (force == 0 || (force == -1 && (sizeof(T) == 4 || p.L <= kShortSeq))) return launch_fwd_step<32, 1, 16, T, SUM>(p, nseq, st);
-            const int sp = tune_get(key, 1);
+            const int sp = tune_get(SUM ? T_SUM_FWD_SPLIT32 : T_DELTA_FWD_SPLIT32, 1);
             if (sp == 2) return launch_fwd<32, 2, 16, T, SUM>(p, nseq, st);
             if (sp == 4) return launch_fwd<32, 4, 16, T, SUM>(p, nseq, st);
             return launch_fwd<32, 1, 16, T, SUM>(p, nseq, st);
@@ -455,11 +434,11 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
         case 64: {
             if constexpr (!SUM && sizeof(T) == 2) {
                 // chunkwise tensor-core form for bf16 streams ("delta.chunk64" = 0 switches it off)
-                if (force == -1 && p.L > kShortSeq && tune_get("delta.chunk64", 1) == 1 && chunk_bf16_applies(p))
+                if (force == -1 && p.L > kShortSeq && tune_get(T_DELTA_CHUNK64, 1) == 1 && chunk_bf16_applies(p))
                     return launch_fwd_chunk_bf16(p, nseq, st);
             }
             if (force != 1) return launch_fwd_step<64, 2, 8, T, SUM>(p, nseq, st);
-            if (tune_get(key, 2) == 4) return launch_fwd<64, 4, 8, T, SUM>(p, nseq, st);
+            if (tune_get(SUM ? T_SUM_FWD_SPLIT64 : T_DELTA_FWD_SPLIT64, 2) == 4) return launch_fwd<64, 4, 8, T, SUM>(p, nseq, st);
             return launch_fwd<64, 2, 8, T, SUM>(p, nseq, st);
         }
     }
@@ -469,40 +448,35 @@ static int dispatch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st, cons
 template <typename T>
 static int dispatch_bwd(const DeltaBwdParams& p0, int nseq, cudaStream_t st) {
     DeltaBwdParams p = p0;
-    p.bulk = tune_get("delta_bwd.bulk", 1);
+    p.bulk = tune_get(T_DELTA_BWD_BULK, 1);
     const int D = pad_dim(p.E > p.M ? p.E : p.M);
-    char key[48];
-    snprintf(key, sizeof key, "delta_bwd.%d.split", D);
-    const int force = tune_get("delta.blocked", -1);
+    const int force = tune_get(T_DELTA_BLOCKED, -1);
     if (D == 0) return launch_bwd_generic<T>(p, nseq, st);
     switch (D) {
         case 16: {
-            if constexpr (sizeof(T) == 4) {
-                if (p.ws && force == -1 && tune_get("delta.chunk", 0) == 1) return launch_bwd_chunk(p, nseq, st);
-            }
             if (force == 0 || (force == -1 && p.L <= kShortSeq)) return launch_bwd_step<16, 2, 16, T>(p, nseq, st);
-            if (tune_get(key, 2) == 4) return launch_bwd<16, 4, 16, T>(p, nseq, st);
+            if (tune_get(T_DELTA_BWD_SPLIT16, 2) == 4) return launch_bwd<16, 4, 16, T>(p, nseq, st);
             // 32-step chunks staged one chunk ahead (three stages; 203 KB of shared memory for four sequences) against
             // 16-step chunks staged two ahead: 45.3 vs 46.3 us at 256 steps, 149.8 vs 155.4 us at 1024
             // (fp32 streams only: the 16-bit staging copies of bf16 streams do not fit next to 32-step chunks)
-            if (sizeof(T) != 4 || tune_get("delta_bwd.16.chunk", 32) == 16) return launch_bwd<16, 2, 16, T>(p, nseq, st);
+            if (sizeof(T) != 4 || tune_get(T_DELTA_BWD_CHUNK16, 32) == 16) return launch_bwd<16, 2, 16, T>(p, nseq, st);
             return launch_bwd<16, 2, 32, float, 1>(p, nseq, st);
         }
         case 32: {
             // fp32 streams: blocked 138 us vs per-step 175 us; bf16 streams: per-step 201 us vs blocked 207 us
             if (force == 0 || (force == -1 && (p.L <= kShortSeq || sizeof(T) != 4))) return launch_bwd_step<32, 2, 8, T>(p, nseq, st);
-            if (tune_get(key, 2) == 4) return launch_bwd<32, 4, 8, T>(p, nseq, st);
+            if (tune_get(T_DELTA_BWD_SPLIT32, 2) == 4) return launch_bwd<32, 4, 8, T>(p, nseq, st);
             return launch_bwd<32, 2, 8, T>(p, nseq, st);
         }
         case 64: {
             if constexpr (sizeof(T) == 2) {
                 // chunkwise tensor-core form for bf16 streams ("delta.chunk64" = 0 switches it off)
-                if (force == -1 && p.L > kShortSeq && tune_get("delta.chunk64", 1) == 1 && chunk_bf16_applies(p))
+                if (force == -1 && p.L > kShortSeq && tune_get(T_DELTA_CHUNK64, 1) == 1 && chunk_bf16_applies(p))
                     return launch_bwd_chunk_bf16(p, nseq, st);
             }
             const bool blocked = force == 1 || (force == -1 && sizeof(T) == 4 && p.L > 4 * kShortSeq);
             if (!blocked) return launch_bwd_step<64, 4, 4, T>(p, nseq, st);
-            if (tune_get(key, 2) == 4) return launch_bwd<64, 4, 4, T>(p, nseq, st);
+            if (tune_get(T_DELTA_BWD_SPLIT64, 2) == 4) return launch_bwd<64, 4, 4, T>(p, nseq, st);
             return launch_bwd<64, 2, 4, T>(p, nseq, st);
         }
     }
@@ -512,6 +486,7 @@ static int dispatch_bwd(const DeltaBwdParams& p0, int nseq, cudaStream_t st) {
 template <typename T>
 static int dispatch_sum_bwd(const SumBwdParams& p, int nseq, cudaStream_t st) {
     const int D = pad_dim(p.E > p.M ? p.E : p.M);
+    if (D == 0) return launch_sum_bwd_generic<T>(p, nseq, st);
     switch (D) {
         case 16: return launch_sum_bwd<16, 2, 16, T>(p, nseq, st);
         case 32: return launch_sum_bwd<32, 2, 8, T>(p, nseq, st);
@@ -533,17 +508,11 @@ static int check_common(int N, int H, int L, int E, int M, int io_dtype) {
 
 using namespace fwp;
 
-FWP_API size_t fwp_fast_weight_workspace_floats(int N, int H, int L, int E, int M, int io_dtype, int backward) {
-    if (N < 1 || H < 1) return 0;
-    return chunk_ws_floats((long long)N * H, L, E, M, io_dtype, backward != 0);
-}
-
 static int fast_weight_forward_impl(int N, int H, int L, int E, int M,
                                     const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
                                     const fwp_tensor* beta, const fwp_tensor* v_old,
                                     const fwp_tensor* v_insert, const fwp_tensor* kv,
-                                    const fwp_tensor* out, int io_dtype, void* stream, int device,
-                                    float* workspace, size_t workspace_floats) {
+                                    const fwp_tensor* out, int io_dtype, void* stream, int device) {
     if (int rc = check_common(N, H, L, E, M, io_dtype)) return rc;
     const int eb = io_dtype == FWP_F32 ? 4 : 2;
     int rc;
@@ -560,10 +529,8 @@ static int fast_weight_forward_impl(int N, int H, int L, int E, int M,
     p.W = (float*)kv->data; p.wN = kv->stride[0]; p.wH = kv->stride[1]; p.wE = kv->stride[2];
     p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
-    const size_t need = chunk_ws_floats((long long)N * H, L, E, M, io_dtype, false);
-    if (workspace && need && workspace_floats >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) p.ws = workspace;
-    if (io_dtype == FWP_F32) return dispatch_fwd<float, false>(p, N * H, st, "delta_fwd");
-    return dispatch_fwd<__nv_bfloat16, false>(p, N * H, st, "delta_fwd");
+    if (io_dtype == FWP_F32) return dispatch_fwd<float, false>(p, N * H, st);
+    return dispatch_fwd<__nv_bfloat16, false>(p, N * H, st);
 }
 
 FWP_API int fwp_fast_weight_forward(int N, int H, int L, int E, int M,
@@ -571,19 +538,7 @@ FWP_API int fwp_fast_weight_forward(int N, int H, int L, int E, int M,
                                        const fwp_tensor* beta, const fwp_tensor* v_old,
                                        const fwp_tensor* v_insert, const fwp_tensor* kv,
                                        const fwp_tensor* out, int io_dtype, void* stream, int device) {
-    return fast_weight_forward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, kv, out, io_dtype, stream, device, nullptr, 0);
-}
-
-// Same call with a caller-provided workspace (fwp_fast_weight_workspace_floats): shapes that have a
-// chunkwise plan use it; a null or short workspace, or any other shape, takes the plain entry point's path.
-FWP_API int fwp_fast_weight_forward_ws(int N, int H, int L, int E, int M,
-                                       const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
-                                       const fwp_tensor* beta, const fwp_tensor* v_old,
-                                       const fwp_tensor* v_insert, const fwp_tensor* kv,
-                                       const fwp_tensor* out, int io_dtype, void* stream, int device,
-                                       float* workspace, size_t workspace_floats) {
-    return fast_weight_forward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, kv, out, io_dtype, stream, device,
-                                    workspace, workspace_floats);
+    return fast_weight_forward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, kv, out, io_dtype, stream, device);
 }
 
 static int fast_weight_backward_impl(int N, int H, int L, int E, int M,
@@ -593,8 +548,7 @@ static int fast_weight_backward_impl(int N, int H, int L, int E, int M,
                                         const fwp_tensor* fw_mem,
                                         const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
                                         const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
-                                        int io_dtype, void* stream, int device,
-                                        float* workspace, size_t workspace_floats) {
+                                        int io_dtype, void* stream, int device) {
     (void)v_insert;
     if (int rc = check_common(N, H, L, E, M, io_dtype)) return rc;
     const int eb = io_dtype == FWP_F32 ? 4 : 2;
@@ -613,8 +567,6 @@ static int fast_weight_backward_impl(int N, int H, int L, int E, int M,
     p.W = (float*)fw_mem->data; p.wN = fw_mem->stride[0]; p.wH = fw_mem->stride[1]; p.wE = fw_mem->stride[2];
     p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
-    const size_t need = chunk_ws_floats((long long)N * H, L, E, M, io_dtype, true);
-    if (workspace && need && workspace_floats >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) p.ws = workspace;
     if (io_dtype == FWP_F32) return dispatch_bwd<float>(p, N * H, st);
     return dispatch_bwd<__nv_bfloat16>(p, N * H, st);
 }
@@ -628,20 +580,7 @@ FWP_API int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
                                         const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
                                         int io_dtype, void* stream, int device) {
     return fast_weight_backward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, grad_out, fw_mem, grad_Q, grad_K, grad_V,
-                                     grad_beta, io_dtype, stream, device, nullptr, 0);
-}
-
-FWP_API int fwp_fast_weight_backward_ws(int N, int H, int L, int E, int M,
-                                        const fwp_tensor* Q, const fwp_tensor* K, const fwp_tensor* V,
-                                        const fwp_tensor* beta, const fwp_tensor* v_old,
-                                        const fwp_tensor* v_insert, const fwp_tensor* grad_out,
-                                        const fwp_tensor* fw_mem,
-                                        const fwp_tensor* grad_Q, const fwp_tensor* grad_K,
-                                        const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
-                                        int io_dtype, void* stream, int device,
-                                        float* workspace, size_t workspace_floats) {
-    return fast_weight_backward_impl(N, H, L, E, M, Q, K, V, beta, v_old, v_insert, grad_out, fw_mem, grad_Q, grad_K, grad_V,
-                                     grad_beta, io_dtype, stream, device, workspace, workspace_floats);
+                                     grad_beta, io_dtype, stream, device);
 }
 
 FWP_API int fwp_causal_dot_product(int N, int H, int L, int E, int M,
@@ -662,8 +601,8 @@ FWP_API int fwp_causal_dot_product(int N, int H, int L, int E, int M,
     p.W = (float*)kv->data; p.wN = kv->stride[0]; p.wH = kv->stride[1]; p.wE = kv->stride[2];
     p.H = H; p.L = L; p.E = E; p.M = M; p.NH = N * H;
     cudaStream_t st = (cudaStream_t)stream;
-    if (io_dtype == FWP_F32) return dispatch_fwd<float, true>(p, N * H, st, "sum_fwd");
-    return dispatch_fwd<__nv_bfloat16, true>(p, N * H, st, "sum_fwd");
+    if (io_dtype == FWP_F32) return dispatch_fwd<float, true>(p, N * H, st);
+    return dispatch_fwd<__nv_bfloat16, true>(p, N * H, st);
 }
 
 FWP_API int fwp_causal_dot_backward(int N, int H, int L, int E, int M,

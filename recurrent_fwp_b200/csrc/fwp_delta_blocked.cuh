@@ -31,7 +31,6 @@
 //     (dq, dk, in-place rewind of S).
 #pragma once
 #include "fwp_core.cuh"
-#include "fwp_mma.cuh"
 
 namespace fwp {
 
@@ -74,10 +73,9 @@ struct WsFwdSmem {
     static constexpr int kFloats = NS * kStage + 2 * kGram + 2 * kOut;
 };
 
-template <int D, int SPLIT, int TC, typename T, bool SUM, bool MMA = false>
+template <int D, int SPLIT, int TC, typename T, bool SUM>
 __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta_fwd_kernel(const DeltaFwdParams p) {
     using G = Geo<D, SPLIT>;
-    static_assert(!MMA || (D == 16 && SPLIT == 2 && !SUM), "the tensor-core group loop is written for one warp per 16x16 state");
     using SM = WsFwdSmem<D, TC, T>;
     using Stage = WsFwdStage<D, TC, T>;
     static_assert(TC % 4 == 0, "chunk must hold whole groups");
@@ -143,151 +141,26 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                 if (p.v_ins.p) flush_rows<D, 32, float, TC>(o + 2 * TC * D, p.v_ins, n, h, t0, nt, p.M, ptid);
             }
         };
-        FWP_PROF_BEGIN
         issue(0);
         if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         prepare(0);
         slot_barrier(slot, G::NT + 32);
-        FWP_PROF(0)
         for (int c = 0; c <= nchunks; c++) {
             if (c + 2 < nchunks) issue(c + 2);      // lands while this iteration's other work runs
-            FWP_PROF(4)
             if (c >= 1) flush(c - 1);
-            FWP_PROF(3)
             if (c + 1 < nchunks) {
                 if (c + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
-                FWP_PROF(1)
                 prepare(c + 1);
             }
-            FWP_PROF(2)
-            slot_barrier(slot, G::NT + 32);
-            FWP_PROF(5)
-        }
-        FWP_PROF_END(0, ptid == 0 && slot == 0)
-    } else if constexpr (MMA) {
-        // ===================================================== consumer warp, tensor-core group loop
-        // The state is kept transposed, X = S^T (rows m, columns e), as an mma accumulator fragment: lane
-        // (g = lane/4, t = lane%4) holds rows m = g, g+8 and columns e = 8j+2t, 8j+2t+1.  Per group of four steps:
-        //   P = X [k_0 q_0 k_1 q_1 k_2 q_2 k_3 q_3]     one m16n8k8 product over e (X is the A operand after
-        //                                               relabelling the contraction index); lane t receives
-        //                                               a_t = S0^T k_t and b_t = S0^T q_t for its two rows m
-        //   d_t = v_t - a_t, exchanged inside the quad; every lane runs the scalar recurrence
-        //   u_s = beta_s (d_s - sum_{i<s} u_i k_i.k_s) for both rows; lane t keeps v_old_t, u_t, y_t
-        //   X += U^T K                                  one m16n8k4 product per column tile over the four steps
-        // Operands are split into two TF32 parts (three MMAs per tile), so the result keeps fp32 accuracy.  Against
-        // the FMA loop this needs 11 instead of 25 shared-memory loads per group, none of them a 16-fold broadcast.
-        const int lane = tid & 31, g = lane >> 2, t = lane & 3;
-        float* W = p.W + n * p.wN + h * p.wH;
-        Frag X;
-        ck_load_state_t(X, W, p.wE, p.E, p.M, g, t);
-        slot_barrier(slot, G::NT + 32);
-        for (int c = 0; c <= nchunks; c++) {
-            if (c < nchunks) {
-                Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
-                const float* gram = gram0 + (c & 1) * SM::kGram;
-                float* oy = out0 + (c & 1) * SM::kOut;
-                float* ovo = oy + TC * D;
-                float* ou = ovo + TC * D;
-                const int nt = min(TC, p.L - c * TC), ng = (nt + 3) >> 2;
-                const float* vec0 = ((g & 1) ? s.q.f : s.k.f) + (g >> 1) * D + 2 * t;      // column g of [k_0 q_0 k_1 q_1 ...]
-#pragma unroll 1
-                for (int gi = 0; gi < ng; gi++) {
-                    const int tb = 4 * gi;
-                    // ---- operands that do not depend on the state
-                    const float2 e0 = *reinterpret_cast<const float2*>(vec0 + tb * D);
-                    const float2 e1 = *reinterpret_cast<const float2*>(vec0 + tb * D + 8);
-                    const float vt0 = s.v.f[(tb + t) * D + g], vt1 = s.v.f[(tb + t) * D + g + 8];
-                    const float kt0 = s.k.f[(tb + t) * D + g], kt1 = s.k.f[(tb + t) * D + g + 8];
-                    float gs[16];
-                    load16(gs, gram + gi * 16);
-                    const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
-                    const float be[4] = {b4.x, b4.y, b4.z, b4.w};
-                    unsigned bh[2][2], bl[2][2];
-                    tf32_split(e0.x, bh[0][0], bl[0][0]);
-                    tf32_split(e0.y, bh[0][1], bl[0][1]);
-                    tf32_split(e1.x, bh[1][0], bl[1][0]);
-                    tf32_split(e1.y, bh[1][1], bl[1][1]);
-                    unsigned kh[2], kl[2];
-                    tf32_split(kt0, kh[0], kl[0]);
-                    tf32_split(kt1, kh[1], kl[1]);
-                    // ---- P = X [k q ...]
-                    AFr xa;
-                    a_from_acc(xa, X);
-                    float ph[4] = {0.f, 0.f, 0.f, 0.f}, pl[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int ks = 0; ks < 2; ks++) {
-                        mma_tf32(pl, xa.l[ks], bh[ks]);
-                        mma_tf32(pl, xa.h[ks], bl[ks]);
-                        mma_tf32(ph, xa.h[ks], bh[ks]);
-                    }
-                    const float a0 = ph[0] + pl[0], q0 = ph[1] + pl[1], a1 = ph[2] + pl[2], q1 = ph[3] + pl[3];
-                    // ---- d_s for all four steps, rows m = g (suffix 0) and m = g + 8 (suffix 1)
-                    const float d0 = vt0 - a0, d1 = vt1 - a1;
-                    float ds0[4], ds1[4];
-#pragma unroll
-                    for (int sidx = 0; sidx < 4; sidx++) {
-                        ds0[sidx] = __shfl_sync(0xffffffffu, d0, (lane & ~3) | sidx);
-                        ds1[sidx] = __shfl_sync(0xffffffffu, d1, (lane & ~3) | sidx);
-                    }
-                    float u0[4], u1[4], c0[4], c1[4];       // c = the value before the scaling by beta: v_old_s = v_s - c_s
-#pragma unroll
-                    for (int sidx = 0; sidx < 4; sidx++) {
-                        float x0 = ds0[sidx], x1 = ds1[sidx];
-#pragma unroll
-                        for (int i = 0; i < sidx; i++) {
-                            x0 = fmaf(-u0[i], gs[gram_kk(i, sidx)], x0);
-                            x1 = fmaf(-u1[i], gs[gram_kk(i, sidx)], x1);
-                        }
-                        c0[sidx] = x0; c1[sidx] = x1;
-                        u0[sidx] = be[sidx] * x0; u1[sidx] = be[sidx] * x1;
-                    }
-                    // ---- this lane's step t: u_t, v_old_t, y_t = b_t + sum_{i<=t} u_i (k_i . q_t)
-                    const float ut0 = t == 0 ? u0[0] : t == 1 ? u0[1] : t == 2 ? u0[2] : u0[3];
-                    const float ut1 = t == 0 ? u1[0] : t == 1 ? u1[1] : t == 2 ? u1[2] : u1[3];
-                    const float ct0 = t == 0 ? c0[0] : t == 1 ? c0[1] : t == 2 ? c0[2] : c0[3];
-                    const float ct1 = t == 0 ? c1[0] : t == 1 ? c1[1] : t == 2 ? c1[2] : c1[3];
-                    float cq[4];
-                    cq[0] = t == 0 ? gs[gram_kq(0, 0)] : t == 1 ? gs[gram_kq(0, 1)] : t == 2 ? gs[gram_kq(0, 2)] : gs[gram_kq(0, 3)];
-                    cq[1] = t == 0 ? 0.f : t == 1 ? gs[gram_kq(1, 1)] : t == 2 ? gs[gram_kq(1, 2)] : gs[gram_kq(1, 3)];
-                    cq[2] = t <= 1 ? 0.f : t == 2 ? gs[gram_kq(2, 2)] : gs[gram_kq(2, 3)];
-                    cq[3] = t <= 2 ? 0.f : gs[gram_kq(3, 3)];
-                    float y0 = q0, y1 = q1;
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        y0 = fmaf(u0[i], cq[i], y0);
-                        y1 = fmaf(u1[i], cq[i], y1);
-                    }
-                    const int o0 = (tb + t) * D + g;
-                    oy[o0] = y0; oy[o0 + 8] = y1;
-                    ovo[o0] = vt0 - ct0; ovo[o0 + 8] = vt1 - ct1;
-                    ou[o0] = ut0; ou[o0 + 8] = ut1;
-                    // ---- X += U^T K over the four steps (contraction slot t <-> step t)
-                    unsigned uh[2], ul[2];
-                    tf32_split(ut0, uh[0], ul[0]);
-                    tf32_split(ut1, uh[1], ul[1]);
-                    float lo0[4] = {0.f, 0.f, 0.f, 0.f}, lo1[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_tf32_k4(lo0, ul, kh[0]);
-                    mma_tf32_k4(lo0, uh, kl[0]);
-                    mma_tf32_k4(X.c[0], uh, kh[0]);
-                    mma_tf32_k4(lo1, ul, kh[1]);
-                    mma_tf32_k4(lo1, uh, kl[1]);
-                    mma_tf32_k4(X.c[1], uh, kh[1]);
-#pragma unroll
-                    for (int i = 0; i < 4; i++) { X.c[0][i] += lo0[i]; X.c[1][i] += lo1[i]; }
-                }
-            }
             slot_barrier(slot, G::NT + 32);
         }
-        ck_store_state_t(X, W, p.wE, p.E, p.M, g, t);
     } else {
         // ===================================================== consumer warps: the group loop
         const G g(tid);
         float* W = p.W + n * p.wN + h * p.wH;
         f2 S[G::NP];
-        FWP_PROF_BEGIN
         load_cols(g, S, W, p.wE, p.E, p.M);
         slot_barrier(slot, G::NT + 32);
-        FWP_PROF(0)
         for (int c = 0; c <= nchunks; c++) {
             if (c < nchunks) {
                 Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
@@ -401,273 +274,9 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
                     }
                 }
             }
-            FWP_PROF(1)
             slot_barrier(slot, G::NT + 32);
-            FWP_PROF(2)
         }
         store_cols(g, S, W, p.wE, p.E, p.M);
-        FWP_PROF(3)
-        FWP_PROF_END(8, tid == 0)
-    }
-}
-
-// ------------------------------------------------------------------ forward, three roles
-// Same algebra, but the group loop is split over two warps per sequence so that neither carries
-// the whole instruction stream: the "chain" warp owns S and produces v_old_j, u_j (the only part
-// the next group depends on); the "read-out" warp follows one chunk behind with its own copy of
-// the state, updated with the published u_j, and produces y_j = S^T q_j + sum_i u_i (k_i . q_j).
-template <int D, int TC, typename T>
-struct WsFwd3Smem {
-    static constexpr int NS = 4;                       // in flight, prepared, chain, read-out
-    static constexpr int NB = 3;                       // Gram / output buffers: chain, read-out, flush
-    static constexpr int kStage = WsFwdStage<D, TC, T>::kFloats;
-    static constexpr int kGram = (TC / 4) * 16;
-    static constexpr int kOut = 3 * TC * D;            // y, v_old, u
-    static constexpr int kBars = r4(2 * NS);           // one 8-byte mbarrier per stage
-    static constexpr int kFloats = NS * kStage + NB * kGram + NB * kOut + kBars;
-};
-
-template <int D, int SPLIT, int TC, typename T>
-__global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) delta_fwd3_kernel(const DeltaFwdParams p) {
-    using G = Geo<D, SPLIT>;
-    using SM = WsFwd3Smem<D, TC, T>;
-    using Stage = WsFwdStage<D, TC, T>;
-    static_assert(TC % 4 == 0 && G::NR <= 8, "three-role forward is for small slices");
-    constexpr int NSL = slots_for(G::NT);
-    constexpr int NCONS = NSL * G::NT;
-    const int tid = threadIdx.x;
-    const int role = tid < NCONS ? 0 : (tid < 2 * NCONS ? 1 : 2);     // 0 chain, 1 read-out, 2 producer
-    const int rtid = tid - role * NCONS;
-    const int slot = role == 2 ? rtid >> 5 : rtid / G::NT;
-    const int seq = blockIdx.x * NSL + slot;
-    const int n = seq / p.H, h = seq - n * p.H;
-    extern __shared__ __align__(16) float smem_all[];
-    for (int i = tid; i < NSL * SM::kFloats; i += NSL * (2 * G::NT + 32)) smem_all[i] = 0.f;
-    fence_async_smem();     // the zero fill is ordered before any bulk copy into the same tiles
-    float* smem = smem_all + slot * SM::kFloats;
-    float* gram0 = smem + SM::NS * SM::kStage;
-    float* out0 = gram0 + SM::NB * SM::kGram;
-    const int nchunks = (p.L + TC - 1) / TC;
-    __syncthreads();
-    if (seq >= p.NH) return;      // an empty slot of the last CTA: nobody waits on its barrier
-    if (role == 2) {
-        // ===================================================== producer warp
-        const int ptid = rtid & 31;
-        Src<T> sq, sk, sv, sb;
-        sq.init(p.q, n, h, p.E);
-        sk.init(p.k, n, h, p.E);
-        sv.init(p.v, n, h, p.M);
-        sb.init(p.beta, n, h, 1);
-        // rows that are contiguous and 16-byte aligned travel as one bulk copy per chunk, the rest by cp.async
-        unsigned long long* bars = reinterpret_cast<unsigned long long*>(out0 + SM::NB * SM::kOut);
-        if (ptid == 0) {
-            for (int i = 0; i < SM::NS; i++) mbar_init(&bars[i], 1);
-            mbar_fence_init();
-        }
-        __syncwarp();
-        const bool eq = bulk_rows_ok<D, T>(sq.base, sq.sL, sq.width), ek = bulk_rows_ok<D, T>(sk.base, sk.sL, sk.width),
-                   ev = bulk_rows_ok<D, T>(sv.base, sv.sL, sv.width);
-        unsigned phase = 0;
-        bool failed = false;
-        auto issue = [&](int c) {
-            Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
-            const int t0 = c * TC, nt = min(TC, p.L - t0);
-            const bool eb = bulk_col_ok<T>(sb.base, sb.sL, t0, nt);
-            if (ptid == 0 && (eq || ek || ev || eb)) {
-                unsigned long long* bar = &bars[c % SM::NS];
-                const unsigned rows = nt * D * sizeof(T), col = nt * sizeof(T);
-                mbar_arrive_expect_tx(bar, (eq ? rows : 0) + (ek ? rows : 0) + (ev ? rows : 0) + (eb ? col : 0));
-                if (eq) bulk_g2s(s.q.raw, sq.base + (long long)t0 * D, rows, bar);
-                if (ek) bulk_g2s(s.k.raw, sk.base + (long long)t0 * D, rows, bar);
-                if (ev) bulk_g2s(s.v.raw, sv.base + (long long)t0 * D, rows, bar);
-                if (eb) bulk_g2s(s.b.raw, sb.base + t0, col, bar);
-            }
-            if (!eq) s.q.template load<32>(sq, t0, nt, ptid);
-            if (!ek) s.k.template load<32>(sk, t0, nt, ptid);
-            if (!ev) s.v.template load<32>(sv, t0, nt, ptid);
-            if (!eb) s.b.template load<32>(sb, t0, nt, ptid);
-            cp_async_commit();
-        };
-        auto landed = [&](int c) {      // after the cp.async groups of chunk c were waited for: its bulk copies
-            const int t0 = c * TC, nt = min(TC, p.L - t0);
-            if (eq || ek || ev || bulk_col_ok<T>(sb.base, sb.sL, t0, nt)) {
-                const int st = c % SM::NS;
-                if (!failed && !mbar_wait_bounded(&bars[st], (phase >> st) & 1)) {
-                    failed = true;
-                    atomicExch(&g_delta_fault, 1);
-                }
-                phase ^= 1u << st;
-            }
-        };
-        auto prepare = [&](int c) {
-            Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
-            const int nt = min(TC, p.L - c * TC), ng = (nt + 3) >> 2;
-            __syncwarp();
-            if constexpr (sizeof(T) != 4) {
-                s.q.widen(nt, p.E, ptid, 32);
-                s.k.widen(nt, p.E, ptid, 32);
-                s.v.widen(nt, p.M, ptid, 32);
-                s.b.widen(nt, 1, ptid, 32);
-            }
-            if (nt & 3) {
-                zero_rows<D>(s.q.f, nt, 4 * ng, ptid, 32);
-                zero_rows<D>(s.k.f, nt, 4 * ng, ptid, 32);
-                zero_rows<D>(s.v.f, nt, 4 * ng, ptid, 32);
-                zero_rows<1>(s.b.f, nt, 4 * ng, ptid, 32);
-            }
-            if ((sizeof(T) != 4) || (nt & 3)) __syncwarp();
-            gram_phase<D, 32, TC>(s.k.f, s.q.f, gram0 + (c % SM::NB) * SM::kGram, ng, ptid);
-        };
-        // outputs: fp32 tiles whose destination rows are contiguous leave by one bulk store each
-        const Row4 ro[3] = {p.out, p.v_old, p.v_ins};
-        bool eo[3];
-        float* ob[3];
-#pragma unroll
-        for (int i = 0; i < 3; i++) {
-            ob[i] = reinterpret_cast<float*>(ro[i].p) + n * ro[i].sN + h * ro[i].sH;
-            eo[i] = ro[i].p && (i > 0 || sizeof(T) == 4) && bulk_rows_ok<D, float>(ob[i], ro[i].sL, p.M);
-        }
-        auto flush = [&](int c) {
-            const float* o = out0 + (c % SM::NB) * SM::kOut;
-            const int t0 = c * TC, nt = min(TC, p.L - t0);
-            if (ptid == 0 && (eo[0] || eo[1] || eo[2])) {
-#pragma unroll
-                for (int i = 0; i < 3; i++)
-                    if (eo[i]) bulk_s2g(ob[i] + (long long)t0 * D, o + i * TC * D, nt * D * sizeof(float));
-                bulk_commit();
-            }
-            if (!eo[0]) flush_rows<D, 32, T, TC>(o, p.out, n, h, t0, nt, p.M, ptid);
-            if (!eo[1]) flush_rows<D, 32, float, TC>(o + TC * D, p.v_old, n, h, t0, nt, p.M, ptid);
-            if (!eo[2] && p.v_ins.p) flush_rows<D, 32, float, TC>(o + 2 * TC * D, p.v_ins, n, h, t0, nt, p.M, ptid);
-        };
-        issue(0);
-        if (nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-        landed(0);
-        prepare(0);
-        slot_barrier(slot, 2 * G::NT + 32);
-        for (int c = 0; c <= nchunks + 1; c++) {
-            if (c + 2 < nchunks) issue(c + 2);
-            if (c >= 2) flush(c - 2);
-            if (c + 1 < nchunks) {
-                if (c + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
-                landed(c + 1);
-                prepare(c + 1);
-            }
-            if (ptid == 0) bulk_wait_read_all();     // the flushed tiles may be rewritten after the barrier
-            slot_barrier(slot, 2 * G::NT + 32);
-        }
-        if (ptid == 0) bulk_wait_all();
-    } else if (role == 0) {
-        // ===================================================== chain warp: v_old, u, state update
-        const G g(rtid);
-        float* W = p.W + n * p.wN + h * p.wH;
-        f2 S[G::NP];
-        load_cols(g, S, W, p.wE, p.E, p.M);
-        slot_barrier(slot, 2 * G::NT + 32);
-        for (int c = 0; c <= nchunks + 1; c++) {
-            if (c < nchunks) {
-                Stage s; s.bind(smem + (c % SM::NS) * SM::kStage);
-                const float* gram = gram0 + (c % SM::NB) * SM::kGram;
-                float* ovo = out0 + (c % SM::NB) * SM::kOut + TC * D;
-                float* ou = ovo + TC * D;
-                const int nt = min(TC, p.L - c * TC), ng = (nt + 3) >> 2;
-#pragma unroll 1
-                for (int gi = 0; gi < ng; gi++) {
-                    const int tb = 4 * gi;
-                    f2 kk[4][G::NP];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
-                    f2 aa[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-                    for (int i = 0; i < G::NP; i++) {
-#pragma unroll
-                        for (int j = 0; j < 4; j++) aa[j] = ffma2(S[i], kk[j][i], aa[j]);
-                    }
-                    // the six key-key Gram scalars sit in the first two float4 of the group's block
-                    const float4 g0 = *reinterpret_cast<const float4*>(gram + gi * 16);
-                    const float4 g1 = *reinterpret_cast<const float4*>(gram + gi * 16 + 4);
-                    const float gk[6] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y};
-                    const float4 b4 = *reinterpret_cast<const float4*>(s.b.f + tb);
-                    const float be[4] = {b4.x, b4.y, b4.z, b4.w};
-                    float vv[4], a[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) vv[j] = s.v.f[(tb + j) * D + g.idx];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) a[j] = reduce_split<SPLIT>(f2_hsum(aa[j]));
-                    float u[4], vo[4];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        float acc = a[j];
-#pragma unroll
-                        for (int i = 0; i < j; i++) acc = fmaf(u[i], gk[gram_kk(i, j)], acc);
-                        vo[j] = acc;
-                        u[j] = be[j] * (vv[j] - acc);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; j++) axpy2<G::NP>(S, kk[j], u[j]);
-                    if (g.s == 0) {
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            ovo[(tb + j) * D + g.idx] = vo[j];
-                            ou[(tb + j) * D + g.idx] = u[j];
-                        }
-                    }
-                }
-                fence_async_smem();      // the staged outputs are read by a bulk store
-            }
-            slot_barrier(slot, 2 * G::NT + 32);
-        }
-        store_cols(g, S, W, p.wE, p.E, p.M);
-    } else {
-        // ===================================================== read-out warp: y, one chunk behind
-        const G g(rtid);
-        const float* W = p.W + n * p.wN + h * p.wH;
-        f2 S[G::NP];
-        load_cols(g, S, W, p.wE, p.E, p.M);      // start-of-segment state, read before the chain warp writes it back
-        slot_barrier(slot, 2 * G::NT + 32);
-        for (int c = 0; c <= nchunks + 1; c++) {
-            if (c >= 1 && c - 1 < nchunks) {
-                const int cc = c - 1;
-                Stage s; s.bind(smem + (cc % SM::NS) * SM::kStage);
-                const float* gram = gram0 + (cc % SM::NB) * SM::kGram;
-                float* oy = out0 + (cc % SM::NB) * SM::kOut;
-                const float* ou = oy + 2 * TC * D;
-                const int nt = min(TC, p.L - cc * TC), ng = (nt + 3) >> 2;
-#pragma unroll 1
-                for (int gi = 0; gi < ng; gi++) {
-                    const int tb = 4 * gi;
-                    f2 kk[4][G::NP], qq[4][G::NP];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        lds_slice<G::NR>(qq[j], s.q.f + (tb + j) * D + g.off);
-                        lds_slice<G::NR>(kk[j], s.k.f + (tb + j) * D + g.off);
-                    }
-                    f2 bb[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-                    for (int i = 0; i < G::NP; i++) {
-#pragma unroll
-                        for (int j = 0; j < 4; j++) bb[j] = ffma2(S[i], qq[j][i], bb[j]);
-                    }
-                    float gs[16], u[4], b[4];
-                    load16(gs, gram + gi * 16);
-#pragma unroll
-                    for (int j = 0; j < 4; j++) u[j] = ou[(tb + j) * D + g.idx];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) b[j] = reduce_split<SPLIT>(f2_hsum(bb[j]));
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        float yy = b[j];
-#pragma unroll
-                        for (int i = 0; i <= j; i++) yy = fmaf(u[i], gs[gram_kq(i, j)], yy);
-                        if (g.s == 0) oy[(tb + j) * D + g.idx] = yy;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; j++) axpy2<G::NP>(S, kk[j], u[j]);
-                }
-                fence_async_smem();
-            }
-            slot_barrier(slot, 2 * G::NT + 32);
-        }
     }
 }
 
@@ -857,41 +466,31 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
             if (!es[1]) flush_rows<D, 32, T, TC>(o, p.gq, n, h, t0, nt, p.E, ptid);
             if (!es[2]) flush_rows<D, 32, T, TC>(o + TC * D, p.gk, n, h, t0, nt, p.E, ptid);
         };
-        FWP_PROF_BEGIN
         issue(0);
         if (PF == 2 && nchunks > 1) { issue(1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         landed(0);
         prepare(0);
         slot_barrier(slot, 2 * G::NT + 32);
-        FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i + PF < nchunks) issue(i + PF);    // lands while this iteration's other work runs
-            FWP_PROF(1)
             if (i >= 1 && i - 1 < nchunks) flush_col(i - 1);
             if (i >= 2) flush_row(i - 2);
-            FWP_PROF(2)
             if (i + 1 < nchunks) {
                 if (PF == 2 && i + 2 < nchunks) cp_async_wait<1>(); else cp_async_wait<0>();
                 landed(i + 1);
-                FWP_PROF(3)
                 prepare(i + 1);
             }
-            FWP_PROF(4)
             if (ptid == 0) bulk_wait_read_all();     // the flushed tiles may be rewritten after the barrier
             slot_barrier(slot, 2 * G::NT + 32);
-            FWP_PROF(5)
         }
         if (ptid == 0) bulk_wait_all();
-        FWP_PROF_END(0, ptid == 0 && slot == 0)
     } else if (role == 0) {
         // ===================================================== column role: blocked chain on G
         const G g(rtid);
         f2 Gc[G::NP];
 #pragma unroll
         for (int i = 0; i < G::NP; i++) Gc[i] = 0ull;
-        FWP_PROF_BEGIN
         slot_barrier(slot, 2 * G::NT + 32);
-        FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i < nchunks) {
                 const int jc = i;
@@ -975,11 +574,8 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                 }
                 if (kBulkStores) fence_async_smem();      // beta*r (= dv) is read by a bulk store
             }
-            FWP_PROF(1)
             slot_barrier(slot, 2 * G::NT + 32);
-            FWP_PROF(2)
         }
-        FWP_PROF_END(8, rtid == 0)
     } else {
         // ===================================================== row role: per step, one chunk behind
         const G g(rtid);
@@ -988,9 +584,7 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
         load_rows(g, Sr, W, p.wE, p.E, p.M);
 #pragma unroll
         for (int i = 0; i < G::NP; i++) Gr[i] = 0ull;
-        FWP_PROF_BEGIN
         slot_barrier(slot, 2 * G::NT + 32);
-        FWP_PROF(0)
         for (int i = 0; i <= nchunks + 1; i++) {
             if (i >= 1 && i - 1 < nchunks) {
                 const int jc = i - 1;
@@ -1022,12 +616,9 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
                 }
                 if (kBulkStores) fence_async_smem();
             }
-            FWP_PROF(1)
             slot_barrier(slot, 2 * G::NT + 32);
-            FWP_PROF(2)
         }
         store_rows(g, Sr, W, p.wE, p.E, p.M);
-        FWP_PROF_END(12, rtid == 0)
     }
 }
 

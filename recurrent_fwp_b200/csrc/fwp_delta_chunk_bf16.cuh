@@ -7,8 +7,8 @@
 // rows and b = beta:
 //
 //   Akk = strict_lower(K K^T), Aqk = lower(Q K^T)                          (bf16 products)
-//   [Cv | Ck] : c_t = rhs_t - sum_{i<t} Akk[t,i] b_i c_i  for rhs = [V | K] (fp32 substitution,
-//               one right-hand column per thread: 64 + 64 columns = 128 threads)
+//   [Cv | Ck] = T [V | K],  T = (I + Akk diag(b))^-1   (the unit triangular solve
+//               c_t = rhs_t - sum_{i<t} Akk[t,i] b_i c_i as an explicit inverse, see the forward kernel)
 //   w = Cv - Ck S0  (= v - v_old),  u = b w,  v_old = (V - Cv) + Ck S0
 //   y = Q S0 + Aqk u,   S1 = S0 + K^T u
 //
@@ -33,21 +33,8 @@ constexpr int D = 64;                   // E = M = 64
 constexpr int C = 16;                   // steps per chunk
 constexpr int NT = 128;                 // threads: four warps, and one thread per column of [V | K]
 constexpr int LDT = 72;                 // row stride of the 16 x 64 bf16 tiles (144 B: ldmatrix rows hit distinct banks)
-constexpr int LDA = 20;                 // row stride of Akk (fp32; 16-byte aligned rows)
 constexpr int LDQ = 24;                 // row stride of Aqk (bf16; 48 B)
-constexpr int LDC = 18;                 // row stride of the transposed fp32 tiles Cv^T, (V - Cv)^T  [m][t]
 constexpr int LDO = 68;                 // row stride of the fp32 output tiles [t][m]
-
-struct Smem {
-    __nv_bfloat16 k[2][C * LDT], v[2][C * LDT], q[2][C * LDT];    // input stages
-    __nv_bfloat16 ck[C * LDT];          // Ck, [t][e]
-    __nv_bfloat16 aqk[C * LDQ];         // Aqk, [t][i], zero above the diagonal
-    __nv_bfloat16 ys[C * LDT];          // y, [t][m]
-    float akk[C * LDA];                 // Akk, [t][i], zero on and above the diagonal
-    float cvT[D * LDC];                 // Cv^T, [m][t]
-    float vmcT[D * LDC];                // (V - Cv)^T, [m][t]
-    float b[2][C];
-};
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -96,218 +83,12 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat
 
 }  // namespace cb
 
-// ------------------------------------------------------------------ forward
-// One CTA per sequence, four warps.  Per chunk: (1) the two Gram products, one 16 x 8 tile per warp;
-// (2) the triangular solve, one column of [V | K] per thread; (3) the chain, warp w on rows
-// m in [16w, 16w+16) of S^T; (4) 16-byte stores of y.  Input tiles of the next
-// chunk are in flight (cp.async) meanwhile.
-__global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_kernel(const DeltaFwdParams p) {
-    using namespace cb;
-    using bf16 = __nv_bfloat16;
-    extern __shared__ __align__(16) unsigned char cb_smem[];
-    Smem& s = *reinterpret_cast<Smem*>(cb_smem);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    const int seq = blockIdx.x, n = seq / p.H, h = seq - n * p.H;
-    const bf16* qb = reinterpret_cast<const bf16*>(p.q.p) + n * p.q.sN + h * p.q.sH;
-    const bf16* kb = reinterpret_cast<const bf16*>(p.k.p) + n * p.k.sN + h * p.k.sH;
-    const bf16* vb = reinterpret_cast<const bf16*>(p.v.p) + n * p.v.sN + h * p.v.sH;
-    const bf16* bb = reinterpret_cast<const bf16*>(p.beta.p) + n * p.beta.sN + h * p.beta.sH;
-    bf16* yb = reinterpret_cast<bf16*>(p.out.p) + n * p.out.sN + h * p.out.sH;
-    float* vob = reinterpret_cast<float*>(p.v_old.p) + n * p.v_old.sN + h * p.v_old.sH;
-    float* uib = p.v_ins.p ? reinterpret_cast<float*>(p.v_ins.p) + n * p.v_ins.sN + h * p.v_ins.sH : nullptr;
-    float* W = p.W + n * p.wN + h * p.wH;
-    const int m0 = 16 * warp;
-
-    // S^T rows m0+g, m0+g+8; tile j holds the key indices 8j + 2 t4, +1
-    float S[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; j++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) S[j][i] = W[(long long)(8 * j + 2 * t4 + (i & 1)) * p.wE + m0 + g + 8 * (i >> 1)];
-
-    const int nchunks = (p.L + C - 1) / C;
-    {
-        const int nt = min(C, p.L);
-        load_tile(s.k[0], kb, p.k.sL, 0, nt, tid);
-        load_tile(s.v[0], vb, p.v.sL, 0, nt, tid);
-        load_tile(s.q[0], qb, p.q.sL, 0, nt, tid);
-        cp_async_commit();
-        if (tid < C) s.b[0][tid] = tid < nt ? __bfloat162float(bb[(long long)tid * p.beta.sL]) : 0.f;
-    }
-    for (int c = 0; c < nchunks; c++) {
-        const int cur = c & 1, t0 = c * C, nt = min(C, p.L - t0);
-        float bnext = 0.f;
-        if (c + 1 < nchunks) {
-            const int t1 = t0 + C, nt1 = min(C, p.L - t1);
-            load_tile(s.k[cur ^ 1], kb, p.k.sL, t1, nt1, tid);
-            load_tile(s.v[cur ^ 1], vb, p.v.sL, t1, nt1, tid);
-            load_tile(s.q[cur ^ 1], qb, p.q.sL, t1, nt1, tid);
-            cp_async_commit();
-            if (tid < nt1) bnext = __bfloat162float(bb[(long long)(t1 + tid) * p.beta.sL]);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const bf16* Ks = s.k[cur];
-        const bf16* Qs = s.q[cur];
-        const float* bs = s.b[cur];
-
-        {   // (1) Gram tiles: warps 0, 1 the two column tiles of K K^T, warps 2, 3 of Q K^T
-            const bf16* X = warp < 2 ? Ks : Qs;
-            const int j = warp & 1;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int kp = 0; kp < 2; kp++) {
-                unsigned bfr[4];
-                ldsm4(bfr, Ks + (8 * j + (lane & 7)) * LDT + 8 * (lane >> 3) + 32 * kp);
-#pragma unroll
-                for (int kk = 0; kk < 2; kk++) {
-                    unsigned a[4];
-                    lda_rowmajor(a, X + 16 * (2 * kp + kk), LDT, lane);
-                    mma_bf16(acc, a, bfr[2 * kk], bfr[2 * kk + 1]);
-                }
-            }
-            const int col = 8 * j + 2 * t4;
-            if (warp < 2) {
-                *reinterpret_cast<float2*>(s.akk + g * LDA + col) =
-                    make_float2(col < g ? acc[0] : 0.f, col + 1 < g ? acc[1] : 0.f);
-                *reinterpret_cast<float2*>(s.akk + (g + 8) * LDA + col) =
-                    make_float2(col < g + 8 ? acc[2] : 0.f, col + 1 < g + 8 ? acc[3] : 0.f);
-            } else {
-                *reinterpret_cast<unsigned*>(s.aqk + g * LDQ + col) =
-                    pack_bf16(col <= g ? acc[0] : 0.f, col + 1 <= g ? acc[1] : 0.f);
-                *reinterpret_cast<unsigned*>(s.aqk + (g + 8) * LDQ + col) =
-                    pack_bf16(col <= g + 8 ? acc[2] : 0.f, col + 1 <= g + 8 ? acc[3] : 0.f);
-            }
-        }
-        __syncthreads();
-
-        {   // (2) unit lower triangular solve, one right-hand column per thread
-            const int col = tid & 63;
-            const bool is_v = tid < 64;
-            const bf16* rhs = (is_v ? s.v[cur] : Ks) + col;
-            float x[C];
-#pragma unroll
-            for (int t = 0; t < C; t++) {
-                const float r = __bfloat162float(rhs[t * LDT]);
-                float a0 = r, a1 = 0.f;
-#pragma unroll
-                for (int i4 = 0; i4 * 4 < t; i4++) {
-                    const float4 a = *reinterpret_cast<const float4*>(s.akk + t * LDA + 4 * i4);
-                    a0 = fmaf(-a.x, x[4 * i4], a0);
-                    if (4 * i4 + 1 < t) a1 = fmaf(-a.y, x[4 * i4 + 1], a1);
-                    if (4 * i4 + 2 < t) a0 = fmaf(-a.z, x[4 * i4 + 2], a0);
-                    if (4 * i4 + 3 < t) a1 = fmaf(-a.w, x[4 * i4 + 3], a1);
-                }
-                const float cc = a0 + a1;
-                x[t] = bs[t] * cc;
-                if (is_v) {
-                    s.cvT[col * LDC + t] = cc;
-                    s.vmcT[col * LDC + t] = r - cc;
-                } else {
-                    s.ck[t * LDT + col] = __float2bfloat16_rn(cc);
-                }
-            }
-        }
-        __syncthreads();
-
-        {   // (3) chain
-            unsigned sa[4][4];
-#pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                sa[ks][0] = pack_bf16(S[2 * ks][0], S[2 * ks][1]);
-                sa[ks][1] = pack_bf16(S[2 * ks][2], S[2 * ks][3]);
-                sa[ks][2] = pack_bf16(S[2 * ks + 1][0], S[2 * ks + 1][1]);
-                sa[ks][3] = pack_bf16(S[2 * ks + 1][2], S[2 * ks + 1][3]);
-            }
-            float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            float Y[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                unsigned bc[4], bq[4];
-                ldb_nk(bc, s.ck + 16 * ks, LDT, lane);
-                ldb_nk(bq, Qs + 16 * ks, LDT, lane);
-                mma_bf16(P[0], sa[ks], bc[0], bc[1]);
-                mma_bf16(P[1], sa[ks], bc[2], bc[3]);
-                mma_bf16(Y[0], sa[ks], bq[0], bq[1]);
-                mma_bf16(Y[1], sa[ks], bq[2], bq[3]);
-            }
-            float u[2][4];
-#pragma unroll
-            for (int j = 0; j < 2; j++)
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++) {
-                    const int m = m0 + g + 8 * hr, t = 8 * j + 2 * t4;
-                    const float2 cv = *reinterpret_cast<const float2*>(s.cvT + m * LDC + t);
-                    const float2 vm = *reinterpret_cast<const float2*>(s.vmcT + m * LDC + t);
-                    const float w0 = cv.x - P[j][2 * hr], w1 = cv.y - P[j][2 * hr + 1];
-                    u[j][2 * hr] = bs[t] * w0;
-                    u[j][2 * hr + 1] = bs[t + 1] * w1;
-                    // fp32 rows go straight to global memory: the eight lanes of a quad column fill one 32-byte sector
-                    if (t < nt) {
-                        vob[(long long)(t0 + t) * p.v_old.sL + m] = vm.x + P[j][2 * hr];
-                        if (uib) uib[(long long)(t0 + t) * p.v_ins.sL + m] = u[j][2 * hr];
-                    }
-                    if (t + 1 < nt) {
-                        vob[(long long)(t0 + t + 1) * p.v_old.sL + m] = vm.y + P[j][2 * hr + 1];
-                        if (uib) uib[(long long)(t0 + t + 1) * p.v_ins.sL + m] = u[j][2 * hr + 1];
-                    }
-                }
-            unsigned ua[4] = {pack_bf16(u[0][0], u[0][1]), pack_bf16(u[0][2], u[0][3]),
-                              pack_bf16(u[1][0], u[1][1]), pack_bf16(u[1][2], u[1][3])};
-            {
-                unsigned ba[4];
-                ldb_nk(ba, s.aqk, LDQ, lane);
-                mma_bf16(Y[0], ua, ba[0], ba[1]);
-                mma_bf16(Y[1], ua, ba[2], ba[3]);
-            }
-            // the state takes u as hi + lo (two bf16 parts, 16 mantissa bits): the saved v_old lets the
-            // backward rebuild u in fp32, and the rewind S0 = S1 - K^T u must undo this update
-            unsigned ul[4];
-#pragma unroll
-            for (int r = 0; r < 4; r++) {
-                const float x0 = u[r >> 1][2 * (r & 1)], x1 = u[r >> 1][2 * (r & 1) + 1];
-                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&ua[r]);
-                ul[r] = pack_bf16(x0 - __low2float(hi), x1 - __high2float(hi));
-            }
-#pragma unroll
-            for (int jp = 0; jp < 4; jp++) {
-                unsigned bk[4];
-                ldb_kn(bk, Ks + 16 * jp, LDT, lane);
-                mma_bf16(S[2 * jp], ua, bk[0], bk[1]);
-                mma_bf16(S[2 * jp + 1], ua, bk[2], bk[3]);
-                mma_bf16(S[2 * jp], ul, bk[0], bk[1]);
-                mma_bf16(S[2 * jp + 1], ul, bk[2], bk[3]);
-            }
-#pragma unroll
-            for (int j = 0; j < 2; j++)
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    s.ys[(8 * j + 2 * t4 + (i & 1)) * LDT + m0 + g + 8 * (i >> 1)] = __float2bfloat16_rn(Y[j][i]);
-        }
-        __syncthreads();
-
-        {   // (4) stores: 16-byte row pieces
-            const int row = tid >> 3, part = (tid & 7) * 8;
-            if (row < nt)
-                *reinterpret_cast<uint4*>(yb + (long long)(t0 + row) * p.out.sL + part) =
-                    *reinterpret_cast<const uint4*>(s.ys + row * LDT + part);
-            if (tid < C && c + 1 < nchunks) s.b[cur ^ 1][tid] = bnext;
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < 8; j++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) W[(long long)(8 * j + 2 * t4 + (i & 1)) * p.wE + m0 + g + 8 * (i >> 1)] = S[j][i];
-}
-
 // ------------------------------------------------------------------ backward
 // Chunks are walked from the last to the first.  With S1, G1 = dL/dS1 at the end of the chunk, the saved
 // v_old (w = V - v_old, U = b w) and gY = dL/dy:
 //   S0 = S1 - K^T U
 //   lambda_t = rhs_t - sum_{j>t} Akk[j,t] b_j lambda_j  for rhs = Aqk^T gY + K G1, solved as
-//       lambda = Lt + Kt G1 with [Lt | Kt] the solutions for rhs = [Aqk^T gY | K] (one column per thread)
+//       lambda = Lt + Kt G1 with [Lt | Kt] the solutions for rhs = [Aqk^T gY | K]
 //   dv = b lambda,  dbeta = rowsum(lambda w),  G0 = G1 + Q^T gY - K^T (b lambda)
 //   dQ = gY S0^T + B K,  B = lower(gY U^T)
 //   dK = U G1^T - (b lambda) S0^T + B^T Q - (strict_lower(Z) + strict_lower(Z)^T) K,  Z = (b lambda) U^T
@@ -317,22 +98,6 @@ __global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_kernel(const D
 // (gY S0^T, U G1^T, (b lambda) S0^T), each warp producing its own 16 columns of dQ and dK.  The one product
 // that contracts over e (Kt G1) reads a bf16 copy of G that the warps leave in shared memory once per chunk.
 namespace cb {
-
-struct SmemB {
-    __nv_bfloat16 k[2][C * LDT], q[2][C * LDT], v[2][C * LDT], gy[2][C * LDT];   // input stages
-    float vo[2][C * LDO];               // v_old stages, [t][m]; the current one becomes w = v - v_old in place
-    __nv_bfloat16 uh[C * LDT], ul[C * LDT];   // U = b w as two bf16 parts, [t][m]
-    __nv_bfloat16 bl[C * LDT];          // b lambda = dv, [t][m]
-    __nv_bfloat16 kt[C * LDT];          // Kt, [t][e]
-    __nv_bfloat16 gs[D * LDT];          // G1 rounded to bf16, [e][m]
-    __nv_bfloat16 aqk[C * LDQ];         // Aqk, [t][i], zero above the diagonal
-    __nv_bfloat16 bm[C * LDQ];          // B = lower(gY U^T), [t][i]
-    alignas(16) __nv_bfloat16 dqdk[2 * C * LDT];   // dQ, dK, [t][e]; before the chain the same bytes hold Aqk^T gY, [t][m] fp32
-    float akkT[C * LDA];                // Akk^T, [t][j] = k_j . k_t for j > t, else zero
-    float ltT[D * LDC];                 // Lt^T, [m][t]
-    float dbp[4][C];                    // per-warp partial sums of dbeta
-    float b[2][C];
-};
 
 // Left-operand fragments A[r][k] = X[k][r] from a row-major X (rows k, r contiguous), 16 (k) x 16 (r) block
 __device__ __forceinline__ void lda_trans(unsigned (&a)[4], const __nv_bfloat16* tile, int ld, int lane) {
@@ -374,328 +139,9 @@ __device__ __forceinline__ void load_tile_f32(float* tile, const float* base, lo
 
 }  // namespace cb
 
-__global__ void __launch_bounds__(cb::NT, 3) delta_bwd_chunk_bf16_kernel(const DeltaBwdParams p) {
-    using namespace cb;
-    using bf16 = __nv_bfloat16;
-    extern __shared__ __align__(16) unsigned char cb_smem[];
-    SmemB& s = *reinterpret_cast<SmemB*>(cb_smem);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    const int seq = blockIdx.x, n = seq / p.H, h = seq - n * p.H;
-    const bf16* qb = reinterpret_cast<const bf16*>(p.q.p) + n * p.q.sN + h * p.q.sH;
-    const bf16* kb = reinterpret_cast<const bf16*>(p.k.p) + n * p.k.sN + h * p.k.sH;
-    const bf16* vb = reinterpret_cast<const bf16*>(p.v.p) + n * p.v.sN + h * p.v.sH;
-    const bf16* bb = reinterpret_cast<const bf16*>(p.beta.p) + n * p.beta.sN + h * p.beta.sH;
-    const bf16* gyb = reinterpret_cast<const bf16*>(p.gy.p) + n * p.gy.sN + h * p.gy.sH;
-    const float* vob = reinterpret_cast<const float*>(p.v_old.p) + n * p.v_old.sN + h * p.v_old.sH;
-    bf16* gqb = reinterpret_cast<bf16*>(p.gq.p) + n * p.gq.sN + h * p.gq.sH;
-    bf16* gkb = reinterpret_cast<bf16*>(p.gk.p) + n * p.gk.sN + h * p.gk.sH;
-    bf16* gvb = reinterpret_cast<bf16*>(p.gv.p) + n * p.gv.sN + h * p.gv.sH;
-    bf16* gbb = reinterpret_cast<bf16*>(p.gb.p) + n * p.gb.sN + h * p.gb.sH;
-    float* W = p.W + n * p.wN + h * p.wH;
-    const int e0 = 16 * warp;           // rows of S and G this warp owns; also its rows m of lambda^T
-
-    // S, G rows e0+g, e0+g+8; tile j holds the value indices 8j + 2 t4, +1
-    float S[8][4], G[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; j++)
-#pragma unroll
-        for (int hr = 0; hr < 2; hr++) {
-            const float2 x = *reinterpret_cast<const float2*>(W + (long long)(e0 + g + 8 * hr) * p.wE + 8 * j + 2 * t4);
-            S[j][2 * hr] = x.x; S[j][2 * hr + 1] = x.y;
-            G[j][2 * hr] = 0.f; G[j][2 * hr + 1] = 0.f;
-        }
-
-    const int nchunks = (p.L + C - 1) / C;
-    auto issue = [&](int c, int st) {
-        const int t0 = c * C, nt = min(C, p.L - t0);
-        load_tile(s.k[st], kb, p.k.sL, t0, nt, tid);
-        load_tile(s.q[st], qb, p.q.sL, t0, nt, tid);
-        load_tile(s.v[st], vb, p.v.sL, t0, nt, tid);
-        load_tile(s.gy[st], gyb, p.gy.sL, t0, nt, tid);
-        load_tile_f32(s.vo[st], vob, p.v_old.sL, t0, nt, tid);
-        cp_async_commit();
-    };
-    issue(nchunks - 1, 0);
-    {
-        const int t0 = (nchunks - 1) * C;
-        if (tid < C) s.b[0][tid] = t0 + tid < p.L ? __bfloat162float(bb[(long long)(t0 + tid) * p.beta.sL]) : 0.f;
-    }
-    for (int it = 0; it < nchunks; it++) {
-        const int c = nchunks - 1 - it, cur = it & 1, t0 = c * C, nt = min(C, p.L - t0);
-        float bnext = 0.f;
-        if (c > 0) {
-            issue(c - 1, cur ^ 1);
-            if (tid < C) bnext = __bfloat162float(bb[(long long)(t0 - C + tid) * p.beta.sL]);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const bf16* Ks = s.k[cur];
-        const bf16* Qs = s.q[cur];
-        const bf16* Ys = s.gy[cur];
-        float* Ws = s.vo[cur];
-        const float* bs = s.b[cur];
-        float* r1 = reinterpret_cast<float*>(s.dqdk);      // C x LDO floats fit in the 2 x C x LDT bf16
-        bf16* dqs = s.dqdk;
-        bf16* dks = s.dqdk + C * LDT;
-
-        {   // (1) Gram tiles; w and U; bf16 copy of G1
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            const int j = warp & 1, col = 8 * j + 2 * t4;
-            gram_tile(acc, warp < 2 ? Ks : Qs, Ks, j, lane);
-            if (warp < 2) {
-                s.akkT[col * LDA + g] = col < g ? acc[0] : 0.f;
-                s.akkT[(col + 1) * LDA + g] = col + 1 < g ? acc[1] : 0.f;
-                s.akkT[col * LDA + g + 8] = col < g + 8 ? acc[2] : 0.f;
-                s.akkT[(col + 1) * LDA + g + 8] = col + 1 < g + 8 ? acc[3] : 0.f;
-            } else {
-                *reinterpret_cast<unsigned*>(s.aqk + g * LDQ + col) =
-                    pack_bf16(col <= g ? acc[0] : 0.f, col + 1 <= g ? acc[1] : 0.f);
-                *reinterpret_cast<unsigned*>(s.aqk + (g + 8) * LDQ + col) =
-                    pack_bf16(col <= g + 8 ? acc[2] : 0.f, col + 1 <= g + 8 ? acc[3] : 0.f);
-            }
-            const int row = tid >> 3, part = (tid & 7) * 8;
-            const uint4 vraw = *reinterpret_cast<const uint4*>(s.v[cur] + row * LDT + part);
-            const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vraw);
-            float* wp = Ws + row * LDO + part;
-            const float4 o0 = *reinterpret_cast<const float4*>(wp), o1 = *reinterpret_cast<const float4*>(wp + 4);
-            const float vo8[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
-            float w8[8];
-            unsigned hi[4], lo[4];
-            const float br = bs[row];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                w8[2 * i] = __low2float(v2[i]) - vo8[2 * i];
-                w8[2 * i + 1] = __high2float(v2[i]) - vo8[2 * i + 1];
-                const float u0 = br * w8[2 * i], u1 = br * w8[2 * i + 1];
-                hi[i] = pack_bf16(u0, u1);
-                const __nv_bfloat162 hh = *reinterpret_cast<const __nv_bfloat162*>(&hi[i]);
-                lo[i] = pack_bf16(u0 - __low2float(hh), u1 - __high2float(hh));
-            }
-            *reinterpret_cast<float4*>(wp) = make_float4(w8[0], w8[1], w8[2], w8[3]);
-            *reinterpret_cast<float4*>(wp + 4) = make_float4(w8[4], w8[5], w8[6], w8[7]);
-            *reinterpret_cast<uint4*>(s.uh + row * LDT + part) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4*>(s.ul + row * LDT + part) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-#pragma unroll
-            for (int jj = 0; jj < 8; jj++) {
-                *reinterpret_cast<unsigned*>(s.gs + (e0 + g) * LDT + 8 * jj + 2 * t4) = pack_bf16(G[jj][0], G[jj][1]);
-                *reinterpret_cast<unsigned*>(s.gs + (e0 + g + 8) * LDT + 8 * jj + 2 * t4) = pack_bf16(G[jj][2], G[jj][3]);
-            }
-        }
-        __syncthreads();
-
-        {   // (2) Aqk^T gY, the warp's 16 columns m; B = lower(gY U^T), one column tile on each of warps 0 and 1
-            unsigned a[4], bg[4];
-            lda_trans(a, s.aqk, LDQ, lane);
-            ldb_kn(bg, Ys + e0, LDT, lane);
-            float r[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            mma_bf16(r[0], a, bg[0], bg[1]);
-            mma_bf16(r[1], a, bg[2], bg[3]);
-#pragma unroll
-            for (int jj = 0; jj < 2; jj++) {
-                *reinterpret_cast<float2*>(r1 + g * LDO + e0 + 8 * jj + 2 * t4) = make_float2(r[jj][0], r[jj][1]);
-                *reinterpret_cast<float2*>(r1 + (g + 8) * LDO + e0 + 8 * jj + 2 * t4) = make_float2(r[jj][2], r[jj][3]);
-            }
-            if (warp < 2) {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                const int col = 8 * warp + 2 * t4;
-                gram_tile(acc, Ys, s.uh, warp, lane);
-                *reinterpret_cast<unsigned*>(s.bm + g * LDQ + col) =
-                    pack_bf16(col <= g ? acc[0] : 0.f, col + 1 <= g ? acc[1] : 0.f);
-                *reinterpret_cast<unsigned*>(s.bm + (g + 8) * LDQ + col) =
-                    pack_bf16(col <= g + 8 ? acc[2] : 0.f, col + 1 <= g + 8 ? acc[3] : 0.f);
-            }
-        }
-        __syncthreads();
-
-        {   // (3) backward substitution, one right-hand column per thread
-            const int col = tid & 63;
-            const bool is_l = tid < 64;
-            float y[C];
-#pragma unroll
-            for (int t = C - 1; t >= 0; t--) {
-                float a0 = is_l ? r1[t * LDO + col] : __bfloat162float(Ks[t * LDT + col]);
-                float a1 = 0.f;
-#pragma unroll
-                for (int j4 = 3; j4 * 4 + 3 > t; j4--) {
-                    const float4 a = *reinterpret_cast<const float4*>(s.akkT + t * LDA + 4 * j4);
-                    if (4 * j4 + 3 > t) a1 = fmaf(-a.w, y[4 * j4 + 3], a1);
-                    if (4 * j4 + 2 > t) a0 = fmaf(-a.z, y[4 * j4 + 2], a0);
-                    if (4 * j4 + 1 > t) a1 = fmaf(-a.y, y[4 * j4 + 1], a1);
-                    if (4 * j4 > t) a0 = fmaf(-a.x, y[4 * j4], a0);
-                }
-                const float cc = a0 + a1;
-                y[t] = bs[t] * cc;
-                if (is_l) s.ltT[col * LDC + t] = cc;
-                else s.kt[t * LDT + col] = __float2bfloat16_rn(cc);
-            }
-        }
-        __syncthreads();
-
-        {   // (4a) lambda^T rows m in [e0, e0+16): Lt^T + G1^T Kt^T; dv = b lambda; partial sums of dbeta
-            float lm[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                unsigned a[4], bk[4];
-                lda_trans(a, s.gs + 16 * ks * LDT + e0, LDT, lane);
-                ldb_nk(bk, s.kt + 16 * ks, LDT, lane);
-                mma_bf16(lm[0], a, bk[0], bk[1]);
-                mma_bf16(lm[1], a, bk[2], bk[3]);
-            }
-            float db[2][2];
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                db[j][0] = 0.f; db[j][1] = 0.f;
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++) {
-                    const int m = e0 + g + 8 * hr, t = 8 * j + 2 * t4;
-                    const float2 lt = *reinterpret_cast<const float2*>(s.ltT + m * LDC + t);
-                    const float l0 = lt.x + lm[j][2 * hr], l1 = lt.y + lm[j][2 * hr + 1];
-                    db[j][0] = fmaf(l0, Ws[t * LDO + m], db[j][0]);
-                    db[j][1] = fmaf(l1, Ws[(t + 1) * LDO + m], db[j][1]);
-                    s.bl[t * LDT + m] = __float2bfloat16_rn(bs[t] * l0);
-                    s.bl[(t + 1) * LDT + m] = __float2bfloat16_rn(bs[t + 1] * l1);
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 2; j++)
-#pragma unroll
-                for (int par = 0; par < 2; par++) {
-                    float x = db[j][par];
-                    x += __shfl_xor_sync(0xffffffffu, x, 4);
-                    x += __shfl_xor_sync(0xffffffffu, x, 8);
-                    x += __shfl_xor_sync(0xffffffffu, x, 16);
-                    if (g == 0) s.dbp[warp][8 * j + 2 * t4 + par] = x;
-                }
-        }
-        __syncthreads();
-
-        {   // (4b) rewind S, the warp's 16 columns of dQ and dK, then G
-            unsigned ka[4], kan[4];
-            lda_trans(ka, Ks + e0, LDT, lane);          // K^T rows e0.., contraction over the 16 steps
-            neg4(kan, ka);
-#pragma unroll
-            for (int jp = 0; jp < 4; jp++) {
-                unsigned bh[4], bl2[4];
-                ldb_kn(bh, s.uh + 16 * jp, LDT, lane);
-                ldb_kn(bl2, s.ul + 16 * jp, LDT, lane);
-                mma_bf16(S[2 * jp], kan, bh[0], bh[1]);
-                mma_bf16(S[2 * jp + 1], kan, bh[2], bh[3]);
-                mma_bf16(S[2 * jp], kan, bl2[0], bl2[1]);
-                mma_bf16(S[2 * jp + 1], kan, bl2[2], bl2[3]);
-            }
-            float dq[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            float dk[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            float Z[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            float ZT[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                // right operands from the accumulators, each as two bf16 parts: contraction over m in
-                // [16ks, 16ks+16), columns e0+g (first index 0) and e0+8+g (first index 1)
-                unsigned sh[2][2], sl[2][2], gh[2][2], gl[2][2];
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++)
-#pragma unroll
-                    for (int kk = 0; kk < 2; kk++) {
-                        split_bf16(S[2 * ks + kk][2 * hr], S[2 * ks + kk][2 * hr + 1], sh[hr][kk], sl[hr][kk]);
-                        split_bf16(G[2 * ks + kk][2 * hr], G[2 * ks + kk][2 * hr + 1], gh[hr][kk], gl[hr][kk]);
-                    }
-                unsigned ya[4], ua[4], ula[4], la[4], lan[4], bu[4], bb2[4];
-                lda_rowmajor(ya, Ys + 16 * ks, LDT, lane);
-                lda_rowmajor(ua, s.uh + 16 * ks, LDT, lane);
-                lda_rowmajor(ula, s.ul + 16 * ks, LDT, lane);
-                lda_rowmajor(la, s.bl + 16 * ks, LDT, lane);
-                neg4(lan, la);
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++) {
-                    mma_bf16(dq[hr], ya, sh[hr][0], sh[hr][1]);
-                    mma_bf16(dq[hr], ya, sl[hr][0], sl[hr][1]);
-                    mma_bf16(dk[hr], ua, gh[hr][0], gh[hr][1]);
-                    mma_bf16(dk[hr], ua, gl[hr][0], gl[hr][1]);
-                    mma_bf16(dk[hr], ula, gh[hr][0], gh[hr][1]);
-                    mma_bf16(dk[hr], lan, sh[hr][0], sh[hr][1]);
-                    mma_bf16(dk[hr], lan, sl[hr][0], sl[hr][1]);
-                }
-                ldb_nk(bu, s.uh + 16 * ks, LDT, lane);
-                ldb_nk(bb2, s.bl + 16 * ks, LDT, lane);
-                mma_bf16(Z[0], la, bu[0], bu[1]);
-                mma_bf16(Z[1], la, bu[2], bu[3]);
-                mma_bf16(ZT[0], ua, bb2[0], bb2[1]);
-                mma_bf16(ZT[1], ua, bb2[2], bb2[3]);
-            }
-            unsigned bK[4], bQ[4], ba[4], bta[4], za[4], qa[4];
-            ldb_kn(bK, Ks + e0, LDT, lane);
-            ldb_kn(bQ, Qs + e0, LDT, lane);
-            lda_rowmajor(ba, s.bm, LDQ, lane);
-            lda_trans(bta, s.bm, LDQ, lane);
-            mma_bf16(dq[0], ba, bK[0], bK[1]);
-            mma_bf16(dq[1], ba, bK[2], bK[3]);
-            mma_bf16(dk[0], bta, bQ[0], bQ[1]);
-            mma_bf16(dk[1], bta, bQ[2], bQ[3]);
-            {
-                float z[2][4];
-#pragma unroll
-                for (int j = 0; j < 2; j++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int r = g + 8 * (i >> 1), cc = 8 * j + 2 * t4 + (i & 1);
-                        z[j][i] = -((cc < r ? Z[j][i] : 0.f) + (cc > r ? ZT[j][i] : 0.f));
-                    }
-                za[0] = pack_bf16(z[0][0], z[0][1]); za[1] = pack_bf16(z[0][2], z[0][3]);
-                za[2] = pack_bf16(z[1][0], z[1][1]); za[3] = pack_bf16(z[1][2], z[1][3]);
-            }
-            mma_bf16(dk[0], za, bK[0], bK[1]);
-            mma_bf16(dk[1], za, bK[2], bK[3]);
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int col = e0 + 8 * j + 2 * t4;
-                *reinterpret_cast<unsigned*>(dqs + g * LDT + col) = pack_bf16(dq[j][0], dq[j][1]);
-                *reinterpret_cast<unsigned*>(dqs + (g + 8) * LDT + col) = pack_bf16(dq[j][2], dq[j][3]);
-                *reinterpret_cast<unsigned*>(dks + g * LDT + col) = pack_bf16(dk[j][0], dk[j][1]);
-                *reinterpret_cast<unsigned*>(dks + (g + 8) * LDT + col) = pack_bf16(dk[j][2], dk[j][3]);
-            }
-            // G0 = G1 + Q^T gY - K^T (b lambda)
-            lda_trans(qa, Qs + e0, LDT, lane);
-#pragma unroll
-            for (int jp = 0; jp < 4; jp++) {
-                unsigned bg[4], bd[4];
-                ldb_kn(bg, Ys + 16 * jp, LDT, lane);
-                ldb_kn(bd, s.bl + 16 * jp, LDT, lane);
-                mma_bf16(G[2 * jp], qa, bg[0], bg[1]);
-                mma_bf16(G[2 * jp + 1], qa, bg[2], bg[3]);
-                mma_bf16(G[2 * jp], kan, bd[0], bd[1]);
-                mma_bf16(G[2 * jp + 1], kan, bd[2], bd[3]);
-            }
-        }
-        __syncthreads();
-
-        {   // (5) stores: 16-byte row pieces of dQ, dK, dv; dbeta
-            const int row = tid >> 3, part = (tid & 7) * 8;
-            if (row < nt) {
-                *reinterpret_cast<uint4*>(gqb + (long long)(t0 + row) * p.gq.sL + part) =
-                    *reinterpret_cast<const uint4*>(dqs + row * LDT + part);
-                *reinterpret_cast<uint4*>(gkb + (long long)(t0 + row) * p.gk.sL + part) =
-                    *reinterpret_cast<const uint4*>(dks + row * LDT + part);
-                *reinterpret_cast<uint4*>(gvb + (long long)(t0 + row) * p.gv.sL + part) =
-                    *reinterpret_cast<const uint4*>(s.bl + row * LDT + part);
-            }
-            if (tid < nt)
-                gbb[(long long)(t0 + tid) * p.gb.sL] =
-                    __float2bfloat16_rn(s.dbp[0][tid] + s.dbp[1][tid] + s.dbp[2][tid] + s.dbp[3][tid]);
-            if (tid < C && c > 0) s.b[cur ^ 1][tid] = bnext;
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < 8; j++)
-#pragma unroll
-        for (int hr = 0; hr < 2; hr++)
-            *reinterpret_cast<float2*>(W + (long long)(e0 + g + 8 * hr) * p.wE + 8 * j + 2 * t4) =
-                make_float2(S[j][2 * hr], S[j][2 * hr + 1]);
-}
-
-// ------------------------------------------------------------------ forward, register-resident solve
-// Same algebra as delta_fwd_chunk_bf16_kernel with the triangular solve replaced by the explicit inverse
+// ------------------------------------------------------------------ forward
+// One CTA per sequence, four warps; the input tiles of the next chunk are in flight (cp.async) while a chunk
+// is computed.  The triangular solve is taken as the explicit inverse
 // T = (I + N)^-1, N = Akk diag(b) strictly lower and therefore nilpotent:
 //   T = (I - N)(I + N^2)(I + N^4)(I + N^8)
 // Every warp builds Akk, Aqk and T for itself in accumulator fragments (six 16 x 16 x 16 products whose right
@@ -744,8 +190,7 @@ __device__ __forceinline__ void mm(float (&out)[2][4], const unsigned (&a)[4], c
 
 }  // namespace cb
 
-template <int MINB>
-__global__ void __launch_bounds__(cb::NT, MINB) delta_fwd_chunk_bf16_inv_kernel(const DeltaFwdParams p) {
+__global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_inv_kernel(const DeltaFwdParams p) {
     using namespace cb;
     using bf16 = __nv_bfloat16;
     extern __shared__ __align__(16) unsigned char cb_smem[];
@@ -973,11 +418,11 @@ __global__ void __launch_bounds__(cb::NT, MINB) delta_fwd_chunk_bf16_inv_kernel(
 }
 
 
-// ------------------------------------------------------------------ backward, register-resident solve
-// Same algebra as delta_bwd_chunk_bf16_kernel.  The backward substitution is the transposed system: with
+// ------------------------------------------------------------------ backward kernel
+// The backward substitution is the transposed system: with
 // T' = (I + diag(b) Akk)^-1 (built per warp in registers like T of the forward), [Lt | Kt] = T'^T [Aqk^T gY | K],
 // so Lt^T = gY^T (Aqk T') is one product of the chain warp and Kt = T'^T K is exchanged through shared memory,
-// 16 columns per warp.  The Gram tiles, Aqk^T gY and Lt never touch shared memory, and two barriers per chunk go.
+// 16 columns per warp.  The Gram tiles, Aqk^T gY and Lt never touch shared memory.
 namespace cb {
 struct SmemB2 {
     __nv_bfloat16 k[2][C * LDT], q[2][C * LDT], v[2][C * LDT], gy[2][C * LDT];   // input stages
@@ -993,8 +438,7 @@ struct SmemB2 {
 };
 }  // namespace cb
 
-template <int MINB>
-__global__ void __launch_bounds__(cb::NT, MINB) delta_bwd_chunk_bf16_inv_kernel(const DeltaBwdParams p) {
+__global__ void __launch_bounds__(cb::NT, 3) delta_bwd_chunk_bf16_inv_kernel(const DeltaBwdParams p) {
     using namespace cb;
     using bf16 = __nv_bfloat16;
     extern __shared__ __align__(16) unsigned char cb_smem[];

@@ -28,6 +28,10 @@ static inline size_t gen_bwd_floats(int E, int M) {
     return 2 * (size_t)E * (M + 1) + 3 * E + 6 * M + 4 + 2 * (size_t)gen_max3(kGenThreads, E, M);
 }
 
+static inline size_t gen_sum_bwd_floats(int E, int M) {
+    return (size_t)E * (M + 1) + 2 * E + 2 * M + 2 * (size_t)gen_max3(kGenThreads, E, M);
+}
+
 template <typename T>
 __device__ __forceinline__ float gen_ld(const Row4& r, int n, int h, int t, int c) {
     return to_f32(reinterpret_cast<const T*>(r.p)[n * r.sN + h * r.sH + (long long)t * r.sL + c]);
@@ -202,6 +206,88 @@ __global__ void __launch_bounds__(kGenThreads) delta_bwd_generic_kernel(const De
         __syncthreads();
     }
     for (int i = tid; i < E * M; i += NT) W[(long long)(i / M) * p.wE + (i % M)] = S[(i / M) * LD + (i % M)];
+}
+
+// Sum-rule backward for the same shapes (algorithmic/fast_transformers/causal_product_cuda.cu:369-445 takes any
+// E, M): a forward sweep with S accumulated from zero gives dq_t = S_t gy_t, a backward sweep with
+// G = sum_{s>=t} q_s (x) gy_s gives dk_t = G_t v_t and dv_t = G_t^T k_t.  One E x M matrix in shared memory serves
+// both sweeps.
+template <typename T>
+__global__ void __launch_bounds__(kGenThreads) sum_bwd_generic_kernel(const SumBwdParams p) {
+    const int tid = threadIdx.x, NT = kGenThreads;
+    const int n = blockIdx.x / p.H, h = blockIdx.x - n * p.H;
+    const int E = p.E, M = p.M, LD = M + 1;
+    extern __shared__ __align__(16) float sm[];
+    float* A = sm;                        // [E][LD]  S in the first sweep, G in the second
+    float* ks = A + (size_t)E * LD;       // [E]
+    float* qs = ks + E;                   // [E]
+    float* vs = qs + E;                   // [M]
+    float* gys = vs + M;                  // [M]
+    const int PS = gen_max3(NT, E, M);
+    float* part = gys + M;                // [PS]
+    float* part2 = part + PS;             // [PS]
+    const int MT = gen_pow2_at_least(M), EG = NT / MT, m0 = tid % MT, eg = tid / MT;   // column mapping
+    const int ET = gen_pow2_at_least(E), MG = NT / ET, e0 = tid % ET, mg = tid / ET;   // row mapping
+    for (int sweep = 0; sweep < 2; sweep++) {
+        for (int i = tid; i < E * LD; i += NT) A[i] = 0.f;
+        __syncthreads();
+        for (int i = 0; i < p.L; i++) {
+            const int t = sweep ? p.L - 1 - i : i;
+            for (int e = tid; e < E; e += NT) { ks[e] = gen_ld<T>(p.k, n, h, t, e); qs[e] = gen_ld<T>(p.q, n, h, t, e); }
+            for (int m = tid; m < M; m += NT) { vs[m] = gen_ld<T>(p.v, n, h, t, m); gys[m] = gen_ld<T>(p.gy, n, h, t, m); }
+            __syncthreads();
+            if (sweep == 0) {
+                // S += k (x) v ; dq = S gy  (row mapping)
+                for (int e = e0; e < E; e += ET) {
+                    float a1 = 0.f;
+                    const float ke = ks[e];
+                    for (int m = mg; m < M; m += MG) {
+                        const float s = fmaf(ke, vs[m], A[e * LD + m]);
+                        A[e * LD + m] = s;
+                        a1 = fmaf(s, gys[m], a1);
+                    }
+                    part[mg * E + e] = a1;
+                }
+                __syncthreads();
+                for (int e = tid; e < E; e += NT) {
+                    float dq = 0.f;
+                    for (int g2 = 0; g2 < MG; g2++) dq += part[g2 * E + e];
+                    put<T>(p.gq, n, h, t, e, dq);
+                }
+            } else {
+                // G += q (x) gy ; dk = G v  (row mapping)
+                for (int e = e0; e < E; e += ET) {
+                    float a1 = 0.f;
+                    const float qe = qs[e];
+                    for (int m = mg; m < M; m += MG) {
+                        const float g2 = fmaf(qe, gys[m], A[e * LD + m]);
+                        A[e * LD + m] = g2;
+                        a1 = fmaf(g2, vs[m], a1);
+                    }
+                    part[mg * E + e] = a1;
+                }
+                __syncthreads();
+                for (int e = tid; e < E; e += NT) {
+                    float dk = 0.f;
+                    for (int g2 = 0; g2 < MG; g2++) dk += part[g2 * E + e];
+                    put<T>(p.gk, n, h, t, e, dk);
+                }
+                // dv = G^T k  (column mapping)
+                for (int m = m0; m < M; m += MT) {
+                    float acc = 0.f;
+                    for (int e = eg; e < E; e += EG) acc = fmaf(A[e * LD + m], ks[e], acc);
+                    part2[eg * M + m] = acc;
+                }
+                __syncthreads();
+                for (int m = tid; m < M; m += NT) {
+                    float dv = 0.f;
+                    for (int g2 = 0; g2 < EG; g2++) dv += part2[g2 * M + m];
+                    put<T>(p.gv, n, h, t, m, dv);
+                }
+            }
+            __syncthreads();
+        }
+    }
 }
 
 }  // namespace fwp

@@ -10,7 +10,6 @@ struct DeltaFwdParams {
     float* W; long long wN, wH, wE;
     int H, L, E, M;
     int NH;     // number of sequences (N*H)
-    float* ws = nullptr;    // caller-provided workspace of the chunkwise plan (null: recurrent plans only)
 };
 
 struct DeltaBwdParams {
@@ -19,7 +18,6 @@ struct DeltaBwdParams {
     int H, L, E, M;
     int NH;     // number of sequences (N*H)
     int bulk = 1;           // stage contiguous chunks with bulk copies where the kernel supports it
-    float* ws = nullptr;    // caller-provided workspace of the chunkwise plan (null: recurrent plans only)
 };
 
 template <typename K>
@@ -31,19 +29,16 @@ static int set_smem(K kernel, size_t bytes) {
     return FWP_OK;
 }
 
+// `name` (a string literal) is what fwp_last_kernel() reports for the calling thread afterwards.
 template <typename K, typename P>
-static int launch(K kern, const P& p, int grid, int threads, size_t bytes, cudaStream_t st) {
+static int launch(K kern, const P& p, int grid, int threads, size_t bytes, cudaStream_t st, const char* name) {
     if (int rc = set_smem(kern, bytes)) return rc;
     kern<<<grid, threads, bytes, st>>>(p);
     count_launch();
+    note_kernel(name);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
-
-// chunkwise plan (fwp_delta_chunk.cu): three launches each; p.ws must hold chunk_ws_floats() floats
-size_t chunk_ws_floats(long long nseq, int L, int E, int M, int io_dtype, bool backward);
-int launch_fwd_chunk(const DeltaFwdParams& p, int nseq, cudaStream_t st);
-int launch_bwd_chunk(const DeltaBwdParams& p, int nseq, cudaStream_t st);
 
 // chunkwise plan for bf16 streams with E = M = 64 (fwp_delta_chunk_bf16.cuh): applies when every row is 16-byte aligned
 bool chunk_bf16_applies(const DeltaFwdParams& p);

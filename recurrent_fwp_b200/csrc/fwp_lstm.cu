@@ -382,7 +382,7 @@ static int dispatch_lstm_fwd(const LstmFwdParams& p, int nseq, cudaStream_t st) 
     switch (pad_dim(p.D)) {
         case 16: return launch_lstm_fwd<16, 2, 16, VAR>(p, nseq, st);
         case 32: {
-            const int sp = tune_get("lstm_fwd.32.split", 1);
+            const int sp = tune_get(T_LSTM_FWD_SPLIT32, 1);
             // measured (512 sequences x 512 steps): 1 -> 0.78 ms, 4 -> 0.83 ms, 2 -> 0.85 ms
             if (sp == 2) return launch_lstm_fwd<32, 2, 8, VAR>(p, nseq, st);
             if (sp == 4) return launch_lstm_fwd<32, 4, 8, VAR>(p, nseq, st);
@@ -398,7 +398,7 @@ static int dispatch_lstm_bwd(const LstmBwdParams& p, int nseq, cudaStream_t st) 
     switch (pad_dim(p.D)) {
         case 16: return launch_lstm_bwd<16, 2, 8, VAR>(p, nseq, st);
         case 32: {
-            const int sp = tune_get("lstm_bwd.32.split", 2);
+            const int sp = tune_get(T_LSTM_BWD_SPLIT32, 2);
             // measured: 2 -> 1.37 ms, 4 -> 2.14 ms
             if (sp == 4) return launch_lstm_bwd<32, 4, 4, VAR>(p, nseq, st);
             return launch_lstm_bwd<32, 2, 4, VAR>(p, nseq, st);

@@ -441,7 +441,7 @@ FWP_API int fwp_rec_update_fwm_tanh_forward(int N, int H, int L, int D,
     switch (DP) {
         case 16: return launch_rec_fwd<16, 2, 32>(p, N * H, st);
         case 32: {
-            const int sp = tune_get("rec_fwd.32.split", 1);
+            const int sp = tune_get(T_REC_FWD_SPLIT32, 1);
             // measured on B200 (512 sequences x 256 steps): 1 -> 0.36 ms, 2 -> 0.38 ms, 4 -> 0.41 ms
             if (sp == 2) return launch_rec_fwd<32, 2, 16>(p, N * H, st);
             if (sp == 4) return launch_rec_fwd<32, 4, 16>(p, N * H, st);
@@ -498,7 +498,7 @@ FWP_API int fwp_rec_update_fwm_tanh_backward(int N, int H, int L, int D,
     switch (DP) {
         case 16: rc = launch_rec_bwd<16, 2, 16>(p, N * H, st); break;
         case 32: {
-            const int sp = tune_get("rec_bwd.32.split", 2);
+            const int sp = tune_get(T_REC_BWD_SPLIT32, 2);
             // measured: 2 -> 0.36 ms, 4 -> 0.40 ms, 1 -> 0.43 ms (spills)
             if (sp == 4) rc = launch_rec_bwd<32, 4, 8>(p, N * H, st);
             else if (sp == 1) rc = launch_rec_bwd<32, 1, 8>(p, N * H, st);

@@ -330,7 +330,7 @@ static int rnn_forward(int N, int H, int L, int D,
     switch (DP) {
         case 16: return launch_rnn_fwd<16, 2, 32, V1>(p, N * H, st);
         case 32: {
-            const int sp = tune_get("rnn_fwd.32.split", 1);
+            const int sp = tune_get(T_RNN_FWD_SPLIT32, 1);
             if (sp == 2) return launch_rnn_fwd<32, 2, 16, V1>(p, N * H, st);
             return launch_rnn_fwd<32, 1, 16, V1>(p, N * H, st);
         }
@@ -372,7 +372,7 @@ static int rnn_backward(int N, int H, int L, int D,
     switch (DP) {
         case 16: return launch_rnn_bwd<16, 2, 16, V1>(p, N * H, st);
         case 32: {
-            const int sp = tune_get("rnn_bwd.32.split", 1);
+            const int sp = tune_get(T_RNN_BWD_SPLIT32, 1);
             // measured (512 sequences x 512 steps): 1 -> 0.34 ms, 2 -> 0.39 ms, 4 -> 0.42 ms
             if (sp == 2) return launch_rnn_bwd<32, 2, 8, V1>(p, N * H, st);
             if (sp == 4) return launch_rnn_bwd<32, 4, 8, V1>(p, N * H, st);

@@ -42,11 +42,10 @@ class DeltaFastWeight(torch.autograd.Function):
         # reference's saved-tensor order).
         V_insert = torch.empty(0, device=Q.device, dtype=torch.float32)
         stream, dev = _lib.stream_and_device(Q)
-        ws, ws_floats, _keep = _lib.delta_workspace(N, H, L, E, M, Qc, backward=False)
-        _lib.check(_lib.lib.fwp_fast_weight_forward_ws(
+        _lib.check(_lib.lib.fwp_fast_weight_forward(
             N, H, L, E, M, _lib.desc(Qc), _lib.desc(Kc), _lib.desc(Vc), _lib.desc(bc),
             _lib.desc(V_old), _lib.desc(None), _lib.desc(Wd), _lib.desc(out),
-            dt, stream, dev, ws, ws_floats), 'fast_weight_forward')
+            dt, stream, dev), 'fast_weight_forward')
         ctx.save_for_backward(Qc, Kc, Vc, bc, V_old, V_insert, W)
         return out
 
@@ -61,12 +60,11 @@ class DeltaFastWeight(torch.autograd.Function):
         grad_V = torch.empty_like(V, memory_format=torch.contiguous_format)
         grad_beta = torch.empty_like(beta, memory_format=torch.contiguous_format)
         stream, dev = _lib.stream_and_device(Q)
-        ws, ws_floats, _keep = _lib.delta_workspace(N, H, L, E, M, Q, backward=True)
-        _lib.check(_lib.lib.fwp_fast_weight_backward_ws(
+        _lib.check(_lib.lib.fwp_fast_weight_backward(
             N, H, L, E, M, _lib.desc(Q), _lib.desc(K), _lib.desc(V), _lib.desc(beta),
             _lib.desc(V_old), _lib.desc(None), _lib.desc(grad_out), _lib.desc(W.detach()),
             _lib.desc(grad_Q), _lib.desc(grad_K), _lib.desc(grad_V), _lib.desc(grad_beta),
-            _lib.io_dtype(Q), stream, dev, ws, ws_floats), 'fast_weight_backward')
+            _lib.io_dtype(Q), stream, dev), 'fast_weight_backward')
         return grad_Q, grad_K, grad_V, grad_beta, None
 
 

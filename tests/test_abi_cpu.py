@@ -74,28 +74,10 @@ def test_product_does_not_import_the_oracle():
                 assert 'oracle' not in text, '%s mentions the oracle' % fn
 
 
-def test_workspace_size_of_the_chunkwise_plan(L):
-    ws = L.lib.fwp_fast_weight_workspace_floats
-    # 16-step chunks; 1280 floats per chunk forward, 1792 backward; fp32 with E, M <= 16 only
-    assert ws(64, 8, 256, 16, 16, L.F32, 0) == 64 * 8 * 16 * 1280
-    assert ws(64, 8, 256, 16, 16, L.F32, 1) == 64 * 8 * 16 * 1792
-    assert ws(2, 3, 17, 9, 5, L.F32, 0) == 2 * 3 * 2 * 1280          # a ragged last chunk counts as a chunk
-    assert ws(2, 3, 17, 16, 16, L.BF16, 0) == 0
-    assert ws(2, 3, 17, 32, 16, L.F32, 0) == 0 and ws(2, 3, 17, 16, 17, L.F32, 1) == 0
-    assert ws(0, 3, 17, 16, 16, L.F32, 0) == 0 and ws(2, 3, 0, 16, 16, L.F32, 0) == 0
-
-
-def test_workspace_entry_points_validate_like_the_plain_ones(L):
-    global L_mod
-    L_mod = L
-    ok = _fake()
-    f = L.lib.fwp_fast_weight_forward_ws
-    b = L.lib.fwp_fast_weight_backward_ws
-    before = L.launch_count()
-    assert f(0, 8, 16, 16, 16, *[ok] * 8, 0, None, -1, None, 0) == 2
-    assert f(2, 8, 16, 16, 16, *[ok] * 8, 7, None, -1, None, 0) == 5
-    assert b(2, 8, 0, 16, 16, *[ok] * 12, 0, None, -1, None, 0) == 2
-    assert b(2, 8, 16, 16, 16, *([L.FwpTensor()] + [ok] * 11), 0, None, -1, None, 0) == 1
-    assert L.launch_count() == before
-    # the host side only hands out a workspace while the plan is switched on
-    assert L.delta_workspace(2, 2, 32, 16, 16, torch.zeros(1), backward=False) == (None, 0, None)
+def test_plan_switches_are_a_closed_set(L):
+    """fwp_tune accepts the library's own switches and refuses anything else (no table that grows)."""
+    assert L.lib.fwp_tune(b'delta.blocked', -1) == 0
+    assert L.lib.fwp_tune(b'delta_bwd.16.chunk', 32) == 0
+    assert L.lib.fwp_tune(b'no.such.switch', 1) == 6
+    assert L.lib.fwp_tune(None, 1) == 1
+    assert L.lib.fwp_last_kernel() == b''      # nothing launched on this thread

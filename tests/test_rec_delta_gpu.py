@@ -1,7 +1,8 @@
 """GPU parity of the recurrent delta net against the fp64 CPU oracle and the golden fixture.
-Tolerances: outputs max-abs <= 1e-4; stream gradients scaled-rel <= 1e-3 vs fp64; parameter
-gradients (sums over batch and time) scaled-rel <= 1e-3.  The reference's own threshold for
-this op is 1e-2, used on its golden self-test case."""
+Tolerances: outputs max-abs <= 1e-4; stream and parameter gradients through ``util.check_grads``
+(scaled-rel <= 1e-3 vs fp64, strict element-wise measure at max(1e-3, 4 x the fp32 CPU recurrence's own
+strict error), all figures recorded).  The reference's own threshold for this op is 1e-2, used on its
+golden self-test case."""
 import pytest
 import torch
 
@@ -10,20 +11,22 @@ from tests import util
 
 pytestmark = pytest.mark.gpu
 DEV = 'cuda:0'
+NAMES = ('qx', 'kx', 'vx', 'bx', 'R_q', 'R_k', 'R_v', 'r_b')
 
 
-def oracle64(ins, W0, h0, gy):
-    ins = [t.double() for t in ins]
+def oracle64(ins, W0, h0, gy, dtype=torch.float64):
+    """The explicit recurrences in ``dtype``: fp64 is the ground truth, fp32 the reference's own arithmetic."""
+    ins = [t.to(dtype) for t in ins]
     N, H, L, d = ins[0].shape
-    W, st = W0.double().clone(), h0.double().clone()
-    z = lambda *s: torch.zeros(*s, dtype=torch.float64)
+    W, st = W0.to(dtype).clone(), h0.to(dtype).clone()
+    z = lambda *s: torch.zeros(*s, dtype=dtype)
     qo, ko, vo_, out, vold = (z(N, H, L, d) for _ in range(5))
     bo = z(N, H, L, 1)
     K.rec_update_fwm_tanh_forward(*ins, qo, ko, vo_, bo, vold, st, W, out)
     W_end = W.clone()
-    od = torch.tanh(torch.cat([h0.double(), out[:, :, :-1]], 2))
+    od = torch.tanh(torch.cat([h0.to(dtype), out[:, :, :-1]], 2))
     g = [torch.zeros_like(t) for t in ins]
-    K.rec_update_fwm_tanh_backward(qo, ko, vo_, bo, vold, od, gy.double(), *ins[4:8], W, *g)
+    K.rec_update_fwm_tanh_backward(qo, ko, vo_, bo, vold, od, gy.to(dtype), *ins[4:8], W, *g)
     return out, g, W_end, st
 
 
@@ -39,10 +42,10 @@ def test_parity_vs_oracle(fwp, B, H, L, d):
     W_end = W.clone()
     y.backward(gy.to(DEV))
     out, g, S_end, st = oracle64(ins, W0, h0, gy)
+    _, g32, _, _ = oracle64(ins, W0, h0, gy, torch.float32)
     assert util.max_abs(y, out) <= 1e-4
     assert util.max_abs(W_end, S_end) <= 1e-4 and util.max_abs(hs, st) <= 1e-4
-    for leaf, ref in zip(leaves, g):
-        assert util.scaled_rel(leaf.grad, ref) <= 1e-3
+    util.check_grads('rec_delta B%d H%d L%d d%d' % (B, H, L, d), NAMES, [l.grad for l in leaves], g32, g)
     assert util.max_abs(W, W0) <= 1e-5
 
 
@@ -74,6 +77,8 @@ def test_config3_shape_slice_and_determinism(fwp):
     for a, b in zip(*runs):
         assert torch.equal(a, b)
     out, g, _, _ = oracle64(ins, torch.zeros(B, H, d, d), torch.zeros(B, H, 1, d), gy)
+    out32, g32, _, _ = oracle64(ins, torch.zeros(B, H, d, d), torch.zeros(B, H, 1, d), gy, torch.float32)
+    util.record('rec_delta recurrent-delta-net shape slice', y_cuda=util.max_abs(runs[0][0], out),
+                y_cpu32=util.max_abs(out32, out))
     assert util.max_abs(runs[0][0], out) <= 1e-4
-    for got, ref in zip(runs[0][1:], g):
-        assert util.scaled_rel(got, ref) <= 1e-3
+    util.check_grads('rec_delta recurrent-delta-net shape slice', NAMES, runs[0][1:], g32, g)

@@ -1,6 +1,7 @@
 """GPU parity of the delta-RNN kernels (v2 and v1) against the CPU oracle and the golden fixtures.
-Tolerances: outputs max-abs <= 1e-4; gradients scaled-rel <= 1e-3 vs the fp64 oracle
-(the reference's own self-test threshold for these ops is 1e-3)."""
+Tolerances: outputs max-abs <= 1e-4; gradients through ``util.check_grads`` (scaled-rel <= 1e-3 vs the fp64
+oracle, strict element-wise measure at max(1e-3, 4 x the fp32 CPU recurrence's own strict error), all
+figures recorded); the reference's own self-test threshold for these ops is 1e-3."""
 import pytest
 import torch
 
@@ -17,12 +18,13 @@ def _ops(fwp):
     return {2: fast_rnn_v2, 1: fast_rnn}
 
 
-def oracle64(ver, z, k, v, b, W0, h0, gy):
-    """fp64 explicit oracle (the kernels' own formulas, epsilon included)."""
-    z, k, v, b, W0, h0, gy = (t.double() for t in (z, k, v, b, W0, h0, gy))
+def oracle64(ver, z, k, v, b, W0, h0, gy, dtype=torch.float64):
+    """Explicit oracle (the kernels' own formulas, epsilon included) in ``dtype``: fp64 is the ground truth,
+    fp32 the reference's own arithmetic."""
+    z, k, v, b, W0, h0, gy = (t.to(dtype) for t in (z, k, v, b, W0, h0, gy))
     N, H, L, d = z.shape
     W, st = W0.clone(), h0.clone()
-    out, nmz, vold = (torch.zeros(N, H, L, d, dtype=torch.float64) for _ in range(3))
+    out, nmz, vold = (torch.zeros(N, H, L, d, dtype=dtype) for _ in range(3))
     if ver == 2:
         K.fast_rnn_v2_forward(z, k, v, b, vold, st, W, out, nmz)
         od = nmz
@@ -47,10 +49,10 @@ def test_parity_vs_oracle(fwp, ver, B, H, L, d):
     W_end = W.clone()
     y.backward(gy.to(DEV))
     out, g, S_end, st = oracle64(ver, z, k, v, b, W0, h0, gy)
+    _, g32, _, _ = oracle64(ver, z, k, v, b, W0, h0, gy, torch.float32)
     assert util.max_abs(y, out) <= 1e-4
     assert util.max_abs(W_end, S_end) <= 1e-4 and util.max_abs(hs, st) <= 1e-4
-    for leaf, ref in zip(leaves, g):
-        assert util.scaled_rel(leaf.grad, ref) <= 1e-3
+    util.check_grads('rnn_v%d B%d H%d L%d d%d' % (ver, B, H, L, d), 'zkvb', [l.grad for l in leaves], g32, g)
     assert util.max_abs(W, W0) <= 1e-5
 
 
@@ -71,15 +73,23 @@ def test_golden_reference_selftest_case(fwp, name, ver):
         assert util.max_rel(leaf.grad, gd['grad_' + n]) < 1e-3
 
 
-def test_config4_shape_slice(fwp):
-    """configs[3] shape (B=128,H=4,L=512,d=32) on a batch slice the CPU oracle finishes quickly."""
+@pytest.mark.parametrize('ver', [2, 1])
+def test_config4_shape_slice(fwp, ver):
+    """The fast-weight RNN benchmark shape (B=128,H=4,L=512,d=32) on a batch slice the CPU oracle finishes
+    quickly, for both versions."""
     B, H, L, d = 8, 4, 512, 32
     z, k, v, b, gy = util.rnn_inputs(13, B, H, L, d)
     leaves = [t.clone().to(DEV).requires_grad_() for t in (z, k, v, b)]
     W, hs = torch.zeros(B, H, d, d, device=DEV), torch.zeros(B, H, 1, d, device=DEV)
-    y = _ops(fwp)[2](leaves[0], leaves[1], leaves[2], W, leaves[3], hs)
+    y = _ops(fwp)[ver](leaves[0], leaves[1], leaves[2], W, leaves[3], hs)
+    W_end = W.clone()
     y.backward(gy.to(DEV))
-    out, g, _, _ = oracle64(2, z, k, v, b, torch.zeros(B, H, d, d), torch.zeros(B, H, 1, d), gy)
+    zero = (torch.zeros(B, H, d, d), torch.zeros(B, H, 1, d))
+    out, g, S_end, _ = oracle64(ver, z, k, v, b, *zero, gy)
+    out32, g32, _, _ = oracle64(ver, z, k, v, b, *zero, gy, torch.float32)
+    util.record('rnn_v%d benchmark shape slice' % ver, y_cuda=util.max_abs(y, out), y_cpu32=util.max_abs(out32, out),
+                y_max=out.abs().max().item())
     assert util.max_abs(y, out) <= 1e-4 * max(1.0, out.abs().max().item())
-    for leaf, ref in zip(leaves, g):
-        assert util.scaled_rel(leaf.grad, ref) <= 1e-3
+    assert util.max_abs(W_end, S_end) <= 1e-4 * max(1.0, S_end.abs().max().item())
+    util.check_grads('rnn_v%d benchmark shape slice' % ver, 'zkvb', [l.grad for l in leaves], g32, g)
+    assert util.max_abs(W, zero[0]) <= 1e-5 * max(1.0, S_end.abs().max().item())
