@@ -639,5 +639,7 @@ FWP_API int fwp_delta_device_fault(void) {
         const int zero = 0;
         cudaMemcpyToSymbol(fwp::g_delta_fault, &zero, sizeof zero);
     }
-    return v;
+    const int t = fwp::tc_fault_read_clear();
+    if (t < 0) return -1;
+    return (v || t) ? 1 : 0;
 }

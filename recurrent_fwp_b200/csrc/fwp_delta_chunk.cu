@@ -1,6 +1,7 @@
 // Chunkwise plan of the delta rule for bf16 streams with E = M = 64: kernels in fwp_delta_chunk_bf16.cuh,
 // applicability test and launches here.  One fused launch per direction, no workspace.
 #include "fwp_delta_chunk_bf16.cuh"
+#include "fwp_delta_tc.cuh"
 
 namespace fwp {
 
@@ -14,7 +15,51 @@ bool chunk_bf16_applies(const DeltaFwdParams& p) {
            rows_ok(p.v_old, 4) && (!p.v_ins.p || rows_ok(p.v_ins, 4));
 }
 
+// tcgen05 forward: needs 16-byte aligned rows for the TMA maps, an 8-byte aligned state with even strides for
+// its two-float accesses, and a caller that does not ask for u_t (v_insert)
+static bool tc_applies(const DeltaFwdParams& p) {
+    return !p.v_ins.p && (reinterpret_cast<uintptr_t>(p.W) & 7) == 0 && p.wN % 2 == 0 && p.wH % 2 == 0 && p.wE % 2 == 0 &&
+           (unsigned long long)p.q.sN * 2 < (1ull << 40) && (unsigned long long)p.k.sN * 2 < (1ull << 40) &&
+           (unsigned long long)p.v.sN * 2 < (1ull << 40);
+}
+
+static int launch_fwd_tc(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
+    CUtensorMap tq, tk, tv;
+    const int N = p.NH / p.H;
+    if (!tc_make_map(&tq, p.q, N, p.H, p.L) || !tc_make_map(&tk, p.k, N, p.H, p.L) || !tc_make_map(&tv, p.v, N, p.H, p.L))
+        return -1;      // the driver refused the layout: the caller takes the warp-level kernel
+    const size_t bytes = sizeof(tcd::Smem) + 1024;
+    if (int rc = set_smem(delta_fwd_tc_kernel, bytes)) return rc;
+    delta_fwd_tc_kernel<<<nseq, tcd::NTH, bytes, st>>>(p, tq, tk, tv);
+    count_launch();
+    note_kernel("delta_fwd_tc_kernel");
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+// 1 if a bounded wait of the tcgen05 kernel ran out on the current device since the last call (reading clears it)
+int tc_fault_read_clear() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_fault, sizeof v) != cudaSuccess) return -1;
+    if (v) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_tc_fault, &zero, sizeof zero);
+    }
+    return v;
+}
+
+#ifdef FWP_TC_PROF
+extern "C" __attribute__((visibility("default"))) int fwp_debug_tc_prof(long long* out) {
+    return cudaMemcpyFromSymbol(out, g_tc_prof, 16 * sizeof(long long)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
+    // "delta.tc64" = 1: the tcgen05 / TMA forward (64-step chunks); 0: the warp-level mma forward (16-step chunks)
+    if (tune_get(T_DELTA_TC64, 0) == 1 && tc_applies(p)) {
+        const int rc = launch_fwd_tc(p, nseq, st);
+        if (rc >= 0) return rc;
+    }
     return launch(delta_fwd_chunk_bf16_inv_kernel, p, nseq, cb::NT, sizeof(cb::SmemI), st, "delta_fwd_chunk_bf16_inv_kernel");
 }
 

@@ -4,8 +4,8 @@ the CPU oracle on identical seeded inputs and against the golden fixtures.
 Tolerances (fp32): max |dy| <= 1e-4; gradients: the reference self-test's measure
 max |d| / (|ref| + 1e-6) <= 1e-3 on the reference-shaped golden case; on the N(0,1)-driven
 configurations ``util.check_grads`` gates max |d| / (|ref| + mean|ref|) <= 1e-3 and the strict
-measure at max(1e-3, 4 x the strict error of the fp32 CPU loop against fp64 on the same inputs),
-recording all figures.
+measure for every entry above 4 x the noise floor of the fp32 CPU loop (its largest absolute error against
+fp64 on the same inputs), recording all figures.
 
 bf16 streams (fp32 state): the oracle is the fp64 recurrence on the bf16-rounded inputs.  Outputs are
 themselves rounded to bf16 (half an ulp is 2^-9 = 2e-3 of the value) on top of products taken with bf16

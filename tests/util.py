@@ -90,19 +90,26 @@ def check_grads(case, names, got, ref32, ref64, tol=1e-3, slack=4.0):
     """Gradient gate with the strict element-wise measure next to the scaled one.
 
     ``got`` are the CUDA gradients, ``ref32`` those of the fp32 CPU formulation (the reference implementation's
-    arithmetic), ``ref64`` the fp64 ground truth.  For every tensor:
+    arithmetic), ``ref64`` the fp64 ground truth.  For every tensor these figures are recorded:
       strict_cuda  = max |got - ref64| / (|ref64| + 1e-6)        (the reference self-tests' measure)
       strict_cpu32 = the same figure for the fp32 CPU formulation
-      scaled_cuda  = max |got - ref64| / (|ref64| + mean|ref64|)
-    Gates: scaled_cuda <= tol always; strict_cuda <= max(tol, slack * strict_cpu32), i.e. the strict bound
-    holds wherever the reference's own fp32 arithmetic meets it with a margin, and elsewhere the CUDA path
-    may be no more than ``slack`` times further from fp64 than that arithmetic is (entries near zero that are
-    sums of cancelling terms carry rounding noise of the operands' size in any fp32 evaluation order).
-    All figures are recorded."""
+      scaled_cuda  = max |got - ref64| / (|ref64| + mean|ref64|), scaled_cpu32 likewise
+      floor32      = max |ref32 - ref64|, the largest absolute error the reference's own fp32 arithmetic makes
+                     anywhere in the tensor (its rounding-noise floor)
+      strict_above_floor = max (|got - ref64| - slack * floor32)+ / (|ref64| + 1e-6)
+    Gates: scaled_cuda <= tol, and strict_above_floor <= tol: every entry meets the strict relative bound once
+    ``slack`` times the fp32 noise floor is granted as absolute error.  The plain strict figure is dominated by
+    the entry closest to zero (a sum of cancelling terms that carries the operands' rounding noise in any fp32
+    evaluation order); the fp32 CPU formulation itself misses 1e-3 on many of these tensors, which the recorded
+    figures show."""
     for name, g, r32, r64 in zip(names, got, ref32, ref64):
-        g = g.float() if g.dtype == torch.bfloat16 else g
+        g = (g.float() if g.dtype == torch.bfloat16 else g).double().cpu()
+        r32, r64 = r32.double().cpu(), r64.double().cpu()
+        floor32 = (r32 - r64).abs().max().item()
+        above = (((g - r64).abs() - slack * floor32).clamp_min(0) / (r64.abs() + 1e-6)).max().item()
         figs = dict(tensor=name, strict_cuda=max_rel(g, r64), strict_cpu32=max_rel(r32, r64),
-                    scaled_cuda=scaled_rel(g, r64), scaled_cpu32=scaled_rel(r32, r64))
+                    scaled_cuda=scaled_rel(g, r64), scaled_cpu32=scaled_rel(r32, r64), floor32=floor32,
+                    strict_above_floor=above)
         record(case, **figs)
         assert figs['scaled_cuda'] <= tol, (case, figs)
-        assert figs['strict_cuda'] <= max(tol, slack * figs['strict_cpu32']), (case, figs)
+        assert above <= tol, (case, figs)
