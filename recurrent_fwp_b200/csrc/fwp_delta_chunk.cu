@@ -48,9 +48,10 @@ int tc_fault_read_clear() {
     return v;
 }
 
+
 #ifdef FWP_TC_PROF
 extern "C" __attribute__((visibility("default"))) int fwp_debug_tc_prof(long long* out) {
-    return cudaMemcpyFromSymbol(out, g_tc_prof, 16 * sizeof(long long)) == cudaSuccess ? 0 : 1;
+    return cudaMemcpyFromSymbol(out, g_tc_prof, 48 * sizeof(long long)) == cudaSuccess ? 0 : 1;
 }
 #endif
 

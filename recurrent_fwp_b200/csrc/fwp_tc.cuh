@@ -50,6 +50,13 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (mbar_try(bar, parity)) return;
     *failed = 1;
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+// barrier among `count` threads of the CTA (a warp group), ids 1..15
+__device__ __forceinline__ void group_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // generic-proxy writes to shared memory -> visible to the async proxy (tcgen05.mma operand reads, TMA stores)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -105,6 +112,44 @@ __device__ __forceinline__ void tmem_st_16x64(uint32_t taddr, const float (&r)[3
           "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]),
           "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31]),
           "r"(taddr) : "memory");
+}
+
+// ---------------------------------------------------------------- fragment <-> tile moves
+// A warp's 16 x 64 tile in accumulator-fragment form, already packed to bf16 pairs: pk[2 * j + h] holds
+// (row g + 8h, columns 8j + 2t, 8j + 2t + 1).  stmatrix writes four 8 x 8 blocks per instruction, every lane
+// supplying the address of one 16-byte row piece, so a swizzled row needs no per-element address arithmetic.
+// `tile` is the 64-row swizzled tile, `row0` the warp's first row.
+__device__ __forceinline__ void st_frag_swz(unsigned char* tile, int row0, const uint32_t (&pk)[16], int lane) {
+    const int mi = lane >> 3, rr = row0 + 8 * (mi & 1) + (lane & 7);       // block mi: row half mi & 1, column block 2jj + (mi >> 1)
+#pragma unroll
+    for (int jj = 0; jj < 4; jj++) {
+        const int j = 2 * jj + (mi >> 1);
+        const uint32_t a = smem_addr(tile) + rr * 128 + (((j ^ rr) & 7) << 4);
+        asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+                     ::"r"(a), "r"(pk[4 * jj]), "r"(pk[4 * jj + 1]), "r"(pk[4 * jj + 2]), "r"(pk[4 * jj + 3]) : "memory");
+    }
+}
+// the same into a row-major tile with `ld` bf16 elements per row (ld a multiple of 8)
+__device__ __forceinline__ void st_frag_rowmajor(__nv_bfloat16* tile, int ld, int row0, const uint32_t (&pk)[16], int lane) {
+    const int mi = lane >> 3, rr = row0 + 8 * (mi & 1) + (lane & 7);
+#pragma unroll
+    for (int jj = 0; jj < 4; jj++) {
+        const int j = 2 * jj + (mi >> 1);
+        const uint32_t a = smem_addr(tile + rr * ld + 8 * j);
+        asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+                     ::"r"(a), "r"(pk[4 * jj]), "r"(pk[4 * jj + 1]), "r"(pk[4 * jj + 2]), "r"(pk[4 * jj + 3]) : "memory");
+    }
+}
+// the inverse move: a warp's 16 x 64 part of a swizzled bf16 tile into pk[] (same indexing)
+__device__ __forceinline__ void ld_frag_swz(uint32_t (&pk)[16], const unsigned char* tile, int row0, int lane) {
+    const int mi = lane >> 3, rr = row0 + 8 * (mi & 1) + (lane & 7);
+#pragma unroll
+    for (int jj = 0; jj < 4; jj++) {
+        const int j = 2 * jj + (mi >> 1);
+        const uint32_t a = smem_addr(tile) + rr * 128 + (((j ^ rr) & 7) << 4);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(pk[4 * jj]), "=r"(pk[4 * jj + 1]), "=r"(pk[4 * jj + 2]), "=r"(pk[4 * jj + 3]) : "r"(a) : "memory");
+    }
 }
 
 // ---------------------------------------------------------------- tcgen05.mma
