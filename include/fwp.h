@@ -108,11 +108,15 @@ int fwp_fast_weight_backward(int N, int H, int L, int E, int M,
                              const fwp_tensor* grad_V, const fwp_tensor* grad_beta,
                              int io_dtype, void* stream, int device);
 
-/* The delta-rule kernels move contiguous chunks with bulk asynchronous copies whose completion
- * waits are bounded.  Returns 1 if such a wait ever ran out on the current device since the last
+/* The delta-rule kernels move contiguous chunks with bulk asynchronous copies (in the tcgen05 plan also TMA
+ * tile loads and tensor-core products) whose completion waits are bounded.  Returns 1 if such a wait ever ran out on the current device since the last
  * call (that launch then produced wrong numbers instead of hanging the GPU), 0 if not, -1 on a
  * CUDA error.  Synchronises the device; reading clears the flag.  No counterpart in the reference. */
 int fwp_delta_device_fault(void);
+/* Test hook for that mechanism: launches one CTA that waits, with a limit of `polls` (1..65536) polls, on a
+ * barrier nothing completes; the wait runs out, the kernel returns, and the next fwp_delta_device_fault() reads 1.
+ * Nothing hangs and the context stays usable.  No counterpart in the reference. */
+int fwp_debug_bounded_wait_probe(int polls, void* stream, int device);
 
 /* ---- input prologue / output epilogue of the delta-rule attention layer ----
  * One pass each for what the reference's layers do with a chain of elementwise and permute launches around the

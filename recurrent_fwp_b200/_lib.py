@@ -49,6 +49,7 @@ SIGNATURES = {
     'fwp_delta_layer_prologue_forward': [_i] * 4 + [ctypes.c_void_p] * 5 + [_vp, _i],
     'fwp_delta_layer_prologue_backward': [_i] * 4 + [ctypes.c_void_p] * 6 + [_vp, _i],
     'fwp_delta_layer_transpose': [_i] * 4 + [ctypes.c_void_p] * 2 + [ctypes.c_float, _i, _vp, _i],
+    'fwp_debug_bounded_wait_probe': [_i, _vp, _i],
     'fwp_fast_lstm_backward': [_i] * 5 + [_T] + [_T3] * 4 + [_T] * 4 + [_T3] * 6 + [_i, _vp, _i],
 }
 OTHER_SYMBOLS = ['fwp_status_string', 'fwp_last_cuda_error', 'fwp_version', 'fwp_max_head_dim',

@@ -19,7 +19,7 @@ OBJ = os.path.join(PKG, 'build')
 LIB = os.path.join(PKG, 'libfwp.so')
 NVCC = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
 FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
-         '-Xcompiler', '-fPIC', '-Xcompiler', '-fvisibility=hidden'] + os.environ.get('FWP_NVCC_FLAGS', '').split()
+         '-Xcompiler', '-fPIC', '-Xcompiler', '-fvisibility=hidden']
 
 
 def _newer(src_list, target):

@@ -629,6 +629,15 @@ FWP_API int fwp_causal_dot_backward(int N, int H, int L, int E, int M,
     return dispatch_sum_bwd<__nv_bfloat16>(p, N * H, st);
 }
 
+// Test hook: launches a kernel whose only wait can never be satisfied, with a limit of `polls` (1..65536) polls;
+// afterwards fwp_delta_device_fault() must read 1.  Bounded by construction: nothing hangs, the context stays usable.
+FWP_API int fwp_debug_bounded_wait_probe(int polls, void* stream, int device) {
+    if (polls < 1 || polls > 65536) return FWP_ERR_SHAPE;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    return fwp::launch_wait_probe(polls, (cudaStream_t)stream);
+}
+
 // 1 if a bounded wait on a bulk copy ever ran out on the current device since the last call
 // (the affected launch produced wrong numbers instead of hanging), 0 if not, -1 on a CUDA error.
 // Synchronises the device; reading clears the flag.

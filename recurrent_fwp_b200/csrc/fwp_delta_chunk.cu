@@ -49,11 +49,30 @@ int tc_fault_read_clear() {
 }
 
 
-#ifdef FWP_TC_PROF
-extern "C" __attribute__((visibility("default"))) int fwp_debug_tc_prof(long long* out) {
-    return cudaMemcpyFromSymbol(out, g_tc_prof, 48 * sizeof(long long)) == cudaSuccess ? 0 : 1;
+// Test hook for the bounded waits: one CTA waits, with the given poll limit, on an mbarrier that nothing ever
+// completes.  The wait runs out, the kernel returns and the device flag is raised, exactly what a kernel of this file
+// does when a copy or a product it waits for never arrives.
+__global__ void tc_wait_probe_kernel(unsigned limit) {
+    __shared__ uint64_t bar;
+    __shared__ int failed;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&bar, 1);
+        failed = 0;
+        tc::fence_barrier_init();
+    }
+    __syncthreads();
+    tc::mbar_wait(&bar, 0, &failed, limit);
+    __syncthreads();
+    if (failed && threadIdx.x == 0) atomicExch(&g_tc_fault, 1);
 }
-#endif
+
+int launch_wait_probe(int polls, cudaStream_t st) {
+    tc_wait_probe_kernel<<<1, 32, 0, st>>>((unsigned)polls);
+    count_launch();
+    note_kernel("tc_wait_probe_kernel");
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
 
 int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     // "delta.tc64" = 1: the tcgen05 / TMA forward (64-step chunks); 0: the warp-level mma forward (16-step chunks)

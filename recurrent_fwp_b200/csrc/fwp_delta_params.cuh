@@ -46,5 +46,6 @@ int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st);
 bool chunk_bf16_applies(const DeltaBwdParams& p);
 int launch_bwd_chunk_bf16(const DeltaBwdParams& p, int nseq, cudaStream_t st);
 int tc_fault_read_clear();
+int launch_wait_probe(int polls, cudaStream_t st);
 
 }  // namespace fwp

@@ -8,13 +8,15 @@
 //   y = Q S0 + Aqk u,   S1 = S0 + K^T u
 // (the recurrence of algorithmic/fast_weight/fast_weight_cuda.cu:101-169, regrouped over 64 steps).
 //
-// Every 64-deep contraction is a tcgen05.mma (M = N = 64, K = 16, four instructions per product), operands in
-// 128-byte-swizzled shared-memory tiles, fp32 accumulators in tensor memory:
-//   S (the fp32 master copy of the state, updated in place by S += K^T u), w (Cv, then Cv - Ck S0 accumulated into
-//   it with the negated-A form), y, Akk, Aqk, Ck.
+// Every 64-deep contraction is a tcgen05.mma with M = 64, K = 16 (four instructions per product), operands in
+// 128-byte-swizzled shared-memory tiles, fp32 accumulators in tensor memory.  Products that share their left
+// operand are issued 128 columns wide over two adjacent right-hand tiles:
+//   [Akk | Aqk^T] = K [K ; Q]^T     [Ck | Cv] = T [K | V]     [K^T u_hi | K^T u_lo] = K^T [u_hi | u_lo]
+//   w = Cv - Ck S0 (accumulated into the Cv columns with the negated-A form),   y = Q S0 + Aqk u_hi
 // K, Q, V tiles arrive by TMA tile loads (three stages, one mbarrier each).  The tiles the kernel produces itself
-// (Aqk, T, Ck, u, the bf16 copy of S) are written from registers in the same swizzled layout (stmatrix); T and u
-// are kept as two bf16 parts (hi + lo) so that the products they enter carry 16 mantissa bits.
+// (Aqk^T, T, Ck, u, the bf16 copy of S) are written from registers in the same swizzled layout (stmatrix); T and u
+// are kept as two bf16 parts (hi + lo) so that the products they enter carry 16 mantissa bits.  The fp32 master copy
+// of the state lives in the registers of the chain warps, which add the two halves of K^T [u_hi | u_lo] each chunk.
 // The inverse is blocked 16 x 16: warp w of the preparing group owns rows 16w..16w+15 of the chunk (the quarter of
 // the tensor-memory lanes it can read), inverts its diagonal block in registers by the nilpotent product
 // (I - D)(I + D^2)(I + D^4)(I + D^8) and obtains the blocks left of it by block forward substitution,
@@ -22,14 +24,15 @@
 // with the blocks of the warps above exchanged through shared memory (three rounds); these 16-wide products run on
 // warp-level mma, everything 64 wide on tcgen05.
 //
-// One CTA per sequence, three roles that meet only at mbarriers:
-//   * chain warps 0-3   per chunk c: w(c) -> u (two parts) and v_old;  S(c+1) -> bf16 copy;  y(c) -> global
-//   * preparing warps 4-7, one chunk ahead: Gram tiles -> masked Aqk and T;  Ck -> bf16
-//   * warp 8, one thread: every TMA load and every tcgen05.mma, in the order
-//       Gram(c+1) | S += K^T u(c), y(c) | Ck, Cv(c+1) | w(c+1) = Cv - Ck S(c+1) | refill of the stage chunk c used
-//     each product waiting for the mbarrier on which the producers of its operands (128 threads) arrive after
-//     their proxy fence, each batch followed by a tcgen05.commit onto the mbarrier its consumers wait for.
-// The state-dependent chain per chunk is: w product -> u -> state product -> bf16 copy; everything else runs beside it.
+// One CTA per sequence; five roles that meet only at mbarriers:
+//   * chain warps 0-3       per chunk c: w(c) -> u (two parts);  K^T u -> S(c+1) (registers) -> bf16 copy
+//   * preparing warps 4-7   one chunk ahead: Akk -> N -> T
+//   * helper warps 8-11     Aqk^T -> masked operand, Ck -> bf16 operand (one chunk ahead); v_old(c), y(c) -> global
+//   * warp 12, one thread   the products on the chain: Q S(c) | K^T u(c) | Aqk u(c) | w(c+1) = Cv - Ck S(c+1)
+//   * warp 13, one thread   the TMA loads and the products beside the chain: Gram(c+1) | [Ck | Cv](c+1)
+// Each product waits for the mbarriers on which the producers of its operands (128 threads) arrive after their
+// proxy fence, and each batch is followed by a tcgen05.commit onto the mbarrier its consumers wait for.
+// The state-dependent chain per chunk is: w product -> u -> K^T u product -> add, round, store.
 // Every mbarrier wait is bounded; a wait that runs out marks the CTA as failed, after which nobody waits any more,
 // all roles finish their (fixed-length) loops, the CTA frees its tensor memory and raises the device flag that
 // fwp_delta_device_fault() reads.
@@ -41,46 +44,43 @@
 namespace fwp {
 
 static __device__ int g_tc_fault;
-#ifdef FWP_TC_PROF
-static __device__ long long g_tc_prof[48];
-#define TCP(i) { const long long _n = clock64(); _pt[i] += _n - _pc; _pc = _n; }
-#define TCP_BEGIN long long _pt[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, _pc = clock64();
-#define TCP_END(base) if (blockIdx.x == 0 && lane == 0 && gw == 0) { for (int _i = 0; _i < 16; _i++) g_tc_prof[(base) + _i] = _pt[_i]; }
-#else
-#define TCP(i)
-#define TCP_BEGIN
-#define TCP_END(base)
-#endif
 
 namespace tcd {
 
 using namespace cb;     // warp-level mma helpers of the 16-step kernels (pack_bf16, split_bf16, a_of, b_of, mm, ldb_kn)
 
 constexpr int CH = 64;                  // steps per chunk
-constexpr int NTH = 288;                // chain warps 0-3, preparing warps 4-7, issuing warp 8
+constexpr int NTH = 480;                // chain 0-3, preparing 4-7, helper 8-11, issuing warps 12 and 13, loading warp 14
 constexpr int NG = 128;                 // threads per compute group
 constexpr int NSTAGE = 3;
 constexpr int LDX = 72;                 // row stride (bf16) of the row-major exchange and output tiles: 144 B, 16-byte aligned
-constexpr uint32_t COL_S = 0, COL_W = 64, COL_Y = 128, COL_AKK = 192, COL_AQK = 256, COL_CK = 320, TMEM_COLS = 512;
+// Tensor memory.  An M = 64 accumulator occupies lanes 0-15 of each quarter of the 128 lanes; a second one can sit in
+// lanes 16-31 of the same columns.  Lower lanes: K^T [u_hi | u_lo] (columns 0-127), y (128-191) and two buffers of
+// [Ck | w] (192-319, 320-447) for consecutive chunks; upper lanes of columns 0-127: [Akk | Aqk^T].
+constexpr uint32_t COL_D = 0, COL_Y = 128, COL_CKW = 192, TMEM_COLS = 512;
+constexpr uint32_t COL_AKK = 0, COL_AQK = 64, LANE_G = 16u << 16;
+__device__ __forceinline__ uint32_t col_ck(int c) { return COL_CKW + 128u * (uint32_t)(c & 1); }
+__device__ __forceinline__ uint32_t col_w(int c) { return col_ck(c) + 64u; }
 
+struct Stage {                          // one chunk's rows; q follows k and v follows q so that [K ; Q] and [K | V] are one operand
+    unsigned char k[tc::kTileBytes], q[tc::kTileBytes], v[tc::kTileBytes];
+};
 struct Smem {
-    alignas(1024) unsigned char k[NSTAGE][tc::kTileBytes];
-    unsigned char q[NSTAGE][tc::kTileBytes];
-    unsigned char v[NSTAGE][tc::kTileBytes];
-    unsigned char aq[2][tc::kTileBytes];        // Aqk, [t][i], zero above the diagonal (K-major left operand)
+    alignas(1024) Stage st[NSTAGE];
+    unsigned char aq[2][tc::kTileBytes];        // Aqk^T, [i][t], zero below the diagonal (MN-major left operand)
     unsigned char th[tc::kTileBytes];           // T hi, [t][i] (K-major left operand)
     unsigned char tl[tc::kTileBytes];           // T lo
-    unsigned char ck[tc::kTileBytes];           // Ck, [t][e] (K-major left operand)
-    unsigned char uh[tc::kTileBytes];           // u hi, [i][m] (MN-major right operand)
+    unsigned char ck[2][tc::kTileBytes];        // Ck of two consecutive chunks, [t][e] (K-major left operand)
+    unsigned char uh[tc::kTileBytes];           // u hi, [i][m] (MN-major right operand); ul follows it: [u_hi | u_lo] is one operand
     unsigned char ul[tc::kTileBytes];           // u lo
     unsigned char sb[tc::kTileBytes];           // bf16 copy of the state, [e][m] (MN-major right operand)
     __nv_bfloat16 x[CH * LDX];                  // X = T - I, lower blocks, row-major (exchange between preparing warps)
     __nv_bfloat16 ys[CH * LDX];                 // y, [t][m] row-major (staging for 16-byte stores)
-    float b[2][CH];
-    // completion of asynchronous work (one arrival each): TMA stages, tcgen05.commit of the five product batches
-    uint64_t bar_full[NSTAGE], bar_gram, bar_ckcv, bar_p, bar_s, bar_y;
+    float b[4][CH];                             // beta of four consecutive chunks (the preparing warps run up to two ahead)
+    // completion of asynchronous work (one arrival each): TMA stages, tcgen05.commit of the product batches
+    uint64_t bar_full[NSTAGE], bar_gram, bar_ckcv[2], bar_p, bar_d, bar_y;
     // operands written / accumulators read by a compute group (128 arrivals each)
-    uint64_t bar_t_ready, bar_ck_ready, bar_u_ready, bar_s_ready, bar_y_read;
+    uint64_t bar_t_ready, bar_aq_ready[2], bar_ck_ready[2], bar_u_ready[2], bar_s_ready, bar_w_read[2], bar_y_read, bar_free[2];
     uint32_t tmem_base;
     int failed;
 };
@@ -89,14 +89,28 @@ struct Smem {
 static_assert(sizeof(Smem) > 116 * 1024, "two CTAs per SM would deadlock on the tensor-memory allocation");
 static_assert(sizeof(Smem) + 1024 <= 227 * 1024, "shared memory budget");
 
-// the four tcgen05.mma of one 64 x 64 x 64 product, from prebuilt descriptors
-template <bool A_MN, bool B_MN, bool NEG_A>
+// The four tcgen05.mma of one 64-deep product (M = 64, N columns), from prebuilt descriptors.  Called by a whole
+// (converged) warp: every lane carries the same descriptors, which lets them live in uniform registers, and one
+// elected lane issues.
+template <bool A_MN, bool B_MN, bool NEG_A, int N>
 __device__ __forceinline__ void product(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, bool accumulate) {
-    constexpr uint32_t id = tc::idesc(A_MN, B_MN, NEG_A);
+    constexpr uint32_t id = tc::idesc(A_MN, B_MN, NEG_A, N);
+    if (tc::elect_one()) {
 #pragma unroll
-    for (int k = 0; k < 4; k++)
-        tc::mma_issue(d_tmem, a_desc + (uint64_t)(k * (A_MN ? 128 : 2)), b_desc + (uint64_t)(k * (B_MN ? 128 : 2)), id,
-                      (accumulate || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; k++)
+            tc::mma_issue(d_tmem, a_desc + (uint64_t)(k * (A_MN ? 128 : 2)), b_desc + (uint64_t)(k * (B_MN ? 128 : 2)), id,
+                          (accumulate || k > 0) ? 1u : 0u);
+    }
+    __syncwarp();
+}
+
+// fp32 fragment -> bf16 pairs in the order the tile stores take
+__device__ __forceinline__ void pack_frag(uint32_t (&pk)[16], const float (&r)[32]) {
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        pk[2 * j] = pack_bf16(r[4 * j], r[4 * j + 1]);
+        pk[2 * j + 1] = pack_bf16(r[4 * j + 2], r[4 * j + 3]);
+    }
 }
 
 }  // namespace tcd
@@ -109,7 +123,7 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
     extern __shared__ unsigned char tc_smem_raw[];
     Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    const int role = warp >> 2;                         // 0 chain, 1 preparing, 2 issuing
+    const int role = warp >> 2;                         // 0 chain, 1 preparing, 2 helper, 3 issuing
     const int gw = warp & 3, gtid = tid & (NG - 1);     // warp and thread inside a compute group
     const int seq = blockIdx.x, n = seq / p.H, h = seq - n * p.H;
     const bf16* bb = reinterpret_cast<const bf16*>(p.beta.p) + n * p.beta.sN + h * p.beta.sH;
@@ -123,144 +137,162 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
     if (tid == 0) {
         for (int i = 0; i < NSTAGE; i++) tc::mbar_init(&s.bar_full[i], 1);
         tc::mbar_init(&s.bar_gram, 1);
-        tc::mbar_init(&s.bar_ckcv, 1);
+        tc::mbar_init(&s.bar_ckcv[0], 1);
+        tc::mbar_init(&s.bar_ckcv[1], 1);
         tc::mbar_init(&s.bar_p, 1);
-        tc::mbar_init(&s.bar_s, 1);
+        tc::mbar_init(&s.bar_d, 1);
         tc::mbar_init(&s.bar_y, 1);
         tc::mbar_init(&s.bar_t_ready, NG);
-        tc::mbar_init(&s.bar_ck_ready, NG);
-        tc::mbar_init(&s.bar_u_ready, NG);
+        tc::mbar_init(&s.bar_aq_ready[0], NG);
+        tc::mbar_init(&s.bar_aq_ready[1], NG);
+        tc::mbar_init(&s.bar_ck_ready[0], NG);
+        tc::mbar_init(&s.bar_ck_ready[1], NG);
+        tc::mbar_init(&s.bar_u_ready[0], NG);
+        tc::mbar_init(&s.bar_u_ready[1], NG);
         tc::mbar_init(&s.bar_s_ready, NG);
+        tc::mbar_init(&s.bar_w_read[0], NG);
+        tc::mbar_init(&s.bar_w_read[1], NG);
         tc::mbar_init(&s.bar_y_read, NG);
+        tc::mbar_init(&s.bar_free[0], NG);
+        tc::mbar_init(&s.bar_free[1], NG);
         s.failed = 0;
         tc::fence_barrier_init();
     }
-    if (warp == 8) tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
+    if (warp == 12) tc::tmem_alloc(&s.tmem_base, TMEM_COLS);
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = s.tmem_base;
     const uint32_t tlane = tmem + ((uint32_t)(gw * 32) << 16);      // this warp's quarter of the lanes
 
+    float S[32];        // chain warps: the fp32 state, rows r0, r1 in fragment form
     if (role == 0) {
-        // ---- the state: global -> registers -> tensor memory (fp32) and shared memory (bf16)
-        float S[32];
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const float2 a = *reinterpret_cast<const float2*>(W + (long long)r0 * p.wE + 8 * j + 2 * t4);
             const float2 c = *reinterpret_cast<const float2*>(W + (long long)r1 * p.wE + 8 * j + 2 * t4);
             S[4 * j] = a.x; S[4 * j + 1] = a.y; S[4 * j + 2] = c.x; S[4 * j + 3] = c.y;
-            pk[2 * j] = pack_bf16(a.x, a.y);
-            pk[2 * j + 1] = pack_bf16(c.x, c.y);
         }
+        pack_frag(pk, S);
         tc::st_frag_swz(s.sb, row0, pk, lane);
-        tc::tmem_st_16x64(tlane + COL_S, S);
-        tc::tmem_wait_st();
         tc::fence_proxy_async();
-        tc::tc_fence_before();
     }
     __syncthreads();
 
-    if (role == 2) {
-        // =============================================================== issuing thread
-        if (lane == 0) {
+    if (role == 3) {
+        if (warp == 12) {
+            // =========================================================== issuing thread A: the products on the chain
             tc::tc_fence_after();
+            const uint64_t dsb = tc::smem_desc(tc::smem_addr(s.sb));
+            const uint64_t dck[2] = {tc::smem_desc(tc::smem_addr(s.ck[0])), tc::smem_desc(tc::smem_addr(s.ck[1]))};
+            const uint64_t duh = tc::smem_desc(tc::smem_addr(s.uh));
+            const uint64_t du2 = tc::smem_desc_mn128(tc::smem_addr(s.uh), tc::kTileBytes);
+            // w(0) = Cv(0) - Ck(0) S(0)
+            tc::mbar_wait(&s.bar_ck_ready[0], 0, failed);
+            tc::tc_fence_after();
+            product<false, true, true, 64>(tmem + col_w(0), dck[0], dsb, true);
+            if (tc::elect_one()) tc::mma_commit(&s.bar_p);
+            __syncwarp();
+#pragma unroll 1
+    #pragma unroll 1
+        for (int c = 0; c < nchunks; c++) {
+                const int st = c % NSTAGE;
+                const uint64_t dk = tc::smem_desc(tc::smem_addr(s.st[st].k)), dq = tc::smem_desc(tc::smem_addr(s.st[st].q));
+                // y(c) = Q S(c): needs the y columns read (chunk c - 1); the bf16 copy of S(c) was waited for before w(c)
+                tc::mbar_wait(&s.bar_full[st], (c / NSTAGE) & 1, failed);
+                if (c > 0) tc::mbar_wait(&s.bar_y_read, (c - 1) & 1, failed);
+                tc::tc_fence_after();
+                product<false, true, false, 64>(tmem + COL_Y, dq, dsb, false);
+                // [K^T u_hi | K^T u_lo]
+                tc::mbar_wait(&s.bar_u_ready[c & 1], (c >> 1) & 1, failed);
+                tc::tc_fence_after();
+                product<true, true, false, 128>(tmem + COL_D, dk, du2, false);
+                if (tc::elect_one()) tc::mma_commit(&s.bar_d);
+                __syncwarp();
+                // y(c) += Aqk u_hi
+                tc::mbar_wait(&s.bar_aq_ready[c & 1], (c >> 1) & 1, failed);
+                tc::tc_fence_after();
+                product<true, true, false, 64>(tmem + COL_Y, tc::smem_desc(tc::smem_addr(s.aq[c & 1])), duh, true);
+                if (tc::elect_one()) tc::mma_commit(&s.bar_y);
+                __syncwarp();
+                // w(c+1) = Cv(c+1) - Ck(c+1) S(c+1)
+                tc::mbar_wait(&s.bar_s_ready, c & 1, failed);
+                if (c + 1 < nchunks) {
+                    tc::mbar_wait(&s.bar_ck_ready[(c + 1) & 1], ((c + 1) >> 1) & 1, failed);
+                    tc::tc_fence_after();
+                    product<false, true, true, 64>(tmem + col_w(c + 1), (c + 1) & 1 ? dck[1] : dck[0], dsb, true);
+                    if (tc::elect_one()) tc::mma_commit(&s.bar_p);
+            __syncwarp();
+                }
+            }
+        } else if (warp == 13) {
+            // =========================================================== issuing thread B: Gram, [Ck | Cv]
+            tc::tc_fence_after();
+            const uint64_t dth = tc::smem_desc(tc::smem_addr(s.th)), dtl = tc::smem_desc(tc::smem_addr(s.tl));
+            auto gram = [&](int c) {        // [Akk | Aqk^T](c) = K [K ; Q]^T
+                const int st = c % NSTAGE;
+                tc::mbar_wait(&s.bar_full[st], (c / NSTAGE) & 1, failed);
+                tc::tc_fence_after();
+                const uint64_t dk = tc::smem_desc(tc::smem_addr(s.st[st].k));
+                product<false, false, false, 128>(tmem + LANE_G + COL_AKK, dk, dk, false);
+                if (tc::elect_one()) tc::mma_commit(&s.bar_gram);
+                __syncwarp();
+            };
+            // Order: Gram(c+1) as soon as the preparing and helper warps have read Gram(c) (it overwrites those
+            // columns), so that the inverse of chunk c+1 starts while [Ck | Cv](c) still waits for the chain.
+            gram(0);
+#pragma unroll 1
+    #pragma unroll 1
+        for (int c = 0; c < nchunks; c++) {
+                // T(c) written (so Akk(c) is read); Aqk^T(c) read
+                tc::mbar_wait(&s.bar_t_ready, c & 1, failed);
+                if (c + 1 < nchunks) {
+                    tc::mbar_wait(&s.bar_aq_ready[c & 1], (c >> 1) & 1, failed);
+                    gram(c + 1);
+                }
+                // [Ck | Cv](c) goes to the buffer chunk c - 2 used: Ck(c-2) read (ck_ready), w(c-2) read by the chain (u_ready)
+                // and by the helper warps (w_read).  Each of these barriers exists twice, one per buffer, so the phase
+                // waited for here is the one right before the phase this very product makes possible.
+                if (c > 1) {
+                    const uint32_t ph = ((c - 2) >> 1) & 1;
+                    tc::mbar_wait(&s.bar_ck_ready[c & 1], ph, failed);
+                    tc::mbar_wait(&s.bar_u_ready[c & 1], ph, failed);
+                    tc::mbar_wait(&s.bar_w_read[c & 1], ph, failed);
+                }
+                {
+                    const int st = c % NSTAGE;
+                    tc::tc_fence_after();
+                    const uint64_t dkv = tc::smem_desc_mn128(tc::smem_addr(s.st[st].k), 2 * tc::kTileBytes);
+                    product<false, true, false, 128>(tmem + col_ck(c), dth, dkv, false);
+                    product<false, true, false, 128>(tmem + col_ck(c), dtl, dkv, true);
+                    if (tc::elect_one()) tc::mma_commit(&s.bar_ckcv[c & 1]);
+                    __syncwarp();
+                }
+            }
+        }
+        else if (warp == 14) {
+            // =========================================================== loading thread: K, Q, V tiles by TMA
             tc::tma_prefetch_desc(&tm_q);
             tc::tma_prefetch_desc(&tm_k);
             tc::tma_prefetch_desc(&tm_v);
             auto issue_tma = [&](int c) {
-                if (c < nchunks) {
-                    const int st = c % NSTAGE;
+                const int st = c % NSTAGE;
+                if (tc::elect_one()) {
                     tc::mbar_expect_tx(&s.bar_full[st], 3 * tc::kTileBytes);
-                    tc::tma_load_4d(s.k[st], &tm_k, &s.bar_full[st], 0, c * CH, h, n);
-                    tc::tma_load_4d(s.q[st], &tm_q, &s.bar_full[st], 0, c * CH, h, n);
-                    tc::tma_load_4d(s.v[st], &tm_v, &s.bar_full[st], 0, c * CH, h, n);
+                    tc::tma_load_4d(s.st[st].k, &tm_k, &s.bar_full[st], 0, c * CH, h, n);
+                    tc::tma_load_4d(s.st[st].q, &tm_q, &s.bar_full[st], 0, c * CH, h, n);
+                    tc::tma_load_4d(s.st[st].v, &tm_v, &s.bar_full[st], 0, c * CH, h, n);
                 }
+                __syncwarp();
             };
-            issue_tma(0); issue_tma(1); issue_tma(2);
-            uint64_t dk[NSTAGE], dq[NSTAGE], dv[NSTAGE];
-#pragma unroll
-            for (int i = 0; i < NSTAGE; i++) {
-                dk[i] = tc::smem_desc(tc::smem_addr(s.k[i]));
-                dq[i] = tc::smem_desc(tc::smem_addr(s.q[i]));
-                dv[i] = tc::smem_desc(tc::smem_addr(s.v[i]));
+            for (int c = 0; c < NSTAGE && c < nchunks; c++) issue_tma(c);
+            for (int c = 0; c + NSTAGE < nchunks; c++) {
+                // the stage of chunk c is free once the helper warps have read y(c): they read V for v_old before, and
+                // the products that read Q and K completed before y(c) was readable
+                tc::mbar_wait(&s.bar_free[c & 1], (c >> 1) & 1, failed);
+                issue_tma(c + NSTAGE);
             }
-            const uint64_t daq[2] = {tc::smem_desc(tc::smem_addr(s.aq[0])), tc::smem_desc(tc::smem_addr(s.aq[1]))};
-            const uint64_t dth = tc::smem_desc(tc::smem_addr(s.th)), dtl = tc::smem_desc(tc::smem_addr(s.tl));
-            const uint64_t dck = tc::smem_desc(tc::smem_addr(s.ck)), dsb = tc::smem_desc(tc::smem_addr(s.sb));
-            const uint64_t duh = tc::smem_desc(tc::smem_addr(s.uh)), dul = tc::smem_desc(tc::smem_addr(s.ul));
-            auto sel = [&](const uint64_t (&d)[NSTAGE], int st) { return st == 0 ? d[0] : (st == 1 ? d[1] : d[2]); };
-
-            TCP_BEGIN
-            auto gram = [&](int c) {
-                const int st = c % NSTAGE;
-                tc::mbar_wait(&s.bar_full[st], (c / NSTAGE) & 1, failed);
-                TCP(9)
-                tc::tc_fence_after();
-                product<false, false, false>(tmem + COL_AKK, sel(dk, st), sel(dk, st), false);
-                product<false, false, false>(tmem + COL_AQK, sel(dq, st), sel(dk, st), false);
-                tc::mma_commit(&s.bar_gram);
-            };
-            auto ckcv = [&](int c) {
-                const int st = c % NSTAGE;
-                tc::mbar_wait(&s.bar_t_ready, c & 1, failed);
-                TCP(10)
-                tc::tc_fence_after();
-                product<false, true, false>(tmem + COL_CK, dth, sel(dk, st), false);
-                product<false, true, false>(tmem + COL_CK, dtl, sel(dk, st), true);
-                product<false, true, false>(tmem + COL_W, dth, sel(dv, st), false);
-                product<false, true, false>(tmem + COL_W, dtl, sel(dv, st), true);
-                tc::mma_commit(&s.bar_ckcv);
-            };
-            auto wprod = [&](int c) {       // w(c) = Cv(c) - Ck(c) S(c): needs Ck(c) as an operand and the bf16 copy of S(c)
-                tc::mbar_wait(&s.bar_ck_ready, c & 1, failed);
-                TCP(11)
-                tc::tc_fence_after();
-                product<false, true, true>(tmem + COL_W, dck, dsb, true);
-                tc::mma_commit(&s.bar_p);
-            };
-            gram(0);
-            ckcv(0);
-            wprod(0);
-#ifdef FWP_TC_PROF
-            for (int i = 0; i < 16; i++) _pt[i] = 0;
-            _pc = clock64();
-#endif
-            for (int c = 0; c < nchunks; c++) {
-                const int st = c % NSTAGE;
-                const bool has_next = c + 1 < nchunks;
-                if (has_next) gram(c + 1);
-                TCP(0)
-                // the state first (it is on the chain), then y
-                tc::mbar_wait(&s.bar_u_ready, c & 1, failed);
-                TCP(1)
-                tc::tc_fence_after();
-                product<true, true, false>(tmem + COL_S, sel(dk, st), duh, true);
-                product<true, true, false>(tmem + COL_S, sel(dk, st), dul, true);
-                tc::mma_commit(&s.bar_s);
-                TCP(2)
-                if (c > 0) { tc::mbar_wait(&s.bar_y_read, (c - 1) & 1, failed); tc::tc_fence_after(); }
-                TCP(3)
-                product<false, true, false>(tmem + COL_Y, sel(dq, st), dsb, false);
-                product<false, true, false>(tmem + COL_Y, c & 1 ? daq[1] : daq[0], duh, true);
-                tc::mma_commit(&s.bar_y);
-                TCP(4)
-                if (has_next) ckcv(c + 1);
-                TCP(5)
-                tc::mbar_wait(&s.bar_s_ready, c & 1, failed);      // bf16 copy of S(c+1) written
-                TCP(6)
-                if (has_next) wprod(c + 1);
-                TCP(7)
-                // y(c) read by the chain warps: its products (the last readers of this stage) are complete
-                if (c + NSTAGE < nchunks) {
-                    tc::mbar_wait(&s.bar_y_read, c & 1, failed);
-                    TCP(12)
-                    issue_tma(c + NSTAGE);
-                }
-                TCP(8)
-            }
-            TCP_END(32)
         }
     } else if (role == 1) {
         // =============================================================== preparing warps (one chunk ahead of the chain)
@@ -269,37 +301,26 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
             return (gtid < CH && t < p.L) ? __bfloat162float(bb[(long long)t * p.beta.sL]) : 0.f;
         };
         float bnext = load_beta(0);
-        TCP_BEGIN
+#pragma unroll 1
         for (int c = 0; c < nchunks; c++) {
-            float* bs = s.b[c & 1];
+            float* bs = s.b[c & 3];
             if (gtid < CH) bs[gtid] = bnext;
             bnext = load_beta(c + 1);
             tc::group_sync(2, NG);
-            TCP(0)
             tc::mbar_wait(&s.bar_gram, c & 1, failed);
-            TCP(1)
             tc::tc_fence_after();
             float nn[32];
-            {
-                float aqk[32];
-                tc::tmem_ld_16x64(nn, tlane + COL_AKK);
-                tc::tmem_ld_16x64(aqk, tlane + COL_AQK);
-                tc::tmem_wait_ld();
-                uint32_t pk[16];
+            tc::tmem_ld_16x64(nn, tlane + LANE_G + COL_AKK);
+            tc::tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const int c0 = 8 * j + 2 * t4;
-                    const float b0 = bs[c0], b1 = bs[c0 + 1];
-                    pk[2 * j] = pack_bf16(c0 <= r0 ? aqk[4 * j] : 0.f, c0 + 1 <= r0 ? aqk[4 * j + 1] : 0.f);
-                    pk[2 * j + 1] = pack_bf16(c0 <= r1 ? aqk[4 * j + 2] : 0.f, c0 + 1 <= r1 ? aqk[4 * j + 3] : 0.f);
-                    nn[4 * j] = c0 < r0 ? nn[4 * j] * b0 : 0.f;
-                    nn[4 * j + 1] = c0 + 1 < r0 ? nn[4 * j + 1] * b1 : 0.f;
-                    nn[4 * j + 2] = c0 < r1 ? nn[4 * j + 2] * b0 : 0.f;
-                    nn[4 * j + 3] = c0 + 1 < r1 ? nn[4 * j + 3] * b1 : 0.f;
-                }
-                tc::st_frag_swz(s.aq[c & 1], row0, pk, lane);
+            for (int j = 0; j < 8; j++) {
+                const int c0 = 8 * j + 2 * t4;
+                const float b0 = bs[c0], b1 = bs[c0 + 1];
+                nn[4 * j] = c0 < r0 ? nn[4 * j] * b0 : 0.f;
+                nn[4 * j + 1] = c0 + 1 < r0 ? nn[4 * j + 1] * b1 : 0.f;
+                nn[4 * j + 2] = c0 < r1 ? nn[4 * j + 2] * b0 : 0.f;
+                nn[4 * j + 3] = c0 + 1 < r1 ? nn[4 * j + 3] * b1 : 0.f;
             }
-            TCP(2)
             // N as four 16 x 16 blocks of this warp's rows, in the [2][4] fragment form of the warp-level mma helpers
             float N[4][2][4], X[4][2][4];
 #pragma unroll
@@ -377,7 +398,7 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
             unsigned ya[4];
             a_of(ya, Y);
             // block forward substitution, one block diagonal per round: round d gives X[gw][gw - d]
-#pragma unroll
+#pragma unroll 1
             for (int d = 1; d < 4; d++) {
                 tc::group_sync(2, NG);
                 if (gw >= d) {
@@ -428,9 +449,8 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
                         }
                 }
             }
-            TCP(3)
-            // T = I + X in two bf16 parts, rows r0, r1 of the K-major tiles.  The previous chunk's Ck, Cv products, which
-            // read these tiles, completed before this warp passed its wait for them at the end of the last iteration.
+            // T = I + X in two bf16 parts, rows r0, r1 of the K-major tiles; the previous chunk's [Ck | Cv] product,
+            // which reads these tiles, must have completed
             {
                 uint32_t hi[16], lo[16];
 #pragma unroll
@@ -445,66 +465,65 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
                         split_bf16(x0, x1, hi[2 * (2 * cbk + j)], lo[2 * (2 * cbk + j)]);
                         split_bf16(x2, x3, hi[2 * (2 * cbk + j) + 1], lo[2 * (2 * cbk + j) + 1]);
                     }
+                if (c > 0) tc::mbar_wait(&s.bar_ckcv[(c - 1) & 1], ((c - 1) >> 1) & 1, failed);
                 tc::st_frag_swz(s.th, row0, hi, lane);
                 tc::st_frag_swz(s.tl, row0, lo, lane);
             }
             tc::fence_proxy_async();
             tc::tc_fence_before();
             tc::mbar_arrive(&s.bar_t_ready);
-            TCP(4)
-
-            // Ck -> bf16 left operand of the w product
-            tc::mbar_wait(&s.bar_ckcv, c & 1, failed);
-            TCP(5)
+        }
+    } else if (role == 2) {
+        // =============================================================== helper warps
+        auto aq_out = [&](int c) {      // Aqk^T(c): rows are key steps i, columns query steps t; keep t >= i
+            tc::mbar_wait(&s.bar_gram, c & 1, failed);
             tc::tc_fence_after();
-            {
-                float ckr[32];
-                tc::tmem_ld_16x64(ckr, tlane + COL_CK);
-                tc::tmem_wait_ld();
-                uint32_t pk[16];
+            float a[32];
+            tc::tmem_ld_16x64(a, tlane + LANE_G + COL_AQK);
+            tc::tmem_wait_ld();
+            uint32_t pk[16];
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    pk[2 * j] = pack_bf16(ckr[4 * j], ckr[4 * j + 1]);
-                    pk[2 * j + 1] = pack_bf16(ckr[4 * j + 2], ckr[4 * j + 3]);
-                }
-                tc::st_frag_swz(s.ck, row0, pk, lane);
+            for (int j = 0; j < 8; j++) {
+                const int c0 = 8 * j + 2 * t4;
+                pk[2 * j] = pack_bf16(c0 >= r0 ? a[4 * j] : 0.f, c0 + 1 >= r0 ? a[4 * j + 1] : 0.f);
+                pk[2 * j + 1] = pack_bf16(c0 >= r1 ? a[4 * j + 2] : 0.f, c0 + 1 >= r1 ? a[4 * j + 3] : 0.f);
             }
+            tc::st_frag_swz(s.aq[c & 1], row0, pk, lane);
             tc::fence_proxy_async();
             tc::tc_fence_before();
-            tc::mbar_arrive(&s.bar_ck_ready);
-            TCP(6)
-        }
-        TCP_END(16)
-    } else {
-        // =============================================================== chain warps
-        TCP_BEGIN
-        for (int c = 0; c < nchunks; c++) {
-            const int st = c % NSTAGE, t0 = c * CH, nt = min(CH, p.L - t0);
-            const float* bs = s.b[c & 1];
-            // w -> u (two bf16 parts) and v_old
-            tc::mbar_wait(&s.bar_full[st], (c / NSTAGE) & 1, failed);      // the V tile read below (long complete)
+            tc::mbar_arrive(&s.bar_aq_ready[c & 1]);
+        };
+        auto ck_out = [&](int c) {      // Ck(c) -> bf16 left operand of the w product
+            tc::mbar_wait(&s.bar_ckcv[c & 1], (c >> 1) & 1, failed);
+            tc::tc_fence_after();
+            float a[32];
+            tc::tmem_ld_16x64(a, tlane + col_ck(c));
+            tc::tmem_wait_ld();
+            uint32_t pk[16];
+            pack_frag(pk, a);
+            tc::st_frag_swz(s.ck[c & 1], row0, pk, lane);
+            tc::fence_proxy_async();
+            tc::tc_fence_before();
+            tc::mbar_arrive(&s.bar_ck_ready[c & 1]);
+        };
+        // iteration c = -1 only prepares chunk 0
+#pragma unroll 1
+        for (int c = -1; c < nchunks; c++) {
+            const int st = (c + NSTAGE) % NSTAGE, t0 = c * CH, nt = min(CH, p.L - t0);
+            if (c + 1 < nchunks) aq_out(c + 1);
+            if (c < 0) { ck_out(0); continue; }
+            // v_old(c) = V - w
+            tc::mbar_wait(&s.bar_full[st], (c / NSTAGE) & 1, failed);
             tc::mbar_wait(&s.bar_p, c & 1, failed);
-            TCP(0)
             tc::tc_fence_after();
             {
                 float w[32];
-                tc::tmem_ld_16x64(w, tlane + COL_W);
+                tc::tmem_ld_16x64(w, tlane + col_w(c));
                 uint32_t vp[16];
-                tc::ld_frag_swz(vp, s.v[st], row0, lane);
-                const float br0 = bs[r0], br1 = bs[r1];
+                tc::ld_frag_swz(vp, s.st[st].v, row0, lane);
                 tc::tmem_wait_ld();
-                uint32_t hi[16], lo[16];
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    split_bf16(br0 * w[4 * j], br0 * w[4 * j + 1], hi[2 * j], lo[2 * j]);
-                    split_bf16(br1 * w[4 * j + 2], br1 * w[4 * j + 3], hi[2 * j + 1], lo[2 * j + 1]);
-                }
-                tc::st_frag_swz(s.uh, row0, hi, lane);
-                tc::st_frag_swz(s.ul, row0, lo, lane);
-                tc::fence_proxy_async();
                 tc::tc_fence_before();
-                tc::mbar_arrive(&s.bar_u_ready);
-                TCP(1)
+                tc::mbar_arrive(&s.bar_w_read[c & 1]);
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int c0 = 8 * j + 2 * t4;
@@ -518,40 +537,9 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
                             make_float2(__low2float(v1) - w[4 * j + 2], __high2float(v1) - w[4 * j + 3]);
                 }
             }
-            TCP(2)
-            // the new state -> bf16 copy (and, after the last chunk, back to global memory)
-            tc::mbar_wait(&s.bar_s, c & 1, failed);
-            TCP(3)
-            tc::tc_fence_after();
-            {
-                float S[32];
-                tc::tmem_ld_16x64(S, tlane + COL_S);
-                tc::tmem_wait_ld();
-                uint32_t pk[16];
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    pk[2 * j] = pack_bf16(S[4 * j], S[4 * j + 1]);
-                    pk[2 * j + 1] = pack_bf16(S[4 * j + 2], S[4 * j + 3]);
-                }
-                // the y product of this chunk still reads the old copy: wait for it before overwriting
-                TCP(4)
-                tc::mbar_wait(&s.bar_y, c & 1, failed);
-                TCP(5)
-                tc::st_frag_swz(s.sb, row0, pk, lane);
-                tc::fence_proxy_async();
-                tc::tc_fence_before();
-                tc::mbar_arrive(&s.bar_s_ready);
-                TCP(6)
-                if (c + 1 == nchunks) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const int c0 = 8 * j + 2 * t4;
-                        *reinterpret_cast<float2*>(W + (long long)r0 * p.wE + c0) = make_float2(S[4 * j], S[4 * j + 1]);
-                        *reinterpret_cast<float2*>(W + (long long)r1 * p.wE + c0) = make_float2(S[4 * j + 2], S[4 * j + 3]);
-                    }
-                }
-            }
-            // y -> global memory through a row-major staging tile (16-byte stores)
+            if (c + 1 < nchunks) ck_out(c + 1);     // before y: the w product of the next chunk waits for it
+            // y(c) -> global memory through a row-major staging tile (16-byte stores)
+            tc::mbar_wait(&s.bar_y, c & 1, failed);
             tc::tc_fence_after();
             {
                 float y[32];
@@ -559,15 +547,12 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
                 tc::tmem_wait_ld();
                 tc::tc_fence_before();
                 tc::mbar_arrive(&s.bar_y_read);
+                tc::mbar_arrive(&s.bar_free[c & 1]);        // this chunk's K, Q, V tiles have no reader left
                 uint32_t pk[16];
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    pk[2 * j] = pack_bf16(y[4 * j], y[4 * j + 1]);
-                    pk[2 * j + 1] = pack_bf16(y[4 * j + 2], y[4 * j + 3]);
-                }
+                pack_frag(pk, y);
                 tc::st_frag_rowmajor(s.ys, LDX, row0, pk, lane);
             }
-            tc::group_sync(1, NG);
+            tc::group_sync(3, NG);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int idx = gtid + NG * i, row = idx >> 3, part = (idx & 7) * 8;
@@ -575,10 +560,57 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
                     *reinterpret_cast<uint4*>(yb + (long long)(t0 + row) * p.out.sL + part) =
                         *reinterpret_cast<const uint4*>(s.ys + row * LDX + part);
             }
-            tc::group_sync(1, NG);
-            TCP(7)
+            tc::group_sync(3, NG);
         }
-        TCP_END(0)
+    } else {
+        // =============================================================== chain warps
+#pragma unroll 1
+        for (int c = 0; c < nchunks; c++) {
+            const float* bs = s.b[c & 3];
+            // w -> u (two bf16 parts)
+            tc::mbar_wait(&s.bar_p, c & 1, failed);
+            tc::tc_fence_after();
+            {
+                float w[32];
+                tc::tmem_ld_16x64(w, tlane + col_w(c));
+                const float br0 = bs[r0], br1 = bs[r1];
+                tc::tmem_wait_ld();
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    split_bf16(br0 * w[4 * j], br0 * w[4 * j + 1], hi[2 * j], lo[2 * j]);
+                    split_bf16(br1 * w[4 * j + 2], br1 * w[4 * j + 3], hi[2 * j + 1], lo[2 * j + 1]);
+                }
+                tc::st_frag_swz(s.uh, row0, hi, lane);
+                tc::st_frag_swz(s.ul, row0, lo, lane);
+                tc::fence_proxy_async();
+                tc::tc_fence_before();
+                tc::mbar_arrive(&s.bar_u_ready[c & 1]);
+            }
+            // S += K^T u_hi + K^T u_lo; the bf16 copy for the next chunk's products
+            tc::mbar_wait(&s.bar_d, c & 1, failed);
+            tc::tc_fence_after();
+            {
+                float dh[32], dl[32];
+                tc::tmem_ld_16x64(dh, tlane + COL_D);
+                tc::tmem_ld_16x64(dl, tlane + COL_D + 64);
+                tc::tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i++) S[i] += dh[i] + dl[i];
+                uint32_t pk[16];
+                pack_frag(pk, S);
+                tc::st_frag_swz(s.sb, row0, pk, lane);
+                tc::fence_proxy_async();
+                tc::tc_fence_before();
+                tc::mbar_arrive(&s.bar_s_ready);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int c0 = 8 * j + 2 * t4;
+            *reinterpret_cast<float2*>(W + (long long)r0 * p.wE + c0) = make_float2(S[4 * j], S[4 * j + 1]);
+            *reinterpret_cast<float2*>(W + (long long)r1 * p.wE + c0) = make_float2(S[4 * j + 2], S[4 * j + 3]);
+        }
     }
 
     tc::tc_fence_before();
@@ -589,7 +621,7 @@ delta_fwd_tc_kernel(const DeltaFwdParams p, const __grid_constant__ CUtensorMap 
         if (tid == 0) atomicExch(&g_tc_fault, 1);
         __syncthreads();
     }
-    if (warp == 8) tc::tmem_free(tmem, TMEM_COLS);
+    if (warp == 12) tc::tmem_free(tmem, TMEM_COLS);
 }
 
 // ------------------------------------------------------------------ host side

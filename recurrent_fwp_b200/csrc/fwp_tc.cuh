@@ -44,11 +44,24 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after `limit` polls (each poll itself waits up to the hardware's time limit), records
 // that in *failed (a shared-memory word every later wait of the CTA checks first) and returns.  A CTA that gave
 // up keeps walking its barriers without waiting, so it still reaches its clean-up (TMEM release) and exits.
+// The poll loop must not be unrolled: the kernels call this from dozens of places and their code has to stay
+// small enough for the instruction caches (an unrolled version made the tcgen05 forward 30 % slower).
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed, uint32_t limit = 1u << 18) {
     if (*failed) return;
+#pragma unroll 1
     for (uint32_t i = 0; i < limit; i++)
         if (mbar_try(bar, parity)) return;
     *failed = 1;
+}
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -159,10 +172,15 @@ __device__ __forceinline__ void ld_frag_swz(uint32_t (&pk)[16], const unsigned c
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
+// MN-major operand 128 elements wide: two 64-element tiles `block_bytes` apart (the leading-dimension byte offset)
+__device__ __forceinline__ uint64_t smem_desc_mn128(uint32_t saddr, uint32_t block_bytes) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((block_bytes >> 4) & 0x3FFF) << 16) | (64ull << 32) | (1ull << 46) |
+           (2ull << 61);
+}
 // Instruction descriptor: bf16 x bf16 -> fp32, M = 64, N = 64, dense; per-operand major and negation of A.
-__host__ __device__ constexpr uint32_t idesc(bool a_mn_major, bool b_mn_major, bool negate_a) {
+__host__ __device__ constexpr uint32_t idesc(bool a_mn_major, bool b_mn_major, bool negate_a, uint32_t n = 64) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((negate_a ? 1u : 0u) << 13) | ((a_mn_major ? 1u : 0u) << 15) |
-           ((b_mn_major ? 1u : 0u) << 16) | ((64u >> 3) << 17) | ((64u >> 4) << 24);
+           ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((64u >> 4) << 24);
 }
 __device__ __forceinline__ void mma_issue(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t id, uint32_t accumulate) {
     asm volatile(

@@ -397,3 +397,80 @@ def test_fp32_plans_at_4096_steps(fwp, d):
     util.record('delta fp32 d%d L4096' % d, tensor='state', rewound_cuda=util.max_abs(W, W0),
                 rewound_cpu32=util.max_abs(S32_back, W0))
     assert util.max_abs(W, W0) <= 5e-5
+
+
+@pytest.mark.parametrize('B,H,L', [(1, 1, 64), (2, 3, 100), (1, 2, 17), (1, 2, 300), (3, 1, 128), (4, 16, 1024)])
+def test_tcgen05_forward_plan_meets_the_oracle(fwp, B, H, L):
+    """Opt-in forward for bf16 streams at E = M = 64 ('delta.tc64' = 1): 64-step chunks, every 64-wide product a
+    tcgen05.mma with accumulators in tensor memory, K / Q / V tiles by TMA, five warp roles meeting at mbarriers.
+    Same bounds as the warp-level chunkwise plan; the backward (warp-level) consumes its v_old, so the gradients
+    check that tensor too.  No bounded wait may run out."""
+    from recurrent_fwp_b200 import _lib
+    d = 64
+    q, k, v, b, gy = [t.to(torch.bfloat16) for t in util.delta_inputs(501, B, H, L, d)]
+    W0 = torch.randn(B, H, d, d, generator=util.gen(502)) * 0.1
+    res = {}
+    try:
+        for tc in (1, 0):
+            _lib.tune('delta.tc64', tc)
+            W = W0.to(DEV)
+            leaves = [t.detach().to(DEV).requires_grad_() for t in (q, k, v, b)]
+            y = fwp.fast_weight_delta(*leaves, W)
+            kernel = _lib.last_kernel()
+            W_end = W.clone()
+            y.backward(gy.to(DEV))
+            res[tc] = (y.detach(), [l.grad for l in leaves], W_end, W, kernel)
+    finally:
+        _lib.tune('delta.tc64', 0)
+    assert _lib.device_fault() == 0
+    assert res[1][4] == 'delta_fwd_tc_kernel' and res[0][4] == 'delta_fwd_chunk_bf16_inv_kernel'
+    f = [t.float() for t in (q, k, v, b)]
+    y64, g64, S64 = run_loop(*f, W0, gy.float(), torch.float64)
+    y32, g32, _ = run_loop(*f, W0, gy.float(), torch.float32)
+    for tc in (1, 0):
+        y, grads, W_end, W_back, _ = res[tc]
+        bf16_anchor('delta bf16 d64 B%d H%d L%d tcgen05=%d' % (B, H, L, tc), y, grads, y64, g64, y32, g32)
+        assert util.max_abs(W_end, S64) <= 2e-4
+        assert util.max_abs(W_back, W0) <= 1e-5
+    assert util.max_abs(res[1][0].float(), res[0][0].float()) <= 1e-2 * y64.abs().max().item()
+
+
+def test_tcgen05_forward_is_the_kernel_that_ran(fwp):
+    """With the switch on, an eligible call runs delta_fwd_tc_kernel; a caller that asks for v_insert, or whose
+    state is not 8-byte aligned, gets the warp-level kernel (the tcgen05 plan does not apply), never an error."""
+    from recurrent_fwp_b200 import _lib
+    B, H, L, d = 1, 2, 64, 64
+    q, k, v, b, _ = [t.to(torch.bfloat16).to(DEV) for t in util.delta_inputs(503, B, H, L, d)]
+    D = _lib.desc
+    y = torch.empty(B, H, L, d, device=DEV, dtype=torch.bfloat16)
+    vo = torch.empty(B, H, L, d, device=DEV)
+    vi = torch.empty(B, H, L, d, device=DEV)
+    stream, dev = _lib.stream_and_device(q)
+    try:
+        _lib.tune('delta.tc64', 1)
+        for v_ins, want in ((None, 'delta_fwd_tc_kernel'), (vi, 'delta_fwd_chunk_bf16_inv_kernel')):
+            W = torch.zeros(B, H, d, d, device=DEV)
+            _lib.check(_lib.lib.fwp_fast_weight_forward(B, H, L, d, d, D(q), D(k), D(v), D(b), D(vo), D(v_ins), D(W), D(y),
+                                                        _lib.BF16, stream, dev), 'forward')
+            assert _lib.last_kernel() == want
+    finally:
+        _lib.tune('delta.tc64', 0)
+    torch.cuda.synchronize()
+    assert _lib.device_fault() == 0
+
+
+def test_a_wait_that_runs_out_is_reported_not_hung(fwp):
+    """Failure detection without a fault: a probe kernel waits (64 polls) on a barrier nothing completes; it returns,
+    the device flag reads 1 once, and the context keeps working."""
+    from recurrent_fwp_b200 import _lib
+    assert _lib.device_fault() == 0
+    stream, dev = _lib.stream_and_device(torch.zeros(1, device=DEV))
+    _lib.check(_lib.lib.fwp_debug_bounded_wait_probe(64, stream, dev), 'probe')
+    torch.cuda.synchronize()
+    assert _lib.device_fault() == 1
+    assert _lib.device_fault() == 0
+    assert _lib.lib.fwp_debug_bounded_wait_probe(0, stream, dev) == 2      # poll limit out of range: refused
+    q, k, v, b, gy = util.delta_inputs(504, 1, 2, 33, 16)
+    y, _, _ = run_cuda(fwp, q, k, v, b, torch.zeros(1, 2, 16, 16, device=DEV), gy)
+    y64, _, _ = run_loop(q, k, v, b, torch.zeros(1, 2, 16, 16), gy, torch.float64)
+    assert util.max_abs(y, y64) <= 1e-4
