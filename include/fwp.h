@@ -199,9 +199,13 @@ int64_t fwp_rec_update_fwm_tanh_scratch_floats(int N, int H, int D);
  * the library until the process exits), so N*H*(3*D*D+D) must not exceed it; larger
  * problems return FWP_ERR_NOALLOC_TOO_LARGE and launch nothing.  The first call on a
  * device looks up the array's device address (cudaGetSymbolAddress, that device
- * current): make it before any stream capture.  All calls on a device share the
- * array: calls that may overlap on the GPU race, calls ordered on one stream do not.
- * Allocates nothing (no cudaMalloc / cudaFree / allocating library call). */
+ * current): make it before any stream capture.  With lazy module loading the CUDA
+ * runtime creates the array (and the kernels' local-memory pool) when this module is
+ * first used on a device, so make the first recurrent-delta-net call of a process
+ * (forward or backward) on each device before the device memory is handed out
+ * completely; from then on the function itself allocates nothing (no cudaMalloc /
+ * cudaFree / allocating library call).  All calls on a device share the array:
+ * calls that may overlap on the GPU race, calls ordered on one stream do not. */
 #define FWP_NOALLOC_SCRATCH_FLOATS (2 * 1024 * 1024)
 int fwp_rec_update_fwm_tanh_backward_noalloc(int N, int H, int L, int D,
                                              const fwp_tensor* q, const fwp_tensor* k,

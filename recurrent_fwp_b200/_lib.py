@@ -169,6 +169,18 @@ def device_fault():
     return int(lib.fwp_delta_device_fault())
 
 
+def raise_on_device_fault(what):
+    """With FWP_CHECK_DEVICE_FAULT=1 in the environment the delta-rule wrappers call this after every launch: it
+    synchronises the device and raises if a bounded wait inside a kernel ran out (the launch then produced wrong
+    numbers instead of hanging).  Off by default because of the synchronisation; a trainer can instead poll
+    ``device_fault()`` at step or epoch boundaries."""
+    if _CHECK_FAULT and device_fault() != 0:
+        raise RuntimeError('%s: a bounded wait inside the kernel ran out; its results are invalid' % what)
+
+
+_CHECK_FAULT = os.environ.get('FWP_CHECK_DEVICE_FAULT', '0') == '1'
+
+
 def launch_count():
     return int(lib.fwp_launch_count())
 

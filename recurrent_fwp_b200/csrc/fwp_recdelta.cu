@@ -560,6 +560,8 @@ FWP_API int fwp_rec_update_fwm_tanh_backward_noalloc(int N, int H, int L, int D,
                                                      const fwp_tensor* grad_Rv, const fwp_tensor* grad_rb,
                                                      int io_dtype, void* stream, int device) {
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0) return FWP_ERR_SHAPE;
+    if (io_dtype != FWP_F32) return FWP_ERR_DTYPE;          // the same order of checks as the regular entry point,
+    if (!pad_dim(D)) return FWP_ERR_UNSUPPORTED;            // so an unsupported call reports the same status from both
     if (fwp_rec_update_fwm_tanh_scratch_floats(N, H, D) > (int64_t)FWP_NOALLOC_SCRATCH_FLOATS)
         return FWP_ERR_NOALLOC_TOO_LARGE;
     DeviceGuard guard(device);

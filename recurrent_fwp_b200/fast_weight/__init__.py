@@ -46,6 +46,7 @@ class DeltaFastWeight(torch.autograd.Function):
             N, H, L, E, M, _lib.desc(Qc), _lib.desc(Kc), _lib.desc(Vc), _lib.desc(bc),
             _lib.desc(V_old), _lib.desc(None), _lib.desc(Wd), _lib.desc(out),
             dt, stream, dev), 'fast_weight_forward')
+        _lib.raise_on_device_fault('fast_weight_forward')
         ctx.save_for_backward(Qc, Kc, Vc, bc, V_old, V_insert, W)
         return out
 
@@ -65,6 +66,7 @@ class DeltaFastWeight(torch.autograd.Function):
             _lib.desc(V_old), _lib.desc(None), _lib.desc(grad_out), _lib.desc(W.detach()),
             _lib.desc(grad_Q), _lib.desc(grad_K), _lib.desc(grad_V), _lib.desc(grad_beta),
             _lib.io_dtype(Q), stream, dev), 'fast_weight_backward')
+        _lib.raise_on_device_fault('fast_weight_backward')
         return grad_Q, grad_K, grad_V, grad_beta, None
 
 

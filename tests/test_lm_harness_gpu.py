@@ -44,7 +44,7 @@ def test_training_step_gradients_match_the_checker(fwp):
 
 
 def test_configs4_language_model_shape_runs_at_reduced_depth(fwp):
-    """d_model 256, 8 heads of 32, FF 1024, vocab 32768, L=512 (BASELINE configs[4] second part) at
+    """d_model 256, 8 heads of 32, FF 1024, vocab 32768, L=512 (the end-to-end language-model shape of the scale-out benchmark) at
     2 layers and batch 2: finite losses near log(vocab) for random weights."""
     torch.manual_seed(3)
     model = DeltaNetLM(32768, 2, 8, 256, 32, 1024).to(DEV).eval()
