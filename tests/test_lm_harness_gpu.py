@@ -6,7 +6,7 @@ import torch
 
 from recurrent_fwp_b200.lm_harness import DeltaNetLM
 from tests import util
-from tests.test_lm_harness_cpu import build, checker_delta
+from tests.test_lm_harness_cpu import CHECKER_OPS, RECURRENT, build, checker_delta, run_recurrent_fixture
 
 pytestmark = pytest.mark.gpu
 DEV = 'cuda:0'
@@ -39,6 +39,30 @@ def test_training_step_gradients_match_the_checker(fwp):
         loss, _ = model(tokens[:L].to(dev), tokens[1:L + 1].to(dev))
         loss.mean().backward()
         grads[name] = {n: p.grad.detach().cpu() for n, p in model.named_parameters()}
+    for n, g in grads['cpu'].items():
+        assert util.scaled_rel(grads['gpu'][n], g) <= 1e-3, n
+
+
+@pytest.mark.parametrize('name', sorted(RECURRENT))
+def test_recurrent_layers_match_the_reference_fixture(fwp, name):
+    """attn_type 134 / 254 / 934 with the CUDA ops (delta rule + delta RNN v2, delta rules + delta LSTM v4, recurrent
+    delta net) under their layer classes: plain forward and two carried segments against the reference's fixture."""
+    gd = util.golden(name)
+    model = build(gd, None, DEV, attn_type=RECURRENT[name])     # default ops: the CUDA library
+    run_recurrent_fixture(gd, model, gd['tokens'].to(DEV), 1e-4)
+
+
+@pytest.mark.parametrize('name', sorted(RECURRENT))
+def test_recurrent_layers_training_step_gradients_match_the_checker(fwp, name):
+    gd = util.golden(name)
+    tokens = gd['tokens']
+    L = gd['loss_plain'].shape[0]
+    grads = {}
+    for arm, ops, dev in (('gpu', None, DEV), ('cpu', CHECKER_OPS, 'cpu')):
+        model = build(gd, None, dev, attn_type=RECURRENT[name], ops=ops).train()
+        loss, _ = model(tokens[:L].to(dev), tokens[1:L + 1].to(dev))
+        loss.mean().backward()
+        grads[arm] = {n: p.grad.detach().cpu() for n, p in model.named_parameters()}
     for n, g in grads['cpu'].items():
         assert util.scaled_rel(grads['gpu'][n], g) <= 1e-3, n
 
