@@ -57,6 +57,7 @@ enum TuneKey {
     T_DELTA_BWD_BULK,       // "delta_bwd.bulk": 1 bulk-copy staging in the d = 16 backward, 0 cp.async
     T_DELTA_BWD_CHUNK16,    // "delta_bwd.16.chunk": 32 or 16 steps per staged chunk
     T_LSTM_FWD_SPLIT32, T_LSTM_BWD_SPLIT32, T_RNN_FWD_SPLIT32, T_RNN_BWD_SPLIT32, T_REC_FWD_SPLIT32, T_REC_BWD_SPLIT32,
+    T_REC_FWD_WARP32,       // "rec_fwd.32.warp": 1 short-chain one-warp forward of the recurrent delta net at d <= 32, 0 the general kernel
     T_COUNT
 };
 int tune_get(TuneKey key, int fallback);

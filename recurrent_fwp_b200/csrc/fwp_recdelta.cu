@@ -138,6 +138,165 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_fwd_kern
     if (ok && g.s == 0) hp[g.idx] = hv;
 }
 
+// ------------------------------------------------- forward, one warp per sequence, d <= 32
+// The per-step chain of the kernel above at d = 32 is one warp's latency: every instruction waits for the one
+// before it.  This form keeps the arithmetic and shortens the chain:
+//   * the two maxima of the softmaxes are one warp-wide reduction instruction each (redux.sync.max.f32);
+//   * the softmax denominators are summed by every lane from the exchanged vectors it reads anyway (no shuffle tree);
+//   * y_t = S_t^T q is taken from the matrix *before* the update, y = (S^T q + (k.q) c) with c the update's scale, so
+//     the three dot products of a step run side by side and the rank-one update leaves the chain;
+//   * beta's feedback term r_b . tanh(h) is a lane-local product summed by shuffles beside the matrix products;
+//   * tanh by exp2 / reciprocal (a short polynomial near zero), outputs through running pointers.
+__device__ __forceinline__ float warp_max_f32(float x) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+// |error| below 2e-7 over the whole range: odd polynomial to x^9 under 0.25, 1 - 2 / (e^{2|x|} + 1) above
+__device__ __forceinline__ float tanh_fast(float x) {
+    const float ax = fabsf(x), x2 = x * x;
+    const float e = ex2_approx(ax * 2.885390082f);              // e^{2|x|}; inf above 44 gives exactly 1
+    const float big = copysignf(fmaf(-2.f, rcp_approx(e + 1.f), 1.f), x);
+    float pl = fmaf(x2, 2.1869488e-2f, -5.3968254e-2f);
+    pl = fmaf(pl, x2, 1.3333334e-1f);
+    pl = fmaf(pl, x2, -3.3333334e-1f);
+    const float small = fmaf(x * x2, pl, x);
+    return ax < 0.25f ? small : big;
+}
+// Sum over the warp of values in [0, 1] whose total is at least 1 (softmax numerators after the shift by the
+// maximum): fixed point with 26 fractional bits and the integer warp reduction.  The total is below 2^31, each
+// addend is off by at most 2^-27, so the sum is good to 32 * 2^-27 relative -- two ulp -- and does not depend on
+// any order of addition.  Returns 2^26 times the sum.
+__device__ __forceinline__ float warp_sum_unit_scaled(float x) {
+    return (float)__reduce_add_sync(0xffffffffu, __float2uint_rn(x * 67108864.f));
+}
+// Sum over the warp of signed values bounded by 2^24 in magnitude after the caller's scaling.
+__device__ __forceinline__ float warp_sum_scaled(float x) {
+    return (float)__reduce_add_sync(0xffffffffu, __float2int_rn(x));
+}
+constexpr float kLog2e = 1.4426950408889634f;
+
+// FULL: the head dimension is exactly 32 (no padding lanes, no predicates in the step).
+template <int TC, bool FULL>
+__global__ void __launch_bounds__(128) rec_fwd_warp32_kernel(const RecFwdParams p) {
+    constexpr int D = 32;
+    using G = Geo<D, 1>;
+    const G g;
+    const int n = g.seq / p.H, h = g.seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = slot_smem(smem_all, g);
+    using Stage = RecFwdStage<D, TC>;
+    constexpr int kTile = r4(TC * D);     // distance between the q, k and v tiles of a stage
+    constexpr int kX = 3 * D;             // ht[D], eq[D], ek[D]
+    for (int i = g.tid; i < 2 * Stage::kFloats + kX; i += G::NT) smem[i] = 0.f;
+    float* xh = smem + 2 * Stage::kFloats;
+    float* xq = xh + D;
+    float* xk = xq + D;
+
+    Src<float> sq, sk, sv, sb;
+    sq.init(p.qx, n, h, p.D);
+    sk.init(p.kx, n, h, p.D);
+    sv.init(p.vx, n, h, p.D);
+    sb.init(p.bx, n, h, 1);
+
+    f2 S[G::NP], Rq[G::NP], Rk[G::NP], Rv[G::NP];
+    load_cols(g, S, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
+    load_cols(g, Rq, p.Rq + h * p.rH, p.rE, p.D, p.D);
+    load_cols(g, Rk, p.Rk + h * p.rH, p.rE, p.D, p.D);
+    load_cols(g, Rv, p.Rv + h * p.rH, p.rE, p.D, p.D);
+    const bool ok = FULL || g.idx < p.D;
+    // beta's feedback r_b . tanh(h): lane products in fixed point (24 bits below the largest |r_b|), integer warp sum
+    float rbl = ok ? p.rb[h * p.rbH + g.idx] : 0.f;
+    const float rbmax = warp_max_f32(fabsf(rbl));
+    const float rb_unscale = rbmax * (1.f / 8388608.f);         // 2^-23 of the largest entry
+    rbl = rbmax > 0.f ? rbl * (8388608.f / rbmax) : 0.f;
+    float* hp = p.h + n * p.hN + h * p.hH;
+    float hv = ok ? hp[g.idx] : 0.f;
+    const int col = ok ? g.idx : 0;
+    float* po = reinterpret_cast<float*>(p.out.p) + n * p.out.sN + h * p.out.sH + col;
+    float* pq = reinterpret_cast<float*>(p.q_out.p) + n * p.q_out.sN + h * p.q_out.sH + col;
+    float* pk = reinterpret_cast<float*>(p.k_out.p) + n * p.k_out.sN + h * p.k_out.sH + col;
+    float* pv = reinterpret_cast<float*>(p.v_out.p) + n * p.v_out.sN + h * p.v_out.sH + col;
+    float* pvo = reinterpret_cast<float*>(p.v_old.p) + n * p.v_old.sN + h * p.v_old.sH + col;
+    float* pb = reinterpret_cast<float*>(p.b_out.p) + n * p.b_out.sN + h * p.b_out.sH;
+    __syncwarp();
+
+    const int nchunks = (p.L + TC - 1) / TC;
+    auto issue = [&](int c) {
+        Stage s; s.bind(smem + (c & 1) * Stage::kFloats);
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        s.q.template load<G::NT>(sq, t0, nt, g.tid);
+        s.k.template load<G::NT>(sk, t0, nt, g.tid);
+        s.v.template load<G::NT>(sv, t0, nt, g.tid);
+        s.b.template load<G::NT>(sb, t0, nt, g.tid);
+        cp_async_commit();
+    };
+    issue(0);
+    for (int c = 0; c < nchunks; c++) {
+        if (c + 1 < nchunks) { issue(c + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncwarp();
+        const float* row = smem + (c & 1) * Stage::kFloats + g.idx;     // this lane's column of the q tile
+        const float* brow = smem + (c & 1) * Stage::kFloats + 3 * kTile;
+        const int nt = min(TC, p.L - c * TC);
+#pragma unroll 1
+        for (int t = 0; t < nt; t++, row += D, brow++) {
+            const float qin = row[0], kin = row[kTile], vin = row[2 * kTile], bin = brow[0];
+            const float th = tanh_fast(hv);                 // padding lanes hold hv = 0
+            xh[g.idx] = th;
+            __syncwarp();
+            const float bsum = warp_sum_scaled(th * rbl);
+            f2 hs[G::NP];
+            lds_slice<G::NR>(hs, xh);
+            const float qh = qin + dot2<G::NP>(Rq, hs);
+            const float kh = kin + dot2<G::NP>(Rk, hs);
+            const float vv = vin + dot2<G::NP>(Rv, hs);
+            const float mk = warp_max_f32(ok ? kh : -INFINITY);
+            const float mq = warp_max_f32(ok ? qh : -INFINITY);
+            const float ek = ok ? ex2_approx((kh - mk) * kLog2e) : 0.f;
+            const float eq = ok ? ex2_approx((qh - mq) * kLog2e) : 0.f;
+            xk[g.idx] = ek;
+            xq[g.idx] = eq;
+            __syncwarp();
+            const float invk = rcp_approx(warp_sum_unit_scaled(ek)) * 67108864.f;
+            const float invq = rcp_approx(warp_sum_unit_scaled(eq)) * 67108864.f;
+            const float beta = rcp_approx(1.f + ex2_approx(-kLog2e * fmaf(bsum, rb_unscale, bin)));
+            f2 ks[G::NP], qs[G::NP];
+            lds_slice<G::NR>(ks, xk);
+            lds_slice<G::NR>(qs, xq);
+            const float vo_un = dot2<G::NP>(S, ks);
+            const float y_un = dot2<G::NP>(S, qs);
+            const float kq_un = dot2<G::NP>(ks, qs);
+            const float vo = vo_un * invk;
+            const float cc = beta * (vv - vo) * invk;       // S += ek (x) cc
+            const float y = fmaf(kq_un, cc, y_un) * invq;
+            axpy2<G::NP>(S, ks, cc);
+            hv = ok ? y : 0.f;
+            if (ok) {
+                *po = y;
+                *pq = eq * invq;
+                *pk = ek * invk;
+                *pv = vv;
+                *pvo = vo;
+                if (g.idx == 0) *pb = beta;
+            }
+            po += p.out.sL; pq += p.q_out.sL; pk += p.k_out.sL; pv += p.v_out.sL; pvo += p.v_old.sL; pb += p.b_out.sL;
+        }
+        __syncwarp();
+    }
+    store_cols(g, S, p.W + n * p.wN + h * p.wH, p.wE, p.D, p.D);
+    if (ok) hp[g.idx] = hv;
+}
+
 // ------------------------------------------------------------------ backward
 struct RecBwdParams {
     Row4 q, k, v, beta, v_old, od, gy, gq, gk, gv, gb;
@@ -370,6 +529,20 @@ static int launch_rec_fwd(const RecFwdParams& p, int nseq, cudaStream_t st) {
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
 
+template <int TC>
+static int launch_rec_fwd_warp32(const RecFwdParams& p, int nseq, cudaStream_t st) {
+    auto kern = p.D == 32 ? rec_fwd_warp32_kernel<TC, true> : rec_fwd_warp32_kernel<TC, false>;
+    const size_t bytes = (2 * RecFwdStage<32, TC>::kFloats + 3 * 32) * sizeof(float);
+    int slots = 4;
+    while (nseq % slots) slots >>= 1;
+    if (int rc = smem_optin(kern, bytes * slots)) return rc;
+    kern<<<nseq / slots, 32 * slots, bytes * slots, st>>>(p);
+    count_launch();
+    note_kernel("rec_fwd_warp32_kernel");
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
 template <int D, int SPLIT, int TC>
 static int launch_rec_bwd(const RecBwdParams& p, int nseq, cudaStream_t st) {
     auto kern = rec_bwd_kernel<D, SPLIT, TC>;
@@ -443,6 +616,7 @@ FWP_API int fwp_rec_update_fwm_tanh_forward(int N, int H, int L, int D,
         case 32: {
             const int sp = tune_get(T_REC_FWD_SPLIT32, 1);
             // measured on B200 (512 sequences x 256 steps): 1 -> 0.36 ms, 2 -> 0.38 ms, 4 -> 0.41 ms
+            if (sp == 1 && tune_get(T_REC_FWD_WARP32, 1)) return launch_rec_fwd_warp32<16>(p, N * H, st);
             if (sp == 2) return launch_rec_fwd<32, 2, 16>(p, N * H, st);
             if (sp == 4) return launch_rec_fwd<32, 4, 16>(p, N * H, st);
             return launch_rec_fwd<32, 1, 16>(p, N * H, st);
