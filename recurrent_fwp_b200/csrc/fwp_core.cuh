@@ -124,7 +124,49 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+// ---- short-latency forms of the transcendental steps on the recurrent chains (one MUFU each, no range split) ----
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+// e^x for x <= 0 (softmax numerators after the shift): relative error about 2e-7 + 1e-7 |x|
+__device__ __forceinline__ float exp_neg(float x) { return ex2_approx(x * kLog2e); }
+__device__ __forceinline__ float sigmoidf_(float x) { return rcp_approx(1.f + ex2_approx(-kLog2e * x)); }
+// |error| below 2e-7 over the whole range: odd polynomial to x^9 under 0.25, 1 - 2 / (e^{2|x|} + 1) above
+__device__ __forceinline__ float tanh_fast(float x) {
+    const float ax = fabsf(x), x2 = x * x;
+    const float e = ex2_approx(ax * 2.885390082f);              // e^{2|x|}; inf above 44 gives exactly 1
+    const float big = copysignf(fmaf(-2.f, rcp_approx(e + 1.f), 1.f), x);
+    float pl = fmaf(x2, 2.1869488e-2f, -5.3968254e-2f);
+    pl = fmaf(pl, x2, 1.3333334e-1f);
+    pl = fmaf(pl, x2, -3.3333334e-1f);
+    const float small = fmaf(x * x2, pl, x);
+    return ax < 0.25f ? small : big;
+}
+// Warp-wide maximum in one instruction (sm_100a).
+__device__ __forceinline__ float warp_max_f32(float x) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+    return r;
+}
+// Sum over the warp of values in [0, 1] whose total is at least 1 (softmax numerators after the shift by the
+// maximum): fixed point with 26 fractional bits and the integer warp reduction.  The total is below 2^31, each
+// addend is off by at most 2^-27, so the sum is good to 32 * 2^-27 relative -- two ulp -- and does not depend on
+// any order of addition.  Returns 2^26 times the sum.
+__device__ __forceinline__ float warp_sum_unit_scaled(float x) {
+    return (float)__reduce_add_sync(0xffffffffu, __float2uint_rn(x * 67108864.f));
+}
+// Sum over the warp of signed values bounded by 2^24 in magnitude after the caller's scaling.
+__device__ __forceinline__ float warp_sum_scaled(float x) {
+    return (float)__reduce_add_sync(0xffffffffu, __float2int_rn(x));
+}
 
 template <int D_, int SPLIT_>
 struct Geo {
@@ -208,6 +250,7 @@ __device__ __forceinline__ void cta_sync() {
 // this call (callers rotate slots).  Contains one cta_sync when WPS > 1.
 template <class G, bool IS_MAX>
 __device__ __forceinline__ float cta_allreduce_idx(const G& g, float x, float* slot) {
+    if constexpr (IS_MAX && G::WPS == 1) return warp_max_f32(x);      // every idx sits in this warp (SPLIT times)
     x = IS_MAX ? warp_max_idx<G::SPLIT>(x) : warp_sum_idx<G::SPLIT>(x);
     if constexpr (G::WPS > 1) {
         if (g.lane == 0) slot[g.warp] = x;
@@ -218,6 +261,14 @@ __device__ __forceinline__ float cta_allreduce_idx(const G& g, float x, float* s
         x = r;
     }
     return x;
+}
+
+// Denominator of a softmax over idx whose numerators were shifted by the maximum (each in [0, 1], the largest
+// exactly 1; padding lanes pass 0).  One warp per sequence: the integer warp reduction, exact to two ulp.
+template <class G>
+__device__ __forceinline__ float softmax_den(const G& g, float ex, float* slot) {
+    if constexpr (G::WPS == 1) return warp_sum_unit_scaled(ex) * (1.f / (67108864.f * G::SPLIT));
+    else return cta_allreduce_idx<G, false>(g, ex, slot);
 }
 
 // slice of a shared-memory row -> packed registers (row must be 16-byte aligned)

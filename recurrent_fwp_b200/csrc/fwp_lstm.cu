@@ -86,13 +86,29 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) lstm_fwd_ker
         cp_async_commit();
     };
     issue(0);
+    // running output pointers of this thread's column (threads that store nothing keep a valid address)
+    const bool writer = ok && g.s == 0;
+    const int col = writer ? g.idx : 0;
+    auto colptr = [&](const Row4& r) { return reinterpret_cast<float*>(r.p) + n * r.sN + h * r.sH + col; };
+    float* po = colptr(p.out);
+    float* pc = colptr(p.cell);
+    float* pg[3] = {colptr(p.gate[0]), colptr(p.gate[1]), colptr(p.gate[2])};
+    float* pvo[3] = {colptr(p.v_old[0]), colptr(p.v_old[1]), colptr(p.v_old[2])};
+    float* pnm = VAR == 1 ? po : colptr(p.nmz);
+    const long long snm = VAR == 1 ? 0 : p.nmz.sL;
     int par = 0;
     for (int c = 0; c < nchunks; c++) {
         if (c + 1 < nchunks) { issue(c + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         __syncthreads();
         Stage s; s.bind(smem + (c & 1) * Stage::kFloats);
-        const int t0 = c * TC, nt = min(TC, p.L - t0);
-        for (int t = 0; t < nt; t++) {
+        const int nt = min(TC, p.L - c * TC);
+        // the nine tiles of a stage lie r4(TC * D) floats apart (z, k, v of gate 0, then gate 1, gate 2)
+        constexpr int kTile = r4(TC * D);
+        const float* zcol = s.z[0].f + g.idx;          // + (3 a + 0) kTile: z of gate a ; + (3 a + 2) kTile: v
+        const float* krow = s.k[0].f + g.off;          // + 3 a kTile: k of gate a
+        const float* brow = s.b[0].f;                  // + a r4(TC): beta of gate a
+#pragma unroll 1
+        for (int t = 0; t < nt; t++, zcol += D, krow += D, brow++) {
             float* xv = xch + par * kX;
             float* slot = xv + D;
             par ^= 1;
@@ -102,9 +118,9 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) lstm_fwd_ker
                 xe = hv;
             } else {
                 const float mx = cta_allreduce_idx<G, true>(g, ok ? hv : -INFINITY, slot);
-                xe = ok ? expf(hv - mx) : 0.f;
-                const float den = cta_allreduce_idx<G, false>(g, xe, slot + 8);
-                inv = 1.f / (den + kLstmEps);
+                xe = ok ? exp_neg(hv - mx) : 0.f;
+                const float den = softmax_den(g, xe, slot + 8);
+                inv = rcp_approx(den + kLstmEps);
                 xe *= inv;
             }
             if (g.s == 0) xv[g.idx] = xe;
@@ -115,11 +131,11 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) lstm_fwd_ker
 #pragma unroll
             for (int a = 0; a < 3; a++) {
                 f2 kk[G::NP];
-                lds_slice<G::NR>(kk, s.k[a].f + t * D + g.off);
+                lds_slice<G::NR>(kk, krow + 3 * a * kTile);
                 vo[a] = reduce_split<SPLIT>(dot2<G::NP>(S[a], kk));
-                const float u = s.b[a].f[t] * (s.v[a].f[t * D + g.idx] - vo[a]);
+                const float u = brow[a * r4(TC)] * (zcol[(3 * a + 2) * kTile] - vo[a]);
                 axpy2<G::NP>(S[a], kk, u);
-                pre[a] = reduce_split<SPLIT>(dot2<G::NP>(S[a], xs)) + s.z[a].f[t * D + g.idx];
+                pre[a] = reduce_split<SPLIT>(dot2<G::NP>(S[a], xs)) + zcol[3 * a * kTile];
             }
             const float gi = sigmoidf_(pre[0]);
             const float uu = (VAR == 4) ? pre[1] : sigmoidf_(pre[1]);
@@ -128,24 +144,25 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) lstm_fwd_ker
             float hn = go * cv;
             if constexpr (VAR == 1) {
                 const float mx = cta_allreduce_idx<G, true>(g, ok ? hn : -INFINITY, slot);
-                const float ex = ok ? expf(hn - mx) : 0.f;
-                const float den = cta_allreduce_idx<G, false>(g, ex, slot + 8);
-                hn = ex / den;
+                const float ex = ok ? exp_neg(hn - mx) : 0.f;
+                hn = ex * rcp_approx(softmax_den(g, ex, slot + 8));
             } else if constexpr (VAR == 3) {
-                hn += s.z[1].f[t * D + g.idx];
+                hn += zcol[3 * kTile];
             }
             hv = hn;
-            if (ok && g.s == 0) {
-                const int tt = t0 + t;
-                put<float>(p.out, n, h, tt, g.idx, hn);
-                put<float>(p.cell, n, h, tt, g.idx, cv);
-                put<float>(p.gate[0], n, h, tt, g.idx, gi);
-                put<float>(p.gate[1], n, h, tt, g.idx, uu);
-                put<float>(p.gate[2], n, h, tt, g.idx, go);
+            if (writer) {
+                *po = hn;
+                *pc = cv;
+                *pg[0] = gi;
+                *pg[1] = uu;
+                *pg[2] = go;
 #pragma unroll
-                for (int a = 0; a < 3; a++) put<float>(p.v_old[a], n, h, tt, g.idx, vo[a]);
-                if constexpr (VAR != 1) put<float>(p.nmz, n, h, tt, g.idx, xe);
+                for (int a = 0; a < 3; a++) *pvo[a] = vo[a];
+                if constexpr (VAR != 1) *pnm = xe;
             }
+            po += p.out.sL; pc += p.cell.sL; pnm += snm;
+#pragma unroll
+            for (int a = 0; a < 3; a++) { pg[a] += p.gate[a].sL; pvo[a] += p.v_old[a].sL; }
         }
         __syncthreads();
     }

@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_fwd_kern
             float* slot = xk + D;
             par ^= 1;
             const int o = t * D + g.idx;
-            if (g.s == 0) xh[g.idx] = ok ? tanhf(hv) : 0.f;
+            if (g.s == 0) xh[g.idx] = ok ? tanh_fast(hv) : 0.f;
             cta_sync<G::WPS>();
             f2 hs[G::NP];
             lds_slice<G::NR>(hs, xh + g.off);
@@ -108,11 +108,11 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_fwd_kern
             const float beta = sigmoidf_(s.b.f[t] + reduce_split<SPLIT>(dot2<G::NP>(rb, hs)));
             const float mq = cta_allreduce_idx<G, true>(g, ok ? qh : -INFINITY, slot);
             const float mk = cta_allreduce_idx<G, true>(g, ok ? kh : -INFINITY, slot + 8);
-            const float eq = ok ? expf(qh - mq) : 0.f;
-            const float ek = ok ? expf(kh - mk) : 0.f;
+            const float eq = ok ? exp_neg(qh - mq) : 0.f;
+            const float ek = ok ? exp_neg(kh - mk) : 0.f;
             if (g.s == 0) { xq[g.idx] = eq; xk[g.idx] = ek; }
-            const float invq = 1.f / cta_allreduce_idx<G, false>(g, eq, slot + 16);
-            const float invk = 1.f / cta_allreduce_idx<G, false>(g, ek, slot + 24);
+            const float invq = rcp_approx(softmax_den(g, eq, slot + 16));
+            const float invk = rcp_approx(softmax_den(g, ek, slot + 24));
             cta_sync<G::WPS>();
             f2 ks[G::NP], qs[G::NP];
             lds_slice<G::NR>(ks, xk + g.off);
@@ -147,45 +147,6 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_fwd_kern
 //     the three dot products of a step run side by side and the rank-one update leaves the chain;
 //   * beta's feedback term r_b . tanh(h) is a lane-local product summed by shuffles beside the matrix products;
 //   * tanh by exp2 / reciprocal (a short polynomial near zero), outputs through running pointers.
-__device__ __forceinline__ float warp_max_f32(float x) {
-    float r;
-    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
-    return r;
-}
-__device__ __forceinline__ float rcp_approx(float x) {
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-    return r;
-}
-__device__ __forceinline__ float ex2_approx(float x) {
-    float r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-    return r;
-}
-// |error| below 2e-7 over the whole range: odd polynomial to x^9 under 0.25, 1 - 2 / (e^{2|x|} + 1) above
-__device__ __forceinline__ float tanh_fast(float x) {
-    const float ax = fabsf(x), x2 = x * x;
-    const float e = ex2_approx(ax * 2.885390082f);              // e^{2|x|}; inf above 44 gives exactly 1
-    const float big = copysignf(fmaf(-2.f, rcp_approx(e + 1.f), 1.f), x);
-    float pl = fmaf(x2, 2.1869488e-2f, -5.3968254e-2f);
-    pl = fmaf(pl, x2, 1.3333334e-1f);
-    pl = fmaf(pl, x2, -3.3333334e-1f);
-    const float small = fmaf(x * x2, pl, x);
-    return ax < 0.25f ? small : big;
-}
-// Sum over the warp of values in [0, 1] whose total is at least 1 (softmax numerators after the shift by the
-// maximum): fixed point with 26 fractional bits and the integer warp reduction.  The total is below 2^31, each
-// addend is off by at most 2^-27, so the sum is good to 32 * 2^-27 relative -- two ulp -- and does not depend on
-// any order of addition.  Returns 2^26 times the sum.
-__device__ __forceinline__ float warp_sum_unit_scaled(float x) {
-    return (float)__reduce_add_sync(0xffffffffu, __float2uint_rn(x * 67108864.f));
-}
-// Sum over the warp of signed values bounded by 2^24 in magnitude after the caller's scaling.
-__device__ __forceinline__ float warp_sum_scaled(float x) {
-    return (float)__reduce_add_sync(0xffffffffu, __float2int_rn(x));
-}
-constexpr float kLog2e = 1.4426950408889634f;
-
 // FULL: the head dimension is exactly 32 (no padding lanes, no predicates in the step).
 template <int TC, bool FULL>
 __global__ void __launch_bounds__(128) rec_fwd_warp32_kernel(const RecFwdParams p) {

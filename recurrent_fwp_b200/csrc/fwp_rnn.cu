@@ -71,35 +71,47 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rnn_fwd_kern
         cp_async_commit();
     };
     issue(0);
+    // running output pointers of this thread's column (threads that store nothing keep a valid address)
+    const bool writer = ok && g.s == 0;
+    const int col = writer ? g.idx : 0;
+    float* po = reinterpret_cast<float*>(p.out.p) + n * p.out.sN + h * p.out.sH + col;
+    float* pvo = reinterpret_cast<float*>(p.v_old.p) + n * p.v_old.sN + h * p.v_old.sH + col;
+    float* pnm = V1 ? po : reinterpret_cast<float*>(p.out_nmz.p) + n * p.out_nmz.sN + h * p.out_nmz.sH + col;
+    const long long so = p.out.sL, svo = p.v_old.sL, snm = V1 ? 0 : p.out_nmz.sL;
     int par = 0;
     for (int c = 0; c < nchunks; c++) {
         if (c + 1 < nchunks) { issue(c + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         __syncthreads();
         Stage s; s.bind(smem + (c & 1) * Stage::kFloats);
-        const int t0 = c * TC, nt = min(TC, p.L - t0);
-        for (int t = 0; t < nt; t++) {
+        const int nt = min(TC, p.L - c * TC);
+        const float* krow = s.k.f + g.off;
+        const float* vcol = s.v.f + g.idx;
+        const float* zcol = s.z.f + g.idx;
+        const float* brow = s.b.f;
+#pragma unroll 1
+        for (int t = 0; t < nt; t++, krow += D, vcol += D, zcol += D, brow++) {
             float* xv = xch + par * (D + 16);
             float* slot = xv + D;
             par ^= 1;
             // delta update of the recurrent matrix (independent of the hidden state)
             f2 kk[G::NP];
-            lds_slice<G::NR>(kk, s.k.f + t * D + g.off);
+            lds_slice<G::NR>(kk, krow);
             const float vo = reduce_split<SPLIT>(dot2<G::NP>(S, kk));
-            const float u = s.b.f[t] * (s.v.f[t * D + g.idx] - vo);
+            const float u = brow[0] * (vcol[0] - vo);
             axpy2<G::NP>(S, kk, u);
-            const float zz = s.z.f[t * D + g.idx];
+            const float zz = zcol[0];
             float hn;
             if constexpr (!V1) {
                 const float mx = cta_allreduce_idx<G, true>(g, ok ? hv : -INFINITY, slot);
-                const float ex = ok ? expf(hv - mx) : 0.f;
+                const float ex = ok ? exp_neg(hv - mx) : 0.f;
                 if (g.s == 0) xv[g.idx] = ex;
-                const float den = cta_allreduce_idx<G, false>(g, ex, slot + 8);
+                const float den = softmax_den(g, ex, slot + 8);
                 cta_sync<G::WPS>();
-                const float inv = 1.f / (den + kSoftmaxEps);
+                const float inv = rcp_approx(den + kSoftmaxEps);
                 f2 ss[G::NP];
                 lds_slice<G::NR>(ss, xv + g.off);
                 hn = reduce_split<SPLIT>(dot2<G::NP>(S, ss)) * inv + zz;
-                if (ok && g.s == 0) put<float>(p.out_nmz, n, h, t0 + t, g.idx, ex * inv);
+                if (writer) *pnm = ex * inv;
             } else {
                 if (g.s == 0) xv[g.idx] = hv;
                 cta_sync<G::WPS>();
@@ -107,15 +119,15 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rnn_fwd_kern
                 lds_slice<G::NR>(ss, xv + g.off);
                 const float pre = reduce_split<SPLIT>(dot2<G::NP>(S, ss)) + zz;
                 const float mx = cta_allreduce_idx<G, true>(g, ok ? pre : -INFINITY, slot);
-                const float ex = ok ? expf(pre - mx) : 0.f;
-                const float den = cta_allreduce_idx<G, false>(g, ex, slot + 8);
-                hn = ex / den;
+                const float ex = ok ? exp_neg(pre - mx) : 0.f;
+                hn = ex * rcp_approx(softmax_den(g, ex, slot + 8));
             }
             hv = hn;
-            if (ok && g.s == 0) {
-                put<float>(p.out, n, h, t0 + t, g.idx, hn);
-                put<float>(p.v_old, n, h, t0 + t, g.idx, vo);
+            if (writer) {
+                *po = hn;
+                *pvo = vo;
             }
+            po += so; pvo += svo; pnm += snm;
         }
         __syncthreads();
     }
