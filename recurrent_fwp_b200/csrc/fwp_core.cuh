@@ -58,6 +58,7 @@ enum TuneKey {
     T_DELTA_BWD_CHUNK16,    // "delta_bwd.16.chunk": 32 or 16 steps per staged chunk
     T_LSTM_FWD_SPLIT32, T_LSTM_BWD_SPLIT32, T_RNN_FWD_SPLIT32, T_RNN_BWD_SPLIT32, T_REC_FWD_SPLIT32, T_REC_BWD_SPLIT32,
     T_REC_FWD_WARP32,       // "rec_fwd.32.warp": 1 short-chain one-warp forward of the recurrent delta net at d <= 32, 0 the general kernel
+    T_RNN_BWD_ROLES32,      // "rnn_bwd.32.roles": 1 / 2 chain-warp + trailing-warp backward of the delta RNN at d <= 32 (16 / 8 steps per chunk), 0 the general kernel
     T_COUNT
 };
 int tune_get(TuneKey key, int fallback);

@@ -277,6 +277,10 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rnn_bwd_kern
     store_rows(g, Sr, W, p.wE, p.D, p.D);
 }
 
+}  // namespace fwp
+#include "fwp_rnn_roles.cuh"
+namespace fwp {
+
 // ------------------------------------------------------------------ launchers
 template <typename K>
 static int smem_optin(K kernel, size_t bytes) {
@@ -309,6 +313,20 @@ static int launch_rnn_bwd(const RnnBwdParams& p, int nseq, cudaStream_t st) {
     if (int rc = smem_optin(kern, bytes * slots)) return rc;
     kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+template <int TC, bool V1>
+static int launch_rnn_bwd_roles32(const RnnBwdParams& p, int nseq, cudaStream_t st) {
+    auto kern = rnn_bwd_roles32_kernel<TC, V1>;
+    int slots = 4;
+    while (nseq % slots) slots >>= 1;
+    const size_t bytes = (size_t)RnnRolesSmem<TC, V1>::kFloats * sizeof(float) * slots;
+    if (int rc = smem_optin(kern, bytes)) return rc;
+    kern<<<nseq / slots, 64 * slots, bytes, st>>>(p);
+    count_launch();
+    note_kernel("rnn_bwd_roles32_kernel");
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
@@ -384,6 +402,9 @@ static int rnn_backward(int N, int H, int L, int D,
     switch (DP) {
         case 16: return launch_rnn_bwd<16, 2, 16, V1>(p, N * H, st);
         case 32: {
+            const int roles = tune_get(T_RNN_BWD_ROLES32, 1);
+            if (roles == 1) return launch_rnn_bwd_roles32<16, V1>(p, N * H, st);
+            if (roles == 2) return launch_rnn_bwd_roles32<8, V1>(p, N * H, st);
             const int sp = tune_get(T_RNN_BWD_SPLIT32, 1);
             // measured (512 sequences x 512 steps): 1 -> 0.34 ms, 2 -> 0.39 ms, 4 -> 0.42 ms
             if (sp == 2) return launch_rnn_bwd<32, 2, 8, V1>(p, N * H, st);
