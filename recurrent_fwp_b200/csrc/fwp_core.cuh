@@ -59,6 +59,7 @@ enum TuneKey {
     T_LSTM_FWD_SPLIT32, T_LSTM_BWD_SPLIT32, T_RNN_FWD_SPLIT32, T_RNN_BWD_SPLIT32, T_REC_FWD_SPLIT32, T_REC_BWD_SPLIT32,
     T_REC_FWD_WARP32,       // "rec_fwd.32.warp": 1 short-chain one-warp forward of the recurrent delta net at d <= 32, 0 the general kernel
     T_RNN_BWD_ROLES32,      // "rnn_bwd.32.roles": 1 / 2 chain-warp + trailing-warp backward of the delta RNN at d <= 32 (16 / 8 steps per chunk), 0 the general kernel
+    T_LSTM_BWD_ROLES32,     // "lstm_bwd.32.roles": 1 chain-warp + three trailing-warp backward of the delta LSTM at d <= 32, 0 the general kernel
     T_COUNT
 };
 int tune_get(TuneKey key, int fallback);
@@ -84,6 +85,11 @@ struct DeviceGuard {
 __host__ __device__
 #endif
 constexpr int r4(int x) { return (x + 3) & ~3; }   // round a float count up to 16 bytes
+
+// every row of every (n, h) slice of a float stream starts on a 16-byte boundary
+static inline bool rows_16B_aligned(const Row4& r) {
+    return (reinterpret_cast<uintptr_t>(r.p) & 15) == 0 && r.sN % 4 == 0 && r.sH % 4 == 0 && r.sL % 4 == 0;
+}
 
 static inline int pad_dim(int d) { return d <= 16 ? 16 : (d <= 32 ? 32 : (d <= 64 ? 64 : 0)); }
 
@@ -495,6 +501,46 @@ __device__ __forceinline__ void stage_rows(T* tile, const Src<T>& src, int t0, i
             if constexpr (sizeof(T) == 4) cp_async4(tile + r * D + c, gp); else tile[r * D + c] = *gp;
         }
     }
+}
+
+// ---- table-driven staging for the kernels whose stages hold many tiles ----------------------------------------
+// A stage is `ntile` tiles of TC rows x 32 floats laid one after the other, followed by `ncol` columns of r4(TC)
+// floats ([L,1] streams).  The sources sit in a small table in shared memory, so one short loop issues every copy of
+// a chunk: a few instructions per 16-byte piece instead of one inlined copy routine per tile.  Requires full-width
+// rows that start on 16-byte boundaries (the host checks with rows_16B_aligned before choosing such a kernel).
+struct StageTable {
+    static constexpr int kMaxTiles = 20, kMaxCols = 4;
+    const float* src[kMaxTiles];        // element (n, h, 0, 0) of each tile's stream; nullptr = tile not used
+    long long sL[kMaxTiles];
+    const float* csrc[kMaxCols];
+    long long csL[kMaxCols];
+};
+__device__ __forceinline__ void stage_table_set(StageTable* tb, int i, const Row4& r, int n, int h) {
+    tb->src[i] = r.p ? reinterpret_cast<const float*>(r.p) + n * r.sN + h * r.sH : nullptr;
+    tb->sL[i] = r.sL;
+}
+__device__ __forceinline__ void stage_table_set_col(StageTable* tb, int i, const Row4& r, int n, int h) {
+    tb->csrc[i] = reinterpret_cast<const float*>(r.p) + n * r.sN + h * r.sH;
+    tb->csL[i] = r.sL;
+}
+template <int TC, int NT>
+__device__ __forceinline__ void stage_table_issue(float* stage, const StageTable* tb, int ntile, int ncol,
+                                                  int t0, int nt, int tid) {
+    static_assert((TC & (TC - 1)) == 0 && TC >= 4, "rows per chunk: a power of two");
+    constexpr int D = 32;
+    const int total = ntile * TC * 8;
+#pragma unroll 1
+    for (int i = tid; i < total; i += NT) {
+        const int piece = i & 7, r = (i >> 3) & (TC - 1), tile = i / (8 * TC);
+        const float* sp = tb->src[tile];
+        if (r < nt && sp) cp_async16(stage + i * 4, sp + (long long)(t0 + r) * tb->sL[tile] + piece * 4);
+    }
+    float* cols = stage + ntile * TC * D;
+    if (tid < ncol * TC) {
+        const int c = tid / TC, r = tid - c * TC;
+        if (r < nt) cp_async4(cols + c * r4(TC) + r, tb->csrc[c] + (long long)(t0 + r) * tb->csL[c]);
+    }
+    cp_async_commit();
 }
 
 // shared-memory tile of one streamed tensor: fp32 rows the compute loop reads,

@@ -358,6 +358,10 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) lstm_bwd_ker
     for (int a = 0; a < 3; a++) store_rows(g, Sr[a], p.W[a] + n * p.wN[a] + h * p.wH[a], p.wE[a], p.D, p.D);
 }
 
+}  // namespace fwp
+#include "fwp_lstm_roles.cuh"
+namespace fwp {
+
 // ------------------------------------------------------------------ launchers
 template <typename K>
 static int smem_optin(K kernel, size_t bytes) {
@@ -395,6 +399,20 @@ static int launch_lstm_bwd(const LstmBwdParams& p, int nseq, cudaStream_t st) {
 }
 
 template <int VAR>
+static int launch_lstm_bwd_roles32(const LstmBwdParams& p, int nseq, cudaStream_t st) {
+    constexpr int TC = 8;
+    auto kern = lstm_bwd_roles32_kernel<TC, VAR>;
+    const int slots = nseq % 2 ? 1 : 2;
+    const size_t bytes = (size_t)LstmRolesSmem<TC>::kFloats * sizeof(float) * slots;
+    if (int rc = smem_optin(kern, bytes)) return rc;
+    kern<<<nseq / slots, 128 * slots, bytes, st>>>(p);
+    count_launch();
+    note_kernel("lstm_bwd_roles32_kernel");
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+template <int VAR>
 static int dispatch_lstm_fwd(const LstmFwdParams& p, int nseq, cudaStream_t st) {
     switch (pad_dim(p.D)) {
         case 16: return launch_lstm_fwd<16, 2, 16, VAR>(p, nseq, st);
@@ -415,6 +433,13 @@ static int dispatch_lstm_bwd(const LstmBwdParams& p, int nseq, cudaStream_t st) 
     switch (pad_dim(p.D)) {
         case 16: return launch_lstm_bwd<16, 2, 8, VAR>(p, nseq, st);
         case 32: {
+            bool fast = p.D == 32 && tune_get(T_LSTM_BWD_ROLES32, 1);      // full width, 16-byte aligned rows
+            for (int a = 0; a < 3 && fast; a++)
+                fast = rows_16B_aligned(p.k[a]) && rows_16B_aligned(p.v[a]) && rows_16B_aligned(p.v_old[a]) &&
+                       rows_16B_aligned(p.gate[a]);
+            fast = fast && rows_16B_aligned(p.gy) && rows_16B_aligned(p.od) && rows_16B_aligned(p.cell) &&
+                   rows_16B_aligned(p.umc) && (VAR != 1 || rows_16B_aligned(p.out));
+            if (fast) return launch_lstm_bwd_roles32<VAR>(p, nseq, st);
             const int sp = tune_get(T_LSTM_BWD_SPLIT32, 2);
             // measured: 2 -> 1.37 ms, 4 -> 2.14 ms
             if (sp == 4) return launch_lstm_bwd<32, 4, 4, VAR>(p, nseq, st);

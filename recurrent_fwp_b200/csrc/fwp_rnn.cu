@@ -402,7 +402,10 @@ static int rnn_backward(int N, int H, int L, int D,
     switch (DP) {
         case 16: return launch_rnn_bwd<16, 2, 16, V1>(p, N * H, st);
         case 32: {
-            const int roles = tune_get(T_RNN_BWD_ROLES32, 1);
+            int roles = tune_get(T_RNN_BWD_ROLES32, 1);
+            if (p.D != 32 || !rows_16B_aligned(p.k) || !rows_16B_aligned(p.v) || !rows_16B_aligned(p.gy) ||
+                !rows_16B_aligned(p.v_old) || !rows_16B_aligned(p.od) || (V1 && !rows_16B_aligned(p.out)))
+                roles = 0;              // the two-warp kernel wants full width and 16-byte aligned rows
             if (roles == 1) return launch_rnn_bwd_roles32<16, V1>(p, N * H, st);
             if (roles == 2) return launch_rnn_bwd_roles32<8, V1>(p, N * H, st);
             const int sp = tune_get(T_RNN_BWD_SPLIT32, 1);

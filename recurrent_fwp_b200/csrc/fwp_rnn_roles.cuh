@@ -14,10 +14,6 @@
 
 namespace fwp {
 
-__device__ __forceinline__ void named_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
 template <int TC, bool V1>
 struct RnnRolesSmem {
     static constexpr int D = 32;
@@ -25,7 +21,8 @@ struct RnnRolesSmem {
     static constexpr int kStages = 3;                 // X on chunk j, Y on chunk j - 1, chunk j + 1 in flight
     static constexpr int kStep = 4 * D;               // per step: g, u, br, r w
     static constexpr int kRing = TC * kStep;
-    static constexpr int kFloats = kStages * Stage::kFloats + 2 * kRing;
+    static constexpr int kTable = (sizeof(StageTable) + 15) / 16 * 4;
+    static constexpr int kFloats = kStages * Stage::kFloats + 2 * kRing + kTable;
 };
 
 template <int TC, bool V1>
@@ -39,56 +36,48 @@ __global__ void __launch_bounds__(256, 1) rnn_bwd_roles32_kernel(const RnnBwdPar
     const int stid = role * 32 + lane;
     const int seq = blockIdx.x * nslots + slot;
     const int n = seq / p.H, h = seq - n * p.H;
-    const int bar_chunk = 1 + slot;
     extern __shared__ __align__(16) float smem_all[];
     float* smem = smem_all + (size_t)slot * SM::kFloats;
-    for (int i = stid; i < SM::kFloats; i += NT) smem[i] = 0.f;
+    for (int i = stid; i < SM::kFloats - SM::kTable; i += NT) smem[i] = 0.f;
     float* ring = smem + SM::kStages * Stage::kFloats;
 
-    Src<float> sk, sv, sg, so, sd, sb, sout;
-    sk.init(p.k, n, h, p.D);
-    sv.init(p.v, n, h, p.D);
-    sg.init(p.gy, n, h, p.D);
-    so.init(p.v_old, n, h, p.D);
-    sd.init(p.od, n, h, p.D);
-    sb.init(p.beta, n, h, 1);
-    if (V1) sout.init(p.out, n, h, p.D);
+    StageTable* tb = reinterpret_cast<StageTable*>(ring + 2 * SM::kRing);
+    if (stid == 0) {                // tile order of RnnBwdStage: k, v, gy, v_old, od, (out)
+        stage_table_set(tb, 0, p.k, n, h);
+        stage_table_set(tb, 1, p.v, n, h);
+        stage_table_set(tb, 2, p.gy, n, h);
+        stage_table_set(tb, 3, p.v_old, n, h);
+        stage_table_set(tb, 4, p.od, n, h);
+        if (V1) stage_table_set(tb, 5, p.out, n, h);
+        stage_table_set_col(tb, 0, p.beta, n, h);
+    }
 
-    const bool ok = lane < p.D;
-    const int col = ok ? lane : 0;
+    const int col = lane;           // the head dimension is exactly 32 (the launcher sends other sizes elsewhere)
     float* W = p.W + n * p.wN + h * p.wH;
     f2 Sr[NP], Gm[NP];              // S by rows (both warps); X: G by columns, Y: G by rows
     {
         float v[2];
 #pragma unroll
         for (int i = 0; i < D; i++) {
-            v[i & 1] = (lane < p.D && i < p.D) ? W[(long long)lane * p.wE + i] : 0.f;
+            v[i & 1] = W[(long long)lane * p.wE + i];
             if (i & 1) Sr[i >> 1] = f2_pack(v[0], v[1]);
         }
 #pragma unroll
         for (int i = 0; i < NP; i++) Gm[i] = 0ull;
     }
-    named_sync(bar_chunk, NT);      // the zero fill is complete before the first copies land
+    slot_barrier(slot, NT);      // the zero fill is complete before the first copies land
 
     const int nchunks = (p.L + TC - 1) / TC;
     auto issue = [&](int j) {
-        Stage s; s.bind(smem + (j % SM::kStages) * Stage::kFloats);
         const int c = nchunks - 1 - j;
         const int t0 = c * TC, nt = min(TC, p.L - t0);
-        s.k.template load<NT>(sk, t0, nt, stid);
-        s.v.template load<NT>(sv, t0, nt, stid);
-        s.gy.template load<NT>(sg, t0, nt, stid);
-        s.vo.template load<NT>(so, t0, nt, stid);
-        s.od.template load<NT>(sd, t0, nt, stid);
-        if (V1) s.out.template load<NT>(sout, t0, nt, stid);
-        s.b.template load<NT>(sb, t0, nt, stid);
-        cp_async_commit();
+        stage_table_issue<TC, NT>(smem + (j % SM::kStages) * Stage::kFloats, tb, V1 ? 6 : 5, 1, t0, nt, stid);
     };
     issue(0);
     float gh = 0.f;                 // X: the gradient handed back through the recurrence (lane = feature index)
     for (int j = 0; j <= nchunks; j++) {
         cp_async_wait<0>();
-        named_sync(bar_chunk, NT);  // chunk j's tiles have landed; X is through chunk j - 1, Y through j - 2
+        slot_barrier(slot, NT);  // chunk j's tiles have landed; X is through chunk j - 1, Y through j - 2
         if (j + 1 < nchunks) issue(j + 1);      // into the stage Y has just left
         if (role == 0 && j < nchunks) {
             // ------------------------------------------------------------ X: the chain
@@ -123,9 +112,10 @@ __global__ void __launch_bounds__(256, 1) rnn_bwd_roles32_kernel(const RnnBwdPar
                 rg[t * SM::kStep + 2 * D + lane] = br;
                 rg[t * SM::kStep + 3 * D + lane] = r * w;
                 __syncwarp();
-                f2 vec[NP];
-                lds_slice<D>(vec, rg + t * SM::kStep);
-                const float gs = dot2<NP>(Sr, vec);
+                f2 vg[NP], vu[NP];                  // two register sets: u is in flight during the product and the reduction
+                lds_slice<D>(vg, rg + t * SM::kStep);
+                lds_slice<D>(vu, rg + t * SM::kStep + D);
+                const float gs = dot2<NP>(Sr, vg);
                 if constexpr (V1) {
                     gh = gs;
                 } else {
@@ -134,8 +124,7 @@ __global__ void __launch_bounds__(256, 1) rnn_bwd_roles32_kernel(const RnnBwdPar
                 }
                 axpy2<NP>(Gm, xs, gcol);
                 axpy2<NP>(Gm, kk, -br);
-                lds_slice<D>(vec, rg + t * SM::kStep + D);
-                axpy2<NP>(Sr, vec, -ke);            // S_{t-1}
+                axpy2<NP>(Sr, vu, -ke);             // S_{t-1}
                 if (t > 0) prep(t - 1);
             }
         } else if (role == 1 && j > 0) {
@@ -156,16 +145,16 @@ __global__ void __launch_bounds__(256, 1) rnn_bwd_roles32_kernel(const RnnBwdPar
                 const float* e = rg + t * SM::kStep;
                 const float gl = e[lane], bl = e[2 * D + lane];
                 const float db = warp_sum_idx<1>(e[3 * D + lane]);
-                f2 vec[NP];
-                lds_slice<D>(vec, e);
-                axpy2<NP>(Gm, vec, se);
-                lds_slice<D>(vec, e + D);
-                const float dkg = dot2<NP>(Gm, vec);
-                axpy2<NP>(Sr, vec, -ke);            // S_{t-1}
-                lds_slice<D>(vec, e + 2 * D);
-                const float dk = dkg - dot2<NP>(Sr, vec);
-                axpy2<NP>(Gm, vec, -ke);
-                if (ok) { *pgk = dk; *pgz = gl; *pgv = bl; }
+                f2 vg[NP], vu[NP], vb[NP];          // three register sets: the loads go out together
+                lds_slice<D>(vg, e);
+                lds_slice<D>(vu, e + D);
+                lds_slice<D>(vb, e + 2 * D);
+                axpy2<NP>(Gm, vg, se);
+                const float dkg = dot2<NP>(Gm, vu);
+                axpy2<NP>(Sr, vu, -ke);             // S_{t-1}
+                const float dk = dkg - dot2<NP>(Sr, vb);
+                axpy2<NP>(Gm, vb, -ke);
+                *pgk = dk; *pgz = gl; *pgv = bl;
                 if (lane == 0) *pgb = db;
                 pgk -= p.gk.sL; pgz -= p.gz.sL; pgv -= p.gv.sL; pgb -= p.gb.sL;
             }
@@ -176,7 +165,7 @@ __global__ void __launch_bounds__(256, 1) rnn_bwd_roles32_kernel(const RnnBwdPar
         for (int i = 0; i < D; i++) {
             float lo, hi;
             f2_unpack(Sr[i >> 1], lo, hi);
-            if (lane < p.D && i < p.D) W[(long long)lane * p.wE + i] = (i & 1) ? hi : lo;
+            W[(long long)lane * p.wE + i] = (i & 1) ? hi : lo;
         }
     }
 }
