@@ -128,6 +128,14 @@ int fwp_debug_bounded_wait_probe(int polls, void* stream, int device);
  *   prologue_backward: gradients of q, k, v, beta (B,H,L,.) and the same qkvb -> gradient of qkvb (L,B,H,3D+1)
  *   transpose:         to_len_major != 0: dst (L,B,H,D) = scale * src (B,H,L,D)  (the layer's output path);
  *                      to_len_major == 0: dst (B,H,L,D) = scale * src (L,B,H,D)  (its gradient) */
+/* The delayed copies the recurrent families' wrappers hand to the backward kernels, in one pass:
+ *   dst[n,h,t,:] = f(t == 0 ? first[n,h,0,:] : src[n,h,t-1,:]),  op 0: f = identity, op 1: f = tanh;
+ * with minuend->data != NULL, dst = minuend[n,h,t,:] - that value.  src, minuend, dst [N,H,L,D]; first [N,H,1,D];
+ * float32, unit inner stride.  Replaces the torch.cat / tanh / subtraction chains of
+ * algorithmic/rec_update_fwm_tanh/__init__.py:108 and language_modeling/src/utils/fast_lstm/__init__.py:142-148. */
+int fwp_delayed(int N, int H, int L, int D, const fwp_tensor* src, const fwp_tensor* first,
+                const fwp_tensor* minuend, const fwp_tensor* dst, int op, void* stream, int device);
+
 int fwp_delta_layer_prologue_forward(int L, int B, int H, int D, const float* qkvb,
                                      float* q, float* k, float* v, float* beta, void* stream, int device);
 int fwp_delta_layer_prologue_backward(int L, int B, int H, int D, const float* qkvb,

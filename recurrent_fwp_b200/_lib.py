@@ -50,6 +50,7 @@ SIGNATURES = {
     'fwp_delta_layer_prologue_backward': [_i] * 4 + [ctypes.c_void_p] * 6 + [_vp, _i],
     'fwp_delta_layer_transpose': [_i] * 4 + [ctypes.c_void_p] * 2 + [ctypes.c_float, _i, _vp, _i],
     'fwp_debug_bounded_wait_probe': [_i, _vp, _i],
+    'fwp_delayed': [_i] * 4 + [_T] * 4 + [_i, _vp, _i],
     'fwp_fast_lstm_backward': [_i] * 5 + [_T] + [_T3] * 4 + [_T] * 4 + [_T3] * 6 + [_i, _vp, _i],
 }
 OTHER_SYMBOLS = ['fwp_status_string', 'fwp_last_cuda_error', 'fwp_version', 'fwp_max_head_dim',
@@ -136,6 +137,18 @@ def desc(t):
     for i in range(4):
         d.stride[i] = 1 if (i == 3 and t.shape[3] == 1) else t.stride(i)
     return d
+
+
+def delayed(src, first, op=0, minuend=None):
+    """``f(cat([first, src[:, :, :-1]], dim=2))`` in one pass (op 0: identity, 1: tanh); with ``minuend``,
+    ``minuend - that``.  The delayed copies the recurrent families' backward kernels take."""
+    N, H, L, M = src.shape
+    out = torch.empty((N, H, L, M), device=src.device, dtype=torch.float32)
+    stream, dev = stream_and_device(src)
+    check(lib.fwp_delayed(N, H, L, M, desc(unit_inner(src)), desc(unit_inner(first)),
+                          desc(None if minuend is None else unit_inner(minuend)), desc(out), op, stream, dev),
+          'delayed')
+    return out
 
 
 def desc3(ts):

@@ -197,6 +197,43 @@ __global__ void __launch_bounds__(kLayerWarps * 32) layer_transpose_kernel(const
     }
 }
 
+// dst[n,h,t,:] = f(t == 0 ? first[n,h,0,:] : src[n,h,t-1,:]), f = identity or tanh; with a minuend, minuend - that.
+// V = float4 when rows are 16-byte aligned and D % 4 == 0.
+struct DelayedParams {
+    const float* src; long long sN, sH, sL;
+    const float* first; long long fN, fH;
+    const float* minuend; long long mN, mH, mL;
+    float* dst; long long dN, dH, dL;
+    int H, L, per_row, op;
+    long long total;
+};
+template <typename V>
+__global__ void __launch_bounds__(256) delayed_kernel(const DelayedParams p) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= p.total) return;
+    constexpr int W = sizeof(V) / 4;
+    const int c = (int)(i % p.per_row) * W;
+    const long long row = i / p.per_row;
+    const int t = (int)(row % p.L);
+    const long long nh = row / p.L;
+    const int h = (int)(nh % p.H);
+    const long long n = nh / p.H;
+    const float* sp = t == 0 ? p.first + n * p.fN + h * p.fH + c : p.src + n * p.sN + h * p.sH + (long long)(t - 1) * p.sL + c;
+    V x = *reinterpret_cast<const V*>(sp);
+    float* xf = reinterpret_cast<float*>(&x);
+    if (p.op == 1) {
+#pragma unroll
+        for (int j = 0; j < W; j++) xf[j] = tanhf(xf[j]);
+    }
+    if (p.minuend) {
+        const V m = *reinterpret_cast<const V*>(p.minuend + n * p.mN + h * p.mH + (long long)t * p.mL + c);
+        const float* mf = reinterpret_cast<const float*>(&m);
+#pragma unroll
+        for (int j = 0; j < W; j++) xf[j] = mf[j] - xf[j];
+    }
+    *reinterpret_cast<V*>(p.dst + n * p.dN + h * p.dH + (long long)t * p.dL + c) = x;
+}
+
 static int layer_dims(int L, int B, int H, int D, LayerDims& d) {
     if (L <= 0 || B <= 0 || H <= 0 || D <= 0) return FWP_ERR_SHAPE;
     if (D > kLayerMaxD) return FWP_ERR_UNSUPPORTED;
@@ -271,5 +308,38 @@ FWP_API int fwp_delta_layer_transpose(int L, int B, int H, int D, const float* s
                                                                               d, per_row, scale, to_len_major ? 1 : 0);
     else
         layer_transpose_kernel<float><<<(int)ctas, kLayerWarps * 32, 0, st>>>(src, dst, d, per_row, scale, to_len_major ? 1 : 0);
+    return finish_launch();
+}
+
+FWP_API int fwp_delayed(int N, int H, int L, int D, const fwp_tensor* src, const fwp_tensor* first,
+                        const fwp_tensor* minuend, const fwp_tensor* dst, int op, void* stream, int device) {
+    if (N <= 0 || H <= 0 || L <= 0 || D <= 0) return FWP_ERR_SHAPE;
+    if (op != 0 && op != 1) return FWP_ERR_UNSUPPORTED;
+    int rc;
+    if ((rc = check_tensor(src, 4, true)) || (rc = check_tensor(first, 4, true)) || (rc = check_tensor(dst, 4, true)) ||
+        (rc = check_tensor(minuend, 4, false)))
+        return rc;
+    const bool sub = minuend && minuend->data;
+    DeviceGuard guard(device);
+    if (guard.status) return guard.status;
+    DelayedParams p;
+    p.src = (const float*)src->data; p.sN = src->stride[0]; p.sH = src->stride[1]; p.sL = src->stride[2];
+    p.first = (const float*)first->data; p.fN = first->stride[0]; p.fH = first->stride[1];
+    p.minuend = sub ? (const float*)minuend->data : nullptr;
+    p.mN = sub ? minuend->stride[0] : 0; p.mH = sub ? minuend->stride[1] : 0; p.mL = sub ? minuend->stride[2] : 0;
+    p.dst = (float*)dst->data; p.dN = dst->stride[0]; p.dH = dst->stride[1]; p.dL = dst->stride[2];
+    p.H = H; p.L = L; p.op = op;
+    auto al = [](const void* q, long long a, long long b, long long c) {
+        return (reinterpret_cast<uintptr_t>(q) & 15) == 0 && a % 4 == 0 && b % 4 == 0 && c % 4 == 0;
+    };
+    const bool vec = D % 4 == 0 && al(p.src, p.sN, p.sH, p.sL) && al(p.first, p.fN, p.fH, 0) &&
+                     al(p.dst, p.dN, p.dH, p.dL) && (!sub || al(p.minuend, p.mN, p.mH, p.mL));
+    p.per_row = vec ? D / 4 : D;
+    p.total = (long long)N * H * L * p.per_row;
+    const long long ctas = (p.total + 255) / 256;
+    if (ctas > 0x7fffffffLL) return FWP_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (vec) delayed_kernel<float4><<<(int)ctas, 256, 0, st>>>(p);
+    else delayed_kernel<float><<<(int)ctas, 256, 0, st>>>(p);
     return finish_launch();
 }

@@ -634,7 +634,9 @@ FWP_API int fwp_rec_update_fwm_tanh_backward(int N, int H, int L, int D,
         case 16: rc = launch_rec_bwd<16, 2, 16>(p, N * H, st); break;
         case 32: {
             const int sp = tune_get(T_REC_BWD_SPLIT32, 2);
-            // measured: 2 -> 0.36 ms, 4 -> 0.40 ms, 1 -> 0.43 ms (spills)
+            // measured: 2 -> 0.36 ms, 4 -> 0.40 ms, 1 -> 0.43 ms (spills).  A single chain warp with a trailing warp for
+            // the parameter gradients (the plan of the RNN and LSTM backward) measured 0.42 ms here: everything but
+            // the parameter gradients sits on this chain, about 390 instructions per step in one warp.
             if (sp == 4) rc = launch_rec_bwd<32, 4, 8>(p, N * H, st);
             else if (sp == 1) rc = launch_rec_bwd<32, 1, 8>(p, N * H, st);
             else rc = launch_rec_bwd<32, 2, 8>(p, N * H, st);

@@ -65,12 +65,9 @@ def make_lstm_function(variant, name):
         h0, c0 = t[20], t[21]
         N, H, L, M = rnn_out.shape
         grad_out = _lib.grad_like(grad_out, rnn_out, (N, H, L, M))
-        if variant == 1:
-            out_delayed = torch.cat([h0, rnn_out[:, :, :-1]], dim=2)
-        else:
-            out_delayed = t[22]
-        c_out_delayed = torch.cat([c0, cell_out[:, :, :-1]], dim=2)
-        u_minus_c = gates[1] - c_out_delayed
+        # cat([h0, out[:, :, :-1]]) and update - cat([c0, cell[:, :, :-1]]), one pass each
+        out_delayed = _lib.delayed(rnn_out, h0) if variant == 1 else t[22]
+        u_minus_c = _lib.delayed(cell_out, c0, minuend=gates[1])
         gZ = [torch.empty_like(rnn_out) for _ in range(3)]
         gK = [torch.empty_like(rnn_out) for _ in range(3)]
         gV = [torch.empty_like(rnn_out) for _ in range(3)]

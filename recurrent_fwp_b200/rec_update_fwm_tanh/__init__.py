@@ -66,7 +66,7 @@ class FastWeightRecUpdateTanh(torch.autograd.Function):
         grad_R_k = torch.empty_like(R_k)
         grad_R_v = torch.empty_like(R_v)
         grad_r_b = torch.empty_like(r_b)
-        out_delayed = torch.tanh(torch.cat([h0, out[:, :, :-1]], dim=2))
+        out_delayed = _lib.delayed(out, h0, op=1)       # tanh(cat([h0, out[:, :, :-1]], dim=2)) in one pass
         n_scratch = int(_lib.lib.fwp_rec_update_fwm_tanh_scratch_floats(N, H, M))
         scratch = torch.empty(n_scratch, device=out.device, dtype=torch.float32)
         stream, dev = _lib.stream_and_device(out)

@@ -81,3 +81,22 @@ def test_language_model_with_fused_layer_io_matches_the_reference_fixture(fwp):
         grads[fused] = {n: p.grad.detach() for n, p in m.named_parameters()}
     for n, gref in grads[False].items():
         assert util.scaled_rel(grads[True][n], gref) <= 1e-4, n
+
+
+@pytest.mark.parametrize('shape', [(2, 3, 7, 32), (1, 2, 5, 20), (2, 2, 1, 16)])
+def test_delayed_copies_match_the_torch_chain(fwp, shape):
+    """fwp_delayed against cat / tanh / subtraction as the reference's wrappers write them; a strided source and a
+    head dimension that is not a multiple of four take the element path."""
+    from recurrent_fwp_b200 import _lib
+    N, H, L, M = shape
+    g = torch.Generator().manual_seed(3)
+    src = torch.randn(N, H, L, M, generator=g).to('cuda:0')
+    first = torch.randn(N, H, 1, M, generator=g).to('cuda:0')
+    other = torch.randn(N, H, L, M, generator=g).to('cuda:0')
+    cat = torch.cat([first, src[:, :, :-1]], dim=2)
+    assert torch.equal(_lib.delayed(src, first), cat)
+    assert (_lib.delayed(src, first, op=1) - torch.tanh(cat)).abs().max().item() <= 2e-7
+    assert torch.equal(_lib.delayed(src, first, minuend=other), other - cat)
+    wide = torch.randn(N, H, L, M + 3, generator=g).to('cuda:0')
+    view = wide[..., 1:M + 1]                       # unit inner stride, rows not 16-byte aligned
+    assert torch.equal(_lib.delayed(view, first), torch.cat([first, view[:, :, :-1]], dim=2))
