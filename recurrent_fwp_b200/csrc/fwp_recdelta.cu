@@ -258,6 +258,12 @@ __global__ void __launch_bounds__(128) rec_fwd_warp32_kernel(const RecFwdParams 
     if (ok) hp[g.idx] = hv;
 }
 
+// Barrier among the warps of one sequence (the sequences that share a CTA do not wait for each other).
+template <class G>
+__device__ __forceinline__ void seq_sync(const G& g) {
+    if constexpr (G::WPS == 1) __syncwarp(); else slot_barrier(g.slot, G::NT);
+}
+
 // ------------------------------------------------------------------ backward
 struct RecBwdParams {
     Row4 q, k, v, beta, v_old, od, gy, gq, gk, gv, gb;
@@ -377,10 +383,18 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_bwd_kern
                 dv = beta * r;
                 axpy2<G::NP>(Gc, kk, -dv);
                 if (g.s == 0) { xg[g.idx] = gcol; xu[g.idx] = beta * w; xbr[g.idx] = dv; }
-                const float db = cta_allreduce_idx<G, false>(g, r * w, slot);
+                // db = sum over idx of r w: the warps' partial sums cross with the exchange below (no barrier of their own)
+                const float dbp = warp_sum_idx<SPLIT>(r * w);
+                if (G::WPS > 1 && g.lane == 0) slot[g.warp] = dbp;
+                seq_sync<G>(g);
+                float db = dbp;
+                if constexpr (G::WPS > 1) {
+                    db = slot[0];
+#pragma unroll
+                    for (int w2 = 1; w2 < G::WPS; w2++) db += slot[w2];
+                }
                 dbh = db * beta * (1.f - beta);
             }
-            cta_sync<G::WPS>();
             // ---- row role: the delta block, then the two softmax backward maps
             float dqh, dkh;
             const float qe = s.q.f[o], ke = s.k.f[o], hte = s.od.f[o];
@@ -397,8 +411,15 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_bwd_kern
                 axpy2<G::NP>(Gr, brr, -ke);
                 dq = reduce_split<SPLIT>(dq);
                 dk = reduce_split<SPLIT>(dk);
-                const float cq = cta_allreduce_idx<G, false>(g, qe * dq, slot + 8);
-                const float ck = cta_allreduce_idx<G, false>(g, ke * dk, slot + 16);
+                // the two softmax backward sums cross the warps behind one barrier
+                float cq = warp_sum_idx<SPLIT>(qe * dq), ck = warp_sum_idx<SPLIT>(ke * dk);
+                if constexpr (G::WPS > 1) {
+                    if (g.lane == 0) { slot[8 + g.warp] = cq; slot[16 + g.warp] = ck; }
+                    seq_sync<G>(g);
+                    cq = slot[8]; ck = slot[16];
+#pragma unroll
+                    for (int w2 = 1; w2 < G::WPS; w2++) { cq += slot[8 + w2]; ck += slot[16 + w2]; }
+                }
                 dqh = qe * (dq - cq);
                 dkh = ke * (dk - ck);
             }
@@ -413,7 +434,7 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rec_bwd_kern
                     if (g.idx == 0) put<float>(p.gb, n, h, tt, 0, dbh);
                 }
             }
-            cta_sync<G::WPS>();
+            seq_sync<G>(g);
             // ---- feedback gradient (row role over R) and parameter gradients (column role)
             {
                 f2 dqs[G::NP], dks[G::NP], dvs[G::NP], rr[G::NP];
