@@ -413,10 +413,29 @@ static int launch_lstm_bwd_roles32(const LstmBwdParams& p, int nseq, cudaStream_
 }
 
 template <int VAR>
+static int launch_lstm_fwd_gates32(const LstmFwdParams& p, int nseq, cudaStream_t st) {
+    constexpr int TC = 16;
+    auto kern = lstm_fwd_gates32_kernel<TC, VAR>;
+    int slots = 4;
+    while (nseq % slots) slots >>= 1;
+    const size_t bytes = (size_t)LstmGatesSmem<TC>::kFloats * sizeof(float) * slots;
+    if (int rc = smem_optin(kern, bytes)) return rc;
+    kern<<<nseq / slots, 96 * slots, bytes, st>>>(p);
+    count_launch();
+    note_kernel("lstm_fwd_gates32_kernel");
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+template <int VAR>
 static int dispatch_lstm_fwd(const LstmFwdParams& p, int nseq, cudaStream_t st) {
     switch (pad_dim(p.D)) {
         case 16: return launch_lstm_fwd<16, 2, 16, VAR>(p, nseq, st);
         case 32: {
+            bool fast = p.D == 32 && tune_get(T_LSTM_FWD_GATES32, 1);       // full width, 16-byte aligned rows
+            for (int a = 0; a < 3 && fast; a++)
+                fast = rows_16B_aligned(p.z[a]) && rows_16B_aligned(p.k[a]) && rows_16B_aligned(p.v[a]);
+            if (fast) return launch_lstm_fwd_gates32<VAR>(p, nseq, st);
             const int sp = tune_get(T_LSTM_FWD_SPLIT32, 1);
             // measured (512 sequences x 512 steps): 1 -> 0.78 ms, 4 -> 0.83 ms, 2 -> 0.85 ms
             if (sp == 2) return launch_lstm_fwd<32, 2, 8, VAR>(p, nseq, st);
