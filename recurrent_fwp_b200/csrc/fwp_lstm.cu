@@ -381,6 +381,7 @@ static int launch_lstm_fwd(const LstmFwdParams& p, int nseq, cudaStream_t st) {
     if (int rc = smem_optin(kern, bytes * slots)) return rc;
     kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
+    note_kernel("lstm_fwd_kernel");
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
@@ -394,6 +395,7 @@ static int launch_lstm_bwd(const LstmBwdParams& p, int nseq, cudaStream_t st) {
     if (int rc = smem_optin(kern, bytes * slots)) return rc;
     kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
+    note_kernel("lstm_bwd_kernel");
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }

@@ -507,6 +507,7 @@ static int launch_rec_fwd(const RecFwdParams& p, int nseq, cudaStream_t st) {
     if (int rc = smem_optin(kern, bytes * slots)) return rc;
     kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
+    note_kernel("rec_fwd_kernel");
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
@@ -534,6 +535,7 @@ static int launch_rec_bwd(const RecBwdParams& p, int nseq, cudaStream_t st) {
     if (int rc = smem_optin(kern, bytes * slots)) return rc;
     kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
+    note_kernel("rec_bwd_kernel");
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }

@@ -300,6 +300,7 @@ static int launch_rnn_fwd(const RnnFwdParams& p, int nseq, cudaStream_t st) {
     if (int rc = smem_optin(kern, bytes * slots)) return rc;
     kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
+    note_kernel("rnn_fwd_kernel");
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
@@ -313,6 +314,7 @@ static int launch_rnn_bwd(const RnnBwdParams& p, int nseq, cudaStream_t st) {
     if (int rc = smem_optin(kern, bytes * slots)) return rc;
     kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
+    note_kernel("rnn_bwd_kernel");
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
