@@ -80,6 +80,9 @@ int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
         const int rc = launch_fwd_tc(p, nseq, st);
         if (rc >= 0) return rc;
     }
+    // "delta.pipe64" = 1 (default): the state-independent part of every chunk is prepared one chunk ahead by a fifth warp
+    if (tune_get(T_DELTA_PIPE64, 1) == 1)
+        return launch(delta_fwd_chunk_bf16_pipe_kernel, p, nseq, cb::NTP, sizeof(cb::SmemP), st, "delta_fwd_chunk_bf16_pipe_kernel");
     return launch(delta_fwd_chunk_bf16_inv_kernel, p, nseq, cb::NT, sizeof(cb::SmemI), st, "delta_fwd_chunk_bf16_inv_kernel");
 }
 

@@ -418,6 +418,293 @@ __global__ void __launch_bounds__(cb::NT, 4) delta_fwd_chunk_bf16_inv_kernel(con
 }
 
 
+// ------------------------------------------------------------------ forward, state-independent part one chunk ahead
+// Everything of a chunk that does not involve the state -- the Gram tiles, the inverse T, Aqk^T and Ck = T K -- is
+// the same for the four chain warps and does not wait for the previous chunk.  In the kernel above every warp
+// computes it for itself, between two CTA-wide barriers, on the critical path of the chunk.  Here a fifth warp
+// prepares it one chunk ahead (and issues all the copies): it leaves the five right-operand fragment sets
+// (T^T and (T - I)^T as two bf16 parts each, Aqk^T) in shared memory in fragment order, one 16-byte piece per lane,
+// and Ck as a row-major tile.  The chain warps wait for that package, run the state-dependent products and hand the
+// buffers back.  Two named barriers per package buffer: FULL (the preparing warp arrives, the chain warps wait) and
+// EMPTY (the chain warps arrive after their last read of the package and of the input stage, the preparing warp
+// waits before it refills either); in this order neither side can arrive twice on a barrier before the other has
+// waited on it.  Input stages are a ring of three, packages a ring of two.
+namespace cb {
+
+constexpr int NTP = 160;                // four chain warps and the preparing warp
+
+struct SmemP {
+    __nv_bfloat16 k[3][C * LDT], v[3][C * LDT], q[3][C * LDT];    // input stages
+    uint4 frag[2][5][32];               // per package: T^T hi, lo; (T - I)^T hi, lo; Aqk^T -- in fragment order
+    __nv_bfloat16 ck[2][C * LDT];       // per package: Ck, [t][e]
+    __nv_bfloat16 ys[2][C * LDT];       // y, [t][m]
+    float b[3][C];
+};
+
+enum { BAR_FULL = 1, BAR_EMPTY = 3, BAR_CHAIN = 5 };     // FULL, EMPTY: + (chunk & 1)
+
+__device__ __forceinline__ void nbar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+__device__ __forceinline__ void nbar_arrive(int id, int n) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+
+}  // namespace cb
+
+__global__ void __launch_bounds__(cb::NTP, 4) delta_fwd_chunk_bf16_pipe_kernel(const DeltaFwdParams p) {
+    using namespace cb;
+    using bf16 = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char cb_smem[];
+    SmemP& s = *reinterpret_cast<SmemP*>(cb_smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int seq = blockIdx.x, n = seq / p.H, h = seq - n * p.H;
+    const int nchunks = (p.L + C - 1) / C;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ the preparing warp
+        const bf16* qb = reinterpret_cast<const bf16*>(p.q.p) + n * p.q.sN + h * p.q.sH;
+        const bf16* kb = reinterpret_cast<const bf16*>(p.k.p) + n * p.k.sN + h * p.k.sH;
+        const bf16* vb = reinterpret_cast<const bf16*>(p.v.p) + n * p.v.sN + h * p.v.sH;
+        const bf16* bb = reinterpret_cast<const bf16*>(p.beta.p) + n * p.beta.sN + h * p.beta.sH;
+        auto stage_in = [&](int c) {        // all copies of chunk c by this warp: 3 tiles x 16 rows x 8 pieces
+            const int st = c % 3, t0 = c * C, nt = min(C, p.L - t0);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int idx = lane + 32 * i, row = idx >> 3, part = (idx & 7) * 8;
+                bf16* dk = s.k[st] + row * LDT + part;
+                bf16* dv = s.v[st] + row * LDT + part;
+                bf16* dq = s.q[st] + row * LDT + part;
+                if (row < nt) {
+                    cp_async16(dk, kb + (long long)(t0 + row) * p.k.sL + part);
+                    cp_async16(dv, vb + (long long)(t0 + row) * p.v.sL + part);
+                    cp_async16(dq, qb + (long long)(t0 + row) * p.q.sL + part);
+                } else {
+                    *reinterpret_cast<uint4*>(dk) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(dv) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(dq) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            cp_async_commit();
+            if (lane < C) s.b[st][lane] = lane < nt ? __bfloat162float(bb[(long long)(t0 + lane) * p.beta.sL]) : 0.f;
+        };
+        stage_in(0);
+        for (int c = 0; c < nchunks; c++) {
+            const int pk = c & 1;
+            if (c >= 2) nbar_sync(BAR_EMPTY + pk, NTP);      // the chain warps are through chunk c - 2
+            if (c + 1 < nchunks) { stage_in(c + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+            __syncwarp();
+            const bf16* Ks = s.k[c % 3];
+            const bf16* Qs = s.q[c % 3];
+            const float* bs = s.b[c % 3];
+            float akk[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float aqk[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int kp = 0; kp < 2; kp++) {
+                unsigned b0[4], b1[4];
+                ldsm4(b0, Ks + (lane & 7) * LDT + 8 * (lane >> 3) + 32 * kp);
+                ldsm4(b1, Ks + (8 + (lane & 7)) * LDT + 8 * (lane >> 3) + 32 * kp);
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    unsigned ak[4], aq[4];
+                    lda_rowmajor(ak, Ks + 16 * (2 * kp + kk), LDT, lane);
+                    lda_rowmajor(aq, Qs + 16 * (2 * kp + kk), LDT, lane);
+                    mma_bf16(akk[0], ak, b0[2 * kk], b0[2 * kk + 1]);
+                    mma_bf16(akk[1], ak, b1[2 * kk], b1[2 * kk + 1]);
+                    mma_bf16(aqk[0], aq, b0[2 * kk], b0[2 * kk + 1]);
+                    mma_bf16(aqk[1], aq, b1[2 * kk], b1[2 * kk + 1]);
+                }
+            }
+            float N1[2][4], Y[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int r = g + 8 * (i >> 1), cc = 8 * j + 2 * t4 + (i & 1);
+                    N1[j][i] = cc < r ? akk[j][i] * bs[cc] : 0.f;
+                    aqk[j][i] = cc <= r ? aqk[j][i] : 0.f;
+                    Y[j][i] = -N1[j][i];
+                }
+            unsigned th[4], tl[4], yh[4], yl[4], qk[4];
+            {
+                unsigned lo[4];
+                bt_of(qk, lo, aqk);
+            }
+            unsigned a[4], bN[4], b2[4];
+            float N2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            a_of(a, N1);
+            b_of(bN, N1);
+            mm(N2, a, bN);                                  // N^2
+            b_of(b2, N2);
+            {
+                float N3[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                mm(N3, a, b2);                              // N^3
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N2[j][i] - N3[j][i];
+            }
+            float N4[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            a_of(a, N2);
+            mm(N4, a, b2);                                  // N^4
+            unsigned b4[4];
+            b_of(b4, N4);
+            {
+                float Z1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                a_of(a, Y);
+                mm(Z1, a, b4);                              // Y N^4
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N4[j][i] + Z1[j][i];
+            }
+            float N8[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            a_of(a, N4);
+            mm(N8, a, b4);                                  // N^8
+            {
+                unsigned b8[4];
+                b_of(b8, N8);
+                float Z2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                a_of(a, Y);
+                mm(Z2, a, b8);                              // Y N^8
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N8[j][i] + Z2[j][i];
+            }
+            float T[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) T[j][i] = Y[j][i] + ((8 * j + 2 * t4 + (i & 1)) == (g + 8 * (i >> 1)) ? 1.f : 0.f);
+            bt_of(th, tl, T);
+            bt_of(yh, yl, Y);
+            s.frag[pk][0][lane] = make_uint4(th[0], th[1], th[2], th[3]);
+            s.frag[pk][1][lane] = make_uint4(tl[0], tl[1], tl[2], tl[3]);
+            s.frag[pk][2][lane] = make_uint4(yh[0], yh[1], yh[2], yh[3]);
+            s.frag[pk][3][lane] = make_uint4(yl[0], yl[1], yl[2], yl[3]);
+            s.frag[pk][4][lane] = make_uint4(qk[0], qk[1], qk[2], qk[3]);
+            unsigned ah[4], al[4];
+            split_bf16(T[0][0], T[0][1], ah[0], al[0]); split_bf16(T[0][2], T[0][3], ah[1], al[1]);
+            split_bf16(T[1][0], T[1][1], ah[2], al[2]); split_bf16(T[1][2], T[1][3], ah[3], al[3]);
+#pragma unroll
+            for (int w = 0; w < 4; w++) {                   // Ck = T K, sixteen columns at a time
+                unsigned bK[4];
+                ldb_kn(bK, Ks + 16 * w, LDT, lane);
+                float ck[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                mm(ck, ah, bK);
+                mm(ck, al, bK);
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    *reinterpret_cast<unsigned*>(s.ck[pk] + g * LDT + 16 * w + 8 * j + 2 * t4) = pack_bf16(ck[j][0], ck[j][1]);
+                    *reinterpret_cast<unsigned*>(s.ck[pk] + (g + 8) * LDT + 16 * w + 8 * j + 2 * t4) = pack_bf16(ck[j][2], ck[j][3]);
+                }
+            }
+            nbar_arrive(BAR_FULL + pk, NTP);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- the chain warps
+    bf16* yb = reinterpret_cast<bf16*>(p.out.p) + n * p.out.sN + h * p.out.sH;
+    float* vob = reinterpret_cast<float*>(p.v_old.p) + n * p.v_old.sN + h * p.v_old.sH;
+    float* uib = p.v_ins.p ? reinterpret_cast<float*>(p.v_ins.p) + n * p.v_ins.sN + h * p.v_ins.sH : nullptr;
+    float* W = p.W + n * p.wN + h * p.wH;
+    const int m0 = 16 * warp;
+    float S[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) S[j][i] = W[(long long)(8 * j + 2 * t4 + (i & 1)) * p.wE + m0 + g + 8 * (i >> 1)];
+
+    for (int c = 0; c < nchunks; c++) {
+        const int pk = c & 1, st = c % 3, t0 = c * C, nt = min(C, p.L - t0);
+        nbar_sync(BAR_FULL + pk, NTP);
+        const bf16* Ks = s.k[st];
+        const bf16* Qs = s.q[st];
+        const float* bs = s.b[st];
+        const bf16* cks = s.ck[pk];
+        unsigned th[4], tl[4], yh[4], yl[4], qk[4];
+        {
+            const uint4 f0 = s.frag[pk][0][lane], f1 = s.frag[pk][1][lane], f2 = s.frag[pk][2][lane],
+                        f3 = s.frag[pk][3][lane], f4 = s.frag[pk][4][lane];
+            th[0] = f0.x; th[1] = f0.y; th[2] = f0.z; th[3] = f0.w;
+            tl[0] = f1.x; tl[1] = f1.y; tl[2] = f1.z; tl[3] = f1.w;
+            yh[0] = f2.x; yh[1] = f2.y; yh[2] = f2.z; yh[3] = f2.w;
+            yl[0] = f3.x; yl[1] = f3.y; yl[2] = f3.z; yl[3] = f3.w;
+            qk[0] = f4.x; qk[1] = f4.y; qk[2] = f4.z; qk[3] = f4.w;
+        }
+        unsigned sa[4][4];
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            sa[ks][0] = pack_bf16(S[2 * ks][0], S[2 * ks][1]);
+            sa[ks][1] = pack_bf16(S[2 * ks][2], S[2 * ks][3]);
+            sa[ks][2] = pack_bf16(S[2 * ks + 1][0], S[2 * ks + 1][1]);
+            sa[ks][3] = pack_bf16(S[2 * ks + 1][2], S[2 * ks + 1][3]);
+        }
+        float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float Yo[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            unsigned bc[4], bq[4];
+            ldb_nk(bc, cks + 16 * ks, LDT, lane);
+            ldb_nk(bq, Qs + 16 * ks, LDT, lane);
+            mm(P, sa[ks], bc);
+            mm(Yo, sa[ks], bq);
+        }
+        float cv[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float py[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            unsigned va[4];
+            lda_trans(va, s.v[st] + m0, LDT, lane);
+            mm(cv, va, th);
+            mm(cv, va, tl);
+            mm(py, va, yh);
+            mm(py, va, yl);
+        }
+        float u[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; j++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int m = m0 + g + 8 * (i >> 1), t = 8 * j + 2 * t4 + (i & 1);
+                u[j][i] = bs[t] * (cv[j][i] - P[j][i]);
+                if (t < nt) {
+                    vob[(long long)(t0 + t) * p.v_old.sL + m] = P[j][i] - py[j][i];
+                    if (uib) uib[(long long)(t0 + t) * p.v_ins.sL + m] = u[j][i];
+                }
+            }
+        unsigned ua[4], ul[4];
+        split_bf16(u[0][0], u[0][1], ua[0], ul[0]); split_bf16(u[0][2], u[0][3], ua[1], ul[1]);
+        split_bf16(u[1][0], u[1][1], ua[2], ul[2]); split_bf16(u[1][2], u[1][3], ua[3], ul[3]);
+        mm(Yo, ua, qk);
+#pragma unroll
+        for (int jp = 0; jp < 4; jp++) {
+            unsigned bk[4];
+            ldb_kn(bk, Ks + 16 * jp, LDT, lane);
+            mma_bf16(S[2 * jp], ua, bk[0], bk[1]);
+            mma_bf16(S[2 * jp + 1], ua, bk[2], bk[3]);
+            mma_bf16(S[2 * jp], ul, bk[0], bk[1]);
+            mma_bf16(S[2 * jp + 1], ul, bk[2], bk[3]);
+        }
+        if (c + 2 < nchunks) nbar_arrive(BAR_EMPTY + pk, NTP);      // last read of the package and of the stage is behind us
+        bf16* ys = s.ys[pk];
+#pragma unroll
+        for (int j = 0; j < 2; j++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                ys[(8 * j + 2 * t4 + (i & 1)) * LDT + m0 + g + 8 * (i >> 1)] = __float2bfloat16_rn(Yo[j][i]);
+        nbar_sync(BAR_CHAIN, NT);
+        {   // y: 16-byte row pieces
+            const int row = tid >> 3, part = (tid & 7) * 8;
+            if (row < nt)
+                *reinterpret_cast<uint4*>(yb + (long long)(t0 + row) * p.out.sL + part) =
+                    *reinterpret_cast<const uint4*>(ys + row * LDT + part);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) W[(long long)(8 * j + 2 * t4 + (i & 1)) * p.wE + m0 + g + 8 * (i >> 1)] = S[j][i];
+}
+
+
 // ------------------------------------------------------------------ backward kernel
 // The backward substitution is the transposed system: with
 // T' = (I + diag(b) Akk)^-1 (built per warp in registers like T of the forward), [Lt | Kt] = T'^T [Aqk^T gY | K],

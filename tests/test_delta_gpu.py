@@ -423,7 +423,7 @@ def test_tcgen05_forward_plan_meets_the_oracle(fwp, B, H, L):
     finally:
         _lib.tune('delta.tc64', 0)
     assert _lib.device_fault() == 0
-    assert res[1][4] == 'delta_fwd_tc_kernel' and res[0][4] == 'delta_fwd_chunk_bf16_inv_kernel'
+    assert res[1][4] == 'delta_fwd_tc_kernel' and res[0][4] == 'delta_fwd_chunk_bf16_pipe_kernel'
     f = [t.float() for t in (q, k, v, b)]
     y64, g64, S64 = run_loop(*f, W0, gy.float(), torch.float64)
     y32, g32, _ = run_loop(*f, W0, gy.float(), torch.float32)
