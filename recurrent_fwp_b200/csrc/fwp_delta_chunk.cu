@@ -81,7 +81,7 @@ int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
         if (rc >= 0) return rc;
     }
     // "delta.pipe64" = 1 (default): the state-independent part of every chunk is prepared one chunk ahead by a fifth warp
-    if (tune_get(T_DELTA_PIPE64, 1) == 1)
+    if (tune_get(T_DELTA_PIPE64, 1) >= 1)
         return launch(delta_fwd_chunk_bf16_pipe_kernel, p, nseq, cb::NTP, sizeof(cb::SmemP), st, "delta_fwd_chunk_bf16_pipe_kernel");
     return launch(delta_fwd_chunk_bf16_inv_kernel, p, nseq, cb::NT, sizeof(cb::SmemI), st, "delta_fwd_chunk_bf16_inv_kernel");
 }
@@ -93,6 +93,9 @@ bool chunk_bf16_applies(const DeltaBwdParams& p) {
 }
 
 int launch_bwd_chunk_bf16(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
+    // "delta.pipe64": 1 both directions with a preparing warp, 2 the forward only, 0 neither
+    if (tune_get(T_DELTA_PIPE64, 1) == 1)
+        return launch(delta_bwd_chunk_bf16_pipe_kernel, p, nseq, cb::NTP, sizeof(cb::SmemBP), st, "delta_bwd_chunk_bf16_pipe_kernel");
     return launch(delta_bwd_chunk_bf16_inv_kernel, p, nseq, cb::NT, sizeof(cb::SmemB2), st, "delta_bwd_chunk_bf16_inv_kernel");
 }
 

@@ -1094,4 +1094,452 @@ __global__ void __launch_bounds__(cb::NT, 3) delta_bwd_chunk_bf16_inv_kernel(con
                 make_float2(S[j][2 * hr], S[j][2 * hr + 1]);
 }
 
+// ------------------------------------------------------------------ backward, state-independent part one chunk ahead
+// The same split as in the forward: a fifth warp issues the copies and prepares, one chunk ahead, everything of a
+// chunk that involves neither S nor G -- the Gram tiles, T' = (I + diag(b) Akk)^-1, X = Aqk T' (a fragment set),
+// Kt = T'^T K, w = v - v_old and U = b w in two bf16 parts, B = lower(gY U^T) -- and the four chain warps keep the
+// products with S and G.  FULL / EMPTY named barriers per package buffer as in the forward; input stages and
+// packages are rings of two (the preparing warp refills a stage as soon as the chain warps have left it, a whole
+// chunk of chain work before it is needed).
+namespace cb {
+
+struct SmemBP {
+    __nv_bfloat16 k[2][C * LDT], q[2][C * LDT], v[2][C * LDT], gy[2][C * LDT];   // input stages
+    float vo[2][C * LDO];               // v_old stages, [t][m]; becomes w = v - v_old in place
+    float b[2][C];
+    uint4 fx[2][32];                    // per package: X = Aqk T' as right-operand fragments
+    __nv_bfloat16 kt[2][C * LDT];       // per package: Kt, [t][e]
+    __nv_bfloat16 uh[2][C * LDT], ul[2][C * LDT];   // per package: U = b w as two bf16 parts, [t][m]
+    __nv_bfloat16 bm[2][C * LDQ];       // per package: B = lower(gY U^T), [t][i]
+    __nv_bfloat16 bl[C * LDT];          // b lambda = dv, [t][m]
+    __nv_bfloat16 gs[D * LDT];          // G1 rounded to bf16, [e][m]
+    alignas(16) __nv_bfloat16 dqdk[2 * C * LDT];   // dQ, dK, [t][e]
+    float dbp[4][C];                    // per-warp partial sums of dbeta
+};
+
+}  // namespace cb
+
+__global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(const DeltaBwdParams p) {
+    using namespace cb;
+    using bf16 = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char cb_smem[];
+    SmemBP& s = *reinterpret_cast<SmemBP*>(cb_smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int seq = blockIdx.x, n = seq / p.H, h = seq - n * p.H;
+    const int nchunks = (p.L + C - 1) / C;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ the preparing warp
+        const bf16* qb = reinterpret_cast<const bf16*>(p.q.p) + n * p.q.sN + h * p.q.sH;
+        const bf16* kb = reinterpret_cast<const bf16*>(p.k.p) + n * p.k.sN + h * p.k.sH;
+        const bf16* vb = reinterpret_cast<const bf16*>(p.v.p) + n * p.v.sN + h * p.v.sH;
+        const bf16* bb = reinterpret_cast<const bf16*>(p.beta.p) + n * p.beta.sN + h * p.beta.sH;
+        const bf16* gyb = reinterpret_cast<const bf16*>(p.gy.p) + n * p.gy.sN + h * p.gy.sH;
+        const float* vob = reinterpret_cast<const float*>(p.v_old.p) + n * p.v_old.sN + h * p.v_old.sH;
+        auto stage_in = [&](int it) {       // all copies of the chunk processed it-th, by this warp
+            const int st = it & 1, c = nchunks - 1 - it, t0 = c * C, nt = min(C, p.L - t0);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int idx = lane + 32 * i, row = idx >> 3, part = (idx & 7) * 8;
+                const int o = row * LDT + part;
+                if (row < nt) {
+                    cp_async16(s.k[st] + o, kb + (long long)(t0 + row) * p.k.sL + part);
+                    cp_async16(s.q[st] + o, qb + (long long)(t0 + row) * p.q.sL + part);
+                    cp_async16(s.v[st] + o, vb + (long long)(t0 + row) * p.v.sL + part);
+                    cp_async16(s.gy[st] + o, gyb + (long long)(t0 + row) * p.gy.sL + part);
+                } else {
+                    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(s.k[st] + o) = z;
+                    *reinterpret_cast<uint4*>(s.q[st] + o) = z;
+                    *reinterpret_cast<uint4*>(s.v[st] + o) = z;
+                    *reinterpret_cast<uint4*>(s.gy[st] + o) = z;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int idx = lane + 32 * i, row = idx >> 4, part = (idx & 15) * 4;
+                float* dst = s.vo[st] + row * LDO + part;
+                if (row < nt) cp_async16(dst, vob + (long long)(t0 + row) * p.v_old.sL + part);
+                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            cp_async_commit();
+            if (lane < C) s.b[st][lane] = lane < nt ? __bfloat162float(bb[(long long)(t0 + lane) * p.beta.sL]) : 0.f;
+        };
+        stage_in(0);
+        for (int it = 0; it < nchunks; it++) {
+            const int pk = it & 1;
+            cp_async_wait<0>();
+            __syncwarp();
+            const bf16* Ks = s.k[pk];
+            const bf16* Qs = s.q[pk];
+            const bf16* Ys = s.gy[pk];
+            float* Ws = s.vo[pk];
+            const float* bs = s.b[pk];
+            unsigned bX[4];
+            float Y[2][4];
+            {
+            float akk[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float aqk[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int kp = 0; kp < 2; kp++) {
+                unsigned b0[4], b1[4];
+                ldsm4(b0, Ks + (lane & 7) * LDT + 8 * (lane >> 3) + 32 * kp);
+                ldsm4(b1, Ks + (8 + (lane & 7)) * LDT + 8 * (lane >> 3) + 32 * kp);
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    unsigned ak[4], aq[4];
+                    lda_rowmajor(ak, Ks + 16 * (2 * kp + kk), LDT, lane);
+                    lda_rowmajor(aq, Qs + 16 * (2 * kp + kk), LDT, lane);
+                    mma_bf16(akk[0], ak, b0[2 * kk], b0[2 * kk + 1]);
+                    mma_bf16(akk[1], ak, b1[2 * kk], b1[2 * kk + 1]);
+                    mma_bf16(aqk[0], aq, b0[2 * kk], b0[2 * kk + 1]);
+                    mma_bf16(aqk[1], aq, b1[2 * kk], b1[2 * kk + 1]);
+                }
+            }
+            float N1[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int r = g + 8 * (i >> 1), cc = 8 * j + 2 * t4 + (i & 1);
+                    N1[j][i] = cc < r ? akk[j][i] * bs[r] : 0.f;
+                    aqk[j][i] = cc <= r ? aqk[j][i] : 0.f;
+                    Y[j][i] = -N1[j][i];
+                }
+            unsigned a[4], bN[4], b2[4], b4[4];
+            float N2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            a_of(a, N1);
+            b_of(bN, N1);
+            mm(N2, a, bN);
+            b_of(b2, N2);
+            {
+                float N3[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                mm(N3, a, b2);
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N2[j][i] - N3[j][i];
+            }
+            float N4[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            a_of(a, N2);
+            mm(N4, a, b2);
+            b_of(b4, N4);
+            {
+                float Z1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                a_of(a, Y);
+                mm(Z1, a, b4);
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N4[j][i] + Z1[j][i];
+            }
+            {
+                float N8[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                a_of(a, N4);
+                mm(N8, a, b4);
+                unsigned b8[4];
+                b_of(b8, N8);
+                float Z2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                a_of(a, Y);
+                mm(Z2, a, b8);
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) Y[j][i] += N8[j][i] + Z2[j][i];
+            }
+            {   // X = Aqk T' = Aqk + Aqk (T' - I)
+                unsigned by[4];
+                b_of(by, Y);
+                a_of(a, aqk);
+                mm(aqk, a, by);
+                b_of(bX, aqk);
+            }
+            }
+            s.fx[pk][lane] = make_uint4(bX[0], bX[1], bX[2], bX[3]);
+            {   // Kt = T'^T K, sixteen columns at a time: the left operand is the transposed fragment, in two bf16 parts
+                float T[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) T[j][i] = Y[j][i] + ((8 * j + 2 * t4 + (i & 1)) == (g + 8 * (i >> 1)) ? 1.f : 0.f);
+                unsigned ah[4], al[4], th2[4], tl2[4];
+                split_bf16(T[0][0], T[0][1], ah[0], al[0]); split_bf16(T[0][2], T[0][3], ah[1], al[1]);
+                split_bf16(T[1][0], T[1][1], ah[2], al[2]); split_bf16(T[1][2], T[1][3], ah[3], al[3]);
+                th2[0] = movm(ah[0]); th2[1] = movm(ah[2]); th2[2] = movm(ah[1]); th2[3] = movm(ah[3]);
+                tl2[0] = movm(al[0]); tl2[1] = movm(al[2]); tl2[2] = movm(al[1]); tl2[3] = movm(al[3]);
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    unsigned bK[4];
+                    ldb_kn(bK, Ks + 16 * w, LDT, lane);
+                    float kt[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                    mm(kt, th2, bK);
+                    mm(kt, tl2, bK);
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        *reinterpret_cast<unsigned*>(s.kt[pk] + g * LDT + 16 * w + 8 * j + 2 * t4) = pack_bf16(kt[j][0], kt[j][1]);
+                        *reinterpret_cast<unsigned*>(s.kt[pk] + (g + 8) * LDT + 16 * w + 8 * j + 2 * t4) = pack_bf16(kt[j][2], kt[j][3]);
+                    }
+                }
+            }
+            // w = v - v_old in place, U = b w in two bf16 parts: sixteen rows of eight 8-element pieces
+#pragma unroll
+            for (int ii = 0; ii < 4; ii++) {
+                const int idx = lane + 32 * ii, row = idx >> 3, part = (idx & 7) * 8;
+                const uint4 vraw = *reinterpret_cast<const uint4*>(s.v[pk] + row * LDT + part);
+                const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vraw);
+                float* wp = Ws + row * LDO + part;
+                const float4 o0 = *reinterpret_cast<const float4*>(wp), o1 = *reinterpret_cast<const float4*>(wp + 4);
+                const float vo8[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+                float w8[8];
+                unsigned hi[4], lo[4];
+                const float br = bs[row];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    w8[2 * i] = __low2float(v2[i]) - vo8[2 * i];
+                    w8[2 * i + 1] = __high2float(v2[i]) - vo8[2 * i + 1];
+                    const float u0 = br * w8[2 * i], u1 = br * w8[2 * i + 1];
+                    hi[i] = pack_bf16(u0, u1);
+                    const __nv_bfloat162 hh = *reinterpret_cast<const __nv_bfloat162*>(&hi[i]);
+                    lo[i] = pack_bf16(u0 - __low2float(hh), u1 - __high2float(hh));
+                }
+                *reinterpret_cast<float4*>(wp) = make_float4(w8[0], w8[1], w8[2], w8[3]);
+                *reinterpret_cast<float4*>(wp + 4) = make_float4(w8[4], w8[5], w8[6], w8[7]);
+                *reinterpret_cast<uint4*>(s.uh[pk] + row * LDT + part) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(s.ul[pk] + row * LDT + part) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int w = 0; w < 2; w++) {   // B = lower(gY U^T), two column tiles
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const int col = 8 * w + 2 * t4;
+                gram_tile(acc, Ys, s.uh[pk], w, lane);
+                *reinterpret_cast<unsigned*>(s.bm[pk] + g * LDQ + col) =
+                    pack_bf16(col <= g ? acc[0] : 0.f, col + 1 <= g ? acc[1] : 0.f);
+                *reinterpret_cast<unsigned*>(s.bm[pk] + (g + 8) * LDQ + col) =
+                    pack_bf16(col <= g + 8 ? acc[2] : 0.f, col + 1 <= g + 8 ? acc[3] : 0.f);
+            }
+            nbar_arrive(BAR_FULL + pk, NTP);
+            if (it + 1 < nchunks) {
+                if (it >= 1) nbar_sync(BAR_EMPTY + (pk ^ 1), NTP);     // the chain warps have left the other stage and package
+                stage_in(it + 1);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- the chain warps
+    bf16* gqb = reinterpret_cast<bf16*>(p.gq.p) + n * p.gq.sN + h * p.gq.sH;
+    bf16* gkb = reinterpret_cast<bf16*>(p.gk.p) + n * p.gk.sN + h * p.gk.sH;
+    bf16* gvb = reinterpret_cast<bf16*>(p.gv.p) + n * p.gv.sN + h * p.gv.sH;
+    bf16* gbb = reinterpret_cast<bf16*>(p.gb.p) + n * p.gb.sN + h * p.gb.sH;
+    float* W = p.W + n * p.wN + h * p.wH;
+    const int e0 = 16 * warp;
+    float S[8][4], G[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int hr = 0; hr < 2; hr++) {
+            const float2 x = *reinterpret_cast<const float2*>(W + (long long)(e0 + g + 8 * hr) * p.wE + 8 * j + 2 * t4);
+            S[j][2 * hr] = x.x; S[j][2 * hr + 1] = x.y;
+            G[j][2 * hr] = 0.f; G[j][2 * hr + 1] = 0.f;
+        }
+    for (int it = 0; it < nchunks; it++) {
+        const int c = nchunks - 1 - it, pk = it & 1, t0 = c * C, nt = min(C, p.L - t0);
+        // the bf16 copy of G1 needs nothing from the package
+#pragma unroll
+        for (int jj = 0; jj < 8; jj++) {
+            *reinterpret_cast<unsigned*>(s.gs + (e0 + g) * LDT + 8 * jj + 2 * t4) = pack_bf16(G[jj][0], G[jj][1]);
+            *reinterpret_cast<unsigned*>(s.gs + (e0 + g + 8) * LDT + 8 * jj + 2 * t4) = pack_bf16(G[jj][2], G[jj][3]);
+        }
+        nbar_sync(BAR_CHAIN, NT);
+        nbar_sync(BAR_FULL + pk, NTP);
+        const bf16* Ks = s.k[pk];
+        const bf16* Qs = s.q[pk];
+        const bf16* Ys = s.gy[pk];
+        const float* Ws = s.vo[pk];
+        const float* bs = s.b[pk];
+        const bf16* s_kt = s.kt[pk];
+        const bf16* s_uh = s.uh[pk];
+        const bf16* s_ul = s.ul[pk];
+        const bf16* s_bm = s.bm[pk];
+        bf16* dqs = s.dqdk;
+        bf16* dks = s.dqdk + C * LDT;
+        unsigned bX[4];
+        {
+            const uint4 f = s.fx[pk][lane];
+            bX[0] = f.x; bX[1] = f.y; bX[2] = f.z; bX[3] = f.w;
+        }
+
+        {   // (4a) lambda^T rows m in [e0, e0+16): Lt^T + G1^T Kt^T with Lt^T = gY^T X; dv = b lambda; partial sums of dbeta
+            float lm[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            {
+                unsigned ya[4];
+                lda_trans(ya, Ys + e0, LDT, lane);
+                mm(lm, ya, bX);
+            }
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                unsigned a[4], bk[4];
+                lda_trans(a, s.gs + 16 * ks * LDT + e0, LDT, lane);
+                ldb_nk(bk, s_kt + 16 * ks, LDT, lane);
+                mma_bf16(lm[0], a, bk[0], bk[1]);
+                mma_bf16(lm[1], a, bk[2], bk[3]);
+            }
+            float db[2][2];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                db[j][0] = 0.f; db[j][1] = 0.f;
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++) {
+                    const int m = e0 + g + 8 * hr, t = 8 * j + 2 * t4;
+                    const float l0 = lm[j][2 * hr], l1 = lm[j][2 * hr + 1];
+                    db[j][0] = fmaf(l0, Ws[t * LDO + m], db[j][0]);
+                    db[j][1] = fmaf(l1, Ws[(t + 1) * LDO + m], db[j][1]);
+                    s.bl[t * LDT + m] = __float2bfloat16_rn(bs[t] * l0);
+                    s.bl[(t + 1) * LDT + m] = __float2bfloat16_rn(bs[t + 1] * l1);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int par = 0; par < 2; par++) {
+                    float x = db[j][par];
+                    x += __shfl_xor_sync(0xffffffffu, x, 4);
+                    x += __shfl_xor_sync(0xffffffffu, x, 8);
+                    x += __shfl_xor_sync(0xffffffffu, x, 16);
+                    if (g == 0) s.dbp[warp][8 * j + 2 * t4 + par] = x;
+                }
+        }
+        nbar_sync(BAR_CHAIN, NT);
+
+        {   // (4b) rewind S, the warp's 16 columns of dQ and dK, then G
+            unsigned ka[4], kan[4];
+            lda_trans(ka, Ks + e0, LDT, lane);          // K^T rows e0.., contraction over the 16 steps
+            neg4(kan, ka);
+#pragma unroll
+            for (int jp = 0; jp < 4; jp++) {
+                unsigned bh[4], bl2[4];
+                ldb_kn(bh, s_uh + 16 * jp, LDT, lane);
+                ldb_kn(bl2, s_ul + 16 * jp, LDT, lane);
+                mma_bf16(S[2 * jp], kan, bh[0], bh[1]);
+                mma_bf16(S[2 * jp + 1], kan, bh[2], bh[3]);
+                mma_bf16(S[2 * jp], kan, bl2[0], bl2[1]);
+                mma_bf16(S[2 * jp + 1], kan, bl2[2], bl2[3]);
+            }
+            float dq[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float dk[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float Z[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float ZT[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                // right operands from the accumulators, each as two bf16 parts: contraction over m in
+                // [16ks, 16ks+16), columns e0+g (first index 0) and e0+8+g (first index 1)
+                unsigned sh[2][2], sl[2][2], gh[2][2], gl[2][2];
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++)
+#pragma unroll
+                    for (int kk = 0; kk < 2; kk++) {
+                        split_bf16(S[2 * ks + kk][2 * hr], S[2 * ks + kk][2 * hr + 1], sh[hr][kk], sl[hr][kk]);
+                        split_bf16(G[2 * ks + kk][2 * hr], G[2 * ks + kk][2 * hr + 1], gh[hr][kk], gl[hr][kk]);
+                    }
+                unsigned ya[4], ua[4], ula[4], la[4], lan[4];
+                lda_rowmajor(ya, Ys + 16 * ks, LDT, lane);
+                lda_rowmajor(ua, s_uh + 16 * ks, LDT, lane);
+                lda_rowmajor(ula, s_ul + 16 * ks, LDT, lane);
+                lda_rowmajor(la, s.bl + 16 * ks, LDT, lane);
+                neg4(lan, la);
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++) {
+                    mma_bf16(dq[hr], ya, sh[hr][0], sh[hr][1]);
+                    mma_bf16(dq[hr], ya, sl[hr][0], sl[hr][1]);
+                    mma_bf16(dk[hr], ua, gh[hr][0], gh[hr][1]);
+                    mma_bf16(dk[hr], ua, gl[hr][0], gl[hr][1]);
+                    mma_bf16(dk[hr], ula, gh[hr][0], gh[hr][1]);
+                    mma_bf16(dk[hr], lan, sh[hr][0], sh[hr][1]);
+                    mma_bf16(dk[hr], lan, sl[hr][0], sl[hr][1]);
+                }
+            }
+            // Z = (b lambda) U^T and its transpose in a loop of their own: fewer accumulators live at once
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                unsigned ua[4], la[4], bu[4], bb2[4];
+                lda_rowmajor(ua, s_uh + 16 * ks, LDT, lane);
+                lda_rowmajor(la, s.bl + 16 * ks, LDT, lane);
+                ldb_nk(bu, s_uh + 16 * ks, LDT, lane);
+                ldb_nk(bb2, s.bl + 16 * ks, LDT, lane);
+                mma_bf16(Z[0], la, bu[0], bu[1]);
+                mma_bf16(Z[1], la, bu[2], bu[3]);
+                mma_bf16(ZT[0], ua, bb2[0], bb2[1]);
+                mma_bf16(ZT[1], ua, bb2[2], bb2[3]);
+            }
+            unsigned bK[4], bQ[4], ba[4], bta[4], za[4], qa[4];
+            ldb_kn(bK, Ks + e0, LDT, lane);
+            ldb_kn(bQ, Qs + e0, LDT, lane);
+            lda_rowmajor(ba, s_bm, LDQ, lane);
+            lda_trans(bta, s_bm, LDQ, lane);
+            mma_bf16(dq[0], ba, bK[0], bK[1]);
+            mma_bf16(dq[1], ba, bK[2], bK[3]);
+            mma_bf16(dk[0], bta, bQ[0], bQ[1]);
+            mma_bf16(dk[1], bta, bQ[2], bQ[3]);
+            {
+                float z[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; j++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int r = g + 8 * (i >> 1), cc = 8 * j + 2 * t4 + (i & 1);
+                        z[j][i] = -((cc < r ? Z[j][i] : 0.f) + (cc > r ? ZT[j][i] : 0.f));
+                    }
+                za[0] = pack_bf16(z[0][0], z[0][1]); za[1] = pack_bf16(z[0][2], z[0][3]);
+                za[2] = pack_bf16(z[1][0], z[1][1]); za[3] = pack_bf16(z[1][2], z[1][3]);
+            }
+            mma_bf16(dk[0], za, bK[0], bK[1]);
+            mma_bf16(dk[1], za, bK[2], bK[3]);
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int col = e0 + 8 * j + 2 * t4;
+                *reinterpret_cast<unsigned*>(dqs + g * LDT + col) = pack_bf16(dq[j][0], dq[j][1]);
+                *reinterpret_cast<unsigned*>(dqs + (g + 8) * LDT + col) = pack_bf16(dq[j][2], dq[j][3]);
+                *reinterpret_cast<unsigned*>(dks + g * LDT + col) = pack_bf16(dk[j][0], dk[j][1]);
+                *reinterpret_cast<unsigned*>(dks + (g + 8) * LDT + col) = pack_bf16(dk[j][2], dk[j][3]);
+            }
+            // G0 = G1 + Q^T gY - K^T (b lambda)
+            lda_trans(qa, Qs + e0, LDT, lane);
+#pragma unroll
+            for (int jp = 0; jp < 4; jp++) {
+                unsigned bg[4], bd[4];
+                ldb_kn(bg, Ys + 16 * jp, LDT, lane);
+                ldb_kn(bd, s.bl + 16 * jp, LDT, lane);
+                mma_bf16(G[2 * jp], qa, bg[0], bg[1]);
+                mma_bf16(G[2 * jp + 1], qa, bg[2], bg[3]);
+                mma_bf16(G[2 * jp], kan, bd[0], bd[1]);
+                mma_bf16(G[2 * jp + 1], kan, bd[2], bd[3]);
+            }
+        }
+        if (it + 2 < nchunks) nbar_arrive(BAR_EMPTY + pk, NTP);      // last read of the stage and of the package is behind us
+        nbar_sync(BAR_CHAIN, NT);
+
+        {   // (5) stores: 16-byte row pieces of dQ, dK, dv; dbeta
+            const int row = tid >> 3, part = (tid & 7) * 8;
+            if (row < nt) {
+                *reinterpret_cast<uint4*>(gqb + (long long)(t0 + row) * p.gq.sL + part) =
+                    *reinterpret_cast<const uint4*>(dqs + row * LDT + part);
+                *reinterpret_cast<uint4*>(gkb + (long long)(t0 + row) * p.gk.sL + part) =
+                    *reinterpret_cast<const uint4*>(dks + row * LDT + part);
+                *reinterpret_cast<uint4*>(gvb + (long long)(t0 + row) * p.gv.sL + part) =
+                    *reinterpret_cast<const uint4*>(s.bl + row * LDT + part);
+            }
+            if (tid < nt)
+                gbb[(long long)(t0 + tid) * p.gb.sL] =
+                    __float2bfloat16_rn(s.dbp[0][tid] + s.dbp[1][tid] + s.dbp[2][tid] + s.dbp[3][tid]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int hr = 0; hr < 2; hr++)
+            *reinterpret_cast<float2*>(W + (long long)(e0 + g + 8 * hr) * p.wE + 8 * j + 2 * t4) =
+                make_float2(S[j][2 * hr], S[j][2 * hr + 1]);
+}
+
 }  // namespace fwp
