@@ -61,6 +61,8 @@ NCU_TRAFFIC = {
                              source='profiles/delta_fwd_bwd_lm_shape_ncu.md'),
     'delta_bwd_chunk_bf16_inv_kernel': dict(bytes=2430927000, seqs=512, steps=4096, d=64, dtype='bf16',
                                             source='profiles/delta_chunkwise_bf16_d64_ncu.md'),
+    'delta_bwd_chunk_bf16_pipe_kernel': dict(bytes=2429864960, seqs=512, steps=4096, d=64, dtype='bf16',
+                                             source='profiles/delta_chunkwise_bf16_d64_ncu.md'),
 }
 
 

@@ -448,7 +448,7 @@ def test_tcgen05_forward_is_the_kernel_that_ran(fwp):
     stream, dev = _lib.stream_and_device(q)
     try:
         _lib.tune('delta.tc64', 1)
-        for v_ins, want in ((None, 'delta_fwd_tc_kernel'), (vi, 'delta_fwd_chunk_bf16_inv_kernel')):
+        for v_ins, want in ((None, 'delta_fwd_tc_kernel'), (vi, 'delta_fwd_chunk_bf16_pipe_kernel')):
             W = torch.zeros(B, H, d, d, device=DEV)
             _lib.check(_lib.lib.fwp_fast_weight_forward(B, H, L, d, d, D(q), D(k), D(v), D(b), D(vo), D(v_ins), D(W), D(y),
                                                         _lib.BF16, stream, dev), 'forward')
