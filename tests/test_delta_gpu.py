@@ -435,6 +435,38 @@ def test_tcgen05_forward_plan_meets_the_oracle(fwp, B, H, L):
     assert util.max_abs(res[1][0].float(), res[0][0].float()) <= 1e-2 * y64.abs().max().item()
 
 
+@pytest.mark.parametrize('B,H,L', [(1, 1, 17), (2, 3, 33), (1, 2, 48), (3, 2, 300), (2, 16, 1024)])
+def test_preparing_warp_kernels_equal_the_self_preparing_ones_bit_for_bit(fwp, B, H, L):
+    """The chunkwise bf16 kernels with a preparing warp ('delta.pipe64' = 1, the default) do the same arithmetic as the
+    kernels in which every warp prepares for itself ('delta.pipe64' = 0), only in another warp and one chunk earlier:
+    outputs, v_old, end state, rewound state and all four gradients must be identical bit for bit, for two-chunk
+    sequences, ragged last chunks and many chunks alike."""
+    from recurrent_fwp_b200 import _lib
+    d = 64
+    q, k, v, b, gy = [t.to(torch.bfloat16) for t in util.delta_inputs(601, B, H, L, d)]
+    W0 = torch.randn(B, H, d, d, generator=util.gen(602)) * 0.1
+    res = {}
+    names = {}
+    try:
+        for pipe in (1, 0):
+            _lib.tune('delta.pipe64', pipe)
+            W = W0.to(DEV)
+            leaves = [t.detach().to(DEV).requires_grad_() for t in (q, k, v, b)]
+            y = fwp.fast_weight_delta(*leaves, W)
+            kf, kb = _lib.last_kernel(), []
+            leaves[0].register_hook(lambda g, kb=kb: kb.append(_lib.last_kernel()))
+            W_end = W.clone()
+            y.backward(gy.to(DEV))
+            res[pipe] = [y.detach(), W_end, W.clone()] + [l.grad for l in leaves]
+            names[pipe] = (kf, kb[0])
+    finally:
+        _lib.tune('delta.pipe64', 1)
+    assert names[1] == ('delta_fwd_chunk_bf16_pipe_kernel', 'delta_bwd_chunk_bf16_pipe_kernel')
+    assert names[0] == ('delta_fwd_chunk_bf16_inv_kernel', 'delta_bwd_chunk_bf16_inv_kernel')
+    for a, r in zip(res[1], res[0]):
+        assert torch.equal(a, r)
+
+
 def test_tcgen05_forward_is_the_kernel_that_ran(fwp):
     """With the switch on, an eligible call runs delta_fwd_tc_kernel; a caller that asks for v_insert, or whose
     state is not 8-byte aligned, gets the warp-level kernel (the tcgen05 plan does not apply), never an error."""
