@@ -7,7 +7,7 @@ the device strings are redirected to the CPU, ``torch.utils.cpp_extension.load``
 is replaced by a stub whose functions are ``oracle.kernels`` (so the oracle
 stands exactly where the JIT-compiled CUDA module stands), and the file is
 executed as ``__main__``.  The reference's own per-timestep autograd loop and
-its own assertions (relative error < 1e-3 / 1e-2) then judge the oracle.
+its own assertions (relative error < 1e-3 / 1e-2) then decide whether the oracle stands.
 
 After each run the seeded inputs and the *reference loop's* outputs and
 gradients are taken from the executed module's globals and stored under

@@ -79,7 +79,7 @@ def scaled_rel(a, b):
 
 def record(case, **figures):
     """Append one line of measured error figures to the file named by FWP_PARITY_REPORT (no-op without it), so a
-    GPU run leaves the numbers behind the pass/fail verdicts."""
+    GPU run leaves the numbers behind the pass/fail outcomes."""
     path = os.environ.get('FWP_PARITY_REPORT')
     if path:
         with open(path, 'a') as fh:
