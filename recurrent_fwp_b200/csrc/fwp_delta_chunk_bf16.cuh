@@ -1111,10 +1111,11 @@ struct SmemBP {
     __nv_bfloat16 kt[2][C * LDT];       // per package: Kt, [t][e]
     __nv_bfloat16 uh[2][C * LDT], ul[2][C * LDT];   // per package: U = b w as two bf16 parts, [t][m]
     __nv_bfloat16 bm[2][C * LDQ];       // per package: B = lower(gY U^T), [t][i]
-    __nv_bfloat16 bl[C * LDT];          // b lambda = dv, [t][m]
+    __nv_bfloat16 bl[2][C * LDT];       // b lambda = dv, [t][m]; two chunk parities (the stores of a chunk may still read it
+                                        // while the next chunk writes)
     __nv_bfloat16 gs[D * LDT];          // G1 rounded to bf16, [e][m]
     alignas(16) __nv_bfloat16 dqdk[2 * C * LDT];   // dQ, dK, [t][e]
-    float dbp[4][C];                    // per-warp partial sums of dbeta
+    float dbp[2][4][C];                 // per-warp partial sums of dbeta, two chunk parities
 };
 
 }  // namespace cb
@@ -1343,15 +1344,16 @@ __global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(c
             S[j][2 * hr] = x.x; S[j][2 * hr + 1] = x.y;
             G[j][2 * hr] = 0.f; G[j][2 * hr + 1] = 0.f;
         }
+    // the bf16 copy of G that the products contracting over e read: written by every warp for its rows at the end of a
+    // chunk (behind the barrier that chunk has anyway), zero before the first
+#pragma unroll
+    for (int jj = 0; jj < 8; jj++) {
+        *reinterpret_cast<unsigned*>(s.gs + (e0 + g) * LDT + 8 * jj + 2 * t4) = 0u;
+        *reinterpret_cast<unsigned*>(s.gs + (e0 + g + 8) * LDT + 8 * jj + 2 * t4) = 0u;
+    }
+    nbar_sync(BAR_CHAIN, NT);
     for (int it = 0; it < nchunks; it++) {
         const int c = nchunks - 1 - it, pk = it & 1, t0 = c * C, nt = min(C, p.L - t0);
-        // the bf16 copy of G1 needs nothing from the package
-#pragma unroll
-        for (int jj = 0; jj < 8; jj++) {
-            *reinterpret_cast<unsigned*>(s.gs + (e0 + g) * LDT + 8 * jj + 2 * t4) = pack_bf16(G[jj][0], G[jj][1]);
-            *reinterpret_cast<unsigned*>(s.gs + (e0 + g + 8) * LDT + 8 * jj + 2 * t4) = pack_bf16(G[jj][2], G[jj][3]);
-        }
-        nbar_sync(BAR_CHAIN, NT);
         nbar_sync(BAR_FULL + pk, NTP);
         const bf16* Ks = s.k[pk];
         const bf16* Qs = s.q[pk];
@@ -1364,6 +1366,8 @@ __global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(c
         const bf16* s_bm = s.bm[pk];
         bf16* dqs = s.dqdk;
         bf16* dks = s.dqdk + C * LDT;
+        bf16* s_bl = s.bl[pk];
+        float (*s_dbp)[C] = s.dbp[pk];
         unsigned bX[4];
         {
             const uint4 f = s.fx[pk][lane];
@@ -1395,8 +1399,8 @@ __global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(c
                     const float l0 = lm[j][2 * hr], l1 = lm[j][2 * hr + 1];
                     db[j][0] = fmaf(l0, Ws[t * LDO + m], db[j][0]);
                     db[j][1] = fmaf(l1, Ws[(t + 1) * LDO + m], db[j][1]);
-                    s.bl[t * LDT + m] = __float2bfloat16_rn(bs[t] * l0);
-                    s.bl[(t + 1) * LDT + m] = __float2bfloat16_rn(bs[t + 1] * l1);
+                    s_bl[t * LDT + m] = __float2bfloat16_rn(bs[t] * l0);
+                    s_bl[(t + 1) * LDT + m] = __float2bfloat16_rn(bs[t + 1] * l1);
                 }
             }
 #pragma unroll
@@ -1407,7 +1411,7 @@ __global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(c
                     x += __shfl_xor_sync(0xffffffffu, x, 4);
                     x += __shfl_xor_sync(0xffffffffu, x, 8);
                     x += __shfl_xor_sync(0xffffffffu, x, 16);
-                    if (g == 0) s.dbp[warp][8 * j + 2 * t4 + par] = x;
+                    if (g == 0) s_dbp[warp][8 * j + 2 * t4 + par] = x;
                 }
         }
         nbar_sync(BAR_CHAIN, NT);
@@ -1446,7 +1450,7 @@ __global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(c
                 lda_rowmajor(ya, Ys + 16 * ks, LDT, lane);
                 lda_rowmajor(ua, s_uh + 16 * ks, LDT, lane);
                 lda_rowmajor(ula, s_ul + 16 * ks, LDT, lane);
-                lda_rowmajor(la, s.bl + 16 * ks, LDT, lane);
+                lda_rowmajor(la, s_bl + 16 * ks, LDT, lane);
                 neg4(lan, la);
 #pragma unroll
                 for (int hr = 0; hr < 2; hr++) {
@@ -1464,9 +1468,9 @@ __global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(c
             for (int ks = 0; ks < 4; ks++) {
                 unsigned ua[4], la[4], bu[4], bb2[4];
                 lda_rowmajor(ua, s_uh + 16 * ks, LDT, lane);
-                lda_rowmajor(la, s.bl + 16 * ks, LDT, lane);
+                lda_rowmajor(la, s_bl + 16 * ks, LDT, lane);
                 ldb_nk(bu, s_uh + 16 * ks, LDT, lane);
-                ldb_nk(bb2, s.bl + 16 * ks, LDT, lane);
+                ldb_nk(bb2, s_bl + 16 * ks, LDT, lane);
                 mma_bf16(Z[0], la, bu[0], bu[1]);
                 mma_bf16(Z[1], la, bu[2], bu[3]);
                 mma_bf16(ZT[0], ua, bb2[0], bb2[1]);
@@ -1509,11 +1513,17 @@ __global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(c
             for (int jp = 0; jp < 4; jp++) {
                 unsigned bg[4], bd[4];
                 ldb_kn(bg, Ys + 16 * jp, LDT, lane);
-                ldb_kn(bd, s.bl + 16 * jp, LDT, lane);
+                ldb_kn(bd, s_bl + 16 * jp, LDT, lane);
                 mma_bf16(G[2 * jp], qa, bg[0], bg[1]);
                 mma_bf16(G[2 * jp + 1], qa, bg[2], bg[3]);
                 mma_bf16(G[2 * jp], kan, bd[0], bd[1]);
                 mma_bf16(G[2 * jp + 1], kan, bd[2], bd[3]);
+            }
+            // the bf16 copy of G0 for the next chunk's products (nobody reads the tile between here and the barrier below)
+#pragma unroll
+            for (int jj = 0; jj < 8; jj++) {
+                *reinterpret_cast<unsigned*>(s.gs + (e0 + g) * LDT + 8 * jj + 2 * t4) = pack_bf16(G[jj][0], G[jj][1]);
+                *reinterpret_cast<unsigned*>(s.gs + (e0 + g + 8) * LDT + 8 * jj + 2 * t4) = pack_bf16(G[jj][2], G[jj][3]);
             }
         }
         if (it + 2 < nchunks) nbar_arrive(BAR_EMPTY + pk, NTP);      // last read of the stage and of the package is behind us
@@ -1527,11 +1537,11 @@ __global__ void __launch_bounds__(cb::NTP, 3) delta_bwd_chunk_bf16_pipe_kernel(c
                 *reinterpret_cast<uint4*>(gkb + (long long)(t0 + row) * p.gk.sL + part) =
                     *reinterpret_cast<const uint4*>(dks + row * LDT + part);
                 *reinterpret_cast<uint4*>(gvb + (long long)(t0 + row) * p.gv.sL + part) =
-                    *reinterpret_cast<const uint4*>(s.bl + row * LDT + part);
+                    *reinterpret_cast<const uint4*>(s_bl + row * LDT + part);
             }
             if (tid < nt)
                 gbb[(long long)(t0 + tid) * p.gb.sL] =
-                    __float2bfloat16_rn(s.dbp[0][tid] + s.dbp[1][tid] + s.dbp[2][tid] + s.dbp[3][tid]);
+                    __float2bfloat16_rn(s_dbp[0][tid] + s_dbp[1][tid] + s_dbp[2][tid] + s_dbp[3][tid]);
         }
     }
 #pragma unroll
