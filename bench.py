@@ -50,6 +50,12 @@ WORKLOADS = {
     'small': (2, 8, 256, 16, 1, 'fp32'),          # the reference's own CPU-runnable case
     'long': (256, 16, 4096, 64, 1, 'bf16'),       # scale-out shape, kernel part
     'long_slice': (32, 16, 4096, 64, 1, 'bf16'),  # an eighth of it (one GPU's shard at N=8)
+    # the other execution plans of the delta and sum rules, for --kernels-only timing and the ncu captures
+    'lm_d32': (64, 8, 256, 32, 1, 'fp32'),        # fp32 at d = 32: per-step forward, blocked backward
+    'lm_d64': (64, 8, 256, 64, 1, 'fp32'),        # fp32 at d = 64
+    'wide': (16, 8, 256, 128, 1, 'fp32'),         # E = M = 128: matrices in shared memory (the generic kernels)
+    'sum_d16': (64, 8, 256, 16, 1, 'fp32'),       # sum rule (causal product and its backward), LM shape
+    'sum_wide': (16, 8, 256, 128, 1, 'fp32'),     # sum rule, E = M = 128
 }
 
 # DRAM read+write bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture), keyed by
@@ -224,9 +230,10 @@ def run_reference_arm(args):
 class DeltaStep:
     """Device-resident fwd+bwd over `segs` carried segments through the C ABI, pre-allocated buffers."""
 
-    def __init__(self, B, H, L, d, segs, dtype, device, seed):
+    def __init__(self, B, H, L, d, segs, dtype, device, seed, rule='delta'):
         from recurrent_fwp_b200 import _lib
         self.L_ = _lib
+        self.rule = rule
         self.shape = (B, H, L, d)
         self.segs = segs
         self.dtype = dtype
@@ -256,6 +263,11 @@ class DeltaStep:
     def fwd(self, s, stream):
         B, H, L, d = self.shape
         q, k, v, b, _ = self.d_in[s]
+        if self.rule == 'sum':
+            self.L_.check(self.L_.lib.fwp_causal_dot_product(
+                B, H, L, d, d, q, k, v, self.d_Ws[s], self.d_y[s], self.code, stream, self.dev_index), 'sum fwd')
+            self.kernels['fwd'] = self.L_.last_kernel()
+            return
         self.L_.check(self.L_.lib.fwp_fast_weight_forward(
             B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_none, self.d_Ws[s], self.d_y[s],
             self.code, stream, self.dev_index), 'fwd')
@@ -265,6 +277,11 @@ class DeltaStep:
         B, H, L, d = self.shape
         q, k, v, b, gy = self.d_in[s]
         gq, gk, gv, gb = self.d_g[s]
+        if self.rule == 'sum':
+            self.L_.check(self.L_.lib.fwp_causal_dot_backward(
+                B, H, L, d, d, q, k, v, gy, gq, gk, gv, self.code, stream, self.dev_index), 'sum bwd')
+            self.kernels['bwd'] = self.L_.last_kernel()
+            return
         self.L_.check(self.L_.lib.fwp_fast_weight_backward(
             B, H, L, d, d, q, k, v, b, self.d_vo[s], self.d_none, gy, self.d_Ws[s], gq, gk, gv, gb,
             self.code, stream, self.dev_index), 'bwd')
@@ -561,7 +578,8 @@ def run_gpu_arm(args):
     B, H, L, d, segs, dts = WORKLOADS[args.workload]
     dtype = torch.float32 if dts == 'fp32' else torch.bfloat16
     esz = 4 if dts == 'fp32' else 2
-    ds = DeltaStep(B, H, L, d, segs, dtype, device, seed=1234 + 100 * rank)
+    ds = DeltaStep(B, H, L, d, segs, dtype, device, seed=1234 + 100 * rank,
+                   rule='sum' if args.workload.startswith('sum_') else 'delta')
     flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
 
     def flush():
@@ -570,7 +588,7 @@ def run_gpu_arm(args):
     if args.kernels_only:
         tf, tb, tf_min, tb_min = time_kernels(ds, flush, reps=max(3, args.steps))
         print(json.dumps({'workload': args.workload, 'fwd_us': tf * 1e6, 'bwd_us': tb * 1e6,
-                          'fwd_min_us': tf_min * 1e6, 'bwd_min_us': tb_min * 1e6}), flush=True)
+                          'fwd_min_us': tf_min * 1e6, 'bwd_min_us': tb_min * 1e6, 'kernels': dict(ds.kernels)}), flush=True)
         return
 
     # ---- the step, captured in a CUDA graph (launch gaps would otherwise dominate microsecond kernels)
