@@ -62,6 +62,7 @@ enum TuneKey {
     T_LSTM_BWD_ROLES32,     // "lstm_bwd.32.roles": 1 chain-warp + three trailing-warp backward of the delta LSTM at d <= 32, 0 the general kernel
     T_LSTM_FWD_GATES32,     // "lstm_fwd.32.gates": 1 one-warp-per-gate forward of the delta LSTM at d = 32, 0 the general kernel
     T_DELTA_PIPE64,         // "delta.pipe64": 1 chunkwise bf16 forward with a preparing warp one chunk ahead, 0 every warp prepares for itself
+    T_REC_BWD_ROLES32,      // "rec_bwd.32.roles": 1 chain-warp + trailing-warp backward of the recurrent delta net at d = 32, 0 the general kernel
     T_COUNT
 };
 int tune_get(TuneKey key, int fallback);

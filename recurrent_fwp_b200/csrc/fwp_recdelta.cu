@@ -488,6 +488,10 @@ __global__ void rec_param_reduce_kernel(const float* __restrict__ scratch, int N
     }
 }
 
+}  // namespace fwp
+#include "fwp_recdelta_roles.cuh"
+namespace fwp {
+
 // ------------------------------------------------------------------ launchers
 template <typename K>
 static int smem_optin(K kernel, size_t bytes) {
@@ -536,6 +540,20 @@ static int launch_rec_bwd(const RecBwdParams& p, int nseq, cudaStream_t st) {
     kern<<<nseq / slots, D * SPLIT * slots, bytes * slots, st>>>(p);
     count_launch();
     note_kernel("rec_bwd_kernel");
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
+static int launch_rec_bwd_roles32(const RecBwdParams& p, int nseq, cudaStream_t st) {
+    constexpr int TC = 8;
+    auto kern = rec_bwd_roles32_kernel<TC>;
+    int slots = 4;
+    while (nseq % slots) slots >>= 1;
+    const size_t bytes = (size_t)RecRolesSmem<TC>::kFloats * sizeof(float) * slots;
+    if (int rc = smem_optin(kern, bytes)) return rc;
+    kern<<<nseq / slots, 64 * slots, bytes, st>>>(p);
+    count_launch();
+    note_kernel("rec_bwd_roles32_kernel");
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
@@ -656,10 +674,14 @@ FWP_API int fwp_rec_update_fwm_tanh_backward(int N, int H, int L, int D,
     switch (DP) {
         case 16: rc = launch_rec_bwd<16, 2, 16>(p, N * H, st); break;
         case 32: {
+            if (p.D == 32 && tune_get(T_REC_BWD_ROLES32, 1) && rows_16B_aligned(p.q) && rows_16B_aligned(p.k) &&
+                rows_16B_aligned(p.v) && rows_16B_aligned(p.v_old) && rows_16B_aligned(p.od) && rows_16B_aligned(p.gy)) {
+                rc = launch_rec_bwd_roles32(p, N * H, st);
+                break;
+            }
             const int sp = tune_get(T_REC_BWD_SPLIT32, 2);
-            // measured: 2 -> 0.36 ms, 4 -> 0.40 ms, 1 -> 0.43 ms (spills).  A single chain warp with a trailing warp for
-            // the parameter gradients (the plan of the RNN and LSTM backward) measured 0.42 ms here: everything but
-            // the parameter gradients sits on this chain, about 390 instructions per step in one warp.
+            // measured: 2 -> 0.32 ms, 4 -> 0.37 ms, 1 -> 0.43 ms (spills); the chain-warp kernel above 0.27 ms
+            // (0.42 ms in a first version that spilled 80 registers: it now fetches its vectors where it uses them)
             if (sp == 4) rc = launch_rec_bwd<32, 4, 8>(p, N * H, st);
             else if (sp == 1) rc = launch_rec_bwd<32, 1, 8>(p, N * H, st);
             else rc = launch_rec_bwd<32, 2, 8>(p, N * H, st);

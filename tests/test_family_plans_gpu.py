@@ -1,6 +1,6 @@
 """The d = 32 execution plans of the recurrent families against the general kernels on the same inputs.
 
-The short-chain / multi-warp kernels (``rec_fwd_warp32_kernel``, ``rnn_bwd_roles32_kernel``,
+The short-chain / multi-warp kernels (``rec_fwd_warp32_kernel``, ``rec_bwd_roles32_kernel``, ``rnn_bwd_roles32_kernel``,
 ``lstm_fwd_gates32_kernel``, ``lstm_bwd_roles32_kernel``) are the default at a head dimension of exactly 32 with
 16-byte aligned rows.  Each test runs the op twice, with the plan on and switched off through ``fwp_tune``, checks
 which kernel ran (``fwp_last_kernel``) and that outputs, end states, rewound states and gradients agree to 2e-5 of
@@ -124,6 +124,37 @@ def test_lstm_plans_agree(fwp, variant, B, H, L):
         assert close(got['h'], ref['h']) and close(got['c'], ref['c'])
         for a, r in zip(got['W_end'] + got['W_back'] + got['g'], ref['W_end'] + ref['W_back'] + ref['g']):
             assert close(a, r)
+
+
+@pytest.mark.parametrize('B,H,L', SHAPES)
+def test_recurrent_delta_backward_plans_agree(fwp, B, H, L):
+    """The chain-warp + trailing-warp backward against the two-warp split kernel on the same saved tensors:
+    stream gradients, parameter gradients and the rewound state."""
+    from recurrent_fwp_b200 import _lib
+    from recurrent_fwp_b200.rec_update_fwm_tanh import rec_update_fwm_tanh
+    *ins, gy = util.rec_inputs(41, B, H, L, D)
+    W0 = torch.randn(B, H, D, D, generator=util.gen(42)) * 0.1
+    h0 = torch.randn(B, H, 1, D, generator=util.gen(43))
+
+    def run(mis=False):
+        leaves = [(misalign(t.to(DEV)) if (mis and i < 3) else t.clone().to(DEV)).requires_grad_()
+                  for i, t in enumerate(ins)]
+        W, hs = W0.clone().to(DEV), h0.clone().to(DEV)
+        y = rec_update_fwm_tanh(*leaves, W, hs)
+        kb = []
+        note_backward_kernel(leaves[0], kb)
+        y.backward(gy.to(DEV))
+        return dict(W_back=W.clone(), g=[l.grad for l in leaves], kb=kb[0])
+    try:
+        fast = run()
+        _lib.tune('rec_bwd.32.roles', 0)
+        ref = run()
+    finally:
+        _lib.tune('rec_bwd.32.roles', 1)
+    assert fast['kb'] == 'rec_bwd_roles32_kernel' and ref['kb'] == 'rec_bwd_kernel'
+    assert close(fast['W_back'], ref['W_back'])
+    for a, r in zip(fast['g'], ref['g']):
+        assert close(a, r)
 
 
 @pytest.mark.parametrize('B,H,L', SHAPES)
