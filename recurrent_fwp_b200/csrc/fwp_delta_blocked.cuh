@@ -89,7 +89,9 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
     const int seq = blockIdx.x * NSL + slot;
     const int n = seq / p.H, h = seq - n * p.H;
     extern __shared__ __align__(16) float smem_all[];
-    for (int i = tid; i < NSL * SM::kFloats; i += NSL * (G::NT + 32)) smem_all[i] = 0.f;
+    static_assert(SM::kFloats % 4 == 0, "the zero fill goes by 16-byte stores");
+    for (int i = tid; i < NSL * SM::kFloats / 4; i += NSL * (G::NT + 32))
+        reinterpret_cast<float4*>(smem_all)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     float* smem = smem_all + slot * SM::kFloats;
     float* gram0 = smem + SM::NS * SM::kStage;
     float* out0 = gram0 + 2 * SM::kGram;
@@ -332,7 +334,9 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
     const int seq = blockIdx.x * NSL + slot;
     const int n = seq / p.H, h = seq - n * p.H;
     extern __shared__ __align__(16) float smem_all[];
-    for (int i = tid; i < NSL * SM::kFloats; i += NSL * (2 * G::NT + 32)) smem_all[i] = 0.f;
+    static_assert(SM::kFloats % 4 == 0, "the zero fill goes by 16-byte stores");
+    for (int i = tid; i < NSL * SM::kFloats / 4; i += NSL * (2 * G::NT + 32))
+        reinterpret_cast<float4*>(smem_all)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     fence_async_smem();     // the zero fill is ordered before any bulk copy into the same tiles
     float* smem = smem_all + slot * SM::kFloats;
     float* gram0 = smem + SM::NS * SM::kStage;
