@@ -83,6 +83,8 @@ unsigned long long fwp_launch_count(void);
  * "lstm_bwd.32.roles" (1 / 0: chain-warp + per-gate trailing-warp backward of the delta LSTM),
  * "lstm_fwd.32.gates" (1 / 0: one-warp-per-gate forward of the delta LSTM),
  * "rec_bwd.32.roles" (1 / 0: chain-warp + trailing-warp backward of the recurrent delta net),
+ * "sum_bwd.roles" (1 / 0: the three gradients of the sum rule computed side by side by warps of their own, or one
+ * after the other by the same warps),
  * "delta.pipe64" (1 / 2 / 0: chunkwise bf16 kernels with a preparing warp one chunk ahead in both directions,
  * in the forward only, or not at all).  Returns 0 if accepted, FWP_ERR_UNSUPPORTED for an unknown key. */
 int fwp_tune(const char* key, int value);

@@ -63,6 +63,7 @@ enum TuneKey {
     T_LSTM_FWD_GATES32,     // "lstm_fwd.32.gates": 1 one-warp-per-gate forward of the delta LSTM at d = 32, 0 the general kernel
     T_DELTA_PIPE64,         // "delta.pipe64": 1 chunkwise bf16 forward with a preparing warp one chunk ahead, 0 every warp prepares for itself
     T_REC_BWD_ROLES32,      // "rec_bwd.32.roles": 1 chain-warp + trailing-warp backward of the recurrent delta net at d = 32, 0 the general kernel
+    T_SUM_BWD_ROLES,        // "sum_bwd.roles": 1 the three gradients of the sum rule in warps of their own, side by side; 0 one after the other
     T_COUNT
 };
 int tune_get(TuneKey key, int fallback);

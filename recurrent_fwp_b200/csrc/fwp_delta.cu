@@ -338,6 +338,101 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) sum_bwd_kern
     }
 }
 
+
+// The three gradients of the sum rule are independent prefix sums, so each gets warps of its own and the
+// three run side by side: dq forwards over S (rows), dk backwards over G (rows), dv backwards over G (columns).
+// Per step a role adds x[idx] * a[slice] to its matrix slice and writes the dot product with b[slice]:
+//   dq: x = k, a = v,  b = gy;    dk: x = q, a = gy, b = v;    dv: x = gy, a = q, b = k.
+// Threads of the CTA: [role][sequence slot][D * SPLIT]; every role stages its own three streams, three or four chunks deep
+// (a chunk is 1 KB per stream and its arithmetic a few hundred cycles, so the copies have to run several chunks
+// ahead to cover the memory latency), and all roles pass the same number of CTA-wide barriers per chunk.
+template <typename T> __host__ __device__ constexpr int sum_stages() { return sizeof(T) == 4 ? 4 : 3; }
+template <int D, int TC, typename T>
+__host__ __device__ constexpr int sum_roles_floats() { return sum_stages<T>() * 3 * r4(Tile<D, TC, T>::kFloats) + 2 * TC * D; }   // per role and sequence
+template <int D, int SPLIT, int TC, typename T>
+__global__ void __launch_bounds__(3 * D * SPLIT * slots_for(D * SPLIT)) sum_bwd_roles_kernel(const SumBwdParams p) {
+    using G = Geo<D, SPLIT>;
+    using Tl = Tile<D, TC, T>;
+    constexpr int TT = r4(Tl::kFloats), NST = sum_stages<T>(), PER = sum_roles_floats<D, TC, T>();
+    const int per_role = blockDim.x / 3;
+    const int role = threadIdx.x / per_role;
+    const G g(threadIdx.x - role * per_role);
+    const int nslots = per_role / G::NT;
+    const int seq = blockIdx.x * nslots + g.slot;
+    const int n = seq / p.H, h = seq - n * p.H;
+    extern __shared__ __align__(16) float smem_all[];
+    float* smem = smem_all + (size_t)(g.slot * 3 + role) * PER;
+    float* const otile = smem + NST * 3 * TT;      // two output tiles [TC][D], flushed a chunk at a time
+    for (int i = g.tid; i < PER; i += G::NT) smem[i] = 0.f;
+    // copies by value: a reference picked at run time would turn every later field access into an indexed
+    // load from the parameter bank
+    const Row4 rx = role == 0 ? p.k : role == 1 ? p.q : p.gy;
+    const Row4 ra = role == 0 ? p.v : role == 1 ? p.gy : p.q;
+    const Row4 rb = role == 0 ? p.gy : role == 1 ? p.v : p.k;
+    const Row4 ro = role == 0 ? p.gq : role == 1 ? p.gk : p.gv;
+    const int xw = role < 2 ? p.E : p.M, sw = role < 2 ? p.M : p.E;
+    Src<T> sx, sa, sb;
+    sx.init(rx, n, h, xw);
+    sa.init(ra, n, h, sw);
+    sb.init(rb, n, h, sw);
+    __syncthreads();
+    const int nchunks = (p.L + TC - 1) / TC;
+    const bool rev = role != 0;
+    const bool writes = g.s == 0;
+    f2 A[G::NP];
+#pragma unroll
+    for (int i = 0; i < G::NP; i++) A[i] = 0ull;
+    auto issue = [&](int j) {
+        float* st = smem + (j % NST) * 3 * TT;
+        Tl x, a, b;
+        x.bind(st); a.bind(st + TT); b.bind(st + 2 * TT);
+        const int c = rev ? nchunks - 1 - j : j;
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        x.template load<G::NT>(sx, t0, nt, g.tid);
+        a.template load<G::NT>(sa, t0, nt, g.tid);
+        b.template load<G::NT>(sb, t0, nt, g.tid);
+        cp_async_commit();
+    };
+    for (int j = 0; j < NST - 1; j++) {
+        if (j < nchunks) issue(j); else cp_async_commit();
+    }
+    for (int j = 0; j < nchunks; j++) {
+        // one group per iteration, empty past the end: chunk j is the NST-th youngest after this commit
+        if (j + NST - 1 < nchunks) issue(j + NST - 1); else cp_async_commit();
+        cp_async_wait<NST - 1>();
+        __syncthreads();
+        float* st = smem + (j % NST) * 3 * TT;
+        Tl x, a, b;
+        x.bind(st); a.bind(st + TT); b.bind(st + 2 * TT);
+        const int c = rev ? nchunks - 1 - j : j;
+        const int t0 = c * TC, nt = min(TC, p.L - t0);
+        if constexpr (sizeof(T) != 4) {
+            x.widen(nt, xw, g.tid, G::NT);
+            a.widen(nt, sw, g.tid, G::NT);
+            b.widen(nt, sw, g.tid, G::NT);
+            __syncthreads();
+        }
+        float* const ot = otile + (j & 1) * TC * D + g.idx;
+        auto step = [&](int t) {
+            f2 ar[G::NP], br[G::NP];
+            lds_slice<G::NR>(ar, a.f + t * D + g.off);
+            lds_slice<G::NR>(br, b.f + t * D + g.off);
+            axpy2<G::NP>(A, ar, x.f[t * D + g.idx]);
+            const float o = reduce_split<SPLIT>(dot2<G::NP>(A, br));
+            if (writes) ot[t * D] = o;
+        };
+        if (nt == TC) {         // unrolled, so that the loads, shuffles and stores of neighbouring steps overlap
+#pragma unroll
+            for (int i = 0; i < TC; i++) step(rev ? TC - 1 - i : i);
+        } else {
+            for (int i = 0; i < nt; i++) step(rev ? nt - 1 - i : i);
+        }
+        __syncthreads();
+        // this tile is written again two chunks on, behind the barriers of the next chunk
+        flush_rows<D, G::NT, T, TC>(otile + (j & 1) * TC * D, ro, n, h, t0, nt, xw, g.tid);
+    }
+}
+
 }  // namespace fwp
 
 #include "fwp_delta_blocked.cuh"
@@ -376,6 +471,9 @@ template <int D, int SPLIT, int TC, typename T>
 static int launch_sum_bwd(const SumBwdParams& p, int nseq, cudaStream_t st) {
     int slots = slots_for(D * SPLIT);
     while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    if (tune_get(T_SUM_BWD_ROLES, 1))
+        return launch(sum_bwd_roles_kernel<D, SPLIT, TC, T>, p, nseq / slots, 3 * D * SPLIT * slots,
+                      slots * 3 * sum_roles_floats<D, TC, T>() * sizeof(float), st, "sum_bwd_roles_kernel");
     return launch(sum_bwd_kernel<D, SPLIT, TC, T>, p, nseq / slots, D * SPLIT * slots,
                   slots * 2 * SumStage<D, TC, T>::kFloats * sizeof(float), st, "sum_bwd_kernel");
 }

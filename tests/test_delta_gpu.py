@@ -234,6 +234,38 @@ def test_sum_rule_above_64_both_directions(fwp, B, H, L, E, M):
         assert util.scaled_rel(leaf.grad, r.grad) <= 1e-3
 
 
+@pytest.mark.parametrize('B,H,L,E,M', [(2, 2, 37, 16, 16), (1, 3, 16, 12, 16), (3, 1, 17, 32, 20), (1, 2, 9, 24, 32),
+                                       (1, 1, 13, 64, 64), (1, 2, 1, 16, 16), (1, 1, 5, 40, 64)])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_sum_rule_backward_side_by_side_equals_one_after_the_other(fwp, B, H, L, E, M, dtype):
+    """The sum rule's dq, dk, dv are independent prefix sums (causal_product_cuda.cu:369-445).  The default kernel
+    gives each of them warps of its own; with ``sum_bwd.roles`` = 0 the same warps compute them one after the other.
+    Both do the same additions in the same order, so the gradients are equal bit for bit; and they meet the oracle."""
+    from recurrent_fwp_b200 import _lib
+    q, k, v, _, gy = util.delta_inputs(71, B, H, L, E, M)
+    q, k, v, gy = (t.to(dtype) for t in (q, k, v, gy))
+    res, names = {}, {}
+    try:
+        for roles in (1, 0):
+            _lib.tune('sum_bwd.roles', roles)
+            leaves = [t.to(DEV).requires_grad_() for t in (q, k, v)]
+            y = fwp.fast_weight_sum(*leaves, torch.zeros(B, H, E, M, device=DEV))
+            seen = []
+            leaves[0].register_hook(lambda g: seen.append(_lib.last_kernel()))
+            y.backward(gy.to(DEV))
+            res[roles], names[roles] = [l.grad for l in leaves], seen[0]
+    finally:
+        _lib.tune('sum_bwd.roles', 1)
+    assert names[1] == 'sum_bwd_roles_kernel' and names[0] == 'sum_bwd_kernel'
+    for a, b in zip(res[1], res[0]):
+        assert torch.equal(a, b)
+    ref = [t.double().requires_grad_() for t in (q, k, v)]
+    y0, _ = loops.sum_rule(*ref, torch.zeros(B, H, E, M, dtype=torch.float64))
+    (y0 * gy.double()).sum().backward()
+    for a, r in zip(res[1], ref):
+        assert util.scaled_rel(a.double(), r.grad) <= (1e-3 if dtype == torch.float32 else 2e-2)
+
+
 @pytest.mark.parametrize('B,H,L,d', [(2, 2, 37, 16), (1, 2, 21, 32), (1, 1, 13, 64)])
 def test_per_step_kernels_agree_with_blocked_form(fwp, B, H, L, d):
     """The four-step blocked kernels and the per-step kernels are two execution plans
