@@ -35,7 +35,7 @@ class FastRNN(torch.autograd.Function):
         rnn_out, K, V, beta, V_old, W, h0 = ctx.saved_tensors
         N, H, L, M = K.shape
         grad_out = _lib.grad_like(grad_out, rnn_out, (N, H, L, M))
-        rnn_out_delayed = torch.cat([h0, rnn_out[:, :, :-1]], dim=2)
+        rnn_out_delayed = _lib.delayed(rnn_out, h0)      # cat([h0, rnn_out[:, :, :-1]], dim=2) in one pass
         grad_Z = torch.empty_like(rnn_out)
         grad_K = torch.empty_like(rnn_out)
         grad_V = torch.empty_like(rnn_out)
