@@ -30,6 +30,7 @@ loops, forward+backward through autograd) on all host threads, on the same step:
 carried segments of the language-model shape.
 """
 import argparse
+import collections
 import ctypes
 import json
 import os
@@ -667,6 +668,7 @@ def run_gpu_arm(args):
     dev_in = [[torch.empty(t.shape, dtype=t.dtype, device=device) for t in host_in[0]] for _ in range(2)]
     last_reader = [None, None]
     counter = [0]
+    in_flight = collections.deque()     # download-complete events of the segments the host has queued
 
     def e2e_step():
         cur = torch.cuda.current_stream(device)
@@ -684,6 +686,11 @@ def run_gpu_arm(args):
 
         ready = upload(0, counter[0] % 2)
         for seg in range(segs):
+            # The host stays at most three segments ahead of the downloads (a bounded prefetch, as a trainer's
+            # loader has): the caching allocator then reuses the same blocks every segment instead of growing
+            # its pool inside the timed region.  Three queued segments are about 3 ms of device work.
+            while len(in_flight) >= 3:
+                in_flight.popleft().synchronize()
             buf = counter[0] % 2
             counter[0] += 1
             nxt = upload(seg + 1, counter[0] % 2) if seg + 1 < segs else None
@@ -702,6 +709,9 @@ def run_gpu_arm(args):
                 for dst, src in zip(host_out[seg], results):
                     dst.copy_(src, non_blocking=True)
                     src.record_stream(s_out)
+                landed = torch.cuda.Event()
+                landed.record(s_out)
+            in_flight.append(landed)
             W = W_next
             ready = nxt
 
@@ -710,7 +720,7 @@ def run_gpu_arm(args):
         cur.wait_stream(s_out)
         cur.wait_stream(s_in)
 
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 20))
     for _ in range(2):
         e2e_step()
     e2e_drain()
@@ -786,7 +796,7 @@ def run_gpu_arm(args):
             'cpu_baseline': cpu,
             'e2e': {'value': e2e_value, 'unit': 'tokens/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
                     'steps': e2e_steps, 'batch': Be, 'api': 'recurrent_fwp_b200.fast_weight_delta (autograd) + .backward()',
-                    'pipeline': 'uploads, compute and downloads on three streams, consecutive steps overlap (no device-wide synchronisation between them); pinned host buffers'},
+                    'pipeline': 'uploads, compute and downloads on three streams, consecutive steps overlap (no device-wide synchronisation between them), the host at most three segments ahead of the downloads; pinned host buffers'},
             'gpu_launches': int(launches), 'clocks': clocks, 'wall_s_timed_region': t_wall,
             'long_strong': strong, 'configs': configs,
         }
