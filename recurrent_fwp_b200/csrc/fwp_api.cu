@@ -19,7 +19,7 @@ static const char* const kTuneNames[T_COUNT] = {
     "delta_bwd.16.split", "delta_bwd.32.split", "delta_bwd.64.split",
     "delta_bwd.bulk", "delta_bwd.16.chunk",
     "lstm_fwd.32.split", "lstm_bwd.32.split", "rnn_fwd.32.split", "rnn_bwd.32.split", "rec_fwd.32.split", "rec_bwd.32.split",
-    "rec_fwd.32.warp", "rnn_bwd.32.roles", "lstm_bwd.32.roles", "lstm_fwd.32.gates", "delta.pipe64", "rec_bwd.32.roles", "sum_bwd.roles",
+    "rec_fwd.32.warp", "rnn_bwd.32.roles", "lstm_bwd.32.roles", "lstm_fwd.32.gates", "delta.pipe64", "rec_bwd.32.roles", "sum_bwd.roles", "launch.dependent",
 };
 struct TuneTable {
     std::atomic<int> v[T_COUNT];

@@ -64,6 +64,7 @@ enum TuneKey {
     T_DELTA_PIPE64,         // "delta.pipe64": 1 chunkwise bf16 forward with a preparing warp one chunk ahead, 0 every warp prepares for itself
     T_REC_BWD_ROLES32,      // "rec_bwd.32.roles": 1 chain-warp + trailing-warp backward of the recurrent delta net at d = 32, 0 the general kernel
     T_SUM_BWD_ROLES,        // "sum_bwd.roles": 1 the three gradients of the sum rule in warps of their own, side by side; 0 one after the other
+    T_LAUNCH_DEPENDENT,     // "launch.dependent": 1 the blocked delta-rule kernels are launched with programmatic stream serialisation (their prologue overlaps the tail of the kernel before), 0 plain launches
     T_COUNT
 };
 int tune_get(TuneKey key, int fallback);
@@ -212,6 +213,15 @@ struct Geo {
         off = s * NR;
     }
 };
+
+// A kernel launched with programmatic stream serialisation may start while the kernel before it in the stream
+// is still draining: everything up to this wait (index arithmetic, the shared-memory zero fill, barrier set-up)
+// overlaps that tail; nothing of global memory is read or written before it.  A no-op for a plain launch.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets a dependent kernel behind this one be scheduled from now on (once every CTA of this grid has said so or
+// left): its CTAs take the SMs this grid leaves free, run their prologue and park in griddep_wait() until this
+// grid has completed.  Without a dependent launch behind it, nothing happens.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Barrier among the warps that serve one sequence slot of a CTA (named barriers 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void slot_barrier(int slot, int nthreads) {

@@ -444,13 +444,13 @@ namespace fwp {
 template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     constexpr int NSL = slots_for(D * SPLIT);
-    return launch(delta_fwd_kernel<D, SPLIT, TC, T, SUM>, p, (nseq + NSL - 1) / NSL, NSL * (D * SPLIT + 32),
+    return launch_dependent(delta_fwd_kernel<D, SPLIT, TC, T, SUM>, p, (nseq + NSL - 1) / NSL, NSL * (D * SPLIT + 32),
                   NSL * WsFwdSmem<D, TC, T>::kFloats * sizeof(float), st, "delta_fwd_kernel");
 }
 template <int D, int SPLIT, int TC, typename T, int PF = 2>
 static int launch_bwd(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     constexpr int NSL = slots_for(D * SPLIT);
-    return launch(delta_bwd_kernel<D, SPLIT, TC, T, PF>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
+    return launch_dependent(delta_bwd_kernel<D, SPLIT, TC, T, PF>, p, (nseq + NSL - 1) / NSL, NSL * (2 * D * SPLIT + 32),
                   NSL * WsBwdSmem<D, TC, T, PF>::kFloats * sizeof(float), st, "delta_bwd_kernel");
 }
 template <int D, int SPLIT, int TC, typename T, bool SUM>

@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (D * SPLIT + 32)) delta
     float* out0 = gram0 + 2 * SM::kGram;
     const int nchunks = (p.L + TC - 1) / TC;
     __syncthreads();
+    griddep_wait();               // global memory is touched from here on
+    griddep_launch_dependents();
     if (seq >= p.NH) return;      // an empty slot of the last CTA: nobody waits on its barrier
 
     if (producer) {
@@ -345,6 +347,8 @@ __global__ void __launch_bounds__(slots_for(D * SPLIT) * (2 * D * SPLIT + 32)) d
     float* dbt = o0 + 2 * SM::kO;       // dbeta of one chunk, assembled by the producer before its flush
     const int nchunks = (p.L + TC - 1) / TC;
     __syncthreads();
+    griddep_wait();               // global memory is touched from here on
+    griddep_launch_dependents();
     if (seq >= p.NH) return;      // an empty slot of the last CTA: nobody waits on its barrier
     // chunk index jc counts from the end of the sequence; nchunks-1-jc is the time-order chunk
     if (role == 2) {

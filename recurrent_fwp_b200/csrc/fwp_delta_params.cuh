@@ -40,6 +40,29 @@ static int launch(K kern, const P& p, int grid, int threads, size_t bytes, cudaS
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
 
+// Same, for kernels that call griddep_wait() before their first access to global memory: launched so that they
+// may be scheduled while the kernel before them in the stream drains ("launch.dependent" = 0: a plain launch).
+template <typename K, typename P>
+static int launch_dependent(K kern, const P& p, int grid, int threads, size_t bytes, cudaStream_t st, const char* name) {
+    if (!tune_get(T_LAUNCH_DEPENDENT, 1)) return launch(kern, p, grid, threads, bytes, st, name);
+    if (int rc = set_smem(kern, bytes)) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    count_launch();
+    note_kernel(name);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
+}
+
 // chunkwise plan for bf16 streams with E = M = 64 (fwp_delta_chunk_bf16.cuh): applies when every row is 16-byte aligned
 bool chunk_bf16_applies(const DeltaFwdParams& p);
 int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st);

@@ -266,6 +266,69 @@ def test_sum_rule_backward_side_by_side_equals_one_after_the_other(fwp, B, H, L,
         assert util.scaled_rel(a.double(), r.grad) <= (1e-3 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize('graph', [False, True])
+def test_dependent_launches_hand_results_on_like_plain_ones(fwp, graph):
+    """The blocked kernels are launched so that their prologue may overlap the kernel before them in the stream
+    (programmatic stream serialisation; they wait before touching global memory and let their own dependents in
+    early).  A chain in which every launch consumes what the one before it wrote -- four forwards that carry the
+    state in place, then the four backwards that rewind it, back to back with no other kernel between them --
+    must give the same bits as with plain launches (``launch.dependent`` = 0), eagerly and replayed from a CUDA
+    graph."""
+    from recurrent_fwp_b200 import _lib
+    B, H, L, d, segs = 8, 8, 96, 16, 4
+    ins = [[t.to(DEV) for t in util.delta_inputs(81 + s, B, H, L, d)] for s in range(segs)]
+    D = _lib.desc
+
+    def chain(out):
+        stream, dev = _lib.stream_and_device(ins[0][0])
+        W = out['W']
+        for s in range(segs):
+            q, k, v, b, _ = ins[s]
+            _lib.check(_lib.lib.fwp_fast_weight_forward(B, H, L, d, d, D(q), D(k), D(v), D(b), D(out['vo'][s]), D(None),
+                                                        D(W), D(out['y'][s]), _lib.F32, stream, dev), 'fwd')
+        for s in reversed(range(segs)):
+            q, k, v, b, gy = ins[s]
+            _lib.check(_lib.lib.fwp_fast_weight_backward(B, H, L, d, d, D(q), D(k), D(v), D(b), D(out['vo'][s]), D(None),
+                                                         D(gy), D(W), *(D(g) for g in out['g'][s]), _lib.F32, stream, dev),
+                       'bwd')
+
+    def buffers():
+        new = lambda w=d: torch.zeros(B, H, L, w, device=DEV)
+        return dict(W=torch.zeros(B, H, d, d, device=DEV), vo=[new() for _ in range(segs)], y=[new() for _ in range(segs)],
+                    g=[[new(), new(), new(), new(1)] for _ in range(segs)])
+
+    res = {}
+    try:
+        for dep in (1, 0):
+            _lib.tune('launch.dependent', dep)
+            out = buffers()
+            if graph:
+                side = torch.cuda.Stream(DEV)
+                with torch.cuda.stream(side):
+                    chain(out)                      # warm-up outside the capture
+                    out['W'].zero_()
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr, stream=side):
+                        chain(out)
+                    out['W'].fill_(7.0)             # the replay must start from the state it finds
+                    out['W'].zero_()
+                    gr.replay()
+                side.synchronize()
+            else:
+                chain(out)
+            torch.cuda.synchronize()
+            assert _lib.last_kernel() == 'delta_bwd_kernel'
+            res[dep] = out
+    finally:
+        _lib.tune('launch.dependent', 1)
+    assert util.max_abs(res[1]['W'], torch.zeros_like(res[1]['W'])) <= 1e-4      # rewound to the initial state
+    for s in range(segs):
+        assert torch.equal(res[1]['y'][s], res[0]['y'][s]) and torch.equal(res[1]['vo'][s], res[0]['vo'][s])
+        for a, b in zip(res[1]['g'][s], res[0]['g'][s]):
+            assert torch.equal(a, b)
+    assert torch.equal(res[1]['W'], res[0]['W'])
+
+
 @pytest.mark.parametrize('B,H,L,d', [(2, 2, 37, 16), (1, 2, 21, 32), (1, 1, 13, 64)])
 def test_per_step_kernels_agree_with_blocked_form(fwp, B, H, L, d):
     """The four-step blocked kernels and the per-step kernels are two execution plans
