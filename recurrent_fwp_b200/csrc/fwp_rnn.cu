@@ -93,19 +93,20 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rnn_fwd_kern
             float* xv = xch + par * (D + 16);
             float* slot = xv + D;
             par ^= 1;
-            // delta update of the recurrent matrix (independent of the hidden state)
+            // delta update of the recurrent matrix: independent of the hidden state, so in the v2 step it is placed
+            // between the start of the softmax (max, exp, sum: long fixed latencies) and its use
             f2 kk[G::NP];
             lds_slice<G::NR>(kk, krow);
-            const float vo = reduce_split<SPLIT>(dot2<G::NP>(S, kk));
-            const float u = brow[0] * (vcol[0] - vo);
-            axpy2<G::NP>(S, kk, u);
             const float zz = zcol[0];
-            float hn;
+            float hn, vo;
             if constexpr (!V1) {
                 const float mx = cta_allreduce_idx<G, true>(g, ok ? hv : -INFINITY, slot);
                 const float ex = ok ? exp_neg(hv - mx) : 0.f;
                 if (g.s == 0) xv[g.idx] = ex;
                 const float den = softmax_den(g, ex, slot + 8);
+                vo = reduce_split<SPLIT>(dot2<G::NP>(S, kk));
+                const float u = brow[0] * (vcol[0] - vo);
+                axpy2<G::NP>(S, kk, u);
                 cta_sync<G::WPS>();
                 const float inv = rcp_approx(den + kSoftmaxEps);
                 f2 ss[G::NP];
@@ -113,6 +114,9 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) rnn_fwd_kern
                 hn = reduce_split<SPLIT>(dot2<G::NP>(S, ss)) * inv + zz;
                 if (writer) *pnm = ex * inv;
             } else {
+                vo = reduce_split<SPLIT>(dot2<G::NP>(S, kk));
+                const float u = brow[0] * (vcol[0] - vo);
+                axpy2<G::NP>(S, kk, u);
                 if (g.s == 0) xv[g.idx] = hv;
                 cta_sync<G::WPS>();
                 f2 ss[G::NP];
