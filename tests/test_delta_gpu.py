@@ -267,7 +267,8 @@ def test_sum_rule_backward_side_by_side_equals_one_after_the_other(fwp, B, H, L,
 
 
 @pytest.mark.parametrize('graph', [False, True])
-def test_dependent_launches_hand_results_on_like_plain_ones(fwp, graph):
+@pytest.mark.parametrize('B,H,L', [(8, 8, 96), (64, 32, 48)])      # one wave of CTAs; several waves (512 CTAs)
+def test_dependent_launches_hand_results_on_like_plain_ones(fwp, graph, B, H, L):
     """The blocked kernels are launched so that their prologue may overlap the kernel before them in the stream
     (programmatic stream serialisation; they wait before touching global memory and let their own dependents in
     early).  A chain in which every launch consumes what the one before it wrote -- four forwards that carry the
@@ -275,7 +276,7 @@ def test_dependent_launches_hand_results_on_like_plain_ones(fwp, graph):
     must give the same bits as with plain launches (``launch.dependent`` = 0), eagerly and replayed from a CUDA
     graph."""
     from recurrent_fwp_b200 import _lib
-    B, H, L, d, segs = 8, 8, 96, 16, 4
+    d, segs = 16, 4
     ins = [[t.to(DEV) for t in util.delta_inputs(81 + s, B, H, L, d)] for s in range(segs)]
     D = _lib.desc
 
