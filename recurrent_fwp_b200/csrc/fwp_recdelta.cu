@@ -203,6 +203,9 @@ __global__ void __launch_bounds__(128) rec_fwd_warp32_kernel(const RecFwdParams 
         cp_async_commit();
     };
     issue(0);
+    // tanh of the fed-back vector is the head of the next step's chain: it is taken as soon as y is known, and
+    // the matrix update and the stores of the step follow it and fill its latency
+    float th = tanh_fast(hv);                               // padding lanes hold hv = 0
     for (int c = 0; c < nchunks; c++) {
         if (c + 1 < nchunks) { issue(c + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         __syncwarp();
@@ -212,7 +215,6 @@ __global__ void __launch_bounds__(128) rec_fwd_warp32_kernel(const RecFwdParams 
 #pragma unroll 1
         for (int t = 0; t < nt; t++, row += D, brow++) {
             const float qin = row[0], kin = row[kTile], vin = row[2 * kTile], bin = brow[0];
-            const float th = tanh_fast(hv);                 // padding lanes hold hv = 0
             xh[g.idx] = th;
             __syncwarp();
             const float bsum = warp_sum_scaled(th * rbl);
@@ -240,8 +242,9 @@ __global__ void __launch_bounds__(128) rec_fwd_warp32_kernel(const RecFwdParams 
             const float vo = vo_un * invk;
             const float cc = beta * (vv - vo) * invk;       // S += ek (x) cc
             const float y = fmaf(kq_un, cc, y_un) * invq;
-            axpy2<G::NP>(S, ks, cc);
             hv = ok ? y : 0.f;
+            th = tanh_fast(hv);
+            axpy2<G::NP>(S, ks, cc);
             if (ok) {
                 *po = y;
                 *pq = eq * invq;
