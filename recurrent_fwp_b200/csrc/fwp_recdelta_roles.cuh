@@ -103,7 +103,10 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
             const float* rrow = rmem + lane * SM::kRS;
             const float rbl = rmem[3 * D * SM::kRS + lane];
             float r0, qk, dk0, w, beta, qe, ke, ul;
-            auto prep = [&](int t) {                // everything of step t that does not wait for g_h
+            // Everything of step t that does not wait for g_h.  `live` = 0 makes the call inert (the rewind adds
+            // zero): the step loop calls it without a branch, so that it can be scheduled beside the end of the
+            // step before, and the last call of a chunk repeats step 0 with live = 0.
+            auto prep = [&](int t, float live) {
                 const int o = t * D + lane;
                 beta = s.b.f[t];
                 w = s.v.f[o] - s.vo.f[o];
@@ -118,10 +121,10 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
                 qk = dot2<NP>(va, vb);
                 __syncwarp();
                 lds_slice<D>(va, xu);
-                axpy2<NP>(B, va, -ke);              // S_{t-1}
+                axpy2<NP>(B, va, -ke * live);       // S_{t-1}
                 dk0 = dot2<NP>(C, va);
             };
-            prep(nt - 1);
+            prep(nt - 1, 1.f);
 #pragma unroll 1
             for (int t = nt - 1; t >= 0; t--) {
                 const int o = t * D + lane;
@@ -155,16 +158,17 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
                     pq += __shfl_xor_sync(0xffffffffu, pq, sft);
                     pk += __shfl_xor_sync(0xffffffffu, pk, sft);
                 }
-                const float dqh = qe * (dq - pq), dkh = ke * (dk - pk);
-                e[lane] = dqh;
-                e[D + lane] = dkh;
-                if (lane == 0) e[3 * D] = dbh;
-                // the part of the feedback that needs dv only, and the two updates of G by rows, while the exchange is in flight
+                // the part of the feedback that needs dv only, and the two updates of G by rows: placed ahead of the
+                // stores below so that they may be scheduled inside the shuffle sequence above
                 f2 rr[NP];
                 lds_slice<D>(rr, rrow + 2 * D * SM::kRS);
                 float back = fmaf(rbl, dbh, dot2<NP>(rr, dvv));
                 axpy2<NP>(C, gv, qe);               // G by rows: += q (x) g, -= k (x) dv
                 axpy2<NP>(C, dvv, -ke);
+                const float dqh = qe * (dq - pq), dkh = ke * (dk - pk);
+                e[lane] = dqh;
+                e[D + lane] = dkh;
+                if (lane == 0) e[3 * D] = dbh;
                 __syncwarp();
                 lds_slice<D>(gv, e);                // dq~
                 lds_slice<D>(rr, rrow);
@@ -178,7 +182,7 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
                 axpy2<NP>(A, gv, gcol);
                 lds_slice<D>(dvv, s.k.f + t * D);
                 axpy2<NP>(A, dvv, -dv);
-                if (t > 0) prep(t - 1);
+                prep(t > 0 ? t - 1 : 0, t > 0 ? 1.f : 0.f);
             }
         } else if (role == 1 && j > 0) {
             // ------------------------------------------------------------ Y: one chunk behind
