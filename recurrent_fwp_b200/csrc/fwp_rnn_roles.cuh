@@ -111,21 +111,24 @@ __global__ void __launch_bounds__(256, 1) rnn_bwd_roles32_kernel(const RnnBwdPar
                 rg[t * SM::kStep + lane] = gcol;
                 rg[t * SM::kStep + 2 * D + lane] = br;
                 rg[t * SM::kStep + 3 * D + lane] = r * w;
+                // G takes this step's own vectors, so it is brought to G_{t-1} here, and the next step is prepared
+                // (without a branch: the last call of a chunk repeats step 0, which rewrites the same ring entry)
+                // beside the exchange and the reduction below: once g_h is known the next step starts at once
+                axpy2<NP>(Gm, xs, gcol);
+                axpy2<NP>(Gm, kk, -br);
                 __syncwarp();
                 f2 vg[NP], vu[NP];                  // two register sets: u is in flight during the product and the reduction
                 lds_slice<D>(vg, rg + t * SM::kStep);
                 lds_slice<D>(vu, rg + t * SM::kStep + D);
                 const float gs = dot2<NP>(Sr, vg);
+                prep(t > 0 ? t - 1 : 0);
                 if constexpr (V1) {
                     gh = gs;
                 } else {
                     const float dotp = warp_sum_idx<1>(se * gs);
                     gh = se * (gs - dotp);
                 }
-                axpy2<NP>(Gm, xs, gcol);
-                axpy2<NP>(Gm, kk, -br);
                 axpy2<NP>(Sr, vu, -ke);             // S_{t-1}
-                if (t > 0) prep(t - 1);
             }
         } else if (role == 1 && j > 0) {
             // ------------------------------------------------------------ Y: one chunk behind
