@@ -103,10 +103,12 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
             const float* rrow = rmem + lane * SM::kRS;
             const float rbl = rmem[3 * D * SM::kRS + lane];
             float r0, qk, dk0, w, beta, qe, ke, ul;
-            // Everything of step t that does not wait for g_h.  `live` = 0 makes the call inert (the rewind adds
-            // zero): the step loop calls it without a branch, so that it can be scheduled beside the end of the
-            // step before, and the last call of a chunk repeats step 0 with live = 0.
-            auto prep = [&](int t, float live) {
+            // Everything of step t that does not wait for g_h, in two parts.  The scalars and the vector u go out
+            // first (u through shared memory, with whatever exchange comes next); the products follow a barrier:
+            // r0 = (G k) and q.k for the head of the step, the early rewind of S and dk0 = G u.  The step loop runs
+            // them for step t - 1 inside step t, without a branch: at t = 0 they repeat step 0 with `live` = 0 (the
+            // rewind then adds zero), so that the compiler may schedule them beside the end of the step.
+            auto prep_scalars = [&](int t) {
                 const int o = t * D + lane;
                 beta = s.b.f[t];
                 w = s.v.f[o] - s.vo.f[o];
@@ -114,17 +116,20 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
                 ke = s.k.f[o];
                 ul = beta * w;
                 xu[lane] = ul;
+            };
+            auto prep_products = [&](int t, float live) {
                 f2 va[NP], vb[NP];
                 lds_slice<D>(va, s.q.f + t * D);
                 lds_slice<D>(vb, s.k.f + t * D);
                 r0 = dot2<NP>(A, vb);
                 qk = dot2<NP>(va, vb);
-                __syncwarp();
                 lds_slice<D>(va, xu);
                 axpy2<NP>(B, va, -ke * live);       // S_{t-1}
                 dk0 = dot2<NP>(C, va);
             };
-            prep(nt - 1, 1.f);
+            prep_scalars(nt - 1);
+            __syncwarp();
+            prep_products(nt - 1, 1.f);
 #pragma unroll 1
             for (int t = nt - 1; t >= 0; t--) {
                 const int o = t * D + lane;
@@ -143,8 +148,13 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
                     pdb += __shfl_xor_sync(0xffffffffu, pdb, sft);
                 }
                 const float dbh = pdb * beta * (1.f - beta);
-                __syncwarp();
                 f2 gv[NP], dvv[NP];
+                // G by columns takes this step's own vectors: += q (x) g, -= k (x) dv (the vectors come back from the tiles)
+                lds_slice<D>(gv, s.q.f + t * D);
+                axpy2<NP>(A, gv, gcol);
+                lds_slice<D>(dvv, s.k.f + t * D);
+                axpy2<NP>(A, dvv, -dv);
+                __syncwarp();
                 lds_slice<D>(gv, xg);
                 lds_slice<D>(dvv, e + 2 * D);
                 const float sg = dot2<NP>(B, gv);
@@ -169,6 +179,8 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
                 e[lane] = dqh;
                 e[D + lane] = dkh;
                 if (lane == 0) e[3 * D] = dbh;
+                const int tn = t > 0 ? t - 1 : 0;
+                prep_scalars(tn);                   // the next step's u travels with this exchange
                 __syncwarp();
                 lds_slice<D>(gv, e);                // dq~
                 lds_slice<D>(rr, rrow);
@@ -177,12 +189,7 @@ __global__ void __launch_bounds__(256, 1) rec_bwd_roles32_kernel(const RecBwdPar
                 lds_slice<D>(rr, rrow + D * SM::kRS);
                 back += dot2<NP>(rr, dvv);
                 gh = (1.f - hte * hte) * back;
-                // G by columns: += q (x) g, -= k (x) dv (the vectors come back from the tiles)
-                lds_slice<D>(gv, s.q.f + t * D);
-                axpy2<NP>(A, gv, gcol);
-                lds_slice<D>(dvv, s.k.f + t * D);
-                axpy2<NP>(A, dvv, -dv);
-                prep(t > 0 ? t - 1 : 0, t > 0 ? 1.f : 0.f);
+                prep_products(tn, t > 0 ? 1.f : 0.f);
             }
         } else if (role == 1 && j > 0) {
             // ------------------------------------------------------------ Y: one chunk behind
