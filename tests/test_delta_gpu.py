@@ -266,6 +266,45 @@ def test_sum_rule_backward_side_by_side_equals_one_after_the_other(fwp, B, H, L,
         assert util.scaled_rel(a.double(), r.grad) <= (1e-3 if dtype == torch.float32 else 2e-2)
 
 
+def test_single_step_calls_replayed_from_a_cuda_graph(fwp):
+    """The RL callers advance one environment step per call (L = 1, RL/model.py:436-448: 4 heads of 32, the state
+    carried in place).  One such call captured in a CUDA graph and replayed over static input buffers -- the way
+    an inference loop avoids the launch path -- gives the bits of eager stepping and meets the fp64 loop over the
+    whole sequence."""
+    B, H, T, d = 32, 4, 12, 32
+    q, k, v, b, _ = util.delta_inputs(91, B, H, T, d)
+    qd, kd, vd, bd = (t.to(DEV) for t in (q, k, v, b))
+    # eager: one call per step on a state carried in place
+    W_eager = torch.zeros(B, H, d, d, device=DEV)
+    ys_eager = [fwp.fast_weight_delta(qd[:, :, t:t + 1], kd[:, :, t:t + 1], vd[:, :, t:t + 1], bd[:, :, t:t + 1], W_eager)
+                for t in range(T)]
+    # graph: static one-step buffers, the state updated in place by every replay
+    sq, sk, sv = (torch.zeros(B, H, 1, d, device=DEV) for _ in range(3))
+    sb = torch.zeros(B, H, 1, 1, device=DEV)
+    W = torch.zeros(B, H, d, d, device=DEV)
+    side = torch.cuda.Stream(DEV)
+    side.wait_stream(torch.cuda.current_stream(DEV))
+    with torch.cuda.stream(side), torch.no_grad():
+        fwp.fast_weight_delta(sq, sk, sv, sb, W)           # warm-up outside the capture
+        W.zero_()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=side):
+            sy = fwp.fast_weight_delta(sq, sk, sv, sb, W)
+        W.zero_()
+        ys_graph = []
+        for t in range(T):
+            sq.copy_(qd[:, :, t:t + 1]); sk.copy_(kd[:, :, t:t + 1]); sv.copy_(vd[:, :, t:t + 1]); sb.copy_(bd[:, :, t:t + 1])
+            gr.replay()
+            ys_graph.append(sy.clone())
+    side.synchronize()
+    torch.cuda.synchronize()
+    for a, e in zip(ys_graph, ys_eager):
+        assert torch.equal(a, e)
+    assert torch.equal(W, W_eager)
+    y64, S64 = loops.delta_rule(q.double(), k.double(), v.double(), b.double(), torch.zeros(B, H, d, d, dtype=torch.float64))
+    assert util.max_abs(torch.cat(ys_graph, dim=2), y64) <= 1e-4 and util.max_abs(W, S64) <= 1e-4
+
+
 @pytest.mark.parametrize('graph', [False, True])
 @pytest.mark.parametrize('B,H,L', [(8, 8, 96), (64, 32, 48)])      # one wave of CTAs; several waves (512 CTAs)
 def test_dependent_launches_hand_results_on_like_plain_ones(fwp, graph, B, H, L):
