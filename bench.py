@@ -522,6 +522,54 @@ def run_lm_e2e(args):
         dist.destroy_process_group()
 
 
+def run_single_step(args):
+    """`--workload rl_step`: the delta rule called one time step at a time (L = 1) at the RL callers' shape (32
+    environments, 4 heads of 32; RL/model.py:436-448), the state carried in place.  Launch latency is the cost here, so
+    two numbers per direction of use: a call through the C ABI from the host loop, and the same call replayed from
+    a CUDA graph.  Device time by CUDA events around `reps` back-to-back steps, host time by the wall clock."""
+    from recurrent_fwp_b200 import _lib
+    dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
+    torch.cuda.set_device(dev)
+    B, H, d, reps = 32, 4, 32, 400
+    ds = DeltaStep(B, H, 1, d, 1, torch.float32, dev, seed=77)
+    stream_obj = torch.cuda.Stream(dev)
+    stream = ctypes.c_void_p(stream_obj.cuda_stream)
+
+    def timed(fn):
+        for _ in range(20):
+            fn()
+        stream_obj.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        a.record(stream_obj)
+        for _ in range(reps):
+            fn()
+        b.record(stream_obj)
+        host = (time.perf_counter() - t0) / reps
+        stream_obj.synchronize()
+        return a.elapsed_time(b) * 1e3 / reps, host * 1e6
+
+    out = {}
+    with torch.cuda.stream(stream_obj):
+        out['abi_call'] = dict(zip(('device_us_per_step', 'host_us_per_step'), timed(lambda: ds.fwd(0, stream))))
+        kernel = _lib.last_kernel()
+        ds.fwd(0, stream)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream_obj):
+            ds.fwd(0, stream)
+        out['graph_replay'] = dict(zip(('device_us_per_step', 'host_us_per_step'), timed(graph.replay)))
+        eight = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(eight, stream=stream_obj):
+            for _ in range(8):
+                ds.fwd(0, stream)
+        dev_us, host_us = timed(eight.replay)
+        out['graph_of_8_steps'] = {'device_us_per_step': dev_us / 8, 'host_us_per_step': host_us / 8}
+    print(json.dumps({'workload': 'rl_step', 'shape': {'B': B, 'H': H, 'L': 1, 'd': d}, 'dtype': 'fp32', 'kernel': kernel,
+                      'forward': out,
+                      'timing': 'CUDA events on the launching stream around %d back-to-back steps; host time by the '
+                                'wall clock around the same loop' % reps}), flush=True)
+
+
 def long_strong(device, flush, rank, world, barrier, steps=5, warmup=3):
     """The scale-out delta-rule shape with its fixed batch of 256 split over the ranks (256 / N batch rows each,
     all 16 heads, no collective): fwd+bwd device time per step, max over ranks."""
@@ -814,7 +862,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='fwp', choices=['fwp', 'reference'])
-    ap.add_argument('--workload', default='lm', choices=sorted(WORKLOADS) + sorted(FAMILY_SHAPES) + ['lm_e2e'])
+    ap.add_argument('--workload', default='lm', choices=sorted(WORKLOADS) + sorted(FAMILY_SHAPES) + ['lm_e2e', 'rl_step'])
     ap.add_argument('--no-graph', action='store_true')
     ap.add_argument('--tune', action='append', default=[], metavar='KEY=INT',
                     help='set an execution-plan switch of the library before the run (repeatable), e.g. delta.chunk=1')
@@ -834,6 +882,8 @@ def main():
             _lib.tune(key, int(val))
     if args.workload == 'lm_e2e':
         run_lm_e2e(args)
+    elif args.workload == 'rl_step':
+        run_single_step(args)
     elif args.workload in FAMILY_SHAPES:
         run_family(args)
     elif args.impl == 'reference':

@@ -37,6 +37,8 @@ delta_fwd_step_kernel(const DeltaFwdParams p) {
     float* smem = slot_smem(smem_all, g);
     using Stage = FwdStage<D, TC, T>;
     for (int i = g.tid; i < 2 * Stage::kFloats; i += G::NT) smem[i] = 0.f;
+    griddep_wait();               // launched as a dependent: global memory is touched from here on
+    griddep_launch_dependents();
 
     Src<T> sq, sk, sv, sb;
     sq.init(p.q, n, h, p.E);
@@ -136,6 +138,8 @@ __global__ void __launch_bounds__(D * SPLIT * slots_for(D * SPLIT)) delta_bwd_st
     constexpr int kXch = 2 * (2 * D + 8);   // per parity: u[D], br[D], dbeta partials[WPS<=8]
     for (int i = g.tid; i < 2 * Stage::kFloats + kXch; i += G::NT) smem[i] = 0.f;
     float* xch = smem + 2 * Stage::kFloats;
+    griddep_wait();               // launched as a dependent: global memory is touched from here on
+    griddep_launch_dependents();
 
     Src<T> sq, sk, sv, sg, sb;
     Src<float> so;
@@ -457,14 +461,14 @@ template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd_step(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     int slots = slots_for(D * SPLIT);
     while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
-    return launch(delta_fwd_step_kernel<D, SPLIT, TC, T, SUM>, p, nseq / slots, D * SPLIT * slots,
+    return launch_dependent(delta_fwd_step_kernel<D, SPLIT, TC, T, SUM>, p, nseq / slots, D * SPLIT * slots,
                   slots * 2 * FwdStage<D, TC, T>::kFloats * sizeof(float), st, "delta_fwd_step_kernel");
 }
 template <int D, int SPLIT, int TC, typename T>
 static int launch_bwd_step(const DeltaBwdParams& p, int nseq, cudaStream_t st) {
     int slots = slots_for(D * SPLIT);
     while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
-    return launch(delta_bwd_step_kernel<D, SPLIT, TC, T>, p, nseq / slots, D * SPLIT * slots,
+    return launch_dependent(delta_bwd_step_kernel<D, SPLIT, TC, T>, p, nseq / slots, D * SPLIT * slots,
                   slots * (2 * BwdStage<D, TC, T>::kFloats + 2 * (2 * D + 8)) * sizeof(float), st, "delta_bwd_step_kernel");
 }
 template <int D, int SPLIT, int TC, typename T>
