@@ -232,9 +232,9 @@ __global__ void __launch_bounds__(256, 1) lstm_bwd_roles32_kernel(const LstmBwdP
 //
 // A step has three delta-rule updates and three read-outs, one per gate, and they meet only in the element-wise
 // cell update.  Warp q of a sequence holds S^q, applies its update (inputs only, so it runs beside the chain),
-// forms its pre-activation S^q_t^T x + z^q and posts it; after the one barrier of the step every warp reads the
-// three pre-activations and computes the gates, the cell, the output and the next fed-back vector for itself (the
-// same instructions on the same numbers in all three warps, so they agree bit for bit).  One barrier per step
+// forms its pre-activation S^q_t^T x + z^q, applies its gate's nonlinearity and posts the gate; after the one
+// barrier of the step every warp reads the three gates and computes the cell, the output and the next fed-back
+// vector for itself (the same instructions on the same numbers in all three warps, so they agree bit for bit).  One barrier per step
 // (about 110 cycles) buys a chain warp of about 150 instead of 400 instructions per step.
 template <int TC>
 struct LstmGatesSmem {
@@ -345,12 +345,11 @@ __global__ void __launch_bounds__(384, 1) lstm_fwd_gates32_kernel(const LstmFwdP
             __syncwarp();
             f2 xs[NP];
             lds_slice<D>(xs, xv);
-            pp[q * D + lane] = dot2<NP>(S, xs) + zcol[0];
+            // each warp posts its gate already activated: one sigmoid per warp and step instead of three
+            const float pre = dot2<NP>(S, xs) + zcol[0];
+            pp[q * D + lane] = (VAR == 4 && q == 1) ? pre : sigmoidf_(pre);
             slot_barrier(slot, NT);
-            const float gi = sigmoidf_(pp[lane]);
-            const float p1 = pp[D + lane];
-            const float uu = (VAR == 4) ? p1 : sigmoidf_(p1);
-            const float go = sigmoidf_(pp[2 * D + lane]);
+            const float gi = pp[lane], uu = pp[D + lane], go = pp[2 * D + lane];
             cv = gi * uu + (1.f - gi) * cv;
             float hn = go * cv;
             if constexpr (VAR == 1) {
