@@ -94,6 +94,18 @@ __global__ void __launch_bounds__(256, 1) lstm_bwd_roles32_kernel(const LstmBwdP
     };
     issue(0);
     float gh = 0.f, gc = 0.f;       // X: gradients handed back through the output and the cell
+    // H_q: this gate's gradient streams, picked once (by value: a reference chosen at run time would make every
+    // later field access an indexed load from the parameter bank)
+    const int gq = role > 0 ? role - 1 : 0;
+    const Row4 rk = gq == 0 ? p.gk[0] : (gq == 1 ? p.gk[1] : p.gk[2]);
+    const Row4 rz = gq == 0 ? p.gz[0] : (gq == 1 ? p.gz[1] : p.gz[2]);
+    const Row4 rv = gq == 0 ? p.gv[0] : (gq == 1 ? p.gv[1] : p.gv[2]);
+    const Row4 rb = gq == 0 ? p.gb[0] : (gq == 1 ? p.gb[1] : p.gb[2]);
+    float* const bgk = reinterpret_cast<float*>(rk.p) + n * rk.sN + h * rk.sH + col;
+    float* const bgz = reinterpret_cast<float*>(rz.p) + n * rz.sN + h * rz.sH + col;
+    float* const bgv = reinterpret_cast<float*>(rv.p) + n * rv.sN + h * rv.sH + col;
+    float* const bgb = reinterpret_cast<float*>(rb.p) + n * rb.sN + h * rb.sH;
+    const long long sgk = rk.sL, sgz = rz.sL, sgv = rv.sL, sgb = rb.sL;
     for (int j = 0; j <= nchunks; j++) {
         cp_async_wait<0>();
         slot_barrier(slot, NT);  // chunk j's tiles have landed; X is through chunk j - 1, the H warps through j - 2
@@ -164,16 +176,11 @@ __global__ void __launch_bounds__(256, 1) lstm_bwd_roles32_kernel(const LstmBwdP
             const float* vtile = q == 0 ? s.v[0].f : (q == 1 ? s.v[1].f : s.v[2].f);
             const float* votile = q == 0 ? s.vo[0].f : (q == 1 ? s.vo[1].f : s.vo[2].f);
             const float* btile = q == 0 ? s.b[0].f : (q == 1 ? s.b[1].f : s.b[2].f);
-            const Row4& rk = q == 0 ? p.gk[0] : (q == 1 ? p.gk[1] : p.gk[2]);
-            const Row4& rz = q == 0 ? p.gz[0] : (q == 1 ? p.gz[1] : p.gz[2]);
-            const Row4& rv = q == 0 ? p.gv[0] : (q == 1 ? p.gv[1] : p.gv[2]);
-            const Row4& rb = q == 0 ? p.gb[0] : (q == 1 ? p.gb[1] : p.gb[2]);
             const long long tl = t0 + nt - 1;
-            float* pgk = reinterpret_cast<float*>(rk.p) + n * rk.sN + h * rk.sH + tl * rk.sL + col;
-            float* pgz = reinterpret_cast<float*>(rz.p) + n * rz.sN + h * rz.sH + tl * rz.sL + col;
-            float* pgv = reinterpret_cast<float*>(rv.p) + n * rv.sN + h * rv.sH + tl * rv.sL + col;
-            float* pgb = reinterpret_cast<float*>(rb.p) + n * rb.sN + h * rb.sH + tl * rb.sL;
-            const long long sgk = rk.sL, sgz = rz.sL, sgv = rv.sL, sgb = rb.sL;
+            float* pgk = bgk + tl * sgk;
+            float* pgz = bgz + tl * sgz;
+            float* pgv = bgv + tl * sgv;
+            float* pgb = bgb + tl * sgb;
 #pragma unroll 1
             for (int t = nt - 1; t >= 0; t--) {
                 const int o = t * D + lane;
