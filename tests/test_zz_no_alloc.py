@@ -4,7 +4,8 @@
 at call time: it keeps its scratch in a fixed array inside the library.  The test drives
 both backward entry points through the C ABI on the same saved tensors, twice in a row with
 different inputs (the built-in array is shared between calls and keeps old contents), and
-requires the same gradients from both (max-abs 1e-6; they run the same kernels).
+requires the same gradients from both (max-abs 1e-6; they run the same kernels) and checks those of the
+no-allocation call against the fp64 oracle with the measure of the other parity tests.
 It also checks that an oversized problem is refused with the dedicated status.
 """
 import ctypes
@@ -71,6 +72,12 @@ def test_noalloc_backward_matches_regular_entry_point_twice(fwp):
         for a, b in zip(got, ref):
             assert util.max_abs(a, b) <= 1e-6, 'call %d' % call
         assert util.max_abs(W_na, W0) <= 1e-5      # rewound like the regular entry point
+        # and against the fp64 explicit recurrences themselves (fp32 recurrences as the noise floor)
+        from tests.test_rec_delta_gpu import NAMES, oracle64
+        cpu = [t.cpu() for t in ins]
+        _, g64, _, _ = oracle64(cpu, W0.cpu(), h0.cpu(), gy.cpu())
+        _, g32, _, _ = oracle64(cpu, W0.cpu(), h0.cpu(), gy.cpu(), torch.float32)
+        util.check_grads('rec_delta no-alloc call %d' % call, NAMES, got, g32, g64)
 
 
 def test_noalloc_refuses_oversized_problem(fwp):
