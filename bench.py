@@ -51,6 +51,7 @@ WORKLOADS = {
     'small': (2, 8, 256, 16, 1, 'fp32'),          # the reference's own CPU-runnable case
     'long': (256, 16, 4096, 64, 1, 'bf16'),       # scale-out shape, kernel part
     'long_slice': (32, 16, 4096, 64, 1, 'bf16'),  # an eighth of it (one GPU's shard at N=8)
+    'long_few': (8, 16, 4096, 64, 1, 'bf16'),     # 128 sequences: fewer than SMs (small-batch use of the scale-out kernels)
     # the other execution plans of the delta and sum rules, for --kernels-only timing and the ncu captures
     'lm_d32': (64, 8, 256, 32, 1, 'fp32'),        # fp32 at d = 32: per-step forward, blocked backward
     'lm_d64': (64, 8, 256, 64, 1, 'fp32'),        # fp32 at d = 64

@@ -77,7 +77,8 @@ unsigned long long fwp_launch_count(void);
 /* Execution-plan switch for experiments and cross-checks (process-wide, atomic):
  * "delta.blocked" (-1 automatic, 0 per-step kernels, 1 four-step blocked kernels),
  * "delta.chunk64" (1 / 0: chunkwise tensor-core plan for bf16 streams at E = M = 64),
- * "delta.tc64" (1 / 0: tcgen05 forward of that plan), "<op>.<D>.split", "delta_bwd.bulk",
+ * "delta.tc64" (-1 / 1 / 0: tcgen05 forward of that plan when the call has no more sequences than the device has SMs
+ * and at least 128 steps, always, or never), "<op>.<D>.split", "delta_bwd.bulk",
  * "delta_bwd.16.chunk", "rec_fwd.32.warp" (1 / 0: short-chain forward of the recurrent delta net),
  * "rnn_bwd.32.roles" (1 / 2 / 0: chain-warp + trailing-warp backward of the delta RNN, 16 or 8 steps per chunk, or off),
  * "lstm_bwd.32.roles" (1 / 0: chain-warp + per-gate trailing-warp backward of the delta LSTM),

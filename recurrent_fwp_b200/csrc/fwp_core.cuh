@@ -50,7 +50,7 @@ void note_kernel(const char* name);     // remembers, per host thread, the kerne
 enum TuneKey {
     T_DELTA_BLOCKED,        // "delta.blocked": -1 automatic, 0 per-step kernels, 1 four-step blocked kernels
     T_DELTA_CHUNK64,        // "delta.chunk64": 1 chunkwise tensor-core plan for bf16 streams at E = M = 64, 0 off
-    T_DELTA_TC64,           // "delta.tc64": 1 tcgen05 forward of that plan, 0 the warp-level mma forward
+    T_DELTA_TC64,           // "delta.tc64": -1 automatic (tcgen05 forward when the call has no more sequences than the device has SMs and at least 128 steps), 1 tcgen05 forward of that plan, 0 the warp-level mma forward
     T_DELTA_FWD_SPLIT16, T_DELTA_FWD_SPLIT32, T_DELTA_FWD_SPLIT64,      // "delta_fwd.<D>.split"
     T_SUM_FWD_SPLIT16, T_SUM_FWD_SPLIT32, T_SUM_FWD_SPLIT64,            // "sum_fwd.<D>.split"
     T_DELTA_BWD_SPLIT16, T_DELTA_BWD_SPLIT32, T_DELTA_BWD_SPLIT64,      // "delta_bwd.<D>.split"

@@ -1,5 +1,6 @@
 // Chunkwise plan of the delta rule for bf16 streams with E = M = 64: kernels in fwp_delta_chunk_bf16.cuh,
 // applicability test and launches here.  One fused launch per direction, no workspace.
+#include <atomic>
 #include "fwp_delta_chunk_bf16.cuh"
 #include "fwp_delta_tc.cuh"
 
@@ -74,9 +75,26 @@ int launch_wait_probe(int polls, cudaStream_t st) {
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
 
+// SMs of the current device (asked once per device)
+static int sm_count() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
 int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
-    // "delta.tc64" = 1: the tcgen05 / TMA forward (64-step chunks); 0: the warp-level mma forward (16-step chunks)
-    if (tune_get(T_DELTA_TC64, 0) == 1 && tc_applies(p)) {
+    // "delta.tc64": the tcgen05 / TMA forward (64-step chunks, one sequence per SM) or the warp-level mma forward
+    // (16-step chunks, four sequences per SM).  -1 (default) picks by the measured crossover: with no more sequences
+    // than SMs every sequence has an SM to itself either way and the tcgen05 kernel is 1.1x (L = 128) to 1.6x
+    // (L = 4096) faster; beyond that the warp-level kernel's four resident sequences per SM win.  1 / 0 force one.
+    const int tc = tune_get(T_DELTA_TC64, -1);
+    if ((tc == 1 || (tc == -1 && p.L >= 128 && nseq <= sm_count())) && tc_applies(p)) {
         const int rc = launch_fwd_tc(p, nseq, st);
         if (rc >= 0) return rc;
     }

@@ -78,7 +78,7 @@ def test_plan_switches_are_a_closed_set(L):
     """fwp_tune accepts the library's own switches and refuses anything else (no table that grows)."""
     assert L.lib.fwp_tune(b'delta.blocked', -1) == 0
     assert L.lib.fwp_tune(b'delta_bwd.16.chunk', 32) == 0
-    assert L.lib.fwp_tune(b'delta.tc64', 0) == 0
+    assert L.lib.fwp_tune(b'delta.tc64', -1) == 0
     assert L.lib.fwp_tune(b'no.such.switch', 1) == 6
     assert L.lib.fwp_tune(None, 1) == 1
     assert L.lib.fwp_last_kernel() == b''      # nothing launched on this thread

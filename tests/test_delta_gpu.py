@@ -495,21 +495,35 @@ def explicit_oracle(q, k, v, b, W0, gy, dtype):
     return y, g, S_end, S
 
 
-def test_chunkwise_bf16_plan_at_the_scale_out_length(fwp):
+@pytest.mark.parametrize('tc64,forward', [(-1, 'delta_fwd_tc_kernel'), (0, 'delta_fwd_chunk_bf16_pipe_kernel')])
+def test_chunkwise_bf16_plan_at_the_scale_out_length(fwp, tc64, forward):
     """The scale-out configuration's own sequence length (L = 4096, E = M = 64, bf16 streams) on a 1 x 2 slice:
     256 chunks of in-place rewinding.  Outputs, all four gradients, the end state and the *rewound* start state
-    against the fp64 explicit recurrence on the bf16-rounded inputs, with the fp32 recurrence beside it."""
+    against the fp64 explicit recurrence on the bf16-rounded inputs, with the fp32 recurrence beside it.  Two
+    sequences are fewer than the SMs, so the default forward here is the tcgen05 kernel; the warp-level forward
+    (what a full shard of the configuration runs) is checked with the switch at 0."""
+    from recurrent_fwp_b200 import _lib
     B, H, L, d = 1, 2, 4096, 64
     q, k, v, b, gy = [t.to(torch.bfloat16) for t in util.delta_inputs(401, B, H, L, d)]
     W0 = torch.randn(B, H, d, d, generator=util.gen(402)) * 0.1
     W = W0.to(DEV)
-    y, grads, W_end = run_cuda(fwp, q, k, v, b, W, gy)
+    try:
+        _lib.tune('delta.tc64', tc64)
+        leaves = [t.detach().to(DEV).requires_grad_() for t in (q, k, v, b)]
+        y = fwp.fast_weight_delta(*leaves, W)
+        assert _lib.last_kernel() == forward
+        W_end = W.clone()
+        y.backward(gy.to(DEV))
+        y, grads = y.detach(), [l.grad for l in leaves]
+    finally:
+        _lib.tune('delta.tc64', -1)
+    assert _lib.device_fault() == 0
     f = [t.float() for t in (q, k, v, b)]
     y64, g64, S64, S64_back = explicit_oracle(*f, W0, gy.float(), torch.float64)
     y32, g32, S32, S32_back = explicit_oracle(*f, W0, gy.float(), torch.float32)
     assert util.max_abs(S64_back, W0) <= 1e-12
-    bf16_anchor('delta bf16 d64 L4096', y, grads, y64, g64, y32, g32)
-    util.record('delta bf16 d64 L4096', tensor='state', end_cuda=util.max_abs(W_end, S64),
+    bf16_anchor('delta bf16 d64 L4096 tc64=%d' % tc64, y, grads, y64, g64, y32, g32)
+    util.record('delta bf16 d64 L4096 tc64=%d' % tc64, tensor='state', end_cuda=util.max_abs(W_end, S64),
                 end_cpu32=util.max_abs(S32, S64), rewound_cuda=util.max_abs(W, W0),
                 rewound_cpu32=util.max_abs(S32_back, W0))
     assert util.max_abs(W_end, S64) <= 2e-4
@@ -556,7 +570,7 @@ def test_tcgen05_forward_plan_meets_the_oracle(fwp, B, H, L):
             y.backward(gy.to(DEV))
             res[tc] = (y.detach(), [l.grad for l in leaves], W_end, W, kernel)
     finally:
-        _lib.tune('delta.tc64', 0)
+        _lib.tune('delta.tc64', -1)
     assert _lib.device_fault() == 0
     assert res[1][4] == 'delta_fwd_tc_kernel' and res[0][4] == 'delta_fwd_chunk_bf16_pipe_kernel'
     f = [t.float() for t in (q, k, v, b)]
@@ -583,6 +597,7 @@ def test_preparing_warp_kernels_equal_the_self_preparing_ones_bit_for_bit(fwp, B
     res = {}
     names = {}
     try:
+        _lib.tune('delta.tc64', 0)          # the warp-level forward whatever the sequence count
         for pipe in (1, 0):
             _lib.tune('delta.pipe64', pipe)
             W = W0.to(DEV)
@@ -596,6 +611,7 @@ def test_preparing_warp_kernels_equal_the_self_preparing_ones_bit_for_bit(fwp, B
             names[pipe] = (kf, kb[0])
     finally:
         _lib.tune('delta.pipe64', 1)
+        _lib.tune('delta.tc64', -1)
     assert names[1] == ('delta_fwd_chunk_bf16_pipe_kernel', 'delta_bwd_chunk_bf16_pipe_kernel')
     assert names[0] == ('delta_fwd_chunk_bf16_inv_kernel', 'delta_bwd_chunk_bf16_inv_kernel')
     for a, r in zip(res[1], res[0]):
@@ -621,7 +637,7 @@ def test_tcgen05_forward_is_the_kernel_that_ran(fwp):
                                                         _lib.BF16, stream, dev), 'forward')
             assert _lib.last_kernel() == want
     finally:
-        _lib.tune('delta.tc64', 0)
+        _lib.tune('delta.tc64', -1)
     torch.cuda.synchronize()
     assert _lib.device_fault() == 0
 
