@@ -86,6 +86,8 @@ unsigned long long fwp_launch_count(void);
  * "rec_bwd.32.roles" (1 / 0: chain-warp + trailing-warp backward of the recurrent delta net),
  * "sum_bwd.roles" (1 / 0: the three gradients of the sum rule computed side by side by warps of their own, or one
  * after the other by the same warps),
+ * "step.spread" (1 / 0: the per-step forward packs fewer sequences into a CTA while that puts CTAs on more SMs, or
+ * always four warps per CTA),
  * "launch.dependent" (1 / 0: the register-resident delta-rule kernels are launched with programmatic stream serialisation, so that
  * their prologue overlaps the tail of the kernel before them in the stream, or plainly),
  * "delta.pipe64" (1 / 2 / 0: chunkwise bf16 kernels with a preparing warp one chunk ahead in both directions,

@@ -19,7 +19,7 @@ static const char* const kTuneNames[T_COUNT] = {
     "delta_bwd.16.split", "delta_bwd.32.split", "delta_bwd.64.split",
     "delta_bwd.bulk", "delta_bwd.16.chunk",
     "lstm_fwd.32.split", "lstm_bwd.32.split", "rnn_fwd.32.split", "rnn_bwd.32.split", "rec_fwd.32.split", "rec_bwd.32.split",
-    "rec_fwd.32.warp", "rnn_bwd.32.roles", "lstm_bwd.32.roles", "lstm_fwd.32.gates", "delta.pipe64", "rec_bwd.32.roles", "sum_bwd.roles", "launch.dependent",
+    "rec_fwd.32.warp", "rnn_bwd.32.roles", "lstm_bwd.32.roles", "lstm_fwd.32.gates", "delta.pipe64", "rec_bwd.32.roles", "sum_bwd.roles", "launch.dependent", "step.spread",
 };
 struct TuneTable {
     std::atomic<int> v[T_COUNT];
@@ -35,6 +35,19 @@ int set_cuda_error(cudaError_t e) {
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 void note_kernel(const char* name) { g_last_kernel = name; }
+
+// SMs of the current device (asked once per device)
+int sm_count() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
 
 int tune_get(TuneKey key, int fallback) {
     const int v = g_tune.v[key].load(std::memory_order_relaxed);

@@ -65,9 +65,11 @@ enum TuneKey {
     T_REC_BWD_ROLES32,      // "rec_bwd.32.roles": 1 chain-warp + trailing-warp backward of the recurrent delta net at d = 32, 0 the general kernel
     T_SUM_BWD_ROLES,        // "sum_bwd.roles": 1 the three gradients of the sum rule in warps of their own, side by side; 0 one after the other
     T_LAUNCH_DEPENDENT,     // "launch.dependent": 1 the register-resident delta-rule kernels (blocked and per-step) are launched with programmatic stream serialisation (their prologue overlaps the tail of the kernel before), 0 plain launches
+    T_STEP_SPREAD,          // "step.spread": 1 the per-step forward packs fewer sequences into a CTA while that puts CTAs on more SMs, 0 always four warps per CTA
     T_COUNT
 };
 int tune_get(TuneKey key, int fallback);
+int sm_count();             // SMs of the current device
 
 struct DeviceGuard {
     int prev = -1;

@@ -461,6 +461,9 @@ template <int D, int SPLIT, int TC, typename T, bool SUM>
 static int launch_fwd_step(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     int slots = slots_for(D * SPLIT);
     while (nseq % slots) slots >>= 1;          // sequences per CTA must divide the sequence count
+    // few sequences: rather one or two per CTA on twice or four times the SMs than four per CTA on a part of them
+    if (tune_get(T_STEP_SPREAD, 1))
+        while (slots > 1 && nseq / slots < sm_count()) slots >>= 1;
     return launch_dependent(delta_fwd_step_kernel<D, SPLIT, TC, T, SUM>, p, nseq / slots, D * SPLIT * slots,
                   slots * 2 * FwdStage<D, TC, T>::kFloats * sizeof(float), st, "delta_fwd_step_kernel");
 }

@@ -75,19 +75,6 @@ int launch_wait_probe(int polls, cudaStream_t st) {
     return e == cudaSuccess ? FWP_OK : set_cuda_error(e);
 }
 
-// SMs of the current device (asked once per device)
-static int sm_count() {
-    static std::atomic<int> cached[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-    int n = cached[dev].load(std::memory_order_relaxed);
-    if (n == 0) {
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-        cached[dev].store(n, std::memory_order_relaxed);
-    }
-    return n;
-}
-
 int launch_fwd_chunk_bf16(const DeltaFwdParams& p, int nseq, cudaStream_t st) {
     // "delta.tc64": the tcgen05 / TMA forward (64-step chunks, one sequence per SM) or the warp-level mma forward
     // (16-step chunks, four sequences per SM).  -1 (default) picks by the measured crossover: with no more sequences
