@@ -31,6 +31,21 @@ def job_delta(fwp, seed, d):
     return run
 
 
+def job_delta_bf16(fwp, seed):
+    """bf16 streams at d = 64 with fewer sequences than SMs: the tcgen05 forward (tensor maps encoded per call on the
+    calling thread) and the warp-level chunkwise backward."""
+    q, k, v, b, gy = (t.to(torch.bfloat16).to(DEV) for t in util.delta_inputs(seed, 2, 3, 200, 64))
+
+    def run():
+        leaves = [t.clone().requires_grad_() for t in (q, k, v, b)]
+        W = torch.zeros(2, 3, 64, 64, device=DEV)
+        y = fwp.fast_weight_delta(*leaves, W)
+        W_end = W.clone()
+        y.backward(gy)
+        return [y.detach(), W_end, W.clone()] + [l.grad for l in leaves]
+    return run
+
+
 def job_sum(fwp, seed):
     q, k, v, _, gy = (t.to(DEV) for t in util.delta_inputs(seed, 2, 4, 50, 16))
 
@@ -94,7 +109,8 @@ def job_rec(fwp, seed):
 
 def test_calls_from_concurrent_host_threads_give_the_serial_bits(fwp):
     jobs = [job_delta(fwp, 901, 16), job_delta(fwp, 902, 32), job_sum(fwp, 903), job_rnn(fwp, 904), job_lstm(fwp, 905),
-            job_rec(fwp, 906), job_delta(fwp, 907, 16), job_rnn(fwp, 908)]
+            job_rec(fwp, 906), job_delta(fwp, 907, 16), job_rnn(fwp, 908), job_delta_bf16(fwp, 909),
+            job_delta_bf16(fwp, 910)]
     serial = [job() for job in jobs]
     torch.cuda.synchronize()
     results = [[None] * ROUNDS for _ in jobs]
