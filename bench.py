@@ -715,6 +715,34 @@ def run_gpu_arm(args):
     # buffer (its last reader) keeps an upload from overwriting inputs that a backward still needs.
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     dev_in = [[torch.empty(t.shape, dtype=t.dtype, device=device) for t in host_in[0]] for _ in range(2)]
+    # One copy each way per segment: the five input tensors of a segment lie behind one another in one pinned
+    # buffer (and in one device buffer), the five results are gathered into one device buffer before they leave.
+    packed = not args.e2e_unpacked
+
+    def carve(flat, like):
+        """Views of `flat` with the shapes of `like`, each starting on a 256-byte boundary."""
+        views, off = [], 0
+        for t in like:
+            views.append(flat[off:off + t.numel()].view(t.shape))
+            off += (t.numel() + 127) // 128 * 128
+        return views
+
+    if packed:
+        total_in = sum((t.numel() + 127) // 128 * 128 for t in host_in[0])
+        total_out = sum((t.numel() + 127) // 128 * 128 for t in host_out[0])
+        host_in_flat = [torch.empty(total_in, dtype=dtype).pin_memory() for _ in range(segs)]
+        for flat, seg in zip(host_in_flat, host_in):
+            for view, t in zip(carve(flat, seg), seg):
+                view.copy_(t)
+        host_in = [carve(flat, host_in[0]) for flat in host_in_flat]
+        dev_in_flat = [torch.empty(total_in, dtype=dtype, device=device) for _ in range(2)]
+        dev_in = [carve(flat, host_in[0]) for flat in dev_in_flat]
+        host_out_flat = [torch.empty(total_out, dtype=dtype).pin_memory() for _ in range(segs)]
+        like_out = host_out[0]
+        host_out = [carve(flat, like_out) for flat in host_out_flat]
+        dev_out_flat = [torch.empty(total_out, dtype=dtype, device=device) for _ in range(2)]
+        dev_out = [carve(flat, like_out) for flat in dev_out_flat]
+        out_free = [None, None]         # per staging buffer: its last download
     last_reader = [None, None]
     counter = [0]
     in_flight = collections.deque()     # download-complete events of the segments the host has queued
@@ -727,8 +755,11 @@ def run_gpu_arm(args):
             with torch.cuda.stream(s_in):
                 if last_reader[buf] is not None:
                     s_in.wait_event(last_reader[buf])   # the buffer's previous reader (saved tensors of that segment)
-                for dst, src in zip(dev_in[buf], host_in[seg]):
-                    dst.copy_(src, non_blocking=True)
+                if packed:
+                    dev_in_flat[buf].copy_(host_in_flat[seg], non_blocking=True)
+                else:
+                    for dst, src in zip(dev_in[buf], host_in[seg]):
+                        dst.copy_(src, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(s_in)
             return ev
@@ -749,17 +780,27 @@ def run_gpu_arm(args):
             y = fwp.fast_weight_delta(q, k, v, b, W)
             W_next = W.clone()
             y.backward(gy)
+            results = (y.detach(), q.grad, k.grad, v.grad, b.grad)
+            if packed:
+                if out_free[buf] is not None:
+                    cur.wait_event(out_free[buf])       # the staging buffer's previous download
+                for dst, src in zip(dev_out[buf], results):
+                    dst.copy_(src)
             done = torch.cuda.Event()
             done.record(cur)
             last_reader[buf] = done
-            results = (y.detach(), q.grad, k.grad, v.grad, b.grad)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
-                for dst, src in zip(host_out[seg], results):
-                    dst.copy_(src, non_blocking=True)
-                    src.record_stream(s_out)
+                if packed:
+                    host_out_flat[seg].copy_(dev_out_flat[buf], non_blocking=True)
+                else:
+                    for dst, src in zip(host_out[seg], results):
+                        dst.copy_(src, non_blocking=True)
+                        src.record_stream(s_out)
                 landed = torch.cuda.Event()
                 landed.record(s_out)
+            if packed:
+                out_free[buf] = landed
             in_flight.append(landed)
             W = W_next
             ready = nxt
@@ -784,6 +825,14 @@ def run_gpu_arm(args):
     eb.record()
     torch.cuda.synchronize(device)
     e2e_s = max(ea.elapsed_time(eb) * 1e-3, 1e-9)
+    # what arrived on the host is what the op computes: segment 0 again, straight on the device (outside the timing)
+    chk = [t.to(device).requires_grad_() for t in host_in[0][:4]]
+    y_chk = fwp.fast_weight_delta(*chk, torch.zeros(Be, H, d, d, device=device))
+    y_chk.backward(host_in[0][4].to(device))
+    torch.cuda.synchronize(device)
+    for got, want in zip(host_out[0], [y_chk.detach()] + [t.grad for t in chk]):
+        if not torch.equal(got, want.cpu()):
+            raise SystemExit('bench.py: the end-to-end leg returned other numbers than the op computes')
     barrier()
     te = torch.tensor([e2e_s], device=device, dtype=torch.float64)
     if world > 1:
@@ -845,7 +894,7 @@ def run_gpu_arm(args):
             'cpu_baseline': cpu,
             'e2e': {'value': e2e_value, 'unit': 'tokens/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
                     'steps': e2e_steps, 'batch': Be, 'api': 'recurrent_fwp_b200.fast_weight_delta (autograd) + .backward()',
-                    'pipeline': 'uploads, compute and downloads on three streams, consecutive steps overlap (no device-wide synchronisation between them), the host at most three segments ahead of the downloads; pinned host buffers'},
+                    'pipeline': 'uploads, compute and downloads on three streams, consecutive steps overlap (no device-wide synchronisation between them), the host at most three segments ahead of the downloads; pinned host buffers, ' + ('one copy per segment and direction (inputs packed in one buffer, results gathered on the device)' if packed else 'one copy per tensor')},
             'gpu_launches': int(launches), 'clocks': clocks, 'wall_s_timed_region': t_wall,
             'long_strong': strong, 'configs': configs,
         }
@@ -868,6 +917,8 @@ def main():
     ap.add_argument('--tune', action='append', default=[], metavar='KEY=INT',
                     help='set an execution-plan switch of the library before the run (repeatable), e.g. delta.chunk=1')
     ap.add_argument('--skip-cpu', action='store_true')
+    ap.add_argument('--e2e-unpacked', action='store_true',
+                    help='end-to-end leg: one host-device copy per tensor instead of one per segment and direction')
     ap.add_argument('--skip-configs', action='store_true',
                     help='leave out the `configs` and `long_strong` objects (the other benchmark shapes)')
     ap.add_argument('--unfused-layer-io', action='store_true',
