@@ -122,7 +122,7 @@ def test_calls_from_concurrent_host_threads_give_the_serial_bits(fwp):
             torch.cuda.set_device(0)
             stream = torch.cuda.Stream(DEV)
             stream.wait_stream(torch.cuda.default_stream(DEV))
-            start.wait()
+            start.wait(timeout=120)
             with torch.cuda.stream(stream):
                 for r in range(ROUNDS):
                     results[i][r] = jobs[i]()
@@ -130,7 +130,7 @@ def test_calls_from_concurrent_host_threads_give_the_serial_bits(fwp):
         except Exception as e:       # surfaced by the main thread
             errors.append((i, repr(e)))
 
-    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(jobs))]
+    threads = [threading.Thread(target=worker, args=(i,), daemon=True) for i in range(len(jobs))]
     for t in threads:
         t.start()
     for t in threads:
