@@ -79,6 +79,9 @@ def test_plan_switches_are_a_closed_set(L):
     assert L.lib.fwp_tune(b'delta.blocked', -1) == 0
     assert L.lib.fwp_tune(b'delta_bwd.16.chunk', 32) == 0
     assert L.lib.fwp_tune(b'delta.tc64', -1) == 0
+    for key in (b'sum_bwd.roles', b'launch.dependent', b'step.spread', b'rec_bwd.32.roles', b'rnn_bwd.32.roles',
+                b'lstm_bwd.32.roles', b'lstm_fwd.32.gates', b'rec_fwd.32.warp', b'delta.pipe64'):
+        assert L.lib.fwp_tune(key, 1) == 0      # 1 is every one of these switches' default
     assert L.lib.fwp_tune(b'no.such.switch', 1) == 6
     assert L.lib.fwp_tune(None, 1) == 1
     assert L.lib.fwp_last_kernel() == b''      # nothing launched on this thread
